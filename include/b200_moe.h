@@ -1,0 +1,252 @@
+/*
+ * b200_moe.h - C ABI of the sm_100a mixture-of-experts kernels.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream
+ * (passed as void*, it is a cudaStream_t / CUstream) and returns 0 when the
+ * work was enqueued, -1 on a rejected argument or a launch error (message on
+ * stderr) - the convention of the reference's op submitters
+ * (libdataflowops/src/submit_ops/moe_ops.c:30-36). Nothing here allocates
+ * device memory: all buffers, scratch included, belong to the caller, as in
+ * the reference where ops never allocate at submit time.
+ *
+ * Each declaration names the reference interface it stands in for
+ * (paths are relative to the reference project root).
+ *
+ * Element types use the reference's DataflowDatatype numbering
+ * (libdataflow/include/dataflow_common.h:46-74).
+ */
+#ifndef B200_MOE_H
+#define B200_MOE_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200_DT_NONE 0
+#define B200_DT_FP32 3
+#define B200_DT_BF16 5
+
+#define B200_MAX_EXPERTS 4096 /* moe/build_expert_mapping.cu:3 MAX_NUM_EXPERTS */
+#define B200_MAX_TOP_K 32
+
+/* Library / device identification. Returns 0 and fills sm_count, cc_major, cc_minor of the current device. */
+int b200_device_info(int *sm_count, int *cc_major, int *cc_minor);
+
+/* ---- router ------------------------------------------------------------------ */
+
+/*
+ * Replaces dataflow_submit_default_select_experts
+ * (libdataflowops/include/dataflow_ops.h:216-222; kernel
+ * backends/nvidia/src/ops/src/native/src/moe/select_experts.cu:3-295).
+ * Per token: top-k of n_experts logits with the reference's slot order and
+ * tie rule (equal values keep the lower expert index), softmax over the k
+ * kept logits -> token_expert_weights[T,k] (fp32), chosen_experts[T,k] (u16);
+ * expert_counts[n_experts+1] += histogram (caller zeroes it; entry n_experts
+ * is a finished-block counter as in the reference); expert_counts_cumsum
+ * [n_experts] = exclusive prefix sums; host_expert_counts (optional, may be
+ * mapped pinned host memory) = counts. x_dt must be B200_DT_FP32 or
+ * B200_DT_BF16 (bf16 logits are widened to fp32 before comparing).
+ */
+int b200_select_experts(int x_dt, int total_tokens, int n_experts, int top_k_experts, const void *X_routed,
+                        float *token_expert_weights, uint16_t *chosen_experts, int *expert_counts,
+                        int *expert_counts_cumsum, int *host_expert_counts, void *stream);
+
+/*
+ * Replaces dataflow_submit_default_build_expert_mapping
+ * (dataflow_ops.h:225-228; moe/build_expert_mapping.cu:18-103).
+ * Counting-sort scatter: expert_mapping[row] = token, token_mapping[t*k+j] =
+ * row; expert_counts_cumsum goes from exclusive to inclusive prefix sums as in
+ * the reference. Unlike the reference (atomic arrival order) the order inside
+ * an expert is deterministic: tokens ascending, then slots ascending.
+ * workspace: at least b200_build_expert_mapping_workspace_bytes() bytes of
+ * device scratch, 16-byte aligned; contents need no initialisation.
+ */
+size_t b200_build_expert_mapping_workspace_bytes(int total_tokens, int num_routed_experts, int num_selected_experts);
+int b200_build_expert_mapping(int total_tokens, int num_routed_experts, int num_selected_experts,
+                              const uint16_t *chosen_experts, int *expert_counts_cumsum, int *expert_mapping,
+                              int *token_mapping, void *workspace, size_t workspace_bytes, void *stream);
+
+/* ---- permute / combine ---------------------------------------------------------- */
+
+/*
+ * Replaces dataflow_submit_default_prepare_experts (dataflow_ops.h:230-234;
+ * moe/prepare_expert_zone.cu:69-117): expert_zone[token_mapping[t,j], :] = X[t, :].
+ * bf16 rows, model_dim % 8 == 0, 16-byte aligned pointers.
+ */
+int b200_prepare_experts(int total_tokens, int model_dim, int num_selected_experts, const void *X,
+                         const int *token_mapping, void *expert_zone, void *stream);
+
+/*
+ * prepare_experts with every copied row scaled by its gate weight:
+ * expert_zone[token_mapping[t,j], :] = bf16(X[t, :] * token_expert_weights[t,j]).
+ * This is the row rewrite that dataflow_submit_router_bwd_x performs on the
+ * upstream gradient (moe/router_bwd_x.cu:83-90, 190-192), split from the dot
+ * product so the backward needs no recomputed expert output.
+ */
+int b200_prepare_experts_weighted(int total_tokens, int model_dim, int num_selected_experts, const void *X,
+                                  const int *token_mapping, const float *token_expert_weights, void *expert_zone,
+                                  void *stream);
+
+/*
+ * Replaces dataflow_submit_default_prepare_expert_zone (dataflow_ops.h:236-241;
+ * moe/prepare_expert_zone.cu:28-67): gathers one expert's rows; expert_zone
+ * points at that expert's first row; expert_counts_cumsum is inclusive.
+ */
+int b200_prepare_expert_zone(int model_dim, const void *X, int expert_id, const int *expert_counts,
+                             const int *expert_counts_cumsum, const int *expert_mapping, void *expert_zone,
+                             void *stream);
+
+/*
+ * Replaces dataflow_submit_default_merge_experts (dataflow_ops.h:243-249;
+ * moe/merge_expert_result.cu:118-247):
+ * X_combined[t,:] = bf16(f32(X_combined[t,:]) + sum_j w[t,j] * zone[token_mapping[t,j],:]),
+ * fp32 accumulation in slot order, one rounding. token_expert_weights == NULL
+ * means all weights 1.0 (the backward un-permute).
+ */
+int b200_merge_experts(int num_tokens, int model_dim, int top_k_experts, const void *expert_zones,
+                       const int *token_mapping, const float *token_expert_weights, void *X_combined,
+                       void *stream);
+
+/*
+ * Replaces dataflow_submit_default_merge_expert_result (dataflow_ops.h:251-259;
+ * moe/merge_expert_result.cu:3-115): one expert's read-modify-write combine.
+ * num_tokens is that expert's row count, expert_zone its first row.
+ */
+int b200_merge_expert_result(int num_tokens, int model_dim, int top_k_experts, const void *expert_zone,
+                             int expert_id, const int *expert_counts_cumsum, const int *expert_mapping,
+                             const float *token_expert_weights, const uint16_t *chosen_experts,
+                             void *X_combined, void *stream);
+
+/* ---- router backward --------------------------------------------------------------- */
+
+/*
+ * Replaces dataflow_submit_router_bwd_x (dataflow_ops.h:262-272;
+ * moe/router_bwd_x.cu:4-92), one expert per call:
+ * dX_routed[t, expert_id] = bf16(<expert_out[r,:], upstream_dX[t,:]>) and
+ * dX_expert_out[r,:] = bf16(upstream_dX[t,:] * w[t, expert_id]); expert_out and
+ * dX_expert_out point at the expert's first row and may be the same buffer.
+ */
+int b200_router_bwd_x(int num_expert_tokens, int model_dim, int num_routed_experts, int top_k_active,
+                      int expert_id, const int *expert_counts_cumsum, const int *expert_mapping,
+                      const uint16_t *chosen_experts, const float *token_expert_weights, const void *expert_out,
+                      const void *upstream_dX, void *dX_routed, void *dX_expert_out, void *stream);
+
+/*
+ * Replaces dataflow_submit_router_gate_bwd_x (dataflow_ops.h:275-280;
+ * moe/router_gate_bwd_x.cu:7-57): softmax-over-k Jacobian in place on the k
+ * chosen columns of dX_routed[T, E] (bf16).
+ */
+int b200_router_gate_bwd_x(int num_tokens, int num_routed_experts, int top_k_active,
+                           const uint16_t *chosen_experts, const float *token_expert_weights, void *dX_routed,
+                           void *stream);
+
+/* ---- activations ---------------------------------------------------------------------- */
+
+/* Replaces dataflow_submit_default_swiglu (dataflow_ops.h:284-287;
+ * activations/swiglu.cu:66-151): out = silu(x_w1) * x_w3, bf16, fp32 math. num_cols % 8 == 0. */
+int b200_swiglu(int num_rows, int num_cols, const void *x_w1, const void *x_w3, void *out, void *stream);
+
+/* Replaces dataflow_submit_default_swiglu_bwd_x (dataflow_ops.h:290-294;
+ * activations/swiglu_bwd_x.cu:111-256). */
+int b200_swiglu_bwd_x(int num_rows, int num_cols, const void *x_w1, const void *x_w3, const void *upstream_dX,
+                      void *dX_w1, void *dX_w3, void *stream);
+
+/* ---- dense GEMM --------------------------------------------------------------------------- */
+
+/*
+ * Replaces the matmul external op: dataflow_submit_matmul
+ * (dataflow_ops.h:70-77) -> cublas_matmul
+ * (backends/nvidia/src/ops/src/external/matmul_helper/src/matmul_helper.c:774-946).
+ * Column-major D[M x N] = alpha * op(A) * op(B) + beta * C with packed leading
+ * dimensions (matmul_helper.c:347-420), fp32 accumulation on tcgen05 tensor
+ * cores. a_dt = b_dt = B200_DT_BF16; d_dt (and c_dt when C is used) bf16 or
+ * fp32; C may be NULL (beta ignored) or alias D. M must be a multiple of 8; so must K
+ * unless (to_trans_a == 0 && to_trans_b == 1), and N when to_trans_b == 1 (16-byte rows for TMA).
+ * workspace is unused and may be NULL.
+ */
+int b200_matmul(int a_dt, int b_dt, int c_dt, int d_dt, int to_trans_a, int to_trans_b, int M, int K, int N,
+                float alpha, float beta, const void *A, const void *B, const void *C, void *D,
+                uint64_t workspaceBytes, void *workspace, void *stream);
+
+/*
+ * The GEMM kernels bound every wait on a barrier (about 2 s). A kernel that gives up records a
+ * non-zero code here and returns without finishing its tiles. This call synchronises the
+ * device, reports the code (0 = none) and clears it. The reference has no counterpart: its
+ * asynchronous errors surface at the next stream sync
+ * (backends/nvidia/src/handle/src/cuda_dataflow_handle.c:354-448).
+ */
+int b200_gemm_status(int *status_out);
+
+/* ---- grouped expert GEMMs (additive ops; the reference loops experts on the host) ----------- */
+
+/*
+ * Expert weights: W1, W3 are [ffn_dim][model_dim] and W2 is [model_dim][ffn_dim]
+ * per expert (models/init_model.py:291-306), bf16; expert e's matrix starts at
+ * base + e * stride_elems (the reference packs w1,w3,w2 per expert,
+ * libdataflowmodels/src/transformer/src/prep_transformer.c:155-159, so strides
+ * larger than one matrix are allowed; they must be multiples of 8 elements).
+ * expert_counts_cumsum is the INCLUSIVE cumsum left by build_expert_mapping;
+ * expert_counts the histogram from select_experts. Rows of expert e are
+ * [cumsum[e]-counts[e], cumsum[e]) of every [R, *] array.
+ */
+
+/*
+ * Forward of all experts in two launches, replacing the host loop
+ * libdataflowmodels/src/transformer/src/dataflow_transformer.c:2848-2940:
+ * x1 = Z W1^T, x3 = Z W3^T, h = silu(x1)*x3 (all bf16 [R, ffn_dim]), then
+ * Y = h W2^T ([R, model_dim]; may alias zone).
+ */
+int b200_moe_experts_fwd(int total_rows, int model_dim, int ffn_dim, int num_experts, const void *zone,
+                         const void *W1, const void *W3, const void *W2, int64_t w1_stride_elems,
+                         int64_t w3_stride_elems, int64_t w2_stride_elems, const int *expert_counts,
+                         const int *expert_counts_cumsum, void *x1, void *x3, void *h, void *Y, void *stream);
+
+/*
+ * Backward-x of all experts, replacing dataflow_transformer.c:3460-3641
+ * without recomputing the W2 forward. dY_zone holds the upstream gradient
+ * rows scaled by their gate weight and gathered into expert order
+ * (b200_prepare_experts_weighted on dOut - the rows router_bwd_x leaves in the
+ * zone); row_weights[R] the gate weight of each routed row. Per row r:
+ *   dh     = dY W2 (rounded to bf16 as the reference stores it)
+ *   dP[r] += <h[r,:], dh[r,:]> / w_r   (fp32; equals <Y[r,:], dOut[t,:]>, the
+ *             dot product router_bwd_x takes against the recomputed output)
+ *   (dx1, dx3) = swiglu'(x1, x3, dh);  hs = silu(x1)*x3 again if hs != NULL
+ *   dZ     = dx1 W1 + dx3 W3           (must not alias dY_zone while dW2 is
+ *                                       still to be computed from it)
+ * dP must be zeroed by the caller (the kernel accumulates into it).
+ */
+int b200_moe_experts_bwd_x(int total_rows, int model_dim, int ffn_dim, int num_experts, const void *dY_zone,
+                           const float *row_weights, const void *x1, const void *x3, const void *W1,
+                           const void *W3, const void *W2, int64_t w1_stride_elems, int64_t w3_stride_elems,
+                           int64_t w2_stride_elems, const int *expert_counts, const int *expert_counts_cumsum,
+                           void *dx1, void *dx3, void *hs, float *dP, void *dZ, void *stream);
+
+/*
+ * Weight gradients of all experts (dataflow_transformer.c:3548-3560 and
+ * 4101-4148), accumulated into bf16 gradient buffers with one rounding
+ * (beta = 1, C = D): dW2[e] += dY_e^T hs_e; dW1[e] += dx1_e^T Z_e;
+ * dW3[e] += dx3_e^T Z_e. dY_zone is the weight-scaled gathered upstream
+ * gradient, hs the SwiGLU output h (saved by the forward or rewritten by
+ * b200_moe_experts_bwd_x), zone_x the gathered layer input.
+ * Any of the three products is skipped when its gradient pointer is NULL.
+ */
+int b200_moe_experts_bwd_w(int total_rows, int model_dim, int ffn_dim, int num_experts, const void *dY_zone,
+                           const void *hs, const void *zone_x, const void *dx1, const void *dx3, void *dW1,
+                           void *dW3, void *dW2, int64_t dw1_stride_elems, int64_t dw3_stride_elems,
+                           int64_t dw2_stride_elems, const int *expert_counts, const int *expert_counts_cumsum,
+                           void *stream);
+
+/* row_weights[token_mapping[t,j]] = token_expert_weights[t,j]; dP_tok[t, chosen[t,j]] (bf16 [T,E], pre-zeroed)
+ * = bf16(dP[token_mapping[t,j]]). Small helpers around the fused backward. */
+int b200_scatter_row_weights(int num_tokens, int top_k, const int *token_mapping, const float *token_expert_weights,
+                             float *row_weights, void *stream);
+int b200_gather_router_grad(int num_tokens, int num_routed_experts, int top_k, const int *token_mapping,
+                            const uint16_t *chosen_experts, const float *dP, void *dX_routed, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200_MOE_H */

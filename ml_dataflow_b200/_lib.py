@@ -1,0 +1,57 @@
+"""Loads the C-ABI library and declares the argument types of every entry point in include/b200_moe.h.
+
+There is no fallback: if the library is missing the import of any op fails with an error that says how to build it.
+"""
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "lib", "libb200moe.so")
+
+_vp, _i, _f, _i64, _u64, _sz = C.c_void_p, C.c_int, C.c_float, C.c_int64, C.c_uint64, C.c_size_t
+
+# name -> (restype, argtypes); mirrors include/b200_moe.h
+SIGNATURES = {
+    "b200_device_info": (_i, [_vp, _vp, _vp]),
+    "b200_select_experts": (_i, [_i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "b200_build_expert_mapping_workspace_bytes": (_sz, [_i, _i, _i]),
+    "b200_build_expert_mapping": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
+    "b200_prepare_experts": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp]),
+    "b200_prepare_experts_weighted": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp]),
+    "b200_prepare_expert_zone": (_i, [_i, _vp, _i, _vp, _vp, _vp, _vp, _vp]),
+    "b200_merge_experts": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp]),
+    "b200_merge_expert_result": (_i, [_i, _i, _i, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "b200_router_bwd_x": (_i, [_i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "b200_router_gate_bwd_x": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp]),
+    "b200_swiglu": (_i, [_i, _i, _vp, _vp, _vp, _vp]),
+    "b200_swiglu_bwd_x": (_i, [_i, _i, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "b200_matmul": (_i, [_i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _f, _vp, _vp, _vp, _vp, _u64, _vp, _vp]),
+    "b200_gemm_status": (_i, [_vp]),
+    "b200_moe_experts_fwd": (_i, [_i, _i, _i, _i, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "b200_moe_experts_bwd_x": (_i, [_i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp,
+                                    _vp, _vp, _vp, _vp, _vp, _vp]),
+    "b200_moe_experts_bwd_w": (_i, [_i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp,
+                                    _vp]),
+    "b200_scatter_row_weights": (_i, [_i, _i, _vp, _vp, _vp, _vp]),
+    "b200_gather_router_grad": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp]),
+}
+
+_lib = None
+
+
+def load():
+    """Returns the loaded library; raises if it has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: build it with `python -m ml_dataflow_b200.build` "
+                "(nvcc, sm_100a). There is no CPU or library fallback for these ops."
+            )
+        lib = C.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(lib, name)  # AttributeError if the header and the library disagree
+            fn.restype = res
+            fn.argtypes = args
+        _lib = lib
+    return _lib

@@ -1,0 +1,72 @@
+// Shared helpers for the sm_100a MoE kernels: argument checks, launch error
+// reporting, bf16 packing.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#define B200_FAIL(...)                         \
+  do {                                         \
+    fprintf(stderr, "b200_moe: " __VA_ARGS__); \
+    fprintf(stderr, "\n");                     \
+    return -1;                                 \
+  } while (0)
+
+#define B200_REQUIRE(cond, ...)         \
+  do {                                  \
+    if (!(cond)) B200_FAIL(__VA_ARGS__); \
+  } while (0)
+
+#define B200_CHECK_LAUNCH(name)                                                         \
+  do {                                                                                  \
+    cudaError_t e__ = cudaGetLastError();                                               \
+    if (e__ != cudaSuccess) B200_FAIL("%s: launch failed: %s", name, cudaGetErrorString(e__)); \
+  } while (0)
+
+#define B200_CUDA(call)                                                                   \
+  do {                                                                                    \
+    cudaError_t e__ = (call);                                                             \
+    if (e__ != cudaSuccess) B200_FAIL("%s failed: %s", #call, cudaGetErrorString(e__)); \
+  } while (0)
+
+static inline bool b200_aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+namespace b200 {
+
+__device__ __forceinline__ float bf16lo(uint32_t v) { return __uint_as_float(v << 16); }
+__device__ __forceinline__ float bf16hi(uint32_t v) { return __uint_as_float(v & 0xffff0000u); }
+
+// Two fp32 -> packed bf16x2 (round to nearest even); lo goes to the low half.
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+
+__device__ __forceinline__ float bf16_round(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+
+__device__ __forceinline__ void unpack8(const uint4 &v, float *f) {
+  f[0] = bf16lo(v.x); f[1] = bf16hi(v.x);
+  f[2] = bf16lo(v.y); f[3] = bf16hi(v.y);
+  f[4] = bf16lo(v.z); f[5] = bf16hi(v.z);
+  f[6] = bf16lo(v.w); f[7] = bf16hi(v.w);
+}
+
+__device__ __forceinline__ uint4 pack8(const float *f) {
+  uint4 v;
+  v.x = pack_bf16(f[0], f[1]);
+  v.y = pack_bf16(f[2], f[3]);
+  v.z = pack_bf16(f[4], f[5]);
+  v.w = pack_bf16(f[6], f[7]);
+  return v;
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+}  // namespace b200

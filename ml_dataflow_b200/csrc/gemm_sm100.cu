@@ -1,0 +1,831 @@
+// bf16 GEMM for sm_100a on tcgen05 tensor cores: operands staged in shared memory by TMA
+// (128-byte swizzle, 64x64 boxes), fp32 accumulators in tensor memory, one persistent CTA per
+// SM with three roles - a TMA producer warp, an MMA-issuing warp, four epilogue warps.
+//
+// One kernel body serves
+//   * the dense matmul op (any combination of K-major / MN-major operands),
+//   * the expert-grouped forward / dgrad GEMMs (groups along the rows, weights picked by the
+//     third TMA coordinate), with fused SwiGLU forward or backward epilogues,
+//   * the expert-grouped wgrad GEMMs (groups along the reduction; the rows of the last 64-row
+//     slab that belong to the next expert are zeroed in shared memory before the MMA).
+//
+// Tile: 128 rows x up to 256 columns x 64 deep per stage, 4 stages, two 256-column
+// accumulator buffers in tensor memory so the epilogue of one tile overlaps the next tile's MMAs.
+#include "common.cuh"
+#include "sm100_ptx.cuh"
+#include "../../include/b200_moe.h"
+
+namespace b200 {
+
+constexpr int BM = 128;
+constexpr int BK = 64;
+constexpr int BLK_BYTES = 64 * 64 * 2;  // one TMA box: 64 rows of 128 bytes
+constexpr int A_BLKS = 2;
+constexpr int B_BLKS = 4;
+constexpr int STAGE_BYTES = (A_BLKS + B_BLKS) * BLK_BYTES;  // 48 KiB
+constexpr int STAGES = 4;
+constexpr int ACC_COLS = 256;
+constexpr int TMEM_COLS = 512;
+constexpr int GEMM_THREADS = 192;
+constexpr int MAX_GROUPS = 1024;
+
+enum GroupMode { DENSE = 0, GROUPED_M = 1, GROUPED_K = 2 };
+enum Epilogue { EPI_STORE = 0, EPI_SWIGLU_FWD = 1, EPI_SWIGLU_BWD = 2 };
+
+enum StatusCode { ST_OK = 0, ST_PRODUCER_TIMEOUT = 1, ST_MMA_TIMEOUT = 2, ST_EPILOGUE_TIMEOUT = 3 };
+
+__device__ int g_gemm_status = 0;
+
+struct GemmParams {
+  CUtensorMap tmA, tmA2, tmB, tmB2;
+  int group_mode, num_groups;
+  int M, N, K;
+  int a_mn_major, b_mn_major;
+  int dual_b, k_segments;
+  const int *counts, *cumsum_incl;
+  float alpha, beta;
+  int out_fp32, c_fp32;
+  void *D;
+  const void *C;
+  int64_t ldd, d_group_stride;
+  // fused SwiGLU forward outputs ([rows, N] bf16)
+  void *x1_out, *x3_out, *h_out;
+  // fused SwiGLU backward
+  const void *x1_in, *x3_in;
+  const float *row_w;
+  void *dx1, *dx3, *hs;
+  float *dP;
+  int *status;
+};
+
+struct Tile {
+  int group;    // expert (0 for dense)
+  int a_row0;   // first row of the A tile (GROUPED_K: first column of the [R, M] array)
+  int out_row0; // first output row
+  int m_valid;  // valid rows in this tile
+  int n0, n_valid, nw;  // first column, valid columns, columns rounded up to 64
+  int k_row0, k_len;    // GROUPED_K: reduction range inside the [R, *] arrays
+};
+
+struct Sched {
+  int mode, tiles_n, tiles_m, n_tile_w, total_tiles, M, N, K, num_groups;
+  const int *s_cnt, *s_base, *s_tpre;
+  int cursor;
+
+  __device__ __forceinline__ bool get(int tile_id, Tile &t) {
+    if (tile_id >= total_tiles) return false;
+    int nt;
+    if (mode == DENSE) {
+      const int mt = tile_id / tiles_n;
+      nt = tile_id - mt * tiles_n;
+      t.group = 0;
+      t.a_row0 = t.out_row0 = mt * BM;
+      t.m_valid = min(BM, M - mt * BM);
+      t.k_row0 = 0;
+      t.k_len = K;
+    } else if (mode == GROUPED_M) {
+      const int mtg = tile_id / tiles_n;
+      nt = tile_id - mtg * tiles_n;
+      while (s_tpre[cursor + 1] <= mtg) cursor++;
+      const int ml = mtg - s_tpre[cursor];
+      t.group = cursor;
+      t.a_row0 = t.out_row0 = s_base[cursor] + ml * BM;
+      t.m_valid = min(BM, s_cnt[cursor] - ml * BM);
+      t.k_row0 = 0;
+      t.k_len = K;
+    } else {
+      const int per = tiles_m * tiles_n;
+      const int e = tile_id / per;
+      const int rem = tile_id - e * per;
+      const int mt = rem / tiles_n;
+      nt = rem - mt * tiles_n;
+      t.group = e;
+      t.a_row0 = t.out_row0 = mt * BM;
+      t.m_valid = min(BM, M - mt * BM);
+      t.k_row0 = s_base[e];
+      t.k_len = s_cnt[e];
+    }
+    t.n0 = nt * n_tile_w;
+    t.n_valid = min(n_tile_w, N - t.n0);
+    t.nw = (t.n_valid + 63) & ~63;
+    return true;
+  }
+};
+
+__device__ __forceinline__ float silu_f(float a) { return a / (1.0f + __expf(-a)); }
+
+template <int EPI>
+__global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __grid_constant__ GemmParams p) {
+  extern __shared__ unsigned char gemm_smem_raw[];
+  // 1024-byte alignment is required by the 128-byte swizzle atoms
+  unsigned char *smem = reinterpret_cast<unsigned char *>(
+      (reinterpret_cast<uintptr_t>(gemm_smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint64_t *bars = reinterpret_cast<uint64_t *>(smem + STAGES * STAGE_BYTES);
+  // bars: full[STAGES] | empty[STAGES] | tmem_full[2] | tmem_empty[2]
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 4);
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+  int *s_cnt = reinterpret_cast<int *>(tmem_slot + 4);
+  int *s_base = s_cnt + MAX_GROUPS;
+  int *s_tpre = s_base + MAX_GROUPS;  // MAX_GROUPS + 1 entries
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const uint32_t smem_base = ptx::smem_u32(smem);
+  const uint32_t bar_base = ptx::smem_u32(bars);
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+  auto tfull_bar = [&](int s) { return bar_base + 8u * (2 * STAGES + s); };
+  auto tempty_bar = [&](int s) { return bar_base + 8u * (2 * STAGES + 2 + s); };
+
+  if (tid == 0) {
+    for (int s = 0; s < STAGES; s++) {
+      ptx::mbar_init(full_bar(s), 1);
+      ptx::mbar_init(empty_bar(s), 1);
+    }
+    for (int s = 0; s < 2; s++) {
+      ptx::mbar_init(tfull_bar(s), 1);
+      ptx::mbar_init(tempty_bar(s), 4);
+    }
+    *abort_flag = 0;
+    ptx::fence_barrier_init();
+    ptx::fence_proxy_async_smem();
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(ptx::smem_u32(tmem_slot), TMEM_COLS);
+    ptx::tmem_relinquish();
+  }
+  if (warp == 0 && lane == 0) {
+    ptx::tma_prefetch_desc(&p.tmA);
+    ptx::tma_prefetch_desc(&p.tmB);
+    if (p.k_segments > 1) ptx::tma_prefetch_desc(&p.tmA2);
+    if (p.k_segments > 1 || p.dual_b) ptx::tma_prefetch_desc(&p.tmB2);
+  }
+
+  // group tables
+  const int G = p.num_groups;
+  if (p.group_mode != DENSE) {
+    for (int e = tid; e < G; e += GEMM_THREADS) {
+      const int c = p.counts[e];
+      s_cnt[e] = c;
+      s_base[e] = p.cumsum_incl[e] - c;
+    }
+  }
+  __syncthreads();
+  if (p.group_mode == GROUPED_M && warp == 2) {
+    int running = 0;
+    for (int e0 = 0; e0 < G; e0 += 32) {
+      const int e = e0 + lane;
+      const int v = (e < G) ? (s_cnt[e] + BM - 1) / BM : 0;
+      int incl = v;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int t = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += t;
+      }
+      if (e < G) s_tpre[e] = running + incl - v;
+      running += __shfl_sync(0xffffffffu, incl, 31);
+    }
+    if (lane == 0) s_tpre[G] = running;
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  Sched sched;
+  sched.mode = p.group_mode;
+  sched.M = p.M;
+  sched.N = p.N;
+  sched.K = p.K;
+  sched.num_groups = G;
+  sched.n_tile_w = p.dual_b ? 128 : 256;
+  sched.tiles_n = (p.N + sched.n_tile_w - 1) / sched.n_tile_w;
+  sched.tiles_m = (p.M + BM - 1) / BM;
+  sched.s_cnt = s_cnt;
+  sched.s_base = s_base;
+  sched.s_tpre = s_tpre;
+  sched.cursor = 0;
+  if (p.group_mode == DENSE) sched.total_tiles = sched.tiles_m * sched.tiles_n;
+  else if (p.group_mode == GROUPED_M) sched.total_tiles = s_tpre[G] * sched.tiles_n;
+  else sched.total_tiles = G * sched.tiles_m * sched.tiles_n;
+
+  Tile t;
+  if (warp == 0) {
+    // ================= TMA producer =================
+    int stage = 0;
+    uint32_t phase = 0;
+    for (int tile = blockIdx.x; sched.get(tile, t); tile += gridDim.x) {
+      const int ksteps_seg = (t.k_len + BK - 1) / BK;
+      const int ksteps = ksteps_seg * p.k_segments;
+      const int nblk = t.nw >> 6;
+      for (int ks = 0; ks < ksteps; ks++) {
+        bool ok = true;
+        if (lane == 0) {
+          ok = ptx::mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, ST_PRODUCER_TIMEOUT);
+          if (ok) {
+            const int seg = ks / ksteps_seg;
+            const int kk = (ks - seg * ksteps_seg) * BK;
+            const CUtensorMap *mA = seg ? &p.tmA2 : &p.tmA;
+            const CUtensorMap *mB = seg ? &p.tmB2 : &p.tmB;
+            const uint32_t sA = smem_base + stage * STAGE_BYTES;
+            const uint32_t sB = sA + A_BLKS * BLK_BYTES;
+            const uint32_t bar = full_bar(stage);
+            const int nb_total = p.dual_b ? 2 * nblk : nblk;
+            ptx::mbar_arrive_expect_tx(bar, (uint32_t)((A_BLKS + nb_total) * BLK_BYTES));
+            if (!p.a_mn_major) {
+              ptx::tma_load_2d(sA, mA, bar, kk, t.a_row0);
+              ptx::tma_load_2d(sA + BLK_BYTES, mA, bar, kk, t.a_row0 + 64);
+            } else {
+              ptx::tma_load_2d(sA, mA, bar, t.a_row0, t.k_row0 + kk);
+              ptx::tma_load_2d(sA + BLK_BYTES, mA, bar, t.a_row0 + 64, t.k_row0 + kk);
+            }
+            const int g3 = (p.group_mode == GROUPED_M) ? t.group : 0;
+            if (p.dual_b) {
+              for (int i = 0; i < nblk; i++) ptx::tma_load_3d(sB + i * BLK_BYTES, &p.tmB, bar, kk, t.n0 + 64 * i, g3);
+              for (int i = 0; i < nblk; i++)
+                ptx::tma_load_3d(sB + (nblk + i) * BLK_BYTES, &p.tmB2, bar, kk, t.n0 + 64 * i, g3);
+            } else if (!p.b_mn_major) {
+              for (int i = 0; i < nblk; i++) ptx::tma_load_3d(sB + i * BLK_BYTES, mB, bar, kk, t.n0 + 64 * i, g3);
+            } else {
+              for (int i = 0; i < nblk; i++)
+                ptx::tma_load_3d(sB + i * BLK_BYTES, mB, bar, t.n0 + 64 * i, t.k_row0 + kk, g3);
+            }
+          }
+        }
+        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+        if (!ok) goto teardown;
+        if (++stage == STAGES) {
+          stage = 0;
+          phase ^= 1u;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ================= MMA issuer =================
+    int stage = 0;
+    uint32_t phase = 0;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int tile = blockIdx.x; sched.get(tile, t); tile += gridDim.x) {
+      const int ksteps_seg = (t.k_len + BK - 1) / BK;
+      const int ksteps = ksteps_seg * p.k_segments;
+      if (ksteps == 0) continue;
+      const int nblk = t.nw >> 6;
+      const int mma_n = p.dual_b ? 2 * t.nw : t.nw;
+      const uint32_t idesc = ptx::make_idesc_bf16(BM, mma_n, p.a_mn_major, p.b_mn_major);
+      const uint32_t d_tmem = tmem_base + (uint32_t)(acc * ACC_COLS);
+      bool ok = ptx::mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, p.status, ST_MMA_TIMEOUT);
+      if (!__all_sync(0xffffffffu, ok)) goto teardown;
+      ptx::tc_fence_after();
+      for (int ks = 0; ks < ksteps; ks++) {
+        ok = ptx::mbar_wait(full_bar(stage), phase, abort_flag, p.status, ST_MMA_TIMEOUT);
+        if (!__all_sync(0xffffffffu, ok)) goto teardown;
+        ptx::tc_fence_after();
+        unsigned char *stA = smem + stage * STAGE_BYTES;
+        const uint32_t sA = smem_base + stage * STAGE_BYTES;
+        const uint32_t sB = sA + A_BLKS * BLK_BYTES;
+        if (p.group_mode == GROUPED_K) {
+          const int kv = t.k_len - (ks % ksteps_seg) * BK;  // valid reduction rows in this slab
+          if (kv < BK) {
+            // rows kv..63 of every 64x64 block belong to the next expert (or lie past the end):
+            // clear them in both operands. A row is 128 contiguous bytes in the swizzled layout.
+            const int chunks_per_blk = (BK - kv) * 8;
+            const int nb_all = A_BLKS + nblk;
+            for (int i = lane; i < nb_all * chunks_per_blk; i += 32) {
+              const int b = i / chunks_per_blk, c = i - b * chunks_per_blk;
+              *reinterpret_cast<uint4 *>(stA + b * BLK_BYTES + kv * 128 + c * 16) = make_uint4(0, 0, 0, 0);
+            }
+            ptx::fence_proxy_async_smem();
+            __syncwarp();
+          }
+        }
+        if (lane == 0) {
+#pragma unroll
+          for (int k16 = 0; k16 < BK / 16; k16++) {
+            const uint64_t adesc = p.a_mn_major ? ptx::make_smem_desc(sA + k16 * 2048, BLK_BYTES, 1024)
+                                                : ptx::make_smem_desc(sA + k16 * 32, 0, 1024);
+            const uint64_t bdesc = p.b_mn_major ? ptx::make_smem_desc(sB + k16 * 2048, BLK_BYTES, 1024)
+                                                : ptx::make_smem_desc(sB + k16 * 32, 0, 1024);
+            ptx::umma_bf16(d_tmem, adesc, bdesc, idesc, (ks > 0 || k16 > 0) ? 1u : 0u);
+          }
+          ptx::umma_commit(empty_bar(stage));
+        }
+        __syncwarp();
+        if (++stage == STAGES) {
+          stage = 0;
+          phase ^= 1u;
+        }
+      }
+      if (lane == 0) ptx::umma_commit(tfull_bar(acc));
+      __syncwarp();
+      if (++acc == 2) {
+        acc = 0;
+        acc_phase ^= 1u;
+      }
+    }
+  } else {
+    // ================= epilogue (warps 2..5) =================
+    const int quarter = warp & 3;  // TMEM lanes this warp may read: [32*quarter, 32*quarter+32)
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int tile = blockIdx.x; sched.get(tile, t); tile += gridDim.x) {
+      if (t.k_len == 0) continue;
+      bool ok = ptx::mbar_wait(tfull_bar(acc), acc_phase, abort_flag, p.status, ST_EPILOGUE_TIMEOUT);
+      if (!__all_sync(0xffffffffu, ok)) goto teardown;
+      ptx::tc_fence_after();
+      const int row_in_tile = quarter * 32 + lane;
+      const bool row_ok = row_in_tile < t.m_valid;
+      const int64_t orow = (int64_t)t.out_row0 + row_in_tile;
+      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * ACC_COLS);
+
+      if (EPI == EPI_STORE) {
+        const int64_t goff = (p.group_mode == GROUPED_K) ? (int64_t)t.group * p.d_group_stride : 0;
+        const int64_t base = goff + orow * p.ldd + t.n0;
+        const bool use_c = (p.C != nullptr) && (p.beta != 0.0f);
+        for (int c0 = 0; c0 < t.nw; c0 += 32) {
+          uint32_t r[32];
+          ptx::tmem_ld32(taddr + c0, r);
+          ptx::tmem_ld_wait();
+          if (row_ok) {
+#pragma unroll
+            for (int v = 0; v < 4; v++) {
+              const int col = c0 + v * 8;
+              if (col < t.n_valid) {
+                float f[8];
+#pragma unroll
+                for (int q = 0; q < 8; q++) f[q] = p.alpha * __uint_as_float(r[v * 8 + q]);
+                if (use_c) {
+                  if (p.c_fp32) {
+                    const float4 *cp = reinterpret_cast<const float4 *>(static_cast<const float *>(p.C) + base + col);
+                    const float4 c_lo = cp[0], c_hi = cp[1];
+                    f[0] += p.beta * c_lo.x; f[1] += p.beta * c_lo.y; f[2] += p.beta * c_lo.z; f[3] += p.beta * c_lo.w;
+                    f[4] += p.beta * c_hi.x; f[5] += p.beta * c_hi.y; f[6] += p.beta * c_hi.z; f[7] += p.beta * c_hi.w;
+                  } else {
+                    float cf[8];
+                    unpack8(*reinterpret_cast<const uint4 *>(static_cast<const __nv_bfloat16 *>(p.C) + base + col), cf);
+#pragma unroll
+                    for (int q = 0; q < 8; q++) f[q] += p.beta * cf[q];
+                  }
+                }
+                if (p.out_fp32) {
+                  float4 *dp = reinterpret_cast<float4 *>(static_cast<float *>(p.D) + base + col);
+                  dp[0] = make_float4(f[0], f[1], f[2], f[3]);
+                  dp[1] = make_float4(f[4], f[5], f[6], f[7]);
+                } else {
+                  *reinterpret_cast<uint4 *>(static_cast<__nv_bfloat16 *>(p.D) + base + col) = pack8(f);
+                }
+              }
+            }
+          }
+        }
+      } else if (EPI == EPI_SWIGLU_FWD) {
+        // accumulator columns [0, nw) = x1 tile, [nw, 2 nw) = x3 tile
+        const int64_t base = orow * (int64_t)p.N + t.n0;
+        for (int c0 = 0; c0 < t.nw; c0 += 32) {
+          uint32_t r1[32], r3[32];
+          ptx::tmem_ld32(taddr + c0, r1);
+          ptx::tmem_ld32(taddr + t.nw + c0, r3);
+          ptx::tmem_ld_wait();
+          if (row_ok) {
+#pragma unroll
+            for (int v = 0; v < 4; v++) {
+              const int col = c0 + v * 8;
+              if (col < t.n_valid) {
+                float a[8], b[8], h[8];
+#pragma unroll
+                for (int q = 0; q < 8; q++) {
+                  a[q] = bf16_round(__uint_as_float(r1[v * 8 + q]));
+                  b[q] = bf16_round(__uint_as_float(r3[v * 8 + q]));
+                  h[q] = silu_f(a[q]) * b[q];
+                }
+                *reinterpret_cast<uint4 *>(static_cast<__nv_bfloat16 *>(p.x1_out) + base + col) = pack8(a);
+                *reinterpret_cast<uint4 *>(static_cast<__nv_bfloat16 *>(p.x3_out) + base + col) = pack8(b);
+                *reinterpret_cast<uint4 *>(static_cast<__nv_bfloat16 *>(p.h_out) + base + col) = pack8(h);
+              }
+            }
+          }
+        }
+      } else {
+        // EPI_SWIGLU_BWD: accumulator = dh = (w * dOut) W2 for this row
+        const int64_t base = orow * (int64_t)p.N + t.n0;
+        float dp_part = 0.f;
+        for (int c0 = 0; c0 < t.nw; c0 += 32) {
+          uint32_t r[32];
+          ptx::tmem_ld32(taddr + c0, r);
+          ptx::tmem_ld_wait();
+          if (row_ok) {
+#pragma unroll
+            for (int v = 0; v < 4; v++) {
+              const int col = c0 + v * 8;
+              if (col < t.n_valid) {
+                float a[8], b[8], o1[8], o3[8], hv[8];
+                unpack8(*reinterpret_cast<const uint4 *>(static_cast<const __nv_bfloat16 *>(p.x1_in) + base + col), a);
+                unpack8(*reinterpret_cast<const uint4 *>(static_cast<const __nv_bfloat16 *>(p.x3_in) + base + col), b);
+#pragma unroll
+                for (int q = 0; q < 8; q++) {
+                  const float acc_dh = __uint_as_float(r[v * 8 + q]);
+                  const float s = 1.0f / (1.0f + __expf(-a[q]));
+                  const float silu = a[q] * s;
+                  hv[q] = silu * b[q];
+                  dp_part += bf16_round(hv[q]) * acc_dh;
+                  const float dh = bf16_round(acc_dh);  // the reference stores dh as bf16 before swiglu_bwd_x
+                  o3[q] = dh * silu;
+                  o1[q] = dh * b[q] * (s + a[q] * (s * (1.0f - s)));
+                }
+                *reinterpret_cast<uint4 *>(static_cast<__nv_bfloat16 *>(p.dx1) + base + col) = pack8(o1);
+                *reinterpret_cast<uint4 *>(static_cast<__nv_bfloat16 *>(p.dx3) + base + col) = pack8(o3);
+                if (p.hs) *reinterpret_cast<uint4 *>(static_cast<__nv_bfloat16 *>(p.hs) + base + col) = pack8(hv);
+              }
+            }
+          }
+        }
+        if (row_ok) {
+          // <h, (w dOut) W2> = w <Y, dOut>: divide the gate weight back out (w == 0 contributes nothing downstream)
+          const float w = p.row_w[orow];
+          if (w != 0.f) atomicAdd(p.dP + orow, dp_part / w);
+        }
+      }
+
+      ptx::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(tempty_bar(acc));
+      if (++acc == 2) {
+        acc = 0;
+        acc_phase ^= 1u;
+      }
+    }
+  }
+
+teardown:
+  if (*abort_flag) {
+    // give copies that are still in flight time to land before shared memory is released
+    const uint64_t t0 = ptx::globaltimer_ns();
+    while (ptx::globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+constexpr size_t GEMM_SMEM_BYTES =
+    1024 + (size_t)STAGES * STAGE_BYTES + (2 * STAGES + 4) * 8 + 16 + sizeof(int) * (3 * MAX_GROUPS + 1);
+
+// ---------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void *sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      return nullptr;
+    fn = reinterpret_cast<EncodeTiledFn>(sym);
+  }
+  return fn;
+}
+
+// bf16 tensor [d2][d1][d0] (d0 contiguous), 64 x 64 x 1 boxes, 128-byte swizzle, zero fill.
+static int make_tmap(CUtensorMap *m, const void *base, int rank, uint64_t d0, uint64_t d1, uint64_t d2,
+                     uint64_t stride1_bytes, uint64_t stride2_bytes) {
+  EncodeTiledFn fn = get_encode_fn();
+  B200_REQUIRE(fn != nullptr, "gemm: cuTensorMapEncodeTiled is not available from this driver");
+  B200_REQUIRE(b200_aligned16(base), "gemm: operand base must be 16-byte aligned");
+  B200_REQUIRE(stride1_bytes % 16 == 0 && stride2_bytes % 16 == 0, "gemm: operand row pitch must be a multiple of 16 bytes");
+  cuuint64_t dims[3] = {d0, d1, d2};
+  cuuint64_t strides[2] = {stride1_bytes, stride2_bytes};
+  cuuint32_t box[3] = {64, 64, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, (cuuint32_t)rank, const_cast<void *>(base), dims, strides, box,
+                  estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  B200_REQUIRE(r == CUDA_SUCCESS, "gemm: cuTensorMapEncodeTiled failed with code %d", (int)r);
+  return 0;
+}
+
+static int sm_count_cached() {
+  static int sms = 0;
+  if (!sms) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (sms <= 0) sms = 148;
+  }
+  return sms;
+}
+
+static int *status_ptr() {
+  static int *ptr = nullptr;
+  if (!ptr) cudaGetSymbolAddress((void **)&ptr, g_gemm_status);
+  return ptr;
+}
+
+template <int EPI>
+static int launch_gemm(GemmParams &p, int64_t max_tiles, cudaStream_t s) {
+  p.status = status_ptr();
+  B200_REQUIRE(p.status != nullptr, "gemm: status word unavailable");
+  auto kern = gemm_sm100_kernel<EPI>;
+  static bool configured = false;
+  if (!configured) {
+    B200_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GEMM_SMEM_BYTES));
+    configured = true;
+  }
+  int64_t grid = sm_count_cached();
+  if (max_tiles < grid) grid = max_tiles;
+  if (grid < 1) return 0;
+  kern<<<(unsigned)grid, GEMM_THREADS, GEMM_SMEM_BYTES, s>>>(p);
+  B200_CHECK_LAUNCH("gemm_sm100");
+  return 0;
+}
+
+static void zero_params(GemmParams &p) { memset(&p, 0, sizeof(p)); }
+
+}  // namespace b200
+
+using namespace b200;
+
+// Reads (and clears) the status word the GEMM kernels raise when a bounded wait runs out.
+// Synchronises the device. 0 = no kernel has given up since the last call.
+extern "C" int b200_gemm_status(int *status_out) {
+  int v = 0;
+  B200_CUDA(cudaDeviceSynchronize());
+  B200_CUDA(cudaMemcpyFromSymbol(&v, g_gemm_status, sizeof(int)));
+  if (v != 0) {
+    int zero = 0;
+    B200_CUDA(cudaMemcpyToSymbol(g_gemm_status, &zero, sizeof(int)));
+  }
+  if (status_out) *status_out = v;
+  return 0;
+}
+
+extern "C" int b200_matmul(int a_dt, int b_dt, int c_dt, int d_dt, int to_trans_a, int to_trans_b, int M, int K, int N,
+                           float alpha, float beta, const void *A, const void *B, const void *C, void *D,
+                           uint64_t workspaceBytes, void *workspace, void *stream) {
+  (void)workspaceBytes;
+  (void)workspace;
+  B200_REQUIRE(a_dt == B200_DT_BF16 && b_dt == B200_DT_BF16, "matmul: A and B must be bf16 (got %d, %d)", a_dt, b_dt);
+  B200_REQUIRE(d_dt == B200_DT_BF16 || d_dt == B200_DT_FP32, "matmul: D must be bf16 or fp32 (got %d)", d_dt);
+  const bool use_c = (C != nullptr) && (c_dt != B200_DT_NONE) && (beta != 0.0f);
+  B200_REQUIRE(!use_c || c_dt == B200_DT_BF16 || c_dt == B200_DT_FP32, "matmul: C must be bf16 or fp32 (got %d)", c_dt);
+  B200_REQUIRE(M > 0 && N > 0 && K > 0, "matmul: M, K, N must be positive (got %d, %d, %d)", M, K, N);
+  // every dimension that is the contiguous one of some operand must keep rows 16-byte aligned
+  B200_REQUIRE(M % 8 == 0, "matmul: M must be a multiple of 8 (got %d)", M);
+  B200_REQUIRE(!(to_trans_a || !to_trans_b) || K % 8 == 0, "matmul: K must be a multiple of 8 for this layout (got %d)", K);
+  B200_REQUIRE(!to_trans_b || N % 8 == 0, "matmul: N must be a multiple of 8 when B is transposed (got %d)", N);
+  B200_REQUIRE(A && B && D, "matmul: null operand");
+  B200_REQUIRE(b200_aligned16(D) && b200_aligned16(C), "matmul: C and D must be 16-byte aligned");
+
+  // Row-major view: D_rm[N][M] = Brm . Arm^T. Kernel rows come from B, kernel columns from A.
+  GemmParams p;
+  zero_params(p);
+  p.group_mode = DENSE;
+  p.num_groups = 1;
+  p.M = N;
+  p.N = M;
+  p.K = K;
+  p.a_mn_major = to_trans_b ? 1 : 0;  // B stored [N][K] when not transposed, [K][N] when transposed
+  p.b_mn_major = to_trans_a ? 0 : 1;  // A stored [M][K] when transposed, [K][M] when not
+  p.k_segments = 1;
+  p.alpha = alpha;
+  p.beta = use_c ? beta : 0.0f;
+  p.out_fp32 = d_dt == B200_DT_FP32;
+  p.c_fp32 = c_dt == B200_DT_FP32;
+  p.D = D;
+  p.C = use_c ? C : nullptr;
+  p.ldd = M;
+  if (p.a_mn_major) {
+    if (make_tmap(&p.tmA, B, 2, (uint64_t)N, (uint64_t)K, 1, (uint64_t)N * 2, 0)) return -1;
+  } else {
+    if (make_tmap(&p.tmA, B, 2, (uint64_t)K, (uint64_t)N, 1, (uint64_t)K * 2, 0)) return -1;
+  }
+  if (p.b_mn_major) {
+    if (make_tmap(&p.tmB, A, 3, (uint64_t)M, (uint64_t)K, 1, (uint64_t)M * 2, (uint64_t)M * K * 2)) return -1;
+  } else {
+    if (make_tmap(&p.tmB, A, 3, (uint64_t)K, (uint64_t)M, 1, (uint64_t)K * 2, (uint64_t)M * K * 2)) return -1;
+  }
+  p.tmA2 = p.tmA;
+  p.tmB2 = p.tmB;
+  const int64_t tiles = (int64_t)((N + BM - 1) / BM) * ((M + 255) / 256);
+  return launch_gemm<EPI_STORE>(p, tiles, (cudaStream_t)stream);
+}
+
+static int check_grouped(const char *op, int total_rows, int model_dim, int ffn_dim, int num_experts,
+                         const int *counts, const int *cumsum) {
+  B200_REQUIRE(total_rows >= 0, "%s: negative row count", op);
+  B200_REQUIRE(model_dim > 0 && model_dim % 8 == 0 && ffn_dim > 0 && ffn_dim % 8 == 0,
+               "%s: model_dim and ffn_dim must be positive multiples of 8 (got %d, %d)", op, model_dim, ffn_dim);
+  B200_REQUIRE(num_experts >= 1 && num_experts <= MAX_GROUPS, "%s: need 1 <= num_experts <= %d (got %d)", op, MAX_GROUPS,
+               num_experts);
+  B200_REQUIRE(counts && cumsum, "%s: expert_counts / expert_counts_cumsum missing", op);
+  return 0;
+}
+
+extern "C" int b200_moe_experts_fwd(int total_rows, int model_dim, int ffn_dim, int num_experts, const void *zone,
+                                    const void *W1, const void *W3, const void *W2, int64_t w1_stride_elems,
+                                    int64_t w3_stride_elems, int64_t w2_stride_elems, const int *expert_counts,
+                                    const int *expert_counts_cumsum, void *x1, void *x3, void *h, void *Y,
+                                    void *stream) {
+  if (check_grouped("moe_experts_fwd", total_rows, model_dim, ffn_dim, num_experts, expert_counts, expert_counts_cumsum))
+    return -1;
+  B200_REQUIRE(zone && W1 && W3 && W2 && x1 && x3 && h && Y, "moe_experts_fwd: null buffer");
+  B200_REQUIRE(w1_stride_elems % 8 == 0 && w3_stride_elems % 8 == 0 && w2_stride_elems % 8 == 0,
+               "moe_experts_fwd: expert strides must be multiples of 8 elements");
+  B200_REQUIRE(b200_aligned16(x1) && b200_aligned16(x3) && b200_aligned16(h) && b200_aligned16(Y),
+               "moe_experts_fwd: outputs must be 16-byte aligned");
+  if (total_rows == 0) return 0;
+  const int64_t m_tiles_max = (int64_t)(total_rows + BM - 1) / BM + num_experts;
+  cudaStream_t s = (cudaStream_t)stream;
+  {
+    // x1 | x3 = Z [W1 ; W3]^T with the SwiGLU epilogue
+    GemmParams p;
+    zero_params(p);
+    p.group_mode = GROUPED_M;
+    p.num_groups = num_experts;
+    p.N = ffn_dim;
+    p.K = model_dim;
+    p.dual_b = 1;
+    p.k_segments = 1;
+    p.counts = expert_counts;
+    p.cumsum_incl = expert_counts_cumsum;
+    p.x1_out = x1;
+    p.x3_out = x3;
+    p.h_out = h;
+    if (make_tmap(&p.tmA, zone, 2, (uint64_t)model_dim, (uint64_t)total_rows, 1, (uint64_t)model_dim * 2, 0)) return -1;
+    if (make_tmap(&p.tmB, W1, 3, (uint64_t)model_dim, (uint64_t)ffn_dim, (uint64_t)num_experts, (uint64_t)model_dim * 2,
+                  (uint64_t)w1_stride_elems * 2))
+      return -1;
+    if (make_tmap(&p.tmB2, W3, 3, (uint64_t)model_dim, (uint64_t)ffn_dim, (uint64_t)num_experts,
+                  (uint64_t)model_dim * 2, (uint64_t)w3_stride_elems * 2))
+      return -1;
+    p.tmA2 = p.tmA;
+    if (launch_gemm<EPI_SWIGLU_FWD>(p, m_tiles_max * ((ffn_dim + 127) / 128), s)) return -1;
+  }
+  {
+    // Y = h W2^T
+    GemmParams p;
+    zero_params(p);
+    p.group_mode = GROUPED_M;
+    p.num_groups = num_experts;
+    p.N = model_dim;
+    p.K = ffn_dim;
+    p.k_segments = 1;
+    p.counts = expert_counts;
+    p.cumsum_incl = expert_counts_cumsum;
+    p.alpha = 1.0f;
+    p.D = Y;
+    p.ldd = model_dim;
+    if (make_tmap(&p.tmA, h, 2, (uint64_t)ffn_dim, (uint64_t)total_rows, 1, (uint64_t)ffn_dim * 2, 0)) return -1;
+    if (make_tmap(&p.tmB, W2, 3, (uint64_t)ffn_dim, (uint64_t)model_dim, (uint64_t)num_experts, (uint64_t)ffn_dim * 2,
+                  (uint64_t)w2_stride_elems * 2))
+      return -1;
+    p.tmA2 = p.tmA;
+    p.tmB2 = p.tmB;
+    if (launch_gemm<EPI_STORE>(p, m_tiles_max * ((model_dim + 255) / 256), s)) return -1;
+  }
+  return 0;
+}
+
+extern "C" int b200_moe_experts_bwd_x(int total_rows, int model_dim, int ffn_dim, int num_experts, const void *dY_zone,
+                                      const float *row_weights, const void *x1, const void *x3, const void *W1,
+                                      const void *W3, const void *W2, int64_t w1_stride_elems, int64_t w3_stride_elems,
+                                      int64_t w2_stride_elems, const int *expert_counts,
+                                      const int *expert_counts_cumsum, void *dx1, void *dx3, void *hs, float *dP,
+                                      void *dZ, void *stream) {
+  if (check_grouped("moe_experts_bwd_x", total_rows, model_dim, ffn_dim, num_experts, expert_counts,
+                    expert_counts_cumsum))
+    return -1;
+  B200_REQUIRE(dY_zone && row_weights && x1 && x3 && W1 && W3 && W2 && dx1 && dx3 && dP && dZ,
+               "moe_experts_bwd_x: null buffer");
+  B200_REQUIRE(w1_stride_elems % 8 == 0 && w3_stride_elems % 8 == 0 && w2_stride_elems % 8 == 0,
+               "moe_experts_bwd_x: expert strides must be multiples of 8 elements");
+  B200_REQUIRE(b200_aligned16(x1) && b200_aligned16(x3) && b200_aligned16(dx1) && b200_aligned16(dx3) &&
+                   b200_aligned16(hs) && b200_aligned16(dZ),
+               "moe_experts_bwd_x: buffers must be 16-byte aligned");
+  if (total_rows == 0) return 0;
+  const int64_t m_tiles_max = (int64_t)(total_rows + BM - 1) / BM + num_experts;
+  cudaStream_t s = (cudaStream_t)stream;
+  {
+    // dh = dY W2 (W2_e is [model_dim][ffn_dim]: the reduction index is the slow one -> MN-major B)
+    GemmParams p;
+    zero_params(p);
+    p.group_mode = GROUPED_M;
+    p.num_groups = num_experts;
+    p.N = ffn_dim;
+    p.K = model_dim;
+    p.b_mn_major = 1;
+    p.k_segments = 1;
+    p.counts = expert_counts;
+    p.cumsum_incl = expert_counts_cumsum;
+    p.x1_in = x1;
+    p.x3_in = x3;
+    p.row_w = row_weights;
+    p.dx1 = dx1;
+    p.dx3 = dx3;
+    p.hs = hs;
+    p.dP = dP;
+    if (make_tmap(&p.tmA, dY_zone, 2, (uint64_t)model_dim, (uint64_t)total_rows, 1, (uint64_t)model_dim * 2, 0))
+      return -1;
+    if (make_tmap(&p.tmB, W2, 3, (uint64_t)ffn_dim, (uint64_t)model_dim, (uint64_t)num_experts, (uint64_t)ffn_dim * 2,
+                  (uint64_t)w2_stride_elems * 2))
+      return -1;
+    p.tmA2 = p.tmA;
+    p.tmB2 = p.tmB;
+    if (launch_gemm<EPI_SWIGLU_BWD>(p, m_tiles_max * ((ffn_dim + 255) / 256), s)) return -1;
+  }
+  {
+    // dZ = dx1 W1 + dx3 W3: one accumulator, two reduction segments
+    GemmParams p;
+    zero_params(p);
+    p.group_mode = GROUPED_M;
+    p.num_groups = num_experts;
+    p.N = model_dim;
+    p.K = ffn_dim;
+    p.b_mn_major = 1;
+    p.k_segments = 2;
+    p.counts = expert_counts;
+    p.cumsum_incl = expert_counts_cumsum;
+    p.alpha = 1.0f;
+    p.D = dZ;
+    p.ldd = model_dim;
+    if (make_tmap(&p.tmA, dx1, 2, (uint64_t)ffn_dim, (uint64_t)total_rows, 1, (uint64_t)ffn_dim * 2, 0)) return -1;
+    if (make_tmap(&p.tmA2, dx3, 2, (uint64_t)ffn_dim, (uint64_t)total_rows, 1, (uint64_t)ffn_dim * 2, 0)) return -1;
+    if (make_tmap(&p.tmB, W1, 3, (uint64_t)model_dim, (uint64_t)ffn_dim, (uint64_t)num_experts, (uint64_t)model_dim * 2,
+                  (uint64_t)w1_stride_elems * 2))
+      return -1;
+    if (make_tmap(&p.tmB2, W3, 3, (uint64_t)model_dim, (uint64_t)ffn_dim, (uint64_t)num_experts,
+                  (uint64_t)model_dim * 2, (uint64_t)w3_stride_elems * 2))
+      return -1;
+    if (launch_gemm<EPI_STORE>(p, m_tiles_max * ((model_dim + 255) / 256), s)) return -1;
+  }
+  return 0;
+}
+
+// One grouped wgrad: dW[e][Mrows][Ncols] += A[rows_e, Mrows]^T . B[rows_e, Ncols]
+static int launch_wgrad(int total_rows, int Mrows, int Ncols, int num_experts, const void *A, const void *B, void *dW,
+                        int64_t dw_stride, const int *counts, const int *cumsum, cudaStream_t s) {
+  B200_REQUIRE(dw_stride % 8 == 0 && b200_aligned16(dW), "moe_experts_bwd_w: gradient buffers must be 16-byte aligned");
+  GemmParams p;
+  zero_params(p);
+  p.group_mode = GROUPED_K;
+  p.num_groups = num_experts;
+  p.M = Mrows;
+  p.N = Ncols;
+  p.a_mn_major = 1;
+  p.b_mn_major = 1;
+  p.k_segments = 1;
+  p.counts = counts;
+  p.cumsum_incl = cumsum;
+  p.alpha = 1.0f;
+  p.beta = 1.0f;
+  p.D = dW;
+  p.C = dW;
+  p.ldd = Ncols;
+  p.d_group_stride = dw_stride;
+  if (make_tmap(&p.tmA, A, 2, (uint64_t)Mrows, (uint64_t)total_rows, 1, (uint64_t)Mrows * 2, 0)) return -1;
+  if (make_tmap(&p.tmB, B, 3, (uint64_t)Ncols, (uint64_t)total_rows, 1, (uint64_t)Ncols * 2,
+                (uint64_t)Ncols * 2 * (uint64_t)total_rows))
+    return -1;
+  p.tmA2 = p.tmA;
+  p.tmB2 = p.tmB;
+  const int64_t tiles = (int64_t)num_experts * ((Mrows + BM - 1) / BM) * ((Ncols + 255) / 256);
+  return launch_gemm<EPI_STORE>(p, tiles, s);
+}
+
+extern "C" int b200_moe_experts_bwd_w(int total_rows, int model_dim, int ffn_dim, int num_experts, const void *dY_zone,
+                                      const void *hs, const void *zone_x, const void *dx1, const void *dx3, void *dW1,
+                                      void *dW3, void *dW2, int64_t dw1_stride_elems, int64_t dw3_stride_elems,
+                                      int64_t dw2_stride_elems, const int *expert_counts,
+                                      const int *expert_counts_cumsum, void *stream) {
+  if (check_grouped("moe_experts_bwd_w", total_rows, model_dim, ffn_dim, num_experts, expert_counts,
+                    expert_counts_cumsum))
+    return -1;
+  if (total_rows == 0) return 0;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dW2) {
+    B200_REQUIRE(dY_zone && hs, "moe_experts_bwd_w: dW2 needs dY_zone and hs");
+    if (launch_wgrad(total_rows, model_dim, ffn_dim, num_experts, dY_zone, hs, dW2, dw2_stride_elems, expert_counts,
+                     expert_counts_cumsum, s))
+      return -1;
+  }
+  if (dW1) {
+    B200_REQUIRE(dx1 && zone_x, "moe_experts_bwd_w: dW1 needs dx1 and zone_x");
+    if (launch_wgrad(total_rows, ffn_dim, model_dim, num_experts, dx1, zone_x, dW1, dw1_stride_elems, expert_counts,
+                     expert_counts_cumsum, s))
+      return -1;
+  }
+  if (dW3) {
+    B200_REQUIRE(dx3 && zone_x, "moe_experts_bwd_w: dW3 needs dx3 and zone_x");
+    if (launch_wgrad(total_rows, ffn_dim, model_dim, num_experts, dx3, zone_x, dW3, dw3_stride_elems, expert_counts,
+                     expert_counts_cumsum, s))
+      return -1;
+  }
+  return 0;
+}

@@ -1,0 +1,171 @@
+"""torch-tensor front end of the C ABI (include/b200_moe.h).
+
+One function per reference op, same argument order and meaning as the reference's
+`dataflow_submit_*` functions (libdataflowops/include/dataflow_ops.h:216-294, 70-77) minus the
+handle: tensors stand for the device pointers, the CUDA stream is torch's current stream. A
+non-zero return from the library raises `RuntimeError` (the reference returns -1). torch is only
+used for device memory and streams; every op runs a hand-written sm_100a kernel through ctypes.
+"""
+import ctypes as C
+
+import torch
+
+from . import _lib
+
+DT_NONE, DT_FP32, DT_BF16 = 0, 3, 5
+
+
+def _p(t):
+    return None if t is None else C.c_void_p(t.data_ptr())
+
+
+def _stream():
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _dt(t):
+    if t is None:
+        return DT_NONE
+    if t.dtype == torch.float32:
+        return DT_FP32
+    if t.dtype == torch.bfloat16:
+        return DT_BF16
+    raise TypeError(f"unsupported dtype {t.dtype}")
+
+
+def _check(rc, name):
+    if rc != 0:
+        raise RuntimeError(f"{name} failed (see stderr)")
+
+
+def device_info():
+    sm, major, minor = C.c_int(), C.c_int(), C.c_int()
+    _check(_lib.load().b200_device_info(C.byref(sm), C.byref(major), C.byref(minor)), "b200_device_info")
+    return sm.value, major.value, minor.value
+
+
+def gemm_status():
+    """Synchronises and returns the status word of the GEMM kernels (0 = every wait completed)."""
+    st = C.c_int()
+    _check(_lib.load().b200_gemm_status(C.byref(st)), "b200_gemm_status")
+    return st.value
+
+
+def select_experts(total_tokens, n_experts, top_k_experts, X_routed, token_expert_weights, chosen_experts,
+                   expert_counts, expert_counts_cumsum, host_expert_counts=None):
+    _check(_lib.load().b200_select_experts(_dt(X_routed), total_tokens, n_experts, top_k_experts, _p(X_routed),
+                                           _p(token_expert_weights), _p(chosen_experts), _p(expert_counts),
+                                           _p(expert_counts_cumsum), _p(host_expert_counts), _stream()),
+           "select_experts")
+
+
+def build_expert_mapping_workspace_bytes(total_tokens, num_routed_experts, num_selected_experts):
+    return int(_lib.load().b200_build_expert_mapping_workspace_bytes(total_tokens, num_routed_experts,
+                                                                     num_selected_experts))
+
+
+def build_expert_mapping(total_tokens, num_routed_experts, num_selected_experts, chosen_experts,
+                         expert_counts_cumsum, expert_mapping, token_mapping, workspace):
+    _check(_lib.load().b200_build_expert_mapping(total_tokens, num_routed_experts, num_selected_experts,
+                                                 _p(chosen_experts), _p(expert_counts_cumsum), _p(expert_mapping),
+                                                 _p(token_mapping), _p(workspace),
+                                                 workspace.numel() * workspace.element_size(), _stream()),
+           "build_expert_mapping")
+
+
+def prepare_experts(total_tokens, model_dim, num_selected_experts, X, token_mapping, expert_zone):
+    _check(_lib.load().b200_prepare_experts(total_tokens, model_dim, num_selected_experts, _p(X), _p(token_mapping),
+                                            _p(expert_zone), _stream()), "prepare_experts")
+
+
+def prepare_experts_weighted(total_tokens, model_dim, num_selected_experts, X, token_mapping, token_expert_weights,
+                             expert_zone):
+    _check(_lib.load().b200_prepare_experts_weighted(total_tokens, model_dim, num_selected_experts, _p(X),
+                                                     _p(token_mapping), _p(token_expert_weights), _p(expert_zone),
+                                                     _stream()), "prepare_experts_weighted")
+
+
+def prepare_expert_zone(model_dim, X, expert_id, expert_counts, expert_counts_cumsum, expert_mapping, expert_zone):
+    _check(_lib.load().b200_prepare_expert_zone(model_dim, _p(X), expert_id, _p(expert_counts),
+                                                _p(expert_counts_cumsum), _p(expert_mapping), _p(expert_zone),
+                                                _stream()), "prepare_expert_zone")
+
+
+def merge_experts(num_tokens, model_dim, top_k_experts, expert_zones, token_mapping, token_expert_weights,
+                  X_combined):
+    _check(_lib.load().b200_merge_experts(num_tokens, model_dim, top_k_experts, _p(expert_zones), _p(token_mapping),
+                                          _p(token_expert_weights), _p(X_combined), _stream()), "merge_experts")
+
+
+def merge_expert_result(num_tokens, model_dim, top_k_experts, expert_zone, expert_id, expert_counts_cumsum,
+                        expert_mapping, token_expert_weights, chosen_experts, X_combined):
+    _check(_lib.load().b200_merge_expert_result(num_tokens, model_dim, top_k_experts, _p(expert_zone), expert_id,
+                                                _p(expert_counts_cumsum), _p(expert_mapping),
+                                                _p(token_expert_weights), _p(chosen_experts), _p(X_combined),
+                                                _stream()), "merge_expert_result")
+
+
+def router_bwd_x(num_expert_tokens, model_dim, num_routed_experts, top_k_active, expert_id, expert_counts_cumsum,
+                 expert_mapping, chosen_experts, token_expert_weights, expert_out, upstream_dX, dX_routed,
+                 dX_expert_out):
+    _check(_lib.load().b200_router_bwd_x(num_expert_tokens, model_dim, num_routed_experts, top_k_active, expert_id,
+                                         _p(expert_counts_cumsum), _p(expert_mapping), _p(chosen_experts),
+                                         _p(token_expert_weights), _p(expert_out), _p(upstream_dX), _p(dX_routed),
+                                         _p(dX_expert_out), _stream()), "router_bwd_x")
+
+
+def router_gate_bwd_x(num_tokens, num_routed_experts, top_k_active, chosen_experts, token_expert_weights, dX_routed):
+    _check(_lib.load().b200_router_gate_bwd_x(num_tokens, num_routed_experts, top_k_active, _p(chosen_experts),
+                                              _p(token_expert_weights), _p(dX_routed), _stream()),
+           "router_gate_bwd_x")
+
+
+def swiglu(num_rows, num_cols, x_w1, x_w3, out):
+    _check(_lib.load().b200_swiglu(num_rows, num_cols, _p(x_w1), _p(x_w3), _p(out), _stream()), "swiglu")
+
+
+def swiglu_bwd_x(num_rows, num_cols, x_w1, x_w3, upstream_dX, dX_w1, dX_w3):
+    _check(_lib.load().b200_swiglu_bwd_x(num_rows, num_cols, _p(x_w1), _p(x_w3), _p(upstream_dX), _p(dX_w1),
+                                         _p(dX_w3), _stream()), "swiglu_bwd_x")
+
+
+def matmul(to_trans_a, to_trans_b, M, K, N, alpha, beta, A, B, Cm, D):
+    """Column-major D[MxN] = alpha * op(A) * op(B) + beta * C, the reference's matmul op."""
+    _check(_lib.load().b200_matmul(_dt(A), _dt(B), _dt(Cm), _dt(D), to_trans_a, to_trans_b, M, K, N, alpha, beta,
+                                   _p(A), _p(B), _p(Cm), _p(D), 0, None, _stream()), "matmul")
+
+
+def moe_experts_fwd(total_rows, model_dim, ffn_dim, num_experts, zone, W1, W3, W2, w1_stride, w3_stride, w2_stride,
+                    expert_counts, expert_counts_cumsum, x1, x3, h, Y):
+    _check(_lib.load().b200_moe_experts_fwd(total_rows, model_dim, ffn_dim, num_experts, _p(zone), _p(W1), _p(W3),
+                                            _p(W2), w1_stride, w3_stride, w2_stride, _p(expert_counts),
+                                            _p(expert_counts_cumsum), _p(x1), _p(x3), _p(h), _p(Y), _stream()),
+           "moe_experts_fwd")
+
+
+def moe_experts_bwd_x(total_rows, model_dim, ffn_dim, num_experts, dY_zone, row_weights, x1, x3, W1, W3, W2,
+                      w1_stride, w3_stride, w2_stride, expert_counts, expert_counts_cumsum, dx1, dx3, hs, dP, dZ):
+    _check(_lib.load().b200_moe_experts_bwd_x(total_rows, model_dim, ffn_dim, num_experts, _p(dY_zone),
+                                              _p(row_weights), _p(x1), _p(x3), _p(W1), _p(W3), _p(W2), w1_stride,
+                                              w3_stride, w2_stride, _p(expert_counts), _p(expert_counts_cumsum),
+                                              _p(dx1), _p(dx3), _p(hs), _p(dP), _p(dZ), _stream()),
+           "moe_experts_bwd_x")
+
+
+def moe_experts_bwd_w(total_rows, model_dim, ffn_dim, num_experts, dY_zone, hs, zone_x, dx1, dx3, dW1, dW3, dW2,
+                      dw1_stride, dw3_stride, dw2_stride, expert_counts, expert_counts_cumsum):
+    _check(_lib.load().b200_moe_experts_bwd_w(total_rows, model_dim, ffn_dim, num_experts, _p(dY_zone), _p(hs),
+                                              _p(zone_x), _p(dx1), _p(dx3), _p(dW1), _p(dW3), _p(dW2), dw1_stride,
+                                              dw3_stride, dw2_stride, _p(expert_counts), _p(expert_counts_cumsum),
+                                              _stream()), "moe_experts_bwd_w")
+
+
+def scatter_row_weights(num_tokens, top_k, token_mapping, token_expert_weights, row_weights):
+    _check(_lib.load().b200_scatter_row_weights(num_tokens, top_k, _p(token_mapping), _p(token_expert_weights),
+                                                _p(row_weights), _stream()), "scatter_row_weights")
+
+
+def gather_router_grad(num_tokens, num_routed_experts, top_k, token_mapping, chosen_experts, dP, dX_routed):
+    _check(_lib.load().b200_gather_router_grad(num_tokens, num_routed_experts, top_k, _p(token_mapping),
+                                               _p(chosen_experts), _p(dP), _p(dX_routed), _stream()),
+           "gather_router_grad")

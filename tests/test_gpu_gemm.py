@@ -1,0 +1,176 @@
+"""GPU parity: the tcgen05 GEMM (dense matmul op in all four layouts, grouped expert GEMMs) against the oracle.
+
+bf16 outputs are compared at 2e-2 relative / 1e-3 absolute (fp32 accumulation on both sides, different
+summation order); fp32 outputs at 1e-3 / 1e-3.
+"""
+import numpy as np
+import pytest
+import torch
+
+from gpu_util import dev, dev_bf16, host_bits, rand_bf16, require_b200
+from helpers import assert_close, bf16_bits_to_f32
+
+pytestmark = pytest.mark.gpu
+
+
+def gemm_ok(ops):
+    st = ops.gemm_status()
+    assert st == 0, f"a GEMM kernel gave up waiting (status {st})"
+
+
+@pytest.mark.parametrize("ta,tb", [(1, 0), (0, 0), (0, 1), (1, 1)])
+@pytest.mark.parametrize("M,K,N", [(64, 64, 128), (256, 128, 128), (1408, 4096, 300), (4096, 1408, 129), (72, 200, 40),
+                                   (520, 264, 1000), (64, 4096, 777)])
+def test_matmul_layouts(oracle, ta, tb, M, K, N):
+    require_b200()
+    from ml_dataflow_b200 import ops
+
+    if tb and N % 8:
+        N = (N + 7) // 8 * 8
+    rng = np.random.default_rng(M + 3 * K + 7 * N + ta * 2 + tb)
+    A = rand_bf16(rng, (M, K) if ta else (K, M), std=0.5)   # column-major KxM when transposed == row-major [M][K]
+    B = rand_bf16(rng, (K, N) if tb else (N, K), std=0.5)
+    D_ref = np.zeros((N, M), np.uint16)
+    oracle.matmul(ta, tb, M, K, N, 1.0, 0.0, A, B, None, D_ref)
+    D = torch.zeros((N, M), dtype=torch.bfloat16, device="cuda")
+    ops.matmul(ta, tb, M, K, N, 1.0, 0.0, dev_bf16(A), dev_bf16(B), None, D)
+    gemm_ok(ops)
+    assert_close(bf16_bits_to_f32(host_bits(D)), bf16_bits_to_f32(D_ref), what=f"matmul ta={ta} tb={tb}")
+
+
+def test_matmul_alpha_beta_inplace_and_fp32_out(oracle):
+    require_b200()
+    from ml_dataflow_b200 import ops
+
+    M, K, N = 256, 320, 200
+    rng = np.random.default_rng(2)
+    A, B = rand_bf16(rng, (M, K), 0.3), rand_bf16(rng, (N, K), 0.3)
+    C = rand_bf16(rng, (N, M))
+    ref = C.copy()
+    oracle.matmul(1, 0, M, K, N, 0.5, 1.0, A, B, ref, ref)
+    Dd = dev_bf16(C.copy())
+    ops.matmul(1, 0, M, K, N, 0.5, 1.0, dev_bf16(A), dev_bf16(B), Dd, Dd)  # C = D, beta = 1
+    gemm_ok(ops)
+    assert_close(bf16_bits_to_f32(host_bits(Dd)), bf16_bits_to_f32(ref), what="beta=1 in place")
+    # fp32 output (the router logits form: bf16 x bf16 -> fp32)
+    ref32 = np.zeros((N, M), np.float32)
+    oracle.matmul(1, 0, M, K, N, 1.0, 0.0, A, B, None, ref32)
+    D32 = torch.zeros((N, M), dtype=torch.float32, device="cuda")
+    ops.matmul(1, 0, M, K, N, 1.0, 0.0, dev_bf16(A), dev_bf16(B), None, D32)
+    gemm_ok(ops)
+    assert_close(D32.cpu().numpy(), ref32, rtol=1e-3, atol=1e-3, what="fp32 out")
+
+
+def test_router_gemm_shape(oracle):
+    """logits[T, E] = Xn Wr^T with fp32 output at a production shape (E = 64, d = 4096)."""
+    require_b200()
+    from ml_dataflow_b200 import ops
+
+    T, d, E = 1000, 4096, 64
+    rng = np.random.default_rng(4)
+    Xn, Wr = rand_bf16(rng, (T, d)), rand_bf16(rng, (E, d), 0.02)
+    ref = oracle.linear_fwd(Xn, Wr, out_dtype=np.float32)
+    out = torch.zeros((T, E), dtype=torch.float32, device="cuda")
+    ops.matmul(1, 0, E, d, T, 1.0, 0.0, dev_bf16(Wr), dev_bf16(Xn), None, out)
+    gemm_ok(ops)
+    assert_close(out.cpu().numpy(), ref, rtol=1e-3, atol=1e-3, what="router logits")
+
+
+def make_counts(rng, E, R, empty=()):
+    p = rng.random(E) + 0.05
+    for e in empty:
+        p[e] = 0
+    counts = rng.multinomial(R, p / p.sum()).astype(np.int32)
+    return counts, np.cumsum(counts).astype(np.int32)
+
+
+@pytest.mark.parametrize("R,d,f,E,empty", [(300, 128, 64, 4, ()), (1000, 256, 192, 8, (0, 5)), (2500, 1024, 1408, 16, (15,)),
+                                           (129, 4096, 1408, 2, ())])
+def test_grouped_forward(oracle, R, d, f, E, empty):
+    require_b200()
+    from ml_dataflow_b200 import ops
+
+    rng = np.random.default_rng(R + d + f)
+    counts, cincl = make_counts(rng, E, R, empty)
+    Z = rand_bf16(rng, (R, d))
+    W1, W3, W2 = rand_bf16(rng, (E, f, d), 0.03), rand_bf16(rng, (E, f, d), 0.03), rand_bf16(rng, (E, d, f), 0.03)
+    x1, x3, h = (torch.zeros((R, f), dtype=torch.bfloat16, device="cuda") for _ in range(3))
+    Y = torch.zeros((R, d), dtype=torch.bfloat16, device="cuda")
+    ops.moe_experts_fwd(R, d, f, E, dev_bf16(Z), dev_bf16(W1), dev_bf16(W3), dev_bf16(W2), f * d, f * d, d * f,
+                        dev(counts), dev(cincl), x1, x3, h, Y)
+    gemm_ok(ops)
+    # each op is checked on the inputs the GPU path actually fed it, so every comparison is strict
+    x1g, x3g, hg = host_bits(x1), host_bits(x3), host_bits(h)
+    x1r, x3r = np.zeros((R, f), np.uint16), np.zeros((R, f), np.uint16)
+    Yr = np.zeros((R, d), np.uint16)
+    b = 0
+    for e in range(E):
+        n = int(counts[e])
+        if n:
+            x1r[b:b + n] = oracle.linear_fwd(Z[b:b + n], W1[e])
+            x3r[b:b + n] = oracle.linear_fwd(Z[b:b + n], W3[e])
+            Yr[b:b + n] = oracle.linear_fwd(np.ascontiguousarray(hg[b:b + n]), W2[e])
+        b += n
+    assert_close(bf16_bits_to_f32(x1g), bf16_bits_to_f32(x1r), what="x1")
+    assert_close(bf16_bits_to_f32(x3g), bf16_bits_to_f32(x3r), what="x3")
+    assert_close(bf16_bits_to_f32(hg), bf16_bits_to_f32(oracle.swiglu(x1g, x3g)), what="h")
+    assert_close(bf16_bits_to_f32(host_bits(Y)), bf16_bits_to_f32(Yr), what="Y")
+
+
+@pytest.mark.parametrize("R,d,f,E,empty", [(300, 128, 64, 4, ()), (1000, 256, 192, 8, (2,)), (2500, 1024, 1408, 16, (0, 15))])
+def test_grouped_backward(oracle, R, d, f, E, empty):
+    """bwd_x + bwd_w against the oracle ops chained in the reference's order (with Y recomputed for dP)."""
+    require_b200()
+    from ml_dataflow_b200 import ops
+
+    rng = np.random.default_rng(R * 3 + d + f)
+    counts, cincl = make_counts(rng, E, R, empty)
+    dOutRows = rand_bf16(rng, (R, d))            # upstream gradient rows, already in expert order
+    Zx = rand_bf16(rng, (R, d))
+    roww = (rng.random(R, dtype=np.float32) * 0.5 + 0.05).astype(np.float32)
+    from helpers import assert_close_chained, f32_to_bf16_bits
+    dYs = f32_to_bf16_bits(bf16_bits_to_f32(dOutRows) * roww[:, None])  # what router_bwd_x leaves in the zone
+    x1, x3 = rand_bf16(rng, (R, f)), rand_bf16(rng, (R, f))
+    W1, W3, W2 = rand_bf16(rng, (E, f, d), 0.03), rand_bf16(rng, (E, f, d), 0.03), rand_bf16(rng, (E, d, f), 0.03)
+    g1, g3, g2 = rand_bf16(rng, (E, f, d), 0.1), rand_bf16(rng, (E, f, d), 0.1), rand_bf16(rng, (E, d, f), 0.1)
+
+    dx1r, dx3r = np.zeros((R, f), np.uint16), np.zeros((R, f), np.uint16)
+    dZr = np.zeros((R, d), np.uint16)
+    dPr = np.zeros(R, np.float32)
+    hr = oracle.swiglu(x1, x3)
+    g1r, g3r, g2r = g1.copy(), g3.copy(), g2.copy()
+    b = 0
+    for e in range(E):
+        n = int(counts[e])
+        if n:
+            sl = slice(b, b + n)
+            y = oracle.linear_fwd(hr[sl], W2[e])
+            dPr[sl] = (bf16_bits_to_f32(y) * bf16_bits_to_f32(dOutRows[sl])).sum(axis=1)
+            oracle.linear_wgrad(hr[sl], dYs[sl], g2r[e])
+            dh = oracle.linear_dgrad(dYs[sl], W2[e])
+            dx1r[sl], dx3r[sl] = oracle.swiglu_bwd_x(x1[sl], x3[sl], dh)
+            dz = oracle.linear_dgrad(np.ascontiguousarray(dx1r[sl]), W1[e])
+            dZr[sl] = oracle.linear_dgrad(np.ascontiguousarray(dx3r[sl]), W3[e], accumulate_into=dz)
+            oracle.linear_wgrad(Zx[sl], np.ascontiguousarray(dx1r[sl]), g1r[e])
+            oracle.linear_wgrad(Zx[sl], np.ascontiguousarray(dx3r[sl]), g3r[e])
+        b += n
+
+    dx1, dx3, hs = (torch.zeros((R, f), dtype=torch.bfloat16, device="cuda") for _ in range(3))
+    dZ = torch.zeros((R, d), dtype=torch.bfloat16, device="cuda")
+    dP = torch.zeros(R, dtype=torch.float32, device="cuda")
+    dYd, Zxd, cd, cid = dev_bf16(dYs), dev_bf16(Zx), dev(counts), dev(cincl)
+    W1d, W3d, W2d = dev_bf16(W1), dev_bf16(W3), dev_bf16(W2)
+    ops.moe_experts_bwd_x(R, d, f, E, dYd, torch.from_numpy(roww).cuda(), dev_bf16(x1), dev_bf16(x3), W1d, W3d, W2d,
+                          f * d, f * d, d * f, cd, cid, dx1, dx3, hs, dP, dZ)
+    G1, G3, G2 = dev_bf16(g1), dev_bf16(g3), dev_bf16(g2)
+    ops.moe_experts_bwd_w(R, d, f, E, dYd, hs, Zxd, dx1, dx3, G1, G3, G2, f * d, f * d, d * f, cd, cid)
+    gemm_ok(ops)
+    f32 = bf16_bits_to_f32
+    assert_close(dP.cpu().numpy(), dPr, rtol=2e-2, atol=2e-2 * float(np.abs(dPr).mean() + 1e-6), what="dP")
+    assert_close(f32(host_bits(hs)), f32(hr), what="hs")
+    assert_close_chained(f32(host_bits(dx1)), f32(dx1r), what="dx1")
+    assert_close_chained(f32(host_bits(dx3)), f32(dx3r), what="dx3")
+    assert_close_chained(f32(host_bits(dZ)), f32(dZr), what="dZ")
+    assert_close_chained(f32(host_bits(G2)), f32(g2r), what="dW2")
+    assert_close_chained(f32(host_bits(G1)), f32(g1r), what="dW1")
+    assert_close_chained(f32(host_bits(G3)), f32(g3r), what="dW3")

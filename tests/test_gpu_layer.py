@@ -1,0 +1,182 @@
+"""GPU parity of the whole MoE layer (forward + backward) against the CPU oracle and the golden fixtures.
+
+Routing is bit-exact given the same logits, so each test feeds the oracle the fp32 logits the GPU router GEMM
+produced (compared separately at 1e-3) and then demands: identical chosen experts / counts / cumsums / mappings,
+and every bf16 tensor within 2e-2 relative + 1e-3 absolute (tensors computed from earlier GPU results are
+checked with helpers.assert_close_chained: at most 1e-3 of the elements may exceed that bound, none by more than 8x,
+and the relative Frobenius error must stay below 4e-3).
+"""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from gpu_util import dev_bf16, host_bits, host_u16, rand_bf16, require_b200
+from helpers import assert_close, assert_close_chained, bf16_bits_to_f32
+
+pytestmark = pytest.mark.gpu
+GOLD = os.path.join(os.path.dirname(__file__), "golden")
+f32 = bf16_bits_to_f32
+
+
+def run_layer(path, T, d, E, k, f, X, Wr, W1, W3, W2, dOut, g0, logits=None):
+    from ml_dataflow_b200 import ops
+    from ml_dataflow_b200.moe_layer import MoELayer
+
+    layer = MoELayer(T, d, E, k, f)
+    Xd, Wrd, W1d, W3d, W2d, dOd = (dev_bf16(a) for a in (X, Wr, W1, W3, W2, dOut))
+    out = torch.zeros((T, d), dtype=torch.bfloat16, device="cuda")
+    dXn = torch.empty((T, d), dtype=torch.bfloat16, device="cuda")
+    G = {n: dev_bf16(g0[n].copy()) for n in ("dWr", "dW1", "dW3", "dW2")}
+    lg = None if logits is None else torch.from_numpy(logits).cuda()
+    if path == "fast":
+        layer.forward(Xd, Wrd, W1d, W3d, W2d, out, logits=lg)
+        layer.backward(Xd, Wrd, W1d, W3d, W2d, dOd, dXn, G["dWr"], G["dW1"], G["dW3"], G["dW2"])
+    else:
+        layer.forward_reference_order(Xd, Wrd, W1d, W3d, W2d, out, logits=lg)
+        layer.backward_reference_order(Xd, Wrd, W1d, W3d, W2d, dOd, dXn, G["dWr"], G["dW1"], G["dW3"], G["dW2"])
+    st = ops.gemm_status()
+    assert st == 0, f"GEMM status {st}"
+    return layer, out, dXn, G
+
+
+def compare_with_oracle(oracle, layer, out, dXn, G, X, Wr, W1, W3, W2, dOut, g0, k):
+    E = Wr.shape[0]
+    logits = layer.logits.cpu().numpy()
+    ref_logits = oracle.linear_fwd(X, Wr, out_dtype=np.float32)
+    assert_close(logits, ref_logits, rtol=1e-3, atol=1e-3, what="router logits")
+    fwd = oracle.moe_forward(X, Wr, W1, W3, W2, k, logits=logits)
+    np.testing.assert_array_equal(host_u16(layer.chosen), fwd["chosen"])
+    np.testing.assert_array_equal(layer.counts.cpu().numpy()[:E], fwd["counts"][:E])
+    np.testing.assert_array_equal(layer.cumsum.cpu().numpy(), fwd["cumsum_incl"])
+    np.testing.assert_array_equal(layer.token_mapping.cpu().numpy(), fwd["token_mapping"])
+    np.testing.assert_array_equal(layer.expert_mapping.cpu().numpy(), fwd["expert_mapping"])
+    np.testing.assert_allclose(layer.weights.cpu().numpy(), fwd["weights"], rtol=1e-5, atol=1e-7)
+    np.testing.assert_array_equal(host_bits(layer.zone), fwd["zone"])
+    for name in ("x1", "x3"):
+        assert_close(f32(host_bits(getattr(layer, name))), f32(fwd[name]), what=name)
+    assert_close_chained(f32(host_bits(layer.Y)), f32(fwd["Y"]), what="Y")
+    assert_close_chained(f32(host_bits(out)), f32(fwd["out"]), what="out")
+    grads = {n: g0[n].copy() for n in g0}
+    bwd = oracle.moe_backward(X, Wr, W1, W3, W2, k, fwd, dOut, grads=grads)
+    assert_close_chained(f32(host_bits(layer.dx1)), f32(bwd["dx1"]), what="dx1")
+    assert_close_chained(f32(host_bits(layer.dx3)), f32(bwd["dx3"]), what="dx3")
+    assert_close_chained(f32(host_bits(layer.dZ)), f32(bwd["dZ"]), what="dZ")
+    ref_dl = f32(bwd["dlogits"])
+    # the gate Jacobian subtracts bf16-rounded dot products: allow a few bf16 ulps of their magnitude
+    assert_close(f32(host_bits(layer.dX_routed)), ref_dl, rtol=2e-2,
+                 atol=2e-3 + 4e-2 * float(np.sqrt((ref_dl[ref_dl != 0] ** 2).mean())), what="dlogits")
+    assert_close_chained(f32(host_bits(dXn)), f32(bwd["dXn"]), what="dXn")
+    for n in ("dW1", "dW3", "dW2", "dWr"):
+        assert_close_chained(f32(host_bits(G[n])), f32(bwd[n]), what=n)
+
+
+def make_case(seed, T, d, E, k, f, wstd=0.02, grad_init=0.0):
+    rng = np.random.default_rng(seed)
+    X, dOut = rand_bf16(rng, (T, d)), rand_bf16(rng, (T, d))
+    Wr = rand_bf16(rng, (E, d), wstd)
+    W1, W3, W2 = rand_bf16(rng, (E, f, d), wstd), rand_bf16(rng, (E, f, d), wstd), rand_bf16(rng, (E, d, f), wstd)
+    g0 = dict(dWr=rand_bf16(rng, (E, d), grad_init), dW1=rand_bf16(rng, (E, f, d), grad_init),
+              dW3=rand_bf16(rng, (E, f, d), grad_init), dW2=rand_bf16(rng, (E, d, f), grad_init))
+    return X, Wr, W1, W3, W2, dOut, g0
+
+
+@pytest.mark.parametrize("path", ["fast", "reference_order"])
+@pytest.mark.parametrize("T,d,E,k,f", [(200, 128, 8, 2, 64), (512, 256, 16, 4, 192)])
+def test_layer_small(oracle, path, T, d, E, k, f):
+    require_b200()
+    X, Wr, W1, W3, W2, dOut, g0 = make_case(T + d, T, d, E, k, f, wstd=0.06, grad_init=0.05)
+    layer, out, dXn, G = run_layer(path, T, d, E, k, f, X, Wr, W1, W3, W2, dOut, g0)
+    compare_with_oracle(oracle, layer, out, dXn, G, X, Wr, W1, W3, W2, dOut, g0, k)
+
+
+def test_layer_config1_fast_path(oracle):
+    """BASELINE config 1: T=2048, d=1024, 16 experts, top-2, ffn 1024, weights N(0, 0.02)."""
+    require_b200()
+    T, d, E, k, f = 2048, 1024, 16, 2, 1024
+    X, Wr, W1, W3, W2, dOut, g0 = make_case(1, T, d, E, k, f)
+    layer, out, dXn, G = run_layer("fast", T, d, E, k, f, X, Wr, W1, W3, W2, dOut, g0)
+    compare_with_oracle(oracle, layer, out, dXn, G, X, Wr, W1, W3, W2, dOut, g0, k)
+
+
+@pytest.mark.parametrize("name", ["moe_mlp_small", "moe_mlp_k4"])
+def test_layer_against_reference_pytorch_golden(name):
+    """The CUDA layer against tensors produced by the reference's own PyTorch MoE layer (tests/golden)."""
+    require_b200()
+    g = np.load(os.path.join(GOLD, name + ".npz"))
+    T, d, E, k, f = [int(v) for v in g["shape"]]
+    zeros = dict(dWr=np.zeros((E, d), np.uint16), dW1=np.zeros((E, f, d), np.uint16),
+                 dW3=np.zeros((E, f, d), np.uint16), dW2=np.zeros((E, d, f), np.uint16))
+    layer, out, dXn, G = run_layer("fast", T, d, E, k, f, g["X"], g["Wr"], g["W1"], g["W3"], g["W2"], g["dOut"], zeros,
+                                   logits=np.ascontiguousarray(g["logits"]))
+    ch = host_u16(layer.chosen).astype(np.int32)
+    np.testing.assert_array_equal(np.sort(ch, axis=1), np.sort(g["selected"], axis=1))
+
+    def rms(a):
+        return float(np.sqrt(np.mean(np.asarray(a, np.float64) ** 2)))
+
+    def rel_fro(a, b):
+        return float(np.linalg.norm(a.astype(np.float64) - b) / (np.linalg.norm(b.astype(np.float64)) + 1e-30))
+
+    pairs = [(out, g["out"], "out"), (dXn, g["dX"], "dX"), (G["dW1"], g["dW1"], "dW1"), (G["dW3"], g["dW3"], "dW3"),
+             (G["dW2"], g["dW2"], "dW2")]
+    for got, ref, what in pairs:
+        a, b = f32(host_bits(got)), f32(ref)
+        assert rel_fro(a, b) < 8e-3, what
+        assert_close(a, b, atol=4e-2 * rms(b), what=what)
+    assert rel_fro(f32(host_bits(G["dWr"])), g["dWr"]) < 8e-3
+
+
+def test_layer_properties_full_size():
+    """BASELINE config 2 shape (T=8192, d=4096, 64 experts, top-8, ffn 1408): size-independent properties.
+
+    counts sum to T*k; token_mapping is a permutation of 0..R-1 consistent with expert_mapping; gate weights sum
+    to 1; forward is linear in the gate weights' residual (out with residual r equals out without + r up to one
+    rounding); un-permute(permute(x)) == k * x.
+    """
+    require_b200()
+    from ml_dataflow_b200 import ops
+    from ml_dataflow_b200.moe_layer import MoELayer
+
+    T, d, E, k, f = 8192, 4096, 64, 8, 1408
+    gen = torch.Generator(device="cuda").manual_seed(5)
+    X = torch.randn((T, d), generator=gen, device="cuda").to(torch.bfloat16)
+    Wr = (torch.randn((E, d), generator=gen, device="cuda") * 0.02).to(torch.bfloat16)
+    W1 = (torch.randn((E, f, d), generator=gen, device="cuda") * 0.02).to(torch.bfloat16)
+    W3 = (torch.randn((E, f, d), generator=gen, device="cuda") * 0.02).to(torch.bfloat16)
+    W2 = (torch.randn((E, d, f), generator=gen, device="cuda") * 0.02).to(torch.bfloat16)
+    layer = MoELayer(T, d, E, k, f)
+    out = torch.zeros((T, d), dtype=torch.bfloat16, device="cuda")
+    layer.forward(X, Wr, W1, W3, W2, out)
+    assert ops.gemm_status() == 0
+    counts = layer.counts[:E].cpu().numpy()
+    assert counts.sum() == T * k
+    np.testing.assert_array_equal(layer.cumsum.cpu().numpy(), np.cumsum(counts))
+    tm = layer.token_mapping.cpu().numpy().reshape(-1)
+    em = layer.expert_mapping.cpu().numpy()
+    np.testing.assert_array_equal(np.sort(tm), np.arange(T * k))
+    np.testing.assert_array_equal(em[tm], np.repeat(np.arange(T), k))
+    ch = host_u16(layer.chosen).reshape(-1).astype(np.int64)
+    np.testing.assert_array_equal(np.searchsorted(np.cumsum(counts), tm, side="right"), ch)
+    np.testing.assert_allclose(layer.weights.sum(dim=1).cpu().numpy(), 1.0, rtol=1e-5)
+    assert torch.isfinite(out.float()).all()
+    # permute then un-permute with unit weights gives k copies of every row
+    back = torch.zeros((T, d), dtype=torch.bfloat16, device="cuda")
+    ops.merge_experts(T, d, k, layer.zone, layer.token_mapping, None, back)
+    torch.cuda.synchronize()
+    assert torch.equal(back, (X.float() * k).to(torch.bfloat16))
+    # expert outputs against a torch fp32 evaluation of three sampled experts
+    base = np.concatenate([[0], np.cumsum(counts)])
+    for e in (0, 31, 63):
+        n = int(counts[e])
+        if n == 0:
+            continue
+        z = layer.zone[base[e]:base[e] + n].float()
+        x1 = (z @ W1[e].float().T).to(torch.bfloat16).float()
+        x3 = (z @ W3[e].float().T).to(torch.bfloat16).float()
+        h = (torch.nn.functional.silu(x1) * x3).to(torch.bfloat16).float()
+        y = (h @ W2[e].float().T)
+        got = layer.Y[base[e]:base[e] + n].float()
+        err = (got - y).abs()
+        assert (err <= 1e-3 + 2e-2 * y.abs()).float().mean() > 0.999, f"expert {e}"

@@ -53,8 +53,11 @@ class MoELayer:
         self.dx1 = buf((R, f), bf)
         self.dx3 = buf((R, f), bf)
         self.hs = buf((R, f), bf)
+        self.dh = None  # [R, f], allocated on first use by the reference-order backward only
         self.dZ = buf((R, d), bf)
         self.dX_routed = buf((T, E), bf)
+        self.keep_pre_gate = False  # tests set this to look at dX_routed before the gate Jacobian is applied
+        self.dX_routed_pre = None
 
     # ------------------------------------------------------------------ routing (shared)
     def route(self, Xn, Wr, logits=None):
@@ -98,6 +101,8 @@ class MoELayer:
         ops.merge_experts(T, d, k, self.dZ, self.token_mapping, None, dXn)
         self.dX_routed.zero_()
         ops.gather_router_grad(T, E, k, self.token_mapping, self.chosen, self.dP, self.dX_routed)
+        if self.keep_pre_gate:
+            self.dX_routed_pre = self.dX_routed.clone()
         ops.router_gate_bwd_x(T, E, k, self.chosen, self.weights, self.dX_routed)
         # dXn += dL . Wr   (reference: transa=0, transb=0, M=d, K=E, N=T, beta=1, C=D)
         ops.matmul(0, 0, d, E, T, 1.0, 1.0, Wr, self.dX_routed, dXn, dXn)
@@ -142,7 +147,9 @@ class MoELayer:
             ops.router_bwd_x(n, d, E, k, e, self.cumsum, self.expert_mapping, self.chosen, self.weights, zone[sl],
                              dOut, self.dX_routed, zone[sl])
             ops.matmul(0, 1, f, n, d, 1.0, 1.0, tmp, zone[sl], dW2[e], dW2[e])  # dW2 += dY^T h
-            dh = self.h[sl]
+            if self.dh is None:
+                self.dh = torch.empty_like(self.h)
+            dh = self.dh[sl]
             ops.matmul(0, 0, f, d, n, 1.0, 0.0, W2[e], zone[sl], None, dh)  # dh = dY W2
             ops.swiglu_bwd_x(n, f, x1, x3, dh, self.dx1[sl], self.dx3[sl])
             ops.matmul(0, 0, d, f, n, 1.0, 0.0, W1[e], self.dx1[sl], None, zone[sl])
@@ -150,6 +157,8 @@ class MoELayer:
             base += n
         dXn.zero_()
         ops.merge_experts(T, d, k, zone, self.token_mapping, None, dXn)
+        if self.keep_pre_gate:
+            self.dX_routed_pre = self.dX_routed.clone()
         ops.router_gate_bwd_x(T, E, k, self.chosen, self.weights, self.dX_routed)
         ops.matmul(0, 0, d, E, T, 1.0, 1.0, Wr, self.dX_routed, dXn, dXn)
         # backward-w

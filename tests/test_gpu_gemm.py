@@ -128,16 +128,29 @@ def test_grouped_backward(oracle, R, d, f, E, empty):
     dOutRows = rand_bf16(rng, (R, d))            # upstream gradient rows, already in expert order
     Zx = rand_bf16(rng, (R, d))
     roww = (rng.random(R, dtype=np.float32) * 0.5 + 0.05).astype(np.float32)
-    from helpers import assert_close_chained, f32_to_bf16_bits
+    from helpers import f32_to_bf16_bits
     dYs = f32_to_bf16_bits(bf16_bits_to_f32(dOutRows) * roww[:, None])  # what router_bwd_x leaves in the zone
     x1, x3 = rand_bf16(rng, (R, f)), rand_bf16(rng, (R, f))
     W1, W3, W2 = rand_bf16(rng, (E, f, d), 0.03), rand_bf16(rng, (E, f, d), 0.03), rand_bf16(rng, (E, d, f), 0.03)
     g1, g3, g2 = rand_bf16(rng, (E, f, d), 0.1), rand_bf16(rng, (E, f, d), 0.1), rand_bf16(rng, (E, d, f), 0.1)
 
+    hr = oracle.swiglu(x1, x3)
+    dx1, dx3, hs = (torch.zeros((R, f), dtype=torch.bfloat16, device="cuda") for _ in range(3))
+    dZ = torch.zeros((R, d), dtype=torch.bfloat16, device="cuda")
+    dP = torch.zeros(R, dtype=torch.float32, device="cuda")
+    dYd, Zxd, cd, cid = dev_bf16(dYs), dev_bf16(Zx), dev(counts), dev(cincl)
+    W1d, W3d, W2d = dev_bf16(W1), dev_bf16(W3), dev_bf16(W2)
+    ops.moe_experts_bwd_x(R, d, f, E, dYd, torch.from_numpy(roww).cuda(), dev_bf16(x1), dev_bf16(x3), W1d, W3d, W2d,
+                          f * d, f * d, d * f, cd, cid, dx1, dx3, hs, dP, dZ)
+    G1, G3, G2 = dev_bf16(g1), dev_bf16(g3), dev_bf16(g2)
+    ops.moe_experts_bwd_w(R, d, f, E, dYd, hs, Zxd, dx1, dx3, G1, G3, G2, f * d, f * d, d * f, cd, cid)
+    gemm_ok(ops)
+    dx1g, dx3g = host_bits(dx1), host_bits(dx3)
+
+    # oracle, op by op, every op on the inputs the GPU op consumed
     dx1r, dx3r = np.zeros((R, f), np.uint16), np.zeros((R, f), np.uint16)
     dZr = np.zeros((R, d), np.uint16)
     dPr = np.zeros(R, np.float32)
-    hr = oracle.swiglu(x1, x3)
     g1r, g3r, g2r = g1.copy(), g3.copy(), g2.copy()
     b = 0
     for e in range(E):
@@ -149,28 +162,17 @@ def test_grouped_backward(oracle, R, d, f, E, empty):
             oracle.linear_wgrad(hr[sl], dYs[sl], g2r[e])
             dh = oracle.linear_dgrad(dYs[sl], W2[e])
             dx1r[sl], dx3r[sl] = oracle.swiglu_bwd_x(x1[sl], x3[sl], dh)
-            dz = oracle.linear_dgrad(np.ascontiguousarray(dx1r[sl]), W1[e])
-            dZr[sl] = oracle.linear_dgrad(np.ascontiguousarray(dx3r[sl]), W3[e], accumulate_into=dz)
-            oracle.linear_wgrad(Zx[sl], np.ascontiguousarray(dx1r[sl]), g1r[e])
-            oracle.linear_wgrad(Zx[sl], np.ascontiguousarray(dx3r[sl]), g3r[e])
+            dz = oracle.linear_dgrad(np.ascontiguousarray(dx1g[sl]), W1[e])
+            dZr[sl] = oracle.linear_dgrad(np.ascontiguousarray(dx3g[sl]), W3[e], accumulate_into=dz)
+            oracle.linear_wgrad(Zx[sl], np.ascontiguousarray(dx1g[sl]), g1r[e])
+            oracle.linear_wgrad(Zx[sl], np.ascontiguousarray(dx3g[sl]), g3r[e])
         b += n
-
-    dx1, dx3, hs = (torch.zeros((R, f), dtype=torch.bfloat16, device="cuda") for _ in range(3))
-    dZ = torch.zeros((R, d), dtype=torch.bfloat16, device="cuda")
-    dP = torch.zeros(R, dtype=torch.float32, device="cuda")
-    dYd, Zxd, cd, cid = dev_bf16(dYs), dev_bf16(Zx), dev(counts), dev(cincl)
-    W1d, W3d, W2d = dev_bf16(W1), dev_bf16(W3), dev_bf16(W2)
-    ops.moe_experts_bwd_x(R, d, f, E, dYd, torch.from_numpy(roww).cuda(), dev_bf16(x1), dev_bf16(x3), W1d, W3d, W2d,
-                          f * d, f * d, d * f, cd, cid, dx1, dx3, hs, dP, dZ)
-    G1, G3, G2 = dev_bf16(g1), dev_bf16(g3), dev_bf16(g2)
-    ops.moe_experts_bwd_w(R, d, f, E, dYd, hs, Zxd, dx1, dx3, G1, G3, G2, f * d, f * d, d * f, cd, cid)
-    gemm_ok(ops)
     f32 = bf16_bits_to_f32
     assert_close(dP.cpu().numpy(), dPr, rtol=2e-2, atol=2e-2 * float(np.abs(dPr).mean() + 1e-6), what="dP")
     assert_close(f32(host_bits(hs)), f32(hr), what="hs")
-    assert_close_chained(f32(host_bits(dx1)), f32(dx1r), what="dx1")
-    assert_close_chained(f32(host_bits(dx3)), f32(dx3r), what="dx3")
-    assert_close_chained(f32(host_bits(dZ)), f32(dZr), what="dZ")
-    assert_close_chained(f32(host_bits(G2)), f32(g2r), what="dW2")
-    assert_close_chained(f32(host_bits(G1)), f32(g1r), what="dW1")
-    assert_close_chained(f32(host_bits(G3)), f32(g3r), what="dW3")
+    assert_close(f32(dx1g), f32(dx1r), what="dx1")  # differs from the oracle only through one rounding of dh
+    assert_close(f32(dx3g), f32(dx3r), what="dx3")
+    assert_close(f32(host_bits(dZ)), f32(dZr), what="dZ")
+    assert_close(f32(host_bits(G2)), f32(g2r), what="dW2")
+    assert_close(f32(host_bits(G1)), f32(g1r), what="dW1")
+    assert_close(f32(host_bits(G3)), f32(g3r), what="dW3")

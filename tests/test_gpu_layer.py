@@ -2,9 +2,9 @@
 
 Routing is bit-exact given the same logits, so each test feeds the oracle the fp32 logits the GPU router GEMM
 produced (compared separately at 1e-3) and then demands: identical chosen experts / counts / cumsums / mappings,
-and every bf16 tensor within 2e-2 relative + 1e-3 absolute (tensors computed from earlier GPU results are
-checked with helpers.assert_close_chained: at most 1e-3 of the elements may exceed that bound, none by more than 8x,
-and the relative Frobenius error must stay below 4e-3).
+and every op's bf16 output within 2e-2 relative + 1e-3 absolute of the oracle op applied to the same inputs. The
+end-to-end chain (GPU chain vs oracle chain) is additionally held to a relative Frobenius error, because bf16
+values that round the other way early in a chain move later sums by more than the element-wise bound near zero.
 """
 import os
 
@@ -13,7 +13,7 @@ import pytest
 import torch
 
 from gpu_util import dev_bf16, host_bits, host_u16, rand_bf16, require_b200
-from helpers import assert_close, assert_close_chained, bf16_bits_to_f32
+from helpers import assert_close, bf16_bits_to_f32
 
 pytestmark = pytest.mark.gpu
 GOLD = os.path.join(os.path.dirname(__file__), "golden")
@@ -25,6 +25,7 @@ def run_layer(path, T, d, E, k, f, X, Wr, W1, W3, W2, dOut, g0, logits=None):
     from ml_dataflow_b200.moe_layer import MoELayer
 
     layer = MoELayer(T, d, E, k, f)
+    layer.keep_pre_gate = True
     Xd, Wrd, W1d, W3d, W2d, dOd = (dev_bf16(a) for a in (X, Wr, W1, W3, W2, dOut))
     out = torch.zeros((T, d), dtype=torch.bfloat16, device="cuda")
     dXn = torch.empty((T, d), dtype=torch.bfloat16, device="cuda")
@@ -41,12 +42,17 @@ def run_layer(path, T, d, E, k, f, X, Wr, W1, W3, W2, dOut, g0, logits=None):
     return layer, out, dXn, G
 
 
-def compare_with_oracle(oracle, layer, out, dXn, G, X, Wr, W1, W3, W2, dOut, g0, k):
-    E = Wr.shape[0]
+def compare_with_oracle(oracle, layer, out, dXn, G, X, Wr, W1, W3, W2, dOut, g0, k, path):
+    """Every op against the oracle on the inputs the GPU op consumed (element-wise, strict), then the whole chain
+    against the oracle's own chain (relative Frobenius error)."""
+    from helpers import assert_chain_close, f32_to_bf16_bits
+
+    T, d = X.shape
+    E, f = W1.shape[0], W1.shape[1]
     logits = layer.logits.cpu().numpy()
-    ref_logits = oracle.linear_fwd(X, Wr, out_dtype=np.float32)
-    assert_close(logits, ref_logits, rtol=1e-3, atol=1e-3, what="router logits")
+    assert_close(logits, oracle.linear_fwd(X, Wr, out_dtype=np.float32), rtol=1e-3, atol=1e-3, what="router logits")
     fwd = oracle.moe_forward(X, Wr, W1, W3, W2, k, logits=logits)
+    # ---- integers: bit-exact
     np.testing.assert_array_equal(host_u16(layer.chosen), fwd["chosen"])
     np.testing.assert_array_equal(layer.counts.cpu().numpy()[:E], fwd["counts"][:E])
     np.testing.assert_array_equal(layer.cumsum.cpu().numpy(), fwd["cumsum_incl"])
@@ -54,22 +60,71 @@ def compare_with_oracle(oracle, layer, out, dXn, G, X, Wr, W1, W3, W2, dOut, g0,
     np.testing.assert_array_equal(layer.expert_mapping.cpu().numpy(), fwd["expert_mapping"])
     np.testing.assert_allclose(layer.weights.cpu().numpy(), fwd["weights"], rtol=1e-5, atol=1e-7)
     np.testing.assert_array_equal(host_bits(layer.zone), fwd["zone"])
-    for name in ("x1", "x3"):
-        assert_close(f32(host_bits(getattr(layer, name))), f32(fwd[name]), what=name)
-    assert_close_chained(f32(host_bits(layer.Y)), f32(fwd["Y"]), what="Y")
-    assert_close_chained(f32(host_bits(out)), f32(fwd["out"]), what="out")
-    grads = {n: g0[n].copy() for n in g0}
-    bwd = oracle.moe_backward(X, Wr, W1, W3, W2, k, fwd, dOut, grads=grads)
-    assert_close_chained(f32(host_bits(layer.dx1)), f32(bwd["dx1"]), what="dx1")
-    assert_close_chained(f32(host_bits(layer.dx3)), f32(bwd["dx3"]), what="dx3")
-    assert_close_chained(f32(host_bits(layer.dZ)), f32(bwd["dZ"]), what="dZ")
-    ref_dl = f32(bwd["dlogits"])
-    # the gate Jacobian subtracts bf16-rounded dot products: allow a few bf16 ulps of their magnitude
-    assert_close(f32(host_bits(layer.dX_routed)), ref_dl, rtol=2e-2,
-                 atol=2e-3 + 4e-2 * float(np.sqrt((ref_dl[ref_dl != 0] ** 2).mean())), what="dlogits")
-    assert_close_chained(f32(host_bits(dXn)), f32(bwd["dXn"]), what="dXn")
+    # ---- forward ops
+    x1g, x3g, hg, Yg = (host_bits(getattr(layer, n)) for n in ("x1", "x3", "h", "Y"))
+    assert_close(f32(x1g), f32(fwd["x1"]), what="x1")
+    assert_close(f32(x3g), f32(fwd["x3"]), what="x3")
+    assert_close(f32(hg), f32(oracle.swiglu(x1g, x3g)), what="h")
+    cnt, base = fwd["host_counts"], fwd["cumsum_excl"]
+    tm, em, w, ch = fwd["token_mapping"], fwd["expert_mapping"], fwd["weights"], fwd["chosen"]
+
+    def per_expert(fn, rows_out, cols_out):
+        res = np.zeros((rows_out, cols_out), np.uint16)
+        for e in range(E):
+            n, b = int(cnt[e]), int(base[e])
+            if n:
+                res[b:b + n] = fn(e, slice(b, b + n))
+        return res
+
+    Yr = per_expert(lambda e, sl: oracle.linear_fwd(np.ascontiguousarray(hg[sl]), W2[e]), T * k, d)
+    assert_close(f32(Yg), f32(Yr), what="Y")
+    assert_close(f32(host_bits(out)), f32(oracle.merge_experts(Yg, tm, w, np.zeros((T, d), np.uint16))), what="out")
+    assert_chain_close(f32(host_bits(out)), f32(fwd["out"]), what="out (chain)")
+
+    # ---- backward ops
+    dx1g, dx3g, dZg = host_bits(layer.dx1), host_bits(layer.dx3), host_bits(layer.dZ)
+    dlg, dXng = host_bits(layer.dX_routed), host_bits(dXn)
+    pre = host_bits(layer.dX_routed_pre)
+    dYs = np.zeros((T * k, d), np.uint16)  # w * dOut rows in expert order
+    for j in range(k):
+        dYs[tm[:, j]] = f32_to_bf16_bits(f32(dOut) * w[:, j:j + 1])
+    if path == "fast":
+        np.testing.assert_array_equal(host_bits(layer.dYz), dYs)
+    # dP before the gate Jacobian: <Y, dOut> per routed (token, expert), stored bf16 like the reference
+    dots = (f32(Yg)[tm.reshape(-1)].reshape(T, k, d) * f32(dOut)[:, None, :]).sum(axis=2)
+    pre_ref = np.zeros((T, E), np.float32)
+    np.put_along_axis(pre_ref, ch.astype(np.int64), dots, axis=1)
+    assert_close(f32(pre), pre_ref, rtol=2e-2, atol=2e-2 * float(np.abs(dots).mean()), what="dX_routed before gate")
+    assert_close(f32(dlg), f32(oracle.router_gate_bwd_x(ch, w, pre.copy())), what="dlogits")
+    dh = per_expert(lambda e, sl: oracle.linear_dgrad(np.ascontiguousarray(dYs[sl]), W2[e]), T * k, f)
+    r1, r3 = oracle.swiglu_bwd_x(x1g, x3g, dh)
+    assert_close(f32(dx1g), f32(r1), what="dx1")
+    assert_close(f32(dx3g), f32(r3), what="dx3")
+    dZr = per_expert(lambda e, sl: oracle.linear_dgrad(np.ascontiguousarray(dx3g[sl]), W3[e],
+                                                       accumulate_into=oracle.linear_dgrad(np.ascontiguousarray(dx1g[sl]), W1[e])),
+                     T * k, d)
+    assert_close(f32(dZg), f32(dZr), what="dZ")
+    dXr = oracle.merge_experts(dZg, tm, None, np.zeros((T, d), np.uint16))
+    oracle.linear_dgrad(dlg, Wr, accumulate_into=dXr)
+    assert_close(f32(dXng), f32(dXr), what="dXn")
+    gr = {n: g0[n].copy() for n in g0}
+    for e in range(E):
+        n, b = int(cnt[e]), int(base[e])
+        if n:
+            sl = slice(b, b + n)
+            oracle.linear_wgrad(np.ascontiguousarray(hg[sl]), np.ascontiguousarray(dYs[sl]), gr["dW2"][e])
+            oracle.linear_wgrad(fwd["zone"][sl], np.ascontiguousarray(dx1g[sl]), gr["dW1"][e])
+            oracle.linear_wgrad(fwd["zone"][sl], np.ascontiguousarray(dx3g[sl]), gr["dW3"][e])
+    oracle.linear_wgrad(X, dlg, gr["dWr"])
     for n in ("dW1", "dW3", "dW2", "dWr"):
-        assert_close_chained(f32(host_bits(G[n])), f32(bwd[n]), what=n)
+        assert_close(f32(host_bits(G[n])), f32(gr[n]), what=n)
+
+    # ---- the whole chain against the oracle's own chain
+    bwd = oracle.moe_backward(X, Wr, W1, W3, W2, k, fwd, dOut, grads={n: g0[n].copy() for n in g0})
+    for got, ref, what, lim in [(dXng, bwd["dXn"], "dXn", 1e-2), (host_bits(G["dW1"]), bwd["dW1"], "dW1", 1e-2),
+                                (host_bits(G["dW3"]), bwd["dW3"], "dW3", 1e-2), (host_bits(G["dW2"]), bwd["dW2"], "dW2", 1e-2),
+                                (dlg, bwd["dlogits"], "dlogits", 5e-2), (host_bits(G["dWr"]), bwd["dWr"], "dWr", 5e-2)]:
+        assert_chain_close(f32(got), f32(ref), limit=lim, what=what + " (chain)")
 
 
 def make_case(seed, T, d, E, k, f, wstd=0.02, grad_init=0.0):
@@ -88,7 +143,7 @@ def test_layer_small(oracle, path, T, d, E, k, f):
     require_b200()
     X, Wr, W1, W3, W2, dOut, g0 = make_case(T + d, T, d, E, k, f, wstd=0.06, grad_init=0.05)
     layer, out, dXn, G = run_layer(path, T, d, E, k, f, X, Wr, W1, W3, W2, dOut, g0)
-    compare_with_oracle(oracle, layer, out, dXn, G, X, Wr, W1, W3, W2, dOut, g0, k)
+    compare_with_oracle(oracle, layer, out, dXn, G, X, Wr, W1, W3, W2, dOut, g0, k, path)
 
 
 def test_layer_config1_fast_path(oracle):
@@ -97,7 +152,7 @@ def test_layer_config1_fast_path(oracle):
     T, d, E, k, f = 2048, 1024, 16, 2, 1024
     X, Wr, W1, W3, W2, dOut, g0 = make_case(1, T, d, E, k, f)
     layer, out, dXn, G = run_layer("fast", T, d, E, k, f, X, Wr, W1, W3, W2, dOut, g0)
-    compare_with_oracle(oracle, layer, out, dXn, G, X, Wr, W1, W3, W2, dOut, g0, k)
+    compare_with_oracle(oracle, layer, out, dXn, G, X, Wr, W1, W3, W2, dOut, g0, k, "fast")
 
 
 @pytest.mark.parametrize("name", ["moe_mlp_small", "moe_mlp_k4"])

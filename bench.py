@@ -1,0 +1,379 @@
+"""MoE layer forward+backward benchmark (tokens/s) on B200, with roofline and CPU baseline.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+N = 1: one MoE layer fwd+bwd at T=8192, d=4096, 64 experts, top-8, ffn 1408 (bf16 weights N(0,0.02),
+activations / upstream gradient N(0,1), fp32 router logits from a bf16 router weight); synthetic seeded data.
+N > 1 (launched with torch.distributed.run, one rank per GPU): the expert-parallel layer, 64 experts sharded
+over the ranks, T=32768 tokens per GPU, NCCL all-to-all for dispatch and return (weak scaling).
+
+Prints ONE JSON line on rank 0. `value` is device-timed with inputs resident in HBM; `e2e` is the same step
+driven from pinned host buffers with the host<->device copies inside the timed region; `roofline` covers the
+grouped tcgen05 GEMM launches (the dominant kernel) and `kernels` lists every op group with its own bound;
+`cpu_baseline` is the CPU oracle timed on a bounded token sample of the same shape on this box's host cores.
+`--impl reference` times that CPU restatement of the reference's algorithm only (the reference has no CPU
+implementation of this path of its own, and its CUDA kernels are what this repository replaces).
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "moe_layer_fwd_bwd_tokens_per_s"
+UNIT = "tokens/s"
+CFG_1GPU = dict(T=8192, d=4096, E=64, k=8, f=1408)       # BASELINE configs[1]
+CFG_EP = dict(T=32768, d=4096, E=64, k=8, f=1408)        # BASELINE configs[4], T per GPU
+CPU_SAMPLE_TOKENS = 512
+
+
+def read_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as fh:
+            p = json.load(fh)
+        return dict(hbm_gbs=p["hbm_gbs"], bf16_tflops=p["bf16_tflops"],
+                    bf16_tflops_sustained=p.get("bf16_tflops_sustained", p["bf16_tflops"]), source="measured")
+    return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        fd, self.path = tempfile.mkstemp(prefix="clocks_", suffix=".csv")
+        os.close(fd)
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.gpu_index), "--query-gpu=" + self.FIELDS, "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        out = dict(sm_mhz=None, sm_max_mhz=None, reasons=[], samples=0)
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        clocks, reasons, power = [], set(), []
+        smax = None
+        try:
+            with open(self.path) as fh:
+                for line in fh:
+                    parts = [x.strip() for x in line.split(",")]
+                    if len(parts) < 8:
+                        continue
+                    try:
+                        clocks.append(float(parts[0]))
+                        smax = float(parts[1])
+                        power.append(float(parts[2]))
+                    except ValueError:
+                        continue
+                    for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"),
+                                         parts[4:8]):
+                        if val.lower().startswith("active"):
+                            reasons.add(name)
+        finally:
+            os.unlink(self.path)
+        if clocks:
+            # samples taken while the GPU was busy: the upper half of the power readings
+            busy = sorted(c for c, p in zip(clocks, power) if p >= 0.5 * max(power)) or sorted(clocks)
+            out.update(sm_mhz=busy[len(busy) // 2], sm_max_mhz=smax, reasons=sorted(reasons), samples=len(clocks),
+                       power_w_max=max(power))
+        return out
+
+
+# ------------------------------------------------------------------------------------------ CPU arm
+def cpu_reference_run(cfg, steps, warmup):
+    """Times the CPU oracle (fwd+bwd) on CPU_SAMPLE_TOKENS tokens of the workload's shape. Returns tokens/s."""
+    import numpy as np
+    from oracle import oracle as orc
+
+    orc.build()
+    Ts, d, E, k, f = CPU_SAMPLE_TOKENS, cfg["d"], cfg["E"], cfg["k"], cfg["f"]
+    X, dOut = orc.normal_bf16((Ts, d), 0xB2000001), orc.normal_bf16((Ts, d), 0xB2000002)
+    Wr = orc.normal_bf16((E, d), 0xB2000003, std=0.02)
+    W1 = orc.normal_bf16((E, f, d), 0xB2000004, std=0.02)
+    W3 = orc.normal_bf16((E, f, d), 0xB2000005, std=0.02)
+    W2 = orc.normal_bf16((E, d, f), 0xB2000006, std=0.02)
+    grads = dict(dW1=np.zeros_like(W1), dW3=np.zeros_like(W3), dW2=np.zeros_like(W2), dWr=np.zeros_like(Wr))
+    times = []
+    for i in range(warmup + steps):
+        t0 = time.perf_counter()
+        fwd = orc.moe_forward(X, Wr, W1, W3, W2, k)
+        orc.moe_backward(X, Wr, W1, W3, W2, k, fwd, dOut, grads=grads)
+        if i >= warmup:
+            times.append(time.perf_counter() - t0)
+    sec = sum(times) / len(times)
+    return Ts / sec, sec, orc.num_threads()
+
+
+def run_reference_arm(args, cfg, world):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    steps, warmup = max(1, args.steps), max(0, args.warmup)
+    # keep the whole run within a few minutes: one sample step costs a few seconds of CPU
+    steps, warmup = min(steps, 5), min(warmup, 1)
+    tps, sec, threads = cpu_reference_run(cfg, steps, warmup)
+    sample = (f"{CPU_SAMPLE_TOKENS} tokens of the workload shape (d={cfg['d']}, E={cfg['E']}, top-{cfg['k']}, "
+              f"ffn {cfg['f']}); fwd+bwd through the CPU restatement of the reference kernels, OpenMP")
+    line = dict(metric=METRIC, value=tps, unit=UNIT, n_gpus=world, steps=steps, warmup=warmup, ms_per_step=sec * 1e3,
+                higher_is_better=True, scaling="weak", vs_baseline=None, dtype="bf16", data="synthetic", impl="reference",
+                config=dict(workload=workload_name(cfg, world), T_sample=CPU_SAMPLE_TOKENS),
+                cpu_baseline=dict(value=tps, unit=UNIT, cores=threads, kind="port", sample=sample),
+                e2e=dict(value=tps, unit=UNIT, h2d_bytes_per_step=0, d2h_bytes_per_step=0), gpu_launches=0)
+    print(json.dumps(line), flush=True)
+
+
+def workload_name(cfg, world):
+    base = f"moe_layer_fwd_bwd T={cfg['T']} d={cfg['d']} E={cfg['E']} top{cfg['k']} ffn={cfg['f']}"
+    return base + (f" expert-parallel x{world} (T per GPU)" if world > 1 else "")
+
+
+# ------------------------------------------------------------------------------------------ GPU arm
+def algorithmic_work(cfg):
+    """Algorithmic bytes / flops of each op group for one step (R = T*k routed rows, bf16 = 2 B)."""
+    T, d, E, k, f = cfg["T"], cfg["d"], cfg["E"], cfg["k"], cfg["f"]
+    R = T * k
+    gather = 2 * T * d + 2 * R * d + 4 * R
+    combine = 2 * R * d + 4 * T * d + 8 * R
+    return {
+        "router_gemm": ("hbm", 2 * T * d + 2 * E * d + 4 * T * E),
+        "select_experts": ("hbm", 4 * T * E + 6 * T * k),
+        "build_expert_mapping": ("hbm", 2 * T * k + 8 * T * k),
+        "prepare_experts": ("hbm", gather),
+        "experts_fwd_gemm": ("tensor", 6 * R * d * f),
+        "merge_experts": ("hbm", combine),
+        "prepare_experts_weighted": ("hbm", gather + 4 * R),
+        "experts_bwd_x_gemm": ("tensor", 6 * R * d * f),
+        "experts_bwd_w_gemm": ("tensor", 6 * R * d * f),
+        "unpermute": ("hbm", combine - 4 * R),
+        "router_grad": ("hbm", 4 * R + 2 * T * E * 3 + 4 * T * d + 2 * T * d + 4 * E * d),
+    }
+
+
+def run_gpu_arm(args, world):
+    import torch
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+
+        dist = dist_mod
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    from ml_dataflow_b200 import ops
+    from ml_dataflow_b200.moe_layer import MoELayer
+
+    cfg = CFG_1GPU if world == 1 else CFG_EP
+    T, d, E, k, f = cfg["T"], cfg["d"], cfg["E"], cfg["k"], cfg["f"]
+    steps, warmup = max(1, args.steps), max(3, args.warmup)
+    peaks = read_peaks()
+    dev = torch.device("cuda", local_rank)
+    gen = torch.Generator(device=dev).manual_seed(0xB200 + rank)
+
+    def normal(shape, std):
+        return (torch.randn(shape, generator=gen, device=dev) * std).to(torch.bfloat16)
+
+    X, dOut = normal((T, d), 1.0), normal((T, d), 1.0)
+    wgen = torch.Generator(device=dev).manual_seed(0xB2000003)  # router weight identical on every rank
+    Wr = (torch.randn((E, d), generator=wgen, device=dev) * 0.02).to(torch.bfloat16)
+
+    if world == 1:
+        layer = MoELayer(T, d, E, k, f, device=dev)
+        E_loc = E
+    else:
+        from ml_dataflow_b200.ep import ExpertParallelMoELayer
+
+        layer = ExpertParallelMoELayer(T, d, E, k, f, dist, device=dev)
+        E_loc = E // world
+    W1, W3, W2 = normal((E_loc, f, d), 0.02), normal((E_loc, f, d), 0.02), normal((E_loc, d, f), 0.02)
+    out = torch.zeros((T, d), dtype=torch.bfloat16, device=dev)
+    dXn = torch.empty_like(out)
+    dWr = torch.zeros_like(Wr)
+    dW1, dW3, dW2 = torch.zeros_like(W1), torch.zeros_like(W3), torch.zeros_like(W2)
+
+    def step(Xs, dOs, outs, dXs):
+        outs.zero_()
+        layer.forward(Xs, Wr, W1, W3, W2, outs)
+        layer.backward(Xs, Wr, W1, W3, W2, dOs, dXs, dWr, dW1, dW3, dW2)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(ms):
+        if dist is None:
+            return ms
+        t = torch.tensor([ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---------------- device-resident timing
+    for _ in range(warmup):
+        step(X, dOut, out, dXn)
+    barrier()
+    sampler = ClockSampler(torch.cuda.current_device() if "CUDA_VISIBLE_DEVICES" not in os.environ else local_rank)
+    if rank == 0:
+        sampler.start()
+    ops.LAUNCHES = 0
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(steps):
+        step(X, dOut, out, dXn)
+    e1.record()
+    barrier()
+    launches = ops.LAUNCHES
+    ms_step = max_over_ranks(e0.elapsed_time(e1) / steps)
+    clocks = sampler.stop() if rank == 0 else None
+    status = ops.gemm_status()
+    if status != 0:
+        raise RuntimeError(f"a GEMM kernel gave up waiting (status {status}); the timing is void")
+    value = world * T / (ms_step * 1e-3)
+
+    # ---------------- end to end: pinned host buffers, copies inside the timed region, double buffered
+    Xh, dOh = X.cpu().pin_memory(), dOut.cpu().pin_memory()
+    outh = [torch.empty((T, d), dtype=torch.bfloat16).pin_memory() for _ in range(2)]
+    dXh = [torch.empty((T, d), dtype=torch.bfloat16).pin_memory() for _ in range(2)]
+    Xd, dOd = [torch.empty_like(X) for _ in range(2)], [torch.empty_like(X) for _ in range(2)]
+    outd, dXd = [torch.empty_like(X) for _ in range(2)], [torch.empty_like(X) for _ in range(2)]
+    main = torch.cuda.current_stream()
+    s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
+    ev_in = [torch.cuda.Event() for _ in range(2)]
+    ev_comp = [torch.cuda.Event() for _ in range(2)]
+    ev_out = [torch.cuda.Event() for _ in range(2)]
+
+    def e2e_loop(n):
+        with torch.cuda.stream(s_in):
+            Xd[0].copy_(Xh, non_blocking=True)
+            dOd[0].copy_(dOh, non_blocking=True)
+            ev_in[0].record(s_in)
+        for i in range(n):
+            c, nx = i % 2, (i + 1) % 2
+            if i + 1 < n:
+                with torch.cuda.stream(s_in):
+                    if i >= 1:
+                        s_in.wait_event(ev_comp[nx])  # step i-1 has finished reading buffer nx
+                    Xd[nx].copy_(Xh, non_blocking=True)
+                    dOd[nx].copy_(dOh, non_blocking=True)
+                    ev_in[nx].record(s_in)
+            main.wait_event(ev_in[c])
+            if i >= 2:
+                main.wait_event(ev_out[c])  # results of step i-2 have left buffer c
+            step(Xd[c], dOd[c], outd[c], dXd[c])
+            ev_comp[c].record(main)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(ev_comp[c])
+                outh[c].copy_(outd[c], non_blocking=True)
+                dXh[c].copy_(dXd[c], non_blocking=True)
+                ev_out[c].record(s_out)
+        main.wait_event(ev_out[0])
+        main.wait_event(ev_out[1])
+
+    e2e_loop(2)
+    barrier()
+    e0.record()
+    e2e_loop(steps)
+    e1.record()
+    barrier()
+    ms_e2e = max_over_ranks(e0.elapsed_time(e1) / steps)
+    e2e_value = world * T / (ms_e2e * 1e-3)
+    io_bytes = 2 * T * d * 2
+
+    # ---------------- per-op timing for the roofline (separate pass, events between ops)
+    work = algorithmic_work(cfg)
+    acc = {}
+    for _ in range(max(3, min(steps, 10))):
+        layer.profile = []
+        step(X, dOut, out, dXn)
+        layer.mark("end")
+        torch.cuda.synchronize()
+        marks = layer.profile
+        layer.profile = None
+        for (name, ev), (_, nxt) in zip(marks[:-1], marks[1:]):
+            acc.setdefault(name, []).append(ev.elapsed_time(nxt))
+    kernels = {}
+    gemm_ms, gemm_flops = 0.0, 0
+    for name, (bound, amount) in work.items():
+        if name not in acc:
+            continue
+        ms = sum(acc[name]) / len(acc[name])
+        if bound == "tensor":
+            ach = amount / (ms * 1e-3) / 1e12
+            kernels[name] = dict(ms=round(ms, 4), bound="tensor", achieved=round(ach, 1), unit="TFLOP/s",
+                                 frac=round(ach / peaks["bf16_tflops_sustained"], 4))
+            gemm_ms += ms
+            gemm_flops += amount
+        else:
+            ach = amount / (ms * 1e-3) / 1e9
+            kernels[name] = dict(ms=round(ms, 4), bound="hbm", achieved=round(ach, 1), unit="GB/s",
+                                 frac=round(ach / peaks["hbm_gbs"], 4))
+    ach = gemm_flops / (gemm_ms * 1e-3) / 1e12 if gemm_ms else 0.0
+    roofline = dict(kernel="gemm_sm100_kernel (grouped expert GEMMs: 7 launches per step, 18*R*d*f flop)",
+                    bound="tensor", achieved=round(ach, 1), peak=peaks["bf16_tflops_sustained"], unit="TFLOP/s",
+                    frac=round(ach / peaks["bf16_tflops_sustained"], 4),
+                    frac_of_burst_peak=round(ach / peaks["bf16_tflops"], 4), peak_source=peaks["source"] +
+                    " (sustained cuBLAS bf16, the kernel is timed inside a long step)", traffic=None,
+                    ms_per_step_in_kernel=round(gemm_ms, 4))
+
+    if rank != 0:
+        return
+    cpu_tps, cpu_sec, threads = cpu_reference_run(cfg, 2, 1) if world == 1 else (None, None, None)
+    line = dict(metric=METRIC, value=value, unit=UNIT, n_gpus=world, steps=steps, warmup=warmup, ms_per_step=ms_step,
+                higher_is_better=True, scaling="weak", vs_baseline=None, dtype="bf16", data="synthetic", impl="ours",
+                config=dict(workload=workload_name(cfg, world), T=T, d_model=d, experts=E, top_k=k, ffn=f,
+                            l2="inputs exceed L2 (zone 2*T*k*d bytes per pass)"),
+                e2e=dict(value=e2e_value, unit=UNIT, h2d_bytes_per_step=io_bytes, d2h_bytes_per_step=io_bytes,
+                         ms_per_step=ms_e2e),
+                gpu_launches=launches, clocks=clocks, roofline=roofline, kernels=kernels)
+    if cpu_tps is not None:
+        line["cpu_baseline"] = dict(
+            value=cpu_tps, unit=UNIT, cores=threads, kind="port",
+            sample=f"{CPU_SAMPLE_TOKENS} tokens of the same shape, fwd+bwd, {cpu_sec:.1f} s per pass")
+    print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    world = int(os.environ.get("WORLD_SIZE", str(args.gpus)))
+    if args.impl == "reference":
+        run_reference_arm(args, CFG_1GPU if world == 1 else CFG_EP, world)
+        return
+    if world > 1 and "RANK" not in os.environ:
+        sys.exit("for --gpus > 1 launch with: python -m torch.distributed.run --nproc-per-node N bench.py --gpus N")
+    run_gpu_arm(args, world)
+
+
+if __name__ == "__main__":
+    main()

@@ -56,21 +56,32 @@ class MoELayer:
         self.dh = None  # [R, f], allocated on first use by the reference-order backward only
         self.dZ = buf((R, d), bf)
         self.dX_routed = buf((T, E), bf)
+        self.profile = None  # list of (name, event) when a caller wants per-op timing (see mark())
         self.keep_pre_gate = False  # tests set this to look at dX_routed before the gate Jacobian is applied
         self.dX_routed_pre = None
+
+    def mark(self, name):
+        """Records a CUDA event labelled `name` on the current stream when profiling is switched on."""
+        if self.profile is not None:
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record()
+            self.profile.append((name, ev))
 
     # ------------------------------------------------------------------ routing (shared)
     def route(self, Xn, Wr, logits=None):
         T, d, E, k = self.T, self.d, self.E, self.k
+        self.mark("router_gemm")
         if logits is None:
             # logits[T,E] = Xn . Wr^T, fp32 out (reference call: transa=1, M=E, K=d, N=T)
             ops.matmul(1, 0, E, d, T, 1.0, 0.0, Wr, Xn, None, self.logits)
         else:
             self.logits.copy_(logits)
+        self.mark("select_experts")
         self.counts.zero_()
         self.cumsum.zero_()
         ops.select_experts(T, E, k, self.logits, self.weights, self.chosen, self.counts, self.cumsum,
                            self.dev_counts_copy)
+        self.mark("build_expert_mapping")
         ops.build_expert_mapping(T, E, k, self.chosen, self.cumsum, self.expert_mapping, self.token_mapping,
                                  self.map_ws)
 
@@ -79,26 +90,35 @@ class MoELayer:
         """out[T,d] (bf16, pre-loaded with the residual or zeros) += combined expert outputs."""
         T, d, E, k, f, R = self.T, self.d, self.E, self.k, self.f, self.R
         self.route(Xn, Wr, logits)
+        self.mark("prepare_experts")
         ops.prepare_experts(T, d, k, Xn, self.token_mapping, self.zone)
+        self.mark("experts_fwd_gemm")
         ops.moe_experts_fwd(R, d, f, E, self.zone, W1, W3, W2, f * d, f * d, d * f, self.counts, self.cumsum,
                             self.x1, self.x3, self.h, self.Y)
+        self.mark("merge_experts")
         ops.merge_experts(T, d, k, self.Y, self.token_mapping, self.weights, out)
+        self.mark("fwd_end")
         return out
 
     def backward(self, Xn, Wr, W1, W3, W2, dOut, dXn, dWr, dW1, dW3, dW2):
         """dXn is overwritten; dWr, dW1, dW3, dW2 (bf16) are accumulated into, like the reference's beta=1 GEMMs."""
         T, d, E, k, f, R = self.T, self.d, self.E, self.k, self.f, self.R
         # dY rows = w * dOut in expert order (what the reference's router_bwd_x leaves in the zone)
+        self.mark("prepare_experts_weighted")
         ops.prepare_experts_weighted(T, d, k, dOut, self.token_mapping, self.weights, self.dYz)
         ops.scatter_row_weights(T, k, self.token_mapping, self.weights, self.row_w)
         self.dP.zero_()
+        self.mark("experts_bwd_x_gemm")
         ops.moe_experts_bwd_x(R, d, f, E, self.dYz, self.row_w, self.x1, self.x3, W1, W3, W2, f * d, f * d, d * f,
                               self.counts, self.cumsum, self.dx1, self.dx3, None, self.dP, self.dZ)
         # h is still resident from the forward (the reference recomputes it instead)
+        self.mark("experts_bwd_w_gemm")
         ops.moe_experts_bwd_w(R, d, f, E, self.dYz, self.h, self.zone, self.dx1, self.dx3, dW1, dW3, dW2,
                               f * d, f * d, d * f, self.counts, self.cumsum)
+        self.mark("unpermute")
         dXn.zero_()
         ops.merge_experts(T, d, k, self.dZ, self.token_mapping, None, dXn)
+        self.mark("router_grad")
         self.dX_routed.zero_()
         ops.gather_router_grad(T, E, k, self.token_mapping, self.chosen, self.dP, self.dX_routed)
         if self.keep_pre_gate:
@@ -108,6 +128,7 @@ class MoELayer:
         ops.matmul(0, 0, d, E, T, 1.0, 1.0, Wr, self.dX_routed, dXn, dXn)
         # dWr += dL^T . Xn (reference: transa=0, transb=1, M=d, K=T, N=E, beta=1, C=D)
         ops.matmul(0, 1, d, T, E, 1.0, 1.0, Xn, self.dX_routed, dWr, dWr)
+        self.mark("bwd_end")
         return dXn
 
     # ------------------------------------------------------------------ the reference's own op order

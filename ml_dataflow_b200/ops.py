@@ -33,21 +33,27 @@ def _dt(t):
     raise TypeError(f"unsupported dtype {t.dtype}")
 
 
-def _check(rc, name):
+LAUNCHES = 0  # kernels of this library launched so far (reset it to count a region)
+_KERNELS_PER_CALL = {"build_expert_mapping": 2, "moe_experts_fwd": 2, "moe_experts_bwd_x": 2}
+
+
+def _check(rc, name, launches=None):
+    global LAUNCHES
     if rc != 0:
         raise RuntimeError(f"{name} failed (see stderr)")
+    LAUNCHES += _KERNELS_PER_CALL.get(name, 1) if launches is None else launches
 
 
 def device_info():
     sm, major, minor = C.c_int(), C.c_int(), C.c_int()
-    _check(_lib.load().b200_device_info(C.byref(sm), C.byref(major), C.byref(minor)), "b200_device_info")
+    _check(_lib.load().b200_device_info(C.byref(sm), C.byref(major), C.byref(minor)), "b200_device_info", 0)
     return sm.value, major.value, minor.value
 
 
 def gemm_status():
     """Synchronises and returns the status word of the GEMM kernels (0 = every wait completed)."""
     st = C.c_int()
-    _check(_lib.load().b200_gemm_status(C.byref(st)), "b200_gemm_status")
+    _check(_lib.load().b200_gemm_status(C.byref(st)), "b200_gemm_status", 0)
     return st.value
 
 
@@ -157,7 +163,8 @@ def moe_experts_bwd_w(total_rows, model_dim, ffn_dim, num_experts, dY_zone, hs, 
     _check(_lib.load().b200_moe_experts_bwd_w(total_rows, model_dim, ffn_dim, num_experts, _p(dY_zone), _p(hs),
                                               _p(zone_x), _p(dx1), _p(dx3), _p(dW1), _p(dW3), _p(dW2), dw1_stride,
                                               dw3_stride, dw2_stride, _p(expert_counts), _p(expert_counts_cumsum),
-                                              _stream()), "moe_experts_bwd_w")
+                                              _stream()), "moe_experts_bwd_w",
+           sum(g is not None for g in (dW1, dW3, dW2)))
 
 
 def scatter_row_weights(num_tokens, top_k, token_mapping, token_expert_weights, row_weights):

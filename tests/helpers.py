@@ -47,3 +47,12 @@ def rel_fro(a, b):
 def assert_chain_close(a, b, limit=1e-2, what=""):
     r = rel_fro(a, b)
     assert r < limit, f"{what}: relative Frobenius error {r:.2e} >= {limit:.0e}"
+
+
+def assert_close_with_slack(a, b, slack, rtol=RTOL, atol=ATOL, what=""):
+    """|a-b| <= atol + rtol*|b| + slack, `slack` an element-wise array (e.g. one bf16 ulp of an intermediate)."""
+    a, b, slack = (np.asarray(x, np.float64) for x in (a, b, slack))
+    err = np.abs(a - b)
+    lim = atol + rtol * np.abs(b) + slack
+    bad = err > lim
+    assert not bad.any(), f"{what}: {bad.mean():.3e} of elements outside tol (worst {(err / lim).max():.2f}x)"

@@ -8,7 +8,7 @@ import pytest
 import torch
 
 from gpu_util import dev, dev_bf16, host_bits, rand_bf16, require_b200
-from helpers import assert_close, bf16_bits_to_f32
+from helpers import assert_close, assert_close_with_slack, bf16_bits_to_f32
 
 pytestmark = pytest.mark.gpu
 
@@ -149,7 +149,7 @@ def test_grouped_backward(oracle, R, d, f, E, empty):
 
     # oracle, op by op, every op on the inputs the GPU op consumed
     dx1r, dx3r = np.zeros((R, f), np.uint16), np.zeros((R, f), np.uint16)
-    dZr = np.zeros((R, d), np.uint16)
+    dZr, dz1 = np.zeros((R, d), np.uint16), np.zeros((R, d), np.uint16)
     dPr = np.zeros(R, np.float32)
     g1r, g3r, g2r = g1.copy(), g3.copy(), g2.copy()
     b = 0
@@ -163,6 +163,7 @@ def test_grouped_backward(oracle, R, d, f, E, empty):
             dh = oracle.linear_dgrad(dYs[sl], W2[e])
             dx1r[sl], dx3r[sl] = oracle.swiglu_bwd_x(x1[sl], x3[sl], dh)
             dz = oracle.linear_dgrad(np.ascontiguousarray(dx1g[sl]), W1[e])
+            dz1[sl] = dz
             dZr[sl] = oracle.linear_dgrad(np.ascontiguousarray(dx3g[sl]), W3[e], accumulate_into=dz)
             oracle.linear_wgrad(Zx[sl], np.ascontiguousarray(dx1g[sl]), g1r[e])
             oracle.linear_wgrad(Zx[sl], np.ascontiguousarray(dx3g[sl]), g3r[e])
@@ -172,7 +173,9 @@ def test_grouped_backward(oracle, R, d, f, E, empty):
     assert_close(f32(host_bits(hs)), f32(hr), what="hs")
     assert_close(f32(dx1g), f32(dx1r), what="dx1")  # differs from the oracle only through one rounding of dh
     assert_close(f32(dx3g), f32(dx3r), what="dx3")
-    assert_close(f32(host_bits(dZ)), f32(dZr), what="dZ")
+    # the kernel adds dx1 W1 and dx3 W3 in one fp32 accumulator; the reference rounds the first product to bf16
+    # before adding the second (two GEMM calls, beta = 1): allow one bf16 ulp of that intermediate
+    assert_close_with_slack(f32(host_bits(dZ)), f32(dZr), np.abs(f32(dz1)) * 2.0 ** -8, what="dZ")
     assert_close(f32(host_bits(G2)), f32(g2r), what="dW2")
     assert_close(f32(host_bits(G1)), f32(g1r), what="dW1")
     assert_close(f32(host_bits(G3)), f32(g3r), what="dW3")

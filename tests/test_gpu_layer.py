@@ -13,7 +13,7 @@ import pytest
 import torch
 
 from gpu_util import dev_bf16, host_bits, host_u16, rand_bf16, require_b200
-from helpers import assert_close, bf16_bits_to_f32
+from helpers import assert_close, assert_close_with_slack, bf16_bits_to_f32
 
 pytestmark = pytest.mark.gpu
 GOLD = os.path.join(os.path.dirname(__file__), "golden")
@@ -66,7 +66,8 @@ def compare_with_oracle(oracle, layer, out, dXn, G, X, Wr, W1, W3, W2, dOut, g0,
     assert_close(f32(x3g), f32(fwd["x3"]), what="x3")
     assert_close(f32(hg), f32(oracle.swiglu(x1g, x3g)), what="h")
     cnt, base = fwd["host_counts"], fwd["cumsum_excl"]
-    tm, em, w, ch = fwd["token_mapping"], fwd["expert_mapping"], fwd["weights"], fwd["chosen"]
+    tm, em, ch = fwd["token_mapping"], fwd["expert_mapping"], fwd["chosen"]
+    w = layer.weights.cpu().numpy()  # the gate weights the GPU ops consumed (oracle's agree to 1e-5)
 
     def per_expert(fn, rows_out, cols_out):
         res = np.zeros((rows_out, cols_out), np.uint16)
@@ -100,10 +101,14 @@ def compare_with_oracle(oracle, layer, out, dXn, G, X, Wr, W1, W3, W2, dOut, g0,
     r1, r3 = oracle.swiglu_bwd_x(x1g, x3g, dh)
     assert_close(f32(dx1g), f32(r1), what="dx1")
     assert_close(f32(dx3g), f32(r3), what="dx3")
+    dz1 = per_expert(lambda e, sl: oracle.linear_dgrad(np.ascontiguousarray(dx1g[sl]), W1[e]), T * k, d)
     dZr = per_expert(lambda e, sl: oracle.linear_dgrad(np.ascontiguousarray(dx3g[sl]), W3[e],
-                                                       accumulate_into=oracle.linear_dgrad(np.ascontiguousarray(dx1g[sl]), W1[e])),
-                     T * k, d)
-    assert_close(f32(dZg), f32(dZr), what="dZ")
+                                                       accumulate_into=np.ascontiguousarray(dz1[sl]).copy()), T * k, d)
+    if path == "fast":
+        # one fp32 accumulator for dx1 W1 + dx3 W3; the reference rounds the first product to bf16 in between
+        assert_close_with_slack(f32(dZg), f32(dZr), np.abs(f32(dz1)) * 2.0 ** -8, what="dZ")
+    else:
+        assert_close(f32(dZg), f32(dZr), what="dZ")
     dXr = oracle.merge_experts(dZg, tm, None, np.zeros((T, d), np.uint16))
     oracle.linear_dgrad(dlg, Wr, accumulate_into=dXr)
     assert_close(f32(dXng), f32(dXr), what="dXn")

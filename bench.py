@@ -233,12 +233,17 @@ def run_gpu_arm(args, world):
         return float(t.item())
 
     # ---------------- device-resident timing
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
     for _ in range(warmup):
         step(X, dOut, out, dXn)
     barrier()
-    sampler = ClockSampler(torch.cuda.current_device() if "CUDA_VISIBLE_DEVICES" not in os.environ else local_rank)
-    if rank == 0:
-        sampler.start()
+    # keep the GPU busy until nvidia-smi has started sampling, so the clock record covers the timed region
+    t_spin = time.perf_counter()
+    while rank == 0 and time.perf_counter() - t_spin < 1.0:
+        step(X, dOut, out, dXn)
+        torch.cuda.synchronize()
     ops.LAUNCHES = 0
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
@@ -362,7 +367,7 @@ def run_gpu_arm(args, world):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=30)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     args = ap.parse_args()

@@ -145,7 +145,7 @@ def test_grouped_backward(oracle, R, d, f, E, empty):
     G1, G3, G2 = dev_bf16(g1), dev_bf16(g3), dev_bf16(g2)
     ops.moe_experts_bwd_w(R, d, f, E, dYd, hs, Zxd, dx1, dx3, G1, G3, G2, f * d, f * d, d * f, cd, cid)
     gemm_ok(ops)
-    dx1g, dx3g = host_bits(dx1), host_bits(dx3)
+    dx1g, dx3g, hsg = host_bits(dx1), host_bits(dx3), host_bits(hs)
 
     # oracle, op by op, every op on the inputs the GPU op consumed
     dx1r, dx3r = np.zeros((R, f), np.uint16), np.zeros((R, f), np.uint16)
@@ -159,7 +159,7 @@ def test_grouped_backward(oracle, R, d, f, E, empty):
             sl = slice(b, b + n)
             y = oracle.linear_fwd(hr[sl], W2[e])
             dPr[sl] = (bf16_bits_to_f32(y) * bf16_bits_to_f32(dOutRows[sl])).sum(axis=1)
-            oracle.linear_wgrad(hr[sl], dYs[sl], g2r[e])
+            oracle.linear_wgrad(np.ascontiguousarray(hsg[sl]), dYs[sl], g2r[e])
             dh = oracle.linear_dgrad(dYs[sl], W2[e])
             dx1r[sl], dx3r[sl] = oracle.swiglu_bwd_x(x1[sl], x3[sl], dh)
             dz = oracle.linear_dgrad(np.ascontiguousarray(dx1g[sl]), W1[e])

@@ -69,6 +69,35 @@ int b200_build_expert_mapping(int total_tokens, int num_routed_experts, int num_
                               const uint16_t *chosen_experts, int *expert_counts_cumsum, int *expert_mapping,
                               int *token_mapping, void *workspace, size_t workspace_bytes, void *stream);
 
+/*
+ * build_expert_mapping for callers that cannot supply device scratch. (No counterpart in the
+ * reference: its kernel keeps its tables in shared memory and atomics.)
+ *
+ * Who needs it: code that reaches this library through a fixed op signature - the reference's
+ * backend calls an op with exactly the arguments of its skeleton, seven for this op, so there
+ * is no slot for a workspace pointer - and that runs where allocating is off limits: the
+ * framework carves all device memory into its own slabs at start-up and ops must not call
+ * cudaMalloc while work is being submitted. Same inputs, outputs and result as
+ * b200_build_expert_mapping; the histogram tables sit in a 4 MiB array that is part of the
+ * library image on every GPU that loads it, for the life of the process.
+ *
+ * Limits and rules:
+ *  - b200_build_expert_mapping_workspace_bytes(...) must not exceed
+ *    b200_build_expert_mapping_static_capacity_bytes() (4 MiB: e.g. 64 experts at any token
+ *    count, up to 393 experts at large token counts); larger problems are refused with -1 and a
+ *    message, nothing is launched.
+ *  - The first call on each device looks up the array's device address (the device must be
+ *    current). Make that first call before starting any stream capture.
+ *  - All calls on a device share the one array. It keeps whatever the previous call left; that
+ *    is harmless because every entry is rewritten before it is read. Two calls that can overlap
+ *    on the GPU (different streams, no dependency) race on it - serialise them.
+ *  - Nothing is allocated or freed, on the device or through any library, in any call.
+ */
+size_t b200_build_expert_mapping_static_capacity_bytes(void);
+int b200_build_expert_mapping_static(int total_tokens, int num_routed_experts, int num_selected_experts,
+                                     const uint16_t *chosen_experts, int *expert_counts_cumsum, int *expert_mapping,
+                                     int *token_mapping, void *stream);
+
 /* ---- permute / combine ---------------------------------------------------------- */
 
 /*

@@ -16,6 +16,8 @@ SIGNATURES = {
     "b200_select_experts": (_i, [_i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "b200_build_expert_mapping_workspace_bytes": (_sz, [_i, _i, _i]),
     "b200_build_expert_mapping": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
+    "b200_build_expert_mapping_static_capacity_bytes": (_sz, []),
+    "b200_build_expert_mapping_static": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp]),
     "b200_prepare_experts": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp]),
     "b200_prepare_experts_weighted": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp]),
     "b200_prepare_expert_zone": (_i, [_i, _vp, _i, _vp, _vp, _vp, _vp, _vp]),

@@ -403,6 +403,52 @@ extern "C" int b200_build_expert_mapping(int total_tokens, int num_routed_expert
   return 0;
 }
 
+// ---------------------------------------------------------------------------------------
+// build_expert_mapping without caller-provided scratch.
+//
+// Some hosts of this library cannot hand over device scratch: a backend op slot whose
+// argument list is fixed by the framework's op signature (build_expert_mapping has exactly
+// seven arguments there) and which runs at submit time, when the framework forbids device
+// allocation because all device memory was carved up front. For them the histogram tables
+// live in this fixed array inside the library image. Every GPU that loads the library keeps
+// the array (4 MiB) until the process exits.
+// ---------------------------------------------------------------------------------------
+constexpr size_t STATIC_MAP_SCRATCH_INTS = 1u << 20;  // 4 MiB
+static __device__ __align__(256) int g_static_map_scratch[STATIC_MAP_SCRATCH_INTS];
+
+constexpr int STATIC_MAX_DEVICES = 64;
+static int *g_static_map_scratch_addr[STATIC_MAX_DEVICES];  // device address of the array, per device ordinal
+
+extern "C" size_t b200_build_expert_mapping_static_capacity_bytes(void) {
+  return STATIC_MAP_SCRATCH_INTS * sizeof(int);
+}
+
+extern "C" int b200_build_expert_mapping_static(int total_tokens, int num_routed_experts, int num_selected_experts,
+                                                const uint16_t *chosen_experts, int *expert_counts_cumsum,
+                                                int *expert_mapping, int *token_mapping, void *stream) {
+  const size_t need =
+      b200_build_expert_mapping_workspace_bytes(total_tokens, num_routed_experts, num_selected_experts);
+  B200_REQUIRE(need != 0, "build_expert_mapping_static: bad sizes (tokens %d, experts %d, top_k %d)", total_tokens,
+               num_routed_experts, num_selected_experts);
+  B200_REQUIRE(need <= STATIC_MAP_SCRATCH_INTS * sizeof(int),
+               "build_expert_mapping_static: this problem needs %zu bytes of scratch but the built-in array holds %zu; "
+               "use b200_build_expert_mapping with caller scratch",
+               need, STATIC_MAP_SCRATCH_INTS * sizeof(int));
+  int dev = -1;
+  B200_CUDA(cudaGetDevice(&dev));
+  B200_REQUIRE(dev >= 0 && dev < STATIC_MAX_DEVICES, "build_expert_mapping_static: device ordinal %d out of range", dev);
+  if (g_static_map_scratch_addr[dev] == nullptr) {
+    // In host code the array's name is only a handle; the kernels need its address on the current device.
+    int *addr = nullptr;
+    B200_CUDA(cudaGetSymbolAddress((void **)&addr, g_static_map_scratch));
+    B200_REQUIRE(addr != nullptr, "build_expert_mapping_static: no device address for the built-in scratch");
+    g_static_map_scratch_addr[dev] = addr;
+  }
+  return b200_build_expert_mapping(total_tokens, num_routed_experts, num_selected_experts, chosen_experts,
+                                   expert_counts_cumsum, expert_mapping, token_mapping, g_static_map_scratch_addr[dev],
+                                   STATIC_MAP_SCRATCH_INTS * sizeof(int), stream);
+}
+
 extern "C" int b200_router_gate_bwd_x(int num_tokens, int num_routed_experts, int top_k_active,
                                       const uint16_t *chosen_experts, const float *token_expert_weights,
                                       void *dX_routed, void *stream) {

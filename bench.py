@@ -187,9 +187,11 @@ def run_gpu_arm(args, world):
     from ml_dataflow_b200 import ops
     from ml_dataflow_b200.moe_layer import MoELayer
 
-    cfg = CFG_1GPU if world == 1 else CFG_EP
+    cfg = dict(CFG_1GPU if world == 1 else CFG_EP)
+    if args.tokens > 0:
+        cfg["T"] = args.tokens
     T, d, E, k, f = cfg["T"], cfg["d"], cfg["E"], cfg["k"], cfg["f"]
-    steps, warmup = max(1, args.steps), max(3, args.warmup)
+    steps, warmup = max(1, args.steps), (max(0, args.warmup) if args.quick else max(3, args.warmup))
     peaks = read_peaks()
     dev = torch.device("cuda", local_rank)
     gen = torch.Generator(device=dev).manual_seed(0xB200 + rank)
@@ -234,14 +236,14 @@ def run_gpu_arm(args, world):
 
     # ---------------- device-resident timing
     sampler = ClockSampler(local_rank)
-    if rank == 0:
+    if rank == 0 and not args.quick:
         sampler.start()
     for _ in range(warmup):
         step(X, dOut, out, dXn)
     barrier()
     # keep the GPU busy until nvidia-smi has started sampling, so the clock record covers the timed region
     t_spin = time.perf_counter()
-    while rank == 0 and time.perf_counter() - t_spin < 1.0:
+    while rank == 0 and not args.quick and time.perf_counter() - t_spin < 1.0:
         step(X, dOut, out, dXn)
         torch.cuda.synchronize()
     ops.LAUNCHES = 0
@@ -259,6 +261,14 @@ def run_gpu_arm(args, world):
     if status != 0:
         raise RuntimeError(f"a GEMM kernel gave up waiting (status {status}); the timing is void")
     value = world * T / (ms_step * 1e-3)
+    if args.quick:
+        if rank == 0:
+            print(json.dumps(dict(metric=METRIC, value=value, unit=UNIT, n_gpus=world, steps=steps, warmup=warmup,
+                                  ms_per_step=ms_step, quick=True, gpu_launches=launches,
+                                  config=dict(workload=workload_name(cfg, world)))), flush=True)
+        if dist is not None:
+            dist.destroy_process_group()
+        return
 
     # ---------------- end to end: pinned host buffers, copies inside the timed region, double buffered
     Xh, dOh = X.cpu().pin_memory(), dOut.cpu().pin_memory()
@@ -370,6 +380,9 @@ def main():
     ap.add_argument("--steps", type=int, default=30)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--tokens", type=int, default=0, help="override T (tokens per GPU); for profiler captures")
+    ap.add_argument("--quick", action="store_true",
+                    help="device-timed loop only, exactly --warmup/--steps iterations (for ncu launch lists)")
     args = ap.parse_args()
     world = int(os.environ.get("WORLD_SIZE", str(args.gpus)))
     if args.impl == "reference":

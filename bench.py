@@ -172,6 +172,16 @@ def algorithmic_work(cfg):
     }
 
 
+NVLINK_PEER_GBS = 770.0  # measured peer copy per direction on this pool (nominal 900)
+
+
+def exchange_work(cfg, world):
+    """Bytes each rank sends (and receives) per exchange when rows spread evenly over the ranks."""
+    R = cfg["T"] * cfg["k"]
+    rows = 2 * R * cfg["d"] * (world - 1) / world
+    return {"dispatch": rows, "return": rows, "dispatch_bwd": rows, "return_bwd": rows + 4 * R * (world - 1) / world}
+
+
 def run_gpu_arm(args, world):
     import torch
 
@@ -347,6 +357,13 @@ def run_gpu_arm(args, world):
             ach = amount / (ms * 1e-3) / 1e9
             kernels[name] = dict(ms=round(ms, 4), bound="hbm", achieved=round(ach, 1), unit="GB/s",
                                  frac=round(ach / peaks["hbm_gbs"], 4))
+    if world > 1:
+        for name, amount in exchange_work(cfg, world).items():
+            if name in acc:
+                ms = sum(acc[name]) / len(acc[name])
+                ach_x = amount / (ms * 1e-3) / 1e9
+                kernels[name] = dict(ms=round(ms, 4), bound="nvlink", achieved=round(ach_x, 1), unit="GB/s per direction",
+                                     frac=round(ach_x / NVLINK_PEER_GBS, 4))
     ach = gemm_flops / (gemm_ms * 1e-3) / 1e12 if gemm_ms else 0.0
     roofline = dict(kernel="gemm_sm100_kernel (grouped expert GEMMs: 7 launches per step, 18*R*d*f flop)",
                     bound="tensor", achieved=round(ach, 1), peak=peaks["bf16_tflops_sustained"], unit="TFLOP/s",

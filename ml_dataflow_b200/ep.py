@@ -1,0 +1,232 @@
+"""Expert-parallel MoE layer: experts sharded over the ranks of one node, tokens data-parallel.
+
+The reference is single-GPU (its `MoE_Config.num_local_experts / local_expert_inds`,
+libdataflowmodels/include/dataflow_models.h:51-67, are placeholders), so the per-token maths is the
+only behaviour to match; the exchange is new. Rank g owns experts [g*E/G, (g+1)*E/G) with their
+W1/W3/W2 and gradients; the router weight is replicated and its gradient all-reduced.
+
+Per layer and direction there is one exchange each way:
+
+  route locally (global expert ids) -> counts[E] -> counts exchange (G x E/G ints)
+  -> rows already sit expert-contiguous in the zone, so the block of rows for (destination rank h,
+     local expert j) is one contiguous slice; it is sent straight into the receiver's region of
+     expert j, at the offset of this source rank. The receive buffer is therefore expert-contiguous
+     (source-major inside an expert) with no second permutation, and the grouped GEMMs run on it
+     unchanged with per-expert counts summed over sources.
+  -> grouped expert GEMMs on the received rows -> the reverse exchange -> local weighted combine.
+
+`RowExchange` holds only the bookkeeping and the point-to-point batches (torch.distributed
+`batch_isend_irecv`: one NCCL group per exchange over NVLink; also runs on gloo for the CPU tests).
+The row counts must be known on the host to size the messages, so `plan()` reads the exchanged
+counts back once per layer - the same place where the reference's block synchronises to read
+`host_expert_counts` (dataflow_transformer.c:2789).
+"""
+import torch
+
+
+class RowExchange:
+    """Bookkeeping + transport of routed rows between `world` ranks owning `E // world` experts each."""
+
+    def __init__(self, dist, num_experts, device):
+        self.dist = dist
+        self.world = dist.get_world_size()
+        self.rank = dist.get_rank()
+        assert num_experts % self.world == 0, "experts must divide evenly over the ranks"
+        self.E = num_experts
+        self.E_loc = num_experts // self.world
+        self.device = device
+
+    # -------------------------------------------------------------------------------- plan
+    def plan(self, counts_dev):
+        """counts_dev: int32 [E] per-expert row counts of this rank's tokens (device tensor).
+
+        Exchanges the counts, then fills (host lists / device tensors):
+          send_off[h][j], send_cnt[h][j] : slice of the local zone holding rows for rank h's expert j
+          recv_off[s][j], recv_cnt[s][j] : slice of the receive buffer for rows from rank s, local expert j
+          local_counts, local_cumsum     : int32 [E_loc] device tensors for the grouped GEMMs (inclusive cumsum)
+          rows_recv                      : total received rows
+        """
+        G, El = self.world, self.E_loc
+        mine = counts_dev[: self.E].to(torch.int32).contiguous()
+        gathered = torch.empty(G * self.E, dtype=torch.int32, device=mine.device)
+        self.dist.all_gather_into_tensor(gathered, mine)
+        all_counts = gathered.cpu().view(G, G, El)  # [source rank][destination rank][local expert]  (host sync)
+        send_cnt = all_counts[self.rank]                     # [h][j]
+        recv_cnt = all_counts[:, self.rank, :].contiguous()  # [s][j]
+        send_off = (torch.cumsum(send_cnt.reshape(-1), 0) - send_cnt.reshape(-1)).view(G, El)
+        per_expert = recv_cnt.sum(dim=0)                     # [j]
+        expert_base = torch.cumsum(per_expert, 0) - per_expert
+        within = torch.cumsum(recv_cnt, 0) - recv_cnt        # offset of source s inside expert j
+        recv_off = expert_base.view(1, El) + within
+        self.send_cnt, self.send_off = send_cnt.tolist(), send_off.tolist()
+        self.recv_cnt, self.recv_off = recv_cnt.tolist(), recv_off.tolist()
+        self.rows_recv = int(per_expert.sum())
+        self.rows_send = int(send_cnt.sum())
+        self.local_counts = per_expert.to(torch.int32).to(self.device)
+        self.local_cumsum = torch.cumsum(per_expert, 0).to(torch.int32).to(self.device)
+        return self
+
+    # -------------------------------------------------------------------------------- transport
+    def _exchange(self, src, dst, out_cnt, out_off, in_cnt, in_off):
+        """Rows src[out_off[p][j] : +out_cnt[p][j]] go to rank p; rows from rank p land in dst[in_off[p][j] : ...]."""
+        dist = self.dist
+        ops = []
+        for j in range(self.E_loc):
+            n = out_cnt[self.rank][j]
+            if n:
+                dst[in_off[self.rank][j]: in_off[self.rank][j] + n].copy_(
+                    src[out_off[self.rank][j]: out_off[self.rank][j] + n])
+        for step in range(1, self.world):
+            to, frm = (self.rank + step) % self.world, (self.rank - step) % self.world
+            for j in range(self.E_loc):
+                if out_cnt[to][j]:
+                    ops.append(dist.P2POp(dist.isend, src[out_off[to][j]: out_off[to][j] + out_cnt[to][j]], to))
+                if in_cnt[frm][j]:
+                    ops.append(dist.P2POp(dist.irecv, dst[in_off[frm][j]: in_off[frm][j] + in_cnt[frm][j]], frm))
+        if ops:
+            for req in dist.batch_isend_irecv(ops):
+                req.wait()
+        return dst
+
+    def dispatch(self, zone_rows, recv_rows):
+        """Local zone (expert-contiguous over all E experts) -> receive buffer (this rank's experts)."""
+        return self._exchange(zone_rows, recv_rows, self.send_cnt, self.send_off, self.recv_cnt, self.recv_off)
+
+    def combine(self, recv_rows, zone_rows):
+        """The reverse exchange: rows computed by the owning rank go back to their slot in the source's zone."""
+        return self._exchange(recv_rows, zone_rows, self.recv_cnt, self.recv_off, self.send_cnt, self.send_off)
+
+
+class ExpertParallelMoELayer:
+    """Same call surface as `MoELayer`, with W1/W3/W2 and their gradients holding only this rank's experts."""
+
+    def __init__(self, T, d, E, k, f, dist, device="cuda", recv_capacity_factor=1.5):
+        self.T, self.d, self.E, self.k, self.f = T, d, E, k, f
+        self.dist = dist
+        self.dev = torch.device(device)
+        self.x = RowExchange(dist, E, self.dev)
+        self.E_loc = self.x.E_loc
+        self.R = T * k
+        self.home = _HomeSide(T, d, E, k, self.dev)
+        self.cap = int(self.R * recv_capacity_factor) + 256
+        bf, f32 = torch.bfloat16, torch.float32
+
+        def buf(shape, dt):
+            return torch.empty(shape, dtype=dt, device=self.dev)
+
+        self.zone_r = buf((self.cap, d), bf)   # received rows (kept for backward-w)
+        self.x1, self.x3, self.h = buf((self.cap, f), bf), buf((self.cap, f), bf), buf((self.cap, f), bf)
+        self.Y_r = buf((self.cap, d), bf)
+        self.dY_r = buf((self.cap, d), bf)
+        self.dx1, self.dx3 = buf((self.cap, f), bf), buf((self.cap, f), bf)
+        self.dZ_r = buf((self.cap, d), bf)
+        self.ones = torch.ones(self.cap, dtype=f32, device=self.dev)
+        self.dP_r = buf((self.cap,), f32)
+        self.profile = None
+
+    def mark(self, name):
+        if self.profile is not None:
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record()
+            self.profile.append((name, ev))
+
+    def forward(self, Xn, Wr, W1, W3, W2, out):
+        from . import ops
+
+        hm, x = self.home, self.x
+        T, d, E, k, f = self.T, self.d, self.E, self.k, self.f
+        self.mark("router_gemm")
+        hm.route(Xn, Wr)
+        self.mark("prepare_experts")
+        ops.prepare_experts(T, d, k, Xn, hm.token_mapping, hm.zone)
+        self.mark("dispatch")
+        x.plan(hm.counts)
+        if x.rows_recv > self.cap:
+            raise RuntimeError(f"expert-parallel receive buffer too small: {x.rows_recv} rows > capacity {self.cap}")
+        n = x.rows_recv
+        x.dispatch(hm.zone, self.zone_r)
+        self.mark("experts_fwd_gemm")
+        ops.moe_experts_fwd(n, d, f, self.E_loc, self.zone_r, W1, W3, W2, f * d, f * d, d * f, x.local_counts,
+                            x.local_cumsum, self.x1, self.x3, self.h, self.Y_r)
+        self.mark("return")
+        x.combine(self.Y_r, hm.Y)
+        self.mark("merge_experts")
+        ops.merge_experts(T, d, k, hm.Y, hm.token_mapping, hm.weights, out)
+        self.mark("fwd_end")
+        return out
+
+    def backward(self, Xn, Wr, W1, W3, W2, dOut, dXn, dWr, dW1, dW3, dW2):
+        from . import ops
+
+        hm, x = self.home, self.x
+        T, d, E, k, f = self.T, self.d, self.E, self.k, self.f
+        n = x.rows_recv
+        self.mark("prepare_experts_weighted")
+        ops.prepare_experts_weighted(T, d, k, dOut, hm.token_mapping, hm.weights, hm.dYz)
+        ops.scatter_row_weights(T, k, hm.token_mapping, hm.weights, hm.row_w)
+        self.mark("dispatch_bwd")
+        x.dispatch(hm.dYz, self.dY_r)
+        self.mark("experts_bwd_x_gemm")
+        self.dP_r[:n].zero_()
+        # the gate weight of a row lives on its home rank: accumulate w*<Y,dOut> here, divide there
+        ops.moe_experts_bwd_x(n, d, f, self.E_loc, self.dY_r, self.ones, self.x1, self.x3, W1, W3, W2, f * d, f * d,
+                              d * f, x.local_counts, x.local_cumsum, self.dx1, self.dx3, None, self.dP_r, self.dZ_r)
+        self.mark("experts_bwd_w_gemm")
+        ops.moe_experts_bwd_w(n, d, f, self.E_loc, self.dY_r, self.h, self.zone_r, self.dx1, self.dx3, dW1, dW3, dW2,
+                              f * d, f * d, d * f, x.local_counts, x.local_cumsum)
+        self.mark("return_bwd")
+        x.combine(self.dZ_r, hm.dZ)
+        x.combine(self.dP_r, hm.dP)
+        self.mark("unpermute")
+        hm.dP.div_(hm.row_w)
+        dXn.zero_()
+        ops.merge_experts(T, d, k, hm.dZ, hm.token_mapping, None, dXn)
+        self.mark("router_grad")
+        hm.dX_routed.zero_()
+        ops.gather_router_grad(T, E, k, hm.token_mapping, hm.chosen, hm.dP, hm.dX_routed)
+        ops.router_gate_bwd_x(T, E, k, hm.chosen, hm.weights, hm.dX_routed)
+        ops.matmul(0, 0, d, E, T, 1.0, 1.0, Wr, hm.dX_routed, dXn, dXn)
+        hm.dWr_local.zero_()
+        ops.matmul(0, 1, d, T, E, 1.0, 0.0, Xn, hm.dX_routed, None, hm.dWr_local)
+        self.dist.all_reduce(hm.dWr_local)  # the replicated router weight sees every rank's tokens
+        dWr.add_(hm.dWr_local)
+        self.mark("bwd_end")
+        return dXn
+
+
+class _HomeSide:
+    """Token-side state of one rank: routing results, the expert-ordered zone and its backward twins."""
+
+    def __init__(self, T, d, E, k, dev):
+        from . import ops
+
+        self.T, self.d, self.E, self.k = T, d, E, k
+        R = T * k
+        bf, f32, i32 = torch.bfloat16, torch.float32, torch.int32
+
+        def buf(shape, dt):
+            return torch.empty(shape, dtype=dt, device=dev)
+
+        self.logits = buf((T, E), f32)
+        self.weights = buf((T, k), f32)
+        self.chosen = buf((T, k), torch.int16)
+        self.counts = torch.zeros(E + 1, dtype=i32, device=dev)
+        self.cumsum = torch.zeros(E, dtype=i32, device=dev)
+        self.expert_mapping = buf((R,), i32)
+        self.token_mapping = buf((T, k), i32)
+        self.map_ws = torch.empty(ops.build_expert_mapping_workspace_bytes(T, E, k), dtype=torch.uint8, device=dev)
+        self.zone, self.Y, self.dYz, self.dZ = (buf((R, d), bf) for _ in range(4))
+        self.row_w, self.dP = buf((R,), f32), buf((R,), f32)
+        self.dX_routed = buf((T, E), bf)
+        self.dWr_local = buf((E, d), bf)
+
+    def route(self, Xn, Wr):
+        from . import ops
+
+        T, d, E, k = self.T, self.d, self.E, self.k
+        ops.matmul(1, 0, E, d, T, 1.0, 0.0, Wr, Xn, None, self.logits)
+        self.counts.zero_()
+        self.cumsum.zero_()
+        ops.select_experts(T, E, k, self.logits, self.weights, self.chosen, self.counts, self.cumsum, None)
+        ops.build_expert_mapping(T, E, k, self.chosen, self.cumsum, self.expert_mapping, self.token_mapping,
+                                 self.map_ws)

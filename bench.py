@@ -193,7 +193,11 @@ def run_gpu_arm(args, world):
         import torch.distributed as dist_mod
 
         dist = dist_mod
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        import datetime
+
+        # a short collective timeout: a rank that falls out of step ends the run in minutes, not in ten
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank),
+                                timeout=datetime.timedelta(seconds=180))
     from ml_dataflow_b200 import ops
     from ml_dataflow_b200.moe_layer import MoELayer
 
@@ -248,14 +252,17 @@ def run_gpu_arm(args, world):
     sampler = ClockSampler(local_rank)
     if rank == 0 and not args.quick:
         sampler.start()
+    t_w = time.perf_counter()
     for _ in range(warmup):
         step(X, dOut, out, dXn)
     barrier()
-    # keep the GPU busy until nvidia-smi has started sampling, so the clock record covers the timed region
-    t_spin = time.perf_counter()
-    while rank == 0 and not args.quick and time.perf_counter() - t_spin < 1.0:
-        step(X, dOut, out, dXn)
-        torch.cuda.synchronize()
+    if not args.quick:
+        # keep the GPUs busy until nvidia-smi has started sampling, so the clock record covers the timed region;
+        # every rank runs the same number of extra steps (the step contains collectives when world > 1)
+        per_step_ms = max_over_ranks((time.perf_counter() - t_w) * 1e3 / max(1, warmup))
+        for _ in range(int(min(60, max(1, 1200.0 / max(per_step_ms, 1.0))))):
+            step(X, dOut, out, dXn)
+        barrier()
     ops.LAUNCHES = 0
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
@@ -373,6 +380,8 @@ def run_gpu_arm(args, world):
                     ms_per_step_in_kernel=round(gemm_ms, 4))
 
     if rank != 0:
+        if dist is not None:
+            dist.destroy_process_group()
         return
     cpu_tps, cpu_sec, threads = cpu_reference_run(cfg, 2, 1) if world == 1 else (None, None, None)
     line = dict(metric=METRIC, value=value, unit=UNIT, n_gpus=world, steps=steps, warmup=warmup, ms_per_step=ms_step,

@@ -209,6 +209,13 @@ int b200_matmul(int a_dt, int b_dt, int c_dt, int d_dt, int to_trans_a, int to_t
  */
 int b200_gemm_status(int *status_out);
 
+/*
+ * Tile shape of the GEMM kernels: 1 (default) = pairs of CTAs share one 256-row tcgen05 MMA (cta_group::2),
+ * 0 = one CTA per 128-row tile. The environment variable B200_GEMM_PAIR=0 selects 0 at start-up.
+ * Results are the same up to fp32 summation order. No counterpart in the reference.
+ */
+int b200_gemm_set_pair_mode(int on);
+
 /* ---- grouped expert GEMMs (additive ops; the reference loops experts on the host) ----------- */
 
 /*

@@ -9,30 +9,47 @@
 //   * the expert-grouped wgrad GEMMs (groups along the reduction; the rows of the last 64-row
 //     slab that belong to the next expert are zeroed in shared memory before the MMA).
 //
-// Tile: 128 rows x up to 256 columns x 64 deep per stage, 4 stages, two 256-column
-// accumulator buffers in tensor memory so the epilogue of one tile overlaps the next tile's MMAs.
+// Tile per CTA: 128 rows x up to 256 columns x 64 deep per stage; two 256-column accumulator
+// buffers in tensor memory so the epilogue of one tile overlaps the next tile's MMAs.
+// Two variants of the same body:
+//   single (cta_group::1): 4 stages of 48 KiB (A 128x64 + B 256x64);
+//   pair   (cta_group::2): two CTAs of a cluster share one 256 x 256 MMA; each loads its 128 rows of
+//           A and HALF the columns of B (32 KiB per stage, 6 stages), so the same tensor work needs
+//           two thirds of the shared-memory fill bandwidth and tolerates more load latency. No TMA
+//           multicast is used: every CTA fetches its own boxes, the even CTA issues the MMAs, and
+//           tcgen05.commit tells both CTAs when a stage or an accumulator is done.
+#include <stdlib.h>
+#include <string.h>
+
 #include "common.cuh"
 #include "sm100_ptx.cuh"
 #include "../../include/b200_moe.h"
 
 namespace b200 {
 
-constexpr int BM = 128;
+constexpr int BM = 128;                 // rows of A / of the accumulator per CTA
 constexpr int BK = 64;
 constexpr int BLK_BYTES = 64 * 64 * 2;  // one TMA box: 64 rows of 128 bytes
 constexpr int A_BLKS = 2;
-constexpr int B_BLKS = 4;
-constexpr int STAGE_BYTES = (A_BLKS + B_BLKS) * BLK_BYTES;  // 48 KiB
-constexpr int STAGES = 4;
 constexpr int ACC_COLS = 256;
 constexpr int TMEM_COLS = 512;
-constexpr int GEMM_THREADS = 192;
+constexpr int EPI_WARPS = 8;
+constexpr int GEMM_THREADS = 64 + EPI_WARPS * 32;  // TMA warp, MMA warp, 8 epilogue warps
 constexpr int MAX_GROUPS = 1024;
+constexpr int MAX_STAGES = 6;
+
+template <bool PAIR>
+struct Cfg {
+  static constexpr int B_BLKS = PAIR ? 2 : 4;
+  static constexpr int STAGE_BYTES = (A_BLKS + B_BLKS) * BLK_BYTES;
+  static constexpr int STAGES = PAIR ? 6 : 4;
+  static constexpr int TILE_M = PAIR ? 2 * BM : BM;
+};
 
 enum GroupMode { DENSE = 0, GROUPED_M = 1, GROUPED_K = 2 };
 enum Epilogue { EPI_STORE = 0, EPI_SWIGLU_FWD = 1, EPI_SWIGLU_BWD = 2 };
 
-enum StatusCode { ST_OK = 0, ST_PRODUCER_TIMEOUT = 1, ST_MMA_TIMEOUT = 2, ST_EPILOGUE_TIMEOUT = 3 };
+enum StatusCode { ST_OK = 0, ST_PRODUCER_TIMEOUT = 1, ST_MMA_TIMEOUT = 2, ST_EPILOGUE_TIMEOUT = 3, ST_PEER_TIMEOUT = 4 };
 
 __device__ int g_gemm_status = 0;
 
@@ -59,16 +76,16 @@ struct GemmParams {
 };
 
 struct Tile {
-  int group;    // expert (0 for dense)
-  int a_row0;   // first row of the A tile (GROUPED_K: first column of the [R, M] array)
-  int out_row0; // first output row
-  int m_valid;  // valid rows in this tile
-  int n0, n_valid, nw;  // first column, valid columns, columns rounded up to 64
+  int group;     // expert (0 for dense)
+  int a_row0;    // first row of the tile in A (GROUPED_K: first column of the [R, M] array)
+  int out_row0;  // first output row of the tile
+  int m_valid;   // valid rows in the tile (up to TILE_M)
+  int n0, n_valid, nw;  // first column, valid columns, columns rounded up to the load granule
   int k_row0, k_len;    // GROUPED_K: reduction range inside the [R, *] arrays
 };
 
 struct Sched {
-  int mode, tiles_n, tiles_m, n_tile_w, total_tiles, M, N, K, num_groups;
+  int mode, tiles_n, tiles_m, n_tile_w, n_round, tile_m, total_tiles, M, N, K;
   const int *s_cnt, *s_base, *s_tpre;
   int cursor;
 
@@ -79,8 +96,8 @@ struct Sched {
       const int mt = tile_id / tiles_n;
       nt = tile_id - mt * tiles_n;
       t.group = 0;
-      t.a_row0 = t.out_row0 = mt * BM;
-      t.m_valid = min(BM, M - mt * BM);
+      t.a_row0 = t.out_row0 = mt * tile_m;
+      t.m_valid = min(tile_m, M - mt * tile_m);
       t.k_row0 = 0;
       t.k_len = K;
     } else if (mode == GROUPED_M) {
@@ -89,8 +106,8 @@ struct Sched {
       while (s_tpre[cursor + 1] <= mtg) cursor++;
       const int ml = mtg - s_tpre[cursor];
       t.group = cursor;
-      t.a_row0 = t.out_row0 = s_base[cursor] + ml * BM;
-      t.m_valid = min(BM, s_cnt[cursor] - ml * BM);
+      t.a_row0 = t.out_row0 = s_base[cursor] + ml * tile_m;
+      t.m_valid = min(tile_m, s_cnt[cursor] - ml * tile_m);
       t.k_row0 = 0;
       t.k_len = K;
     } else {
@@ -100,58 +117,72 @@ struct Sched {
       const int mt = rem / tiles_n;
       nt = rem - mt * tiles_n;
       t.group = e;
-      t.a_row0 = t.out_row0 = mt * BM;
-      t.m_valid = min(BM, M - mt * BM);
+      t.a_row0 = t.out_row0 = mt * tile_m;
+      t.m_valid = min(tile_m, M - mt * tile_m);
       t.k_row0 = s_base[e];
       t.k_len = s_cnt[e];
     }
     t.n0 = nt * n_tile_w;
     t.n_valid = min(n_tile_w, N - t.n0);
-    t.nw = (t.n_valid + 63) & ~63;
+    t.nw = (t.n_valid + n_round - 1) & ~(n_round - 1);
     return true;
   }
 };
 
 __device__ __forceinline__ float silu_f(float a) { return a / (1.0f + __expf(-a)); }
 
-template <int EPI>
+// shared-memory bookkeeping that follows the stage buffers
+struct GemmSmemTail {
+  uint64_t full[MAX_STAGES], empty[MAX_STAGES], peer_full[MAX_STAGES], tfull[2], tempty[2];
+  uint32_t tmem_base;
+  int abort_flag;
+  int cnt[MAX_GROUPS], base[MAX_GROUPS], tpre[MAX_GROUPS + 1];
+};
+
+template <int EPI, bool PAIR>
 __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __grid_constant__ GemmParams p) {
+  using CF = Cfg<PAIR>;
+  constexpr int STAGES = CF::STAGES;
+  constexpr int STAGE_BYTES = CF::STAGE_BYTES;
   extern __shared__ unsigned char gemm_smem_raw[];
   // 1024-byte alignment is required by the 128-byte swizzle atoms
   unsigned char *smem = reinterpret_cast<unsigned char *>(
       (reinterpret_cast<uintptr_t>(gemm_smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-  uint64_t *bars = reinterpret_cast<uint64_t *>(smem + STAGES * STAGE_BYTES);
-  // bars: full[STAGES] | empty[STAGES] | tmem_full[2] | tmem_empty[2]
-  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 4);
-  volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
-  int *s_cnt = reinterpret_cast<int *>(tmem_slot + 4);
-  int *s_base = s_cnt + MAX_GROUPS;
-  int *s_tpre = s_base + MAX_GROUPS;  // MAX_GROUPS + 1 entries
+  GemmSmemTail *st = reinterpret_cast<GemmSmemTail *>(smem + STAGES * STAGE_BYTES);
+  volatile int *abort_flag = &st->abort_flag;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const uint32_t cta_rank = PAIR ? ptx::cluster_ctarank() : 0u;
+  const bool leader = cta_rank == 0;
   const uint32_t smem_base = ptx::smem_u32(smem);
-  const uint32_t bar_base = ptx::smem_u32(bars);
-  auto full_bar = [&](int s) { return bar_base + 8u * s; };
-  auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
-  auto tfull_bar = [&](int s) { return bar_base + 8u * (2 * STAGES + s); };
-  auto tempty_bar = [&](int s) { return bar_base + 8u * (2 * STAGES + 2 + s); };
+  auto full_bar = [&](int s) { return ptx::smem_u32(&st->full[s]); };
+  auto empty_bar = [&](int s) { return ptx::smem_u32(&st->empty[s]); };
+  auto peer_bar = [&](int s) { return ptx::smem_u32(&st->peer_full[s]); };
+  auto tfull_bar = [&](int s) { return ptx::smem_u32(&st->tfull[s]); };
+  auto tempty_bar = [&](int s) { return ptx::smem_u32(&st->tempty[s]); };
 
   if (tid == 0) {
     for (int s = 0; s < STAGES; s++) {
       ptx::mbar_init(full_bar(s), 1);
       ptx::mbar_init(empty_bar(s), 1);
+      ptx::mbar_init(peer_bar(s), 1);
     }
     for (int s = 0; s < 2; s++) {
       ptx::mbar_init(tfull_bar(s), 1);
-      ptx::mbar_init(tempty_bar(s), 4);
+      ptx::mbar_init(tempty_bar(s), PAIR ? 2 * EPI_WARPS : EPI_WARPS);
     }
-    *abort_flag = 0;
+    st->abort_flag = 0;
     ptx::fence_barrier_init();
     ptx::fence_proxy_async_smem();
   }
   if (warp == 1) {
-    ptx::tmem_alloc(ptx::smem_u32(tmem_slot), TMEM_COLS);
-    ptx::tmem_relinquish();
+    if (PAIR) {
+      ptx::tmem_alloc_pair(ptx::smem_u32(&st->tmem_base), TMEM_COLS);
+      ptx::tmem_relinquish_pair();
+    } else {
+      ptx::tmem_alloc(ptx::smem_u32(&st->tmem_base), TMEM_COLS);
+      ptx::tmem_relinquish();
+    }
   }
   if (warp == 0 && lane == 0) {
     ptx::tma_prefetch_desc(&p.tmA);
@@ -165,8 +196,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
   if (p.group_mode != DENSE) {
     for (int e = tid; e < G; e += GEMM_THREADS) {
       const int c = p.counts[e];
-      s_cnt[e] = c;
-      s_base[e] = p.cumsum_incl[e] - c;
+      st->cnt[e] = c;
+      st->base[e] = p.cumsum_incl[e] - c;
     }
   }
   __syncthreads();
@@ -174,53 +205,69 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
     int running = 0;
     for (int e0 = 0; e0 < G; e0 += 32) {
       const int e = e0 + lane;
-      const int v = (e < G) ? (s_cnt[e] + BM - 1) / BM : 0;
+      const int v = (e < G) ? (st->cnt[e] + CF::TILE_M - 1) / CF::TILE_M : 0;
       int incl = v;
 #pragma unroll
       for (int o = 1; o < 32; o <<= 1) {
         const int t = __shfl_up_sync(0xffffffffu, incl, o);
         if (lane >= o) incl += t;
       }
-      if (e < G) s_tpre[e] = running + incl - v;
+      if (e < G) st->tpre[e] = running + incl - v;
       running += __shfl_sync(0xffffffffu, incl, 31);
     }
-    if (lane == 0) s_tpre[G] = running;
+    if (lane == 0) st->tpre[G] = running;
   }
   ptx::tc_fence_before();
-  __syncthreads();
+  if (PAIR) ptx::cluster_sync_all();  // the peer's barriers are initialised before anything arrives on them
+  else __syncthreads();
   ptx::tc_fence_after();
-  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_base = st->tmem_base;
 
   Sched sched;
   sched.mode = p.group_mode;
   sched.M = p.M;
   sched.N = p.N;
   sched.K = p.K;
-  sched.num_groups = G;
+  sched.tile_m = CF::TILE_M;
   sched.n_tile_w = p.dual_b ? 128 : 256;
+  sched.n_round = (PAIR && !p.dual_b) ? 128 : 64;
   sched.tiles_n = (p.N + sched.n_tile_w - 1) / sched.n_tile_w;
-  sched.tiles_m = (p.M + BM - 1) / BM;
-  sched.s_cnt = s_cnt;
-  sched.s_base = s_base;
-  sched.s_tpre = s_tpre;
+  sched.tiles_m = (p.M + CF::TILE_M - 1) / CF::TILE_M;
+  sched.s_cnt = st->cnt;
+  sched.s_base = st->base;
+  sched.s_tpre = st->tpre;
   sched.cursor = 0;
   if (p.group_mode == DENSE) sched.total_tiles = sched.tiles_m * sched.tiles_n;
-  else if (p.group_mode == GROUPED_M) sched.total_tiles = s_tpre[G] * sched.tiles_n;
+  else if (p.group_mode == GROUPED_M) sched.total_tiles = st->tpre[G] * sched.tiles_n;
   else sched.total_tiles = G * sched.tiles_m * sched.tiles_n;
+  const int first_tile = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+  const int tile_step = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
+  const int row_off = (int)cta_rank * BM;  // this CTA's rows inside a pair tile
 
+  // barriers that the other CTA of a pair arrives on are polled with a cluster-scope acquire
+  auto xwait = [&](uint32_t bar, uint32_t par, int code) -> bool {
+    return ptx::mbar_wait<PAIR>(bar, par, abort_flag, p.status, code);
+  };
+  auto wait_local = [&](uint32_t bar, uint32_t par, int code) -> bool {
+    return ptx::mbar_wait<false>(bar, par, abort_flag, p.status, code);
+  };
   Tile t;
   if (warp == 0) {
-    // ================= TMA producer =================
+    // ================= TMA producer (every CTA loads its own boxes) =================
     int stage = 0;
     uint32_t phase = 0;
-    for (int tile = blockIdx.x; sched.get(tile, t); tile += gridDim.x) {
+    for (int tile = first_tile; sched.get(tile, t); tile += tile_step) {
       const int ksteps_seg = (t.k_len + BK - 1) / BK;
       const int ksteps = ksteps_seg * p.k_segments;
-      const int nblk = t.nw >> 6;
+      // 64-column boxes of B this CTA fetches per slab, and where they start
+      const int nb = p.dual_b ? (t.nw >> 6) : (PAIR ? (t.nw >> 7) : (t.nw >> 6));
+      const int n_start = t.n0 + ((PAIR && !p.dual_b) ? (int)cta_rank * (t.nw >> 1) : 0);
+      const int nb_loaded = (p.dual_b && !PAIR) ? 2 * nb : nb;
+      const int a_row = t.a_row0 + row_off;
       for (int ks = 0; ks < ksteps; ks++) {
         bool ok = true;
         if (lane == 0) {
-          ok = ptx::mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, ST_PRODUCER_TIMEOUT);
+          ok = xwait(empty_bar(stage), phase ^ 1u, ST_PRODUCER_TIMEOUT);
           if (ok) {
             const int seg = ks / ksteps_seg;
             const int kk = (ks - seg * ksteps_seg) * BK;
@@ -229,25 +276,31 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
             const uint32_t sA = smem_base + stage * STAGE_BYTES;
             const uint32_t sB = sA + A_BLKS * BLK_BYTES;
             const uint32_t bar = full_bar(stage);
-            const int nb_total = p.dual_b ? 2 * nblk : nblk;
-            ptx::mbar_arrive_expect_tx(bar, (uint32_t)((A_BLKS + nb_total) * BLK_BYTES));
+            ptx::mbar_arrive_expect_tx(bar, (uint32_t)((A_BLKS + nb_loaded) * BLK_BYTES));
+            auto ld2 = [&](uint32_t dst, const CUtensorMap *m, int c0, int c1) { ptx::tma_load_2d(dst, m, bar, c0, c1); };
+            auto ld3 = [&](uint32_t dst, const CUtensorMap *m, int c0, int c1, int c2) {
+              ptx::tma_load_3d(dst, m, bar, c0, c1, c2);
+            };
             if (!p.a_mn_major) {
-              ptx::tma_load_2d(sA, mA, bar, kk, t.a_row0);
-              ptx::tma_load_2d(sA + BLK_BYTES, mA, bar, kk, t.a_row0 + 64);
+              ld2(sA, mA, kk, a_row);
+              ld2(sA + BLK_BYTES, mA, kk, a_row + 64);
             } else {
-              ptx::tma_load_2d(sA, mA, bar, t.a_row0, t.k_row0 + kk);
-              ptx::tma_load_2d(sA + BLK_BYTES, mA, bar, t.a_row0 + 64, t.k_row0 + kk);
+              ld2(sA, mA, a_row, t.k_row0 + kk);
+              ld2(sA + BLK_BYTES, mA, a_row + 64, t.k_row0 + kk);
             }
             const int g3 = (p.group_mode == GROUPED_M) ? t.group : 0;
             if (p.dual_b) {
-              for (int i = 0; i < nblk; i++) ptx::tma_load_3d(sB + i * BLK_BYTES, &p.tmB, bar, kk, t.n0 + 64 * i, g3);
-              for (int i = 0; i < nblk; i++)
-                ptx::tma_load_3d(sB + (nblk + i) * BLK_BYTES, &p.tmB2, bar, kk, t.n0 + 64 * i, g3);
+              if (PAIR) {  // even CTA holds the W1 columns, odd CTA the W3 columns
+                const CUtensorMap *mine = cta_rank ? &p.tmB2 : &p.tmB;
+                for (int i = 0; i < nb; i++) ld3(sB + i * BLK_BYTES, mine, kk, t.n0 + 64 * i, g3);
+              } else {
+                for (int i = 0; i < nb; i++) ld3(sB + i * BLK_BYTES, &p.tmB, kk, t.n0 + 64 * i, g3);
+                for (int i = 0; i < nb; i++) ld3(sB + (nb + i) * BLK_BYTES, &p.tmB2, kk, t.n0 + 64 * i, g3);
+              }
             } else if (!p.b_mn_major) {
-              for (int i = 0; i < nblk; i++) ptx::tma_load_3d(sB + i * BLK_BYTES, mB, bar, kk, t.n0 + 64 * i, g3);
+              for (int i = 0; i < nb; i++) ld3(sB + i * BLK_BYTES, mB, kk, n_start + 64 * i, g3);
             } else {
-              for (int i = 0; i < nblk; i++)
-                ptx::tma_load_3d(sB + i * BLK_BYTES, mB, bar, t.n0 + 64 * i, t.k_row0 + kk, g3);
+              for (int i = 0; i < nb; i++) ld3(sB + i * BLK_BYTES, mB, n_start + 64 * i, t.k_row0 + kk, g3);
             }
           }
         }
@@ -260,54 +313,69 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
       }
     }
   } else if (warp == 1) {
-    // ================= MMA issuer =================
+    // ================= MMA issuer (even CTA) / slab forwarder (odd CTA of a pair) =================
     int stage = 0;
     uint32_t phase = 0;
     int acc = 0;
     uint32_t acc_phase = 0;
-    for (int tile = blockIdx.x; sched.get(tile, t); tile += gridDim.x) {
+    for (int tile = first_tile; sched.get(tile, t); tile += tile_step) {
       const int ksteps_seg = (t.k_len + BK - 1) / BK;
       const int ksteps = ksteps_seg * p.k_segments;
       if (ksteps == 0) continue;
-      const int nblk = t.nw >> 6;
+      const int nb = p.dual_b ? (t.nw >> 6) : (PAIR ? (t.nw >> 7) : (t.nw >> 6));
+      const int nb_loaded = (p.dual_b && !PAIR) ? 2 * nb : nb;
       const int mma_n = p.dual_b ? 2 * t.nw : t.nw;
-      const uint32_t idesc = ptx::make_idesc_bf16(BM, mma_n, p.a_mn_major, p.b_mn_major);
+      const uint32_t idesc = ptx::make_idesc_bf16(CF::TILE_M, mma_n, p.a_mn_major, p.b_mn_major);
       const uint32_t d_tmem = tmem_base + (uint32_t)(acc * ACC_COLS);
-      bool ok = ptx::mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, p.status, ST_MMA_TIMEOUT);
-      if (!__all_sync(0xffffffffu, ok)) goto teardown;
-      ptx::tc_fence_after();
-      for (int ks = 0; ks < ksteps; ks++) {
-        ok = ptx::mbar_wait(full_bar(stage), phase, abort_flag, p.status, ST_MMA_TIMEOUT);
+      bool ok = true;
+      if (leader) {
+        ok = xwait(tempty_bar(acc), acc_phase ^ 1u, ST_MMA_TIMEOUT);
         if (!__all_sync(0xffffffffu, ok)) goto teardown;
         ptx::tc_fence_after();
-        unsigned char *stA = smem + stage * STAGE_BYTES;
-        const uint32_t sA = smem_base + stage * STAGE_BYTES;
-        const uint32_t sB = sA + A_BLKS * BLK_BYTES;
-        if (p.group_mode == GROUPED_K) {
-          const int kv = t.k_len - (ks % ksteps_seg) * BK;  // valid reduction rows in this slab
-          if (kv < BK) {
-            // rows kv..63 of every 64x64 block belong to the next expert (or lie past the end):
-            // clear them in both operands. A row is 128 contiguous bytes in the swizzled layout.
-            const int chunks_per_blk = (BK - kv) * 8;
-            const int nb_all = A_BLKS + nblk;
-            for (int i = lane; i < nb_all * chunks_per_blk; i += 32) {
-              const int b = i / chunks_per_blk, c = i - b * chunks_per_blk;
-              *reinterpret_cast<uint4 *>(stA + b * BLK_BYTES + kv * 128 + c * 16) = make_uint4(0, 0, 0, 0);
-            }
-            ptx::fence_proxy_async_smem();
-            __syncwarp();
+      }
+      for (int ks = 0; ks < ksteps; ks++) {
+        // every CTA watches its own slab land ...
+        ok = wait_local(full_bar(stage), phase, ST_MMA_TIMEOUT);
+        if (!__all_sync(0xffffffffu, ok)) goto teardown;
+        const int kv = (p.group_mode == GROUPED_K) ? t.k_len - (ks % ksteps_seg) * BK : BK;  // valid reduction rows
+        if (kv < BK) {
+          // rows kv..63 of every 64x64 block belong to the next expert (or lie past the end):
+          // clear them in both operands. A row is 128 contiguous bytes in the swizzled layout.
+          unsigned char *stA = smem + stage * STAGE_BYTES;
+          const int chunks_per_blk = (BK - kv) * 8;
+          const int nb_all = A_BLKS + nb_loaded;
+          for (int i = lane; i < nb_all * chunks_per_blk; i += 32) {
+            const int b = i / chunks_per_blk, c = i - b * chunks_per_blk;
+            *reinterpret_cast<uint4 *>(stA + b * BLK_BYTES + kv * 128 + c * 16) = make_uint4(0, 0, 0, 0);
           }
+          ptx::fence_proxy_async_smem();
+          __syncwarp();
         }
-        if (lane == 0) {
-#pragma unroll
-          for (int k16 = 0; k16 < BK / 16; k16++) {
-            const uint64_t adesc = p.a_mn_major ? ptx::make_smem_desc(sA + k16 * 2048, BLK_BYTES, 1024)
-                                                : ptx::make_smem_desc(sA + k16 * 32, 0, 1024);
-            const uint64_t bdesc = p.b_mn_major ? ptx::make_smem_desc(sB + k16 * 2048, BLK_BYTES, 1024)
-                                                : ptx::make_smem_desc(sB + k16 * 32, 0, 1024);
-            ptx::umma_bf16(d_tmem, adesc, bdesc, idesc, (ks > 0 || k16 > 0) ? 1u : 0u);
+        if (PAIR && !leader) {
+          // ... the odd CTA then tells the even one that its half is in place
+          if (lane == 0) ptx::mbar_arrive_remote(peer_bar(stage), 0);
+        } else {
+          if (PAIR) {
+            ok = xwait(peer_bar(stage), phase, ST_PEER_TIMEOUT);
+            if (!__all_sync(0xffffffffu, ok)) goto teardown;
           }
-          ptx::umma_commit(empty_bar(stage));
+          ptx::tc_fence_after();
+          if (lane == 0) {
+            const uint32_t sA = smem_base + stage * STAGE_BYTES;
+            const uint32_t sB = sA + A_BLKS * BLK_BYTES;
+#pragma unroll
+            for (int k16 = 0; k16 < BK / 16; k16++) {
+              const uint64_t adesc = p.a_mn_major ? ptx::make_smem_desc(sA + k16 * 2048, BLK_BYTES, 1024)
+                                                  : ptx::make_smem_desc(sA + k16 * 32, 0, 1024);
+              const uint64_t bdesc = p.b_mn_major ? ptx::make_smem_desc(sB + k16 * 2048, BLK_BYTES, 1024)
+                                                  : ptx::make_smem_desc(sB + k16 * 32, 0, 1024);
+              const uint32_t accum = (ks > 0 || k16 > 0) ? 1u : 0u;
+              if (PAIR) ptx::umma_bf16_pair(d_tmem, adesc, bdesc, idesc, accum);
+              else ptx::umma_bf16(d_tmem, adesc, bdesc, idesc, accum);
+            }
+            if (PAIR) ptx::umma_commit_pair(empty_bar(stage));
+            else ptx::umma_commit(empty_bar(stage));
+          }
         }
         __syncwarp();
         if (++stage == STAGES) {
@@ -315,7 +383,10 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
           phase ^= 1u;
         }
       }
-      if (lane == 0) ptx::umma_commit(tfull_bar(acc));
+      if (leader && lane == 0) {
+        if (PAIR) ptx::umma_commit_pair(tfull_bar(acc));
+        else ptx::umma_commit(tfull_bar(acc));
+      }
       __syncwarp();
       if (++acc == 2) {
         acc = 0;
@@ -323,55 +394,73 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
       }
     }
   } else {
-    // ================= epilogue (warps 2..5) =================
-    const int quarter = warp & 3;  // TMEM lanes this warp may read: [32*quarter, 32*quarter+32)
+    // ================= epilogue (warps 2..9) =================
+    // TMEM lanes a warp may read are fixed by warp_id % 4; two warps share a lane quarter and split the columns.
+    const int quarter = warp & 3;
+    const int chalf = (warp - 2) >> 2;
     int acc = 0;
     uint32_t acc_phase = 0;
-    for (int tile = blockIdx.x; sched.get(tile, t); tile += gridDim.x) {
+    for (int tile = first_tile; sched.get(tile, t); tile += tile_step) {
       if (t.k_len == 0) continue;
-      bool ok = ptx::mbar_wait(tfull_bar(acc), acc_phase, abort_flag, p.status, ST_EPILOGUE_TIMEOUT);
-      if (!__all_sync(0xffffffffu, ok)) goto teardown;
-      ptx::tc_fence_after();
-      const int row_in_tile = quarter * 32 + lane;
-      const bool row_ok = row_in_tile < t.m_valid;
-      const int64_t orow = (int64_t)t.out_row0 + row_in_tile;
+      const int row_in_cta = quarter * 32 + lane;
+      const bool row_ok = row_in_cta + row_off < t.m_valid;
+      const int64_t orow = (int64_t)t.out_row0 + row_off + row_in_cta;
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * ACC_COLS);
+      // t.nw is the logical width (per part when the accumulator holds x1 | x3); each warp takes half of it
+      const int cbeg = chalf * (t.nw >> 1), cend = cbeg + (t.nw >> 1);
 
       if (EPI == EPI_STORE) {
         const int64_t goff = (p.group_mode == GROUPED_K) ? (int64_t)t.group * p.d_group_stride : 0;
         const int64_t base = goff + orow * p.ldd + t.n0;
         const bool use_c = (p.C != nullptr) && (p.beta != 0.0f);
-        for (int c0 = 0; c0 < t.nw; c0 += 32) {
-          uint32_t r[32];
-          ptx::tmem_ld32(taddr + c0, r);
-          ptx::tmem_ld_wait();
-          if (row_ok) {
+        // the bf16 C segment of this thread (up to 128 columns) is fetched before waiting on the MMAs
+        uint4 cpre[16];
+        if (use_c && !p.c_fp32) {
 #pragma unroll
-            for (int v = 0; v < 4; v++) {
-              const int col = c0 + v * 8;
-              if (col < t.n_valid) {
-                float f[8];
+          for (int v = 0; v < 16; v++) {
+            const int col = cbeg + v * 8;
+            if (row_ok && col < cend && col < t.n_valid)
+              cpre[v] = *reinterpret_cast<const uint4 *>(static_cast<const __nv_bfloat16 *>(p.C) + base + col);
+          }
+        }
+        bool ok = xwait(tfull_bar(acc), acc_phase, ST_EPILOGUE_TIMEOUT);
+        if (!__all_sync(0xffffffffu, ok)) goto teardown;
+        ptx::tc_fence_after();
 #pragma unroll
-                for (int q = 0; q < 8; q++) f[q] = p.alpha * __uint_as_float(r[v * 8 + q]);
-                if (use_c) {
-                  if (p.c_fp32) {
-                    const float4 *cp = reinterpret_cast<const float4 *>(static_cast<const float *>(p.C) + base + col);
-                    const float4 c_lo = cp[0], c_hi = cp[1];
-                    f[0] += p.beta * c_lo.x; f[1] += p.beta * c_lo.y; f[2] += p.beta * c_lo.z; f[3] += p.beta * c_lo.w;
-                    f[4] += p.beta * c_hi.x; f[5] += p.beta * c_hi.y; f[6] += p.beta * c_hi.z; f[7] += p.beta * c_hi.w;
-                  } else {
-                    float cf[8];
-                    unpack8(*reinterpret_cast<const uint4 *>(static_cast<const __nv_bfloat16 *>(p.C) + base + col), cf);
+        for (int ci = 0; ci < 4; ci++) {
+          const int c0 = cbeg + ci * 32;
+          if (c0 < cend) {
+            uint32_t r[32];
+            ptx::tmem_ld32(taddr + c0, r);
+            ptx::tmem_ld_wait();
+            if (row_ok) {
 #pragma unroll
-                    for (int q = 0; q < 8; q++) f[q] += p.beta * cf[q];
+              for (int v = 0; v < 4; v++) {
+                const int col = c0 + v * 8;
+                if (col < t.n_valid) {
+                  float f[8];
+#pragma unroll
+                  for (int q = 0; q < 8; q++) f[q] = p.alpha * __uint_as_float(r[v * 8 + q]);
+                  if (use_c) {
+                    if (p.c_fp32) {
+                      const float4 *cp = reinterpret_cast<const float4 *>(static_cast<const float *>(p.C) + base + col);
+                      const float4 c_lo = cp[0], c_hi = cp[1];
+                      f[0] += p.beta * c_lo.x; f[1] += p.beta * c_lo.y; f[2] += p.beta * c_lo.z; f[3] += p.beta * c_lo.w;
+                      f[4] += p.beta * c_hi.x; f[5] += p.beta * c_hi.y; f[6] += p.beta * c_hi.z; f[7] += p.beta * c_hi.w;
+                    } else {
+                      float cf[8];
+                      unpack8(cpre[ci * 4 + v], cf);
+#pragma unroll
+                      for (int q = 0; q < 8; q++) f[q] += p.beta * cf[q];
+                    }
                   }
-                }
-                if (p.out_fp32) {
-                  float4 *dp = reinterpret_cast<float4 *>(static_cast<float *>(p.D) + base + col);
-                  dp[0] = make_float4(f[0], f[1], f[2], f[3]);
-                  dp[1] = make_float4(f[4], f[5], f[6], f[7]);
-                } else {
-                  *reinterpret_cast<uint4 *>(static_cast<__nv_bfloat16 *>(p.D) + base + col) = pack8(f);
+                  if (p.out_fp32) {
+                    float4 *dp = reinterpret_cast<float4 *>(static_cast<float *>(p.D) + base + col);
+                    dp[0] = make_float4(f[0], f[1], f[2], f[3]);
+                    dp[1] = make_float4(f[4], f[5], f[6], f[7]);
+                  } else {
+                    *reinterpret_cast<uint4 *>(static_cast<__nv_bfloat16 *>(p.D) + base + col) = pack8(f);
+                  }
                 }
               }
             }
@@ -379,8 +468,11 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
         }
       } else if (EPI == EPI_SWIGLU_FWD) {
         // accumulator columns [0, nw) = x1 tile, [nw, 2 nw) = x3 tile
+        bool ok = xwait(tfull_bar(acc), acc_phase, ST_EPILOGUE_TIMEOUT);
+        if (!__all_sync(0xffffffffu, ok)) goto teardown;
+        ptx::tc_fence_after();
         const int64_t base = orow * (int64_t)p.N + t.n0;
-        for (int c0 = 0; c0 < t.nw; c0 += 32) {
+        for (int c0 = cbeg; c0 < cend; c0 += 32) {
           uint32_t r1[32], r3[32];
           ptx::tmem_ld32(taddr + c0, r1);
           ptx::tmem_ld32(taddr + t.nw + c0, r3);
@@ -407,8 +499,23 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
       } else {
         // EPI_SWIGLU_BWD: accumulator = dh = (w * dOut) W2 for this row
         const int64_t base = orow * (int64_t)p.N + t.n0;
+        // x1 / x3 of the first 32 columns are requested before waiting on the MMAs
+        bool ok = xwait(tfull_bar(acc), acc_phase, ST_EPILOGUE_TIMEOUT);
+        if (!__all_sync(0xffffffffu, ok)) goto teardown;
+        ptx::tc_fence_after();
         float dp_part = 0.f;
-        for (int c0 = 0; c0 < t.nw; c0 += 32) {
+        for (int c0 = cbeg; c0 < cend; c0 += 32) {
+          uint4 xa[4], xb[4];
+          if (row_ok) {
+#pragma unroll
+            for (int v = 0; v < 4; v++) {
+              const int col = c0 + v * 8;
+              if (col < t.n_valid) {
+                xa[v] = *reinterpret_cast<const uint4 *>(static_cast<const __nv_bfloat16 *>(p.x1_in) + base + col);
+                xb[v] = *reinterpret_cast<const uint4 *>(static_cast<const __nv_bfloat16 *>(p.x3_in) + base + col);
+              }
+            }
+          }
           uint32_t r[32];
           ptx::tmem_ld32(taddr + c0, r);
           ptx::tmem_ld_wait();
@@ -418,8 +525,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
               const int col = c0 + v * 8;
               if (col < t.n_valid) {
                 float a[8], b[8], o1[8], o3[8], hv[8];
-                unpack8(*reinterpret_cast<const uint4 *>(static_cast<const __nv_bfloat16 *>(p.x1_in) + base + col), a);
-                unpack8(*reinterpret_cast<const uint4 *>(static_cast<const __nv_bfloat16 *>(p.x3_in) + base + col), b);
+                unpack8(xa[v], a);
+                unpack8(xb[v], b);
 #pragma unroll
                 for (int q = 0; q < 8; q++) {
                   const float acc_dh = __uint_as_float(r[v * 8 + q]);
@@ -447,7 +554,10 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
 
       ptx::tc_fence_before();
       __syncwarp();
-      if (lane == 0) ptx::mbar_arrive(tempty_bar(acc));
+      if (lane == 0) {
+        if (PAIR && !leader) ptx::mbar_arrive_remote(tempty_bar(acc), 0);
+        else ptx::mbar_arrive(tempty_bar(acc));
+      }
       if (++acc == 2) {
         acc = 0;
         acc_phase ^= 1u;
@@ -463,14 +573,18 @@ teardown:
   }
   ptx::tc_fence_before();
   __syncthreads();
+  if (PAIR) ptx::cluster_sync_all();  // neither CTA leaves while the other may still reach into it
   if (warp == 1) {
     ptx::tc_fence_after();
-    ptx::tmem_dealloc(tmem_base, TMEM_COLS);
+    if (PAIR) ptx::tmem_dealloc_pair(tmem_base, TMEM_COLS);
+    else ptx::tmem_dealloc(tmem_base, TMEM_COLS);
   }
 }
 
-constexpr size_t GEMM_SMEM_BYTES =
-    1024 + (size_t)STAGES * STAGE_BYTES + (2 * STAGES + 4) * 8 + 16 + sizeof(int) * (3 * MAX_GROUPS + 1);
+template <bool PAIR>
+constexpr size_t gemm_smem_bytes() {
+  return 1024 + (size_t)Cfg<PAIR>::STAGES * Cfg<PAIR>::STAGE_BYTES + sizeof(GemmSmemTail);
+}
 
 // ---------------------------------------------------------------------------------------
 // host side
@@ -528,22 +642,78 @@ static int *status_ptr() {
   return ptr;
 }
 
-template <int EPI>
-static int launch_gemm(GemmParams &p, int64_t max_tiles, cudaStream_t s) {
-  p.status = status_ptr();
-  B200_REQUIRE(p.status != nullptr, "gemm: status word unavailable");
-  auto kern = gemm_sm100_kernel<EPI>;
+// 0 = one CTA per tile (cta_group::1), 1 = CTA pairs (cta_group::2) wherever a launch allows it.
+// Initialised from the environment variable B200_GEMM_PAIR on first use; b200_gemm_set_pair_mode overrides it.
+static int g_pair_mode = -1;
+
+static int pair_mode() {
+  if (g_pair_mode < 0) {
+    const char *e = getenv("B200_GEMM_PAIR");
+    g_pair_mode = (e && e[0] == '0') ? 0 : 1;
+  }
+  return g_pair_mode;
+}
+
+template <int EPI, bool PAIR>
+static int launch_gemm_variant(GemmParams &p, int64_t max_tiles, cudaStream_t s) {
+  auto kern = gemm_sm100_kernel<EPI, PAIR>;
+  constexpr size_t smem = gemm_smem_bytes<PAIR>();
   static bool configured = false;
+  static int max_clusters = 0;
   if (!configured) {
-    B200_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GEMM_SMEM_BYTES));
+    B200_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    if (PAIR) {
+      cudaLaunchConfig_t q = {};
+      q.gridDim = dim3(2 * (unsigned)(sm_count_cached() / 2));
+      q.blockDim = dim3(GEMM_THREADS);
+      q.dynamicSmemBytes = smem;
+      cudaLaunchAttribute a[1];
+      a[0].id = cudaLaunchAttributeClusterDimension;
+      a[0].val.clusterDim.x = 2;
+      a[0].val.clusterDim.y = 1;
+      a[0].val.clusterDim.z = 1;
+      q.attrs = a;
+      q.numAttrs = 1;
+      if (cudaOccupancyMaxActiveClusters(&max_clusters, kern, &q) != cudaSuccess || max_clusters <= 0) {
+        cudaGetLastError();
+        max_clusters = sm_count_cached() / 2;
+      }
+    }
     configured = true;
   }
-  int64_t grid = sm_count_cached();
-  if (max_tiles < grid) grid = max_tiles;
-  if (grid < 1) return 0;
-  kern<<<(unsigned)grid, GEMM_THREADS, GEMM_SMEM_BYTES, s>>>(p);
-  B200_CHECK_LAUNCH("gemm_sm100");
+  if (max_tiles < 1) return 0;
+  if (!PAIR) {
+    int64_t grid = sm_count_cached();
+    if (max_tiles < grid) grid = max_tiles;
+    kern<<<(unsigned)grid, GEMM_THREADS, smem, s>>>(p);
+    B200_CHECK_LAUNCH("gemm_sm100");
+    return 0;
+  }
+  int64_t pairs = max_clusters;
+  if (max_tiles < pairs) pairs = max_tiles;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(2 * pairs));
+  cfg.blockDim = dim3(GEMM_THREADS);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  B200_CUDA(cudaLaunchKernelEx(&cfg, kern, p));
   return 0;
+}
+
+// max_tiles: an upper bound on the number of 128-row tiles (pair tiles are never more numerous).
+template <int EPI>
+static int launch_gemm(GemmParams &p, int64_t max_tiles, cudaStream_t s, bool pair_ok = true) {
+  p.status = status_ptr();
+  B200_REQUIRE(p.status != nullptr, "gemm: status word unavailable");
+  if (pair_ok && pair_mode()) return launch_gemm_variant<EPI, true>(p, max_tiles, s);
+  return launch_gemm_variant<EPI, false>(p, max_tiles, s);
 }
 
 static void zero_params(GemmParams &p) { memset(&p, 0, sizeof(p)); }
@@ -551,6 +721,11 @@ static void zero_params(GemmParams &p) { memset(&p, 0, sizeof(p)); }
 }  // namespace b200
 
 using namespace b200;
+
+extern "C" int b200_gemm_set_pair_mode(int on) {
+  g_pair_mode = on ? 1 : 0;
+  return 0;
+}
 
 // Reads (and clears) the status word the GEMM kernels raise when a bounded wait runs out.
 // Synchronises the device. 0 = no kernel has given up since the last call.
@@ -614,7 +789,8 @@ extern "C" int b200_matmul(int a_dt, int b_dt, int c_dt, int d_dt, int to_trans_
   p.tmA2 = p.tmA;
   p.tmB2 = p.tmB;
   const int64_t tiles = (int64_t)((N + BM - 1) / BM) * ((M + 255) / 256);
-  return launch_gemm<EPI_STORE>(p, tiles, (cudaStream_t)stream);
+  // a 256-row pair tile only pays off when there are at least 256 output rows
+  return launch_gemm<EPI_STORE>(p, tiles, (cudaStream_t)stream, /*pair_ok=*/N >= 256);
 }
 
 static int check_grouped(const char *op, int total_rows, int model_dim, int ffn_dim, int num_experts,

@@ -57,6 +57,11 @@ def gemm_status():
     return st.value
 
 
+def gemm_set_pair_mode(on):
+    """1: CTA pairs (cta_group::2, 256-row tiles); 0: single-CTA 128-row tiles."""
+    _check(_lib.load().b200_gemm_set_pair_mode(int(bool(on))), "b200_gemm_set_pair_mode", 0)
+
+
 def select_experts(total_tokens, n_experts, top_k_experts, X_routed, token_expert_weights, chosen_experts,
                    expert_counts, expert_counts_cumsum, host_expert_counts=None):
     _check(_lib.load().b200_select_experts(_dt(X_routed), total_tokens, n_experts, top_k_experts, _p(X_routed),

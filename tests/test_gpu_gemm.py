@@ -13,6 +13,19 @@ from helpers import assert_close, assert_close_with_slack, bf16_bits_to_f32
 pytestmark = pytest.mark.gpu
 
 
+@pytest.fixture(params=["pair", "single"], autouse=True)
+def gemm_tile_mode(request):
+    """Every test runs with CTA-pair tiles (cta_group::2, the default) and with single-CTA tiles."""
+    if torch.cuda.is_available():
+        from ml_dataflow_b200 import ops
+
+        ops.gemm_set_pair_mode(request.param == "pair")
+        yield request.param
+        ops.gemm_set_pair_mode(True)
+    else:
+        yield request.param
+
+
 def gemm_ok(ops):
     st = ops.gemm_status()
     assert st == 0, f"a GEMM kernel gave up waiting (status {st})"

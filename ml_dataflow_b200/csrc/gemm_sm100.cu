@@ -254,54 +254,56 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
   Tile t;
   if (warp == 0) {
     // ================= TMA producer (every CTA loads its own boxes) =================
+    // issue the loads of one slab into (sA, sB), counted on `bar`
+    auto slab = [&](const Tile &tt, int ks, uint32_t sA, uint32_t sB, uint32_t bar) {
+      const int ksteps_seg = (tt.k_len + BK - 1) / BK;
+      const int seg = ks / ksteps_seg;
+      const int kk = (ks - seg * ksteps_seg) * BK;
+      const CUtensorMap *mA = seg ? &p.tmA2 : &p.tmA;
+      const CUtensorMap *mB = seg ? &p.tmB2 : &p.tmB;
+      // 64-column boxes of B this CTA fetches per slab, and where they start
+      const int nb = p.dual_b ? (tt.nw >> 6) : (PAIR ? (tt.nw >> 7) : (tt.nw >> 6));
+      const int n_start = tt.n0 + ((PAIR && !p.dual_b) ? (int)cta_rank * (tt.nw >> 1) : 0);
+      const int a_row = tt.a_row0 + row_off;
+      const int g3 = (p.group_mode == GROUPED_M) ? tt.group : 0;
+      auto ld2 = [&](uint32_t dst, const CUtensorMap *m, int c0, int c1) { ptx::tma_load_2d(dst, m, bar, c0, c1); };
+      auto ld3 = [&](uint32_t dst, const CUtensorMap *m, int c0, int c1, int c2) {
+        ptx::tma_load_3d(dst, m, bar, c0, c1, c2);
+      };
+      const int nb_loaded = (p.dual_b && !PAIR) ? 2 * nb : nb;
+      ptx::mbar_arrive_expect_tx(bar, (uint32_t)((A_BLKS + nb_loaded) * BLK_BYTES));
+      if (!p.a_mn_major) {
+        ld2(sA, mA, kk, a_row);
+        ld2(sA + BLK_BYTES, mA, kk, a_row + 64);
+      } else {
+        ld2(sA, mA, a_row, tt.k_row0 + kk);
+        ld2(sA + BLK_BYTES, mA, a_row + 64, tt.k_row0 + kk);
+      }
+      if (p.dual_b) {
+        if (PAIR) {  // even CTA holds the W1 columns, odd CTA the W3 columns
+          const CUtensorMap *mine = cta_rank ? &p.tmB2 : &p.tmB;
+          for (int i = 0; i < nb; i++) ld3(sB + i * BLK_BYTES, mine, kk, tt.n0 + 64 * i, g3);
+        } else {
+          for (int i = 0; i < nb; i++) ld3(sB + i * BLK_BYTES, &p.tmB, kk, tt.n0 + 64 * i, g3);
+          for (int i = 0; i < nb; i++) ld3(sB + (nb + i) * BLK_BYTES, &p.tmB2, kk, tt.n0 + 64 * i, g3);
+        }
+      } else if (!p.b_mn_major) {
+        for (int i = 0; i < nb; i++) ld3(sB + i * BLK_BYTES, mB, kk, n_start + 64 * i, g3);
+      } else {
+        for (int i = 0; i < nb; i++) ld3(sB + i * BLK_BYTES, mB, n_start + 64 * i, tt.k_row0 + kk, g3);
+      }
+    };
     int stage = 0;
     uint32_t phase = 0;
     for (int tile = first_tile; sched.get(tile, t); tile += tile_step) {
-      const int ksteps_seg = (t.k_len + BK - 1) / BK;
-      const int ksteps = ksteps_seg * p.k_segments;
-      // 64-column boxes of B this CTA fetches per slab, and where they start
-      const int nb = p.dual_b ? (t.nw >> 6) : (PAIR ? (t.nw >> 7) : (t.nw >> 6));
-      const int n_start = t.n0 + ((PAIR && !p.dual_b) ? (int)cta_rank * (t.nw >> 1) : 0);
-      const int nb_loaded = (p.dual_b && !PAIR) ? 2 * nb : nb;
-      const int a_row = t.a_row0 + row_off;
+      const int ksteps = ((t.k_len + BK - 1) / BK) * p.k_segments;
       for (int ks = 0; ks < ksteps; ks++) {
         bool ok = true;
         if (lane == 0) {
           ok = xwait(empty_bar(stage), phase ^ 1u, ST_PRODUCER_TIMEOUT);
           if (ok) {
-            const int seg = ks / ksteps_seg;
-            const int kk = (ks - seg * ksteps_seg) * BK;
-            const CUtensorMap *mA = seg ? &p.tmA2 : &p.tmA;
-            const CUtensorMap *mB = seg ? &p.tmB2 : &p.tmB;
             const uint32_t sA = smem_base + stage * STAGE_BYTES;
-            const uint32_t sB = sA + A_BLKS * BLK_BYTES;
-            const uint32_t bar = full_bar(stage);
-            ptx::mbar_arrive_expect_tx(bar, (uint32_t)((A_BLKS + nb_loaded) * BLK_BYTES));
-            auto ld2 = [&](uint32_t dst, const CUtensorMap *m, int c0, int c1) { ptx::tma_load_2d(dst, m, bar, c0, c1); };
-            auto ld3 = [&](uint32_t dst, const CUtensorMap *m, int c0, int c1, int c2) {
-              ptx::tma_load_3d(dst, m, bar, c0, c1, c2);
-            };
-            if (!p.a_mn_major) {
-              ld2(sA, mA, kk, a_row);
-              ld2(sA + BLK_BYTES, mA, kk, a_row + 64);
-            } else {
-              ld2(sA, mA, a_row, t.k_row0 + kk);
-              ld2(sA + BLK_BYTES, mA, a_row + 64, t.k_row0 + kk);
-            }
-            const int g3 = (p.group_mode == GROUPED_M) ? t.group : 0;
-            if (p.dual_b) {
-              if (PAIR) {  // even CTA holds the W1 columns, odd CTA the W3 columns
-                const CUtensorMap *mine = cta_rank ? &p.tmB2 : &p.tmB;
-                for (int i = 0; i < nb; i++) ld3(sB + i * BLK_BYTES, mine, kk, t.n0 + 64 * i, g3);
-              } else {
-                for (int i = 0; i < nb; i++) ld3(sB + i * BLK_BYTES, &p.tmB, kk, t.n0 + 64 * i, g3);
-                for (int i = 0; i < nb; i++) ld3(sB + (nb + i) * BLK_BYTES, &p.tmB2, kk, t.n0 + 64 * i, g3);
-              }
-            } else if (!p.b_mn_major) {
-              for (int i = 0; i < nb; i++) ld3(sB + i * BLK_BYTES, mB, kk, n_start + 64 * i, g3);
-            } else {
-              for (int i = 0; i < nb; i++) ld3(sB + i * BLK_BYTES, mB, n_start + 64 * i, t.k_row0 + kk, g3);
-            }
+            slab(t, ks, sA, sA + A_BLKS * BLK_BYTES, full_bar(stage));
           }
         }
         ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;

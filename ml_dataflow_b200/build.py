@@ -38,5 +38,33 @@ def build(force=False, verbose=False):
     return LIB_PATH
 
 
+ADAPTER_SRC = os.path.join(HERE, "backends", "nvidia", "b200_dataflow_ops.c")
+ADAPTER_PATH = os.path.join(LIB_DIR, "libb200moe_dataflow.so")
+
+
+def build_adapter(reference_root=None, force=False):
+    """Builds the external-op adapter (C) against the reference's headers in place. Needs the reference tree.
+
+    Returns the path of the .so, or None when the reference tree is not present on this machine.
+    """
+    reference_root = reference_root or os.environ.get("REFERENCE_ROOT", "/root/reference")
+    if not os.path.isdir(os.path.join(reference_root, "libdataflowops", "include")):
+        return ADAPTER_PATH if os.path.exists(ADAPTER_PATH) else None
+    build(force=False)
+    if not force and os.path.exists(ADAPTER_PATH) and os.path.getmtime(ADAPTER_PATH) >= max(
+            os.path.getmtime(ADAPTER_SRC), os.path.getmtime(LIB_PATH)):
+        return ADAPTER_PATH
+    inc = [os.path.join(reference_root, p) for p in ("libdataflow/include", "libdataflowops/include",
+                                                     "backends/nvidia/include")]
+    inc += [os.path.join(os.path.dirname(HERE), "include"), "/usr/local/cuda/include"]
+    if not os.path.exists("/usr/include/numa.h"):
+        inc.append(os.path.join(HERE, "backends", "nvidia", "compat"))
+    cmd = [os.environ.get("HOST_CC", "/usr/bin/gcc"), "-O2", "-fPIC", "-shared", "-w"] + ["-I" + i for i in inc]
+    cmd += ["-o", ADAPTER_PATH, ADAPTER_SRC, "-L" + LIB_DIR, "-lb200moe", "-Wl,-rpath,$ORIGIN"]
+    subprocess.check_call(cmd)
+    return ADAPTER_PATH
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    print(build_adapter(force="--force" in sys.argv))

@@ -25,7 +25,8 @@ def build(force=False):
     ):
         subprocess.check_call(["make", "-C", _HERE, "liboracle.so"], stdout=subprocess.DEVNULL)
     if os.path.isdir(os.environ.get("REFERENCE_ROOT", "/root/reference")):
-        subprocess.call(["make", "-C", _HERE, "ref"], stdout=subprocess.DEVNULL)
+        # the reference's own kernels (cubins) and host submitters, compiled from its sources in place
+        subprocess.call(["make", "-C", _HERE, "ref", "dropin"], stdout=subprocess.DEVNULL)
 
 
 _lib = None

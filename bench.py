@@ -172,6 +172,10 @@ def algorithmic_work(cfg):
     }
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum of the seven expert GEMM launches of one step, from one ncu pass on the
+# full-size 1-GPU workload (profiles/gemm_sm100_kernel__moe_layer_T8192_d4096_E64_k8_f1408.md, section 2)
+NCU_GEMM_DRAM_BYTES_PER_STEP = {(8192, 4096, 64, 8, 1408): 16.3e9}
+
 NVLINK_PEER_GBS = 770.0  # measured peer copy per direction on this pool (nominal 900)
 
 
@@ -376,7 +380,9 @@ def run_gpu_arm(args, world):
                     bound="tensor", achieved=round(ach, 1), peak=peaks["bf16_tflops_sustained"], unit="TFLOP/s",
                     frac=round(ach / peaks["bf16_tflops_sustained"], 4),
                     frac_of_burst_peak=round(ach / peaks["bf16_tflops"], 4), peak_source=peaks["source"] +
-                    " (sustained cuBLAS bf16, the kernel is timed inside a long step)", traffic=None,
+                    " (sustained cuBLAS bf16, the kernel is timed inside a long step)",
+                    traffic=NCU_GEMM_DRAM_BYTES_PER_STEP.get((T, d, E, k, f)) if world == 1 else None,
+                    traffic_unit="bytes per step over the 7 launches (ncu, one pass)", algorithmic_flop=gemm_flops,
                     ms_per_step_in_kernel=round(gemm_ms, 4))
 
     if rank != 0:

@@ -73,6 +73,7 @@ struct GemmParams {
   void *dx1, *dx3, *hs;
   float *dP;
   int *status;
+  int wide;  // every bf16 row the epilogue touches is 32-byte aligned: use 256-bit global accesses
 };
 
 struct Tile {
@@ -251,6 +252,24 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
   auto wait_local = [&](uint32_t bar, uint32_t par, int code) -> bool {
     return ptx::mbar_wait<false>(bar, par, abort_flag, p.status, code);
   };
+  // 16 bf16 columns of a row at `ptr` (n_left valid columns remain, a multiple of 8): one 32-byte access when
+  // the launch allows it, else one or two 16-byte accesses
+  auto ld16 = [&](const __nv_bfloat16 *ptr, int n_left, uint4 &lo, uint4 &hi) {
+    if (p.wide && n_left >= 16) {
+      ld_global_256(ptr, lo, hi);
+    } else {
+      lo = *reinterpret_cast<const uint4 *>(ptr);
+      if (n_left > 8) hi = *reinterpret_cast<const uint4 *>(ptr + 8);
+    }
+  };
+  auto st16 = [&](__nv_bfloat16 *ptr, int n_left, const uint4 &lo, const uint4 &hi) {
+    if (p.wide && n_left >= 16) {
+      st_global_256(ptr, lo, hi);
+    } else {
+      *reinterpret_cast<uint4 *>(ptr) = lo;
+      if (n_left > 8) *reinterpret_cast<uint4 *>(ptr + 8) = hi;
+    }
+  };
   Tile t;
   if (warp == 0) {
     // ================= TMA producer (every CTA loads its own boxes) =================
@@ -417,51 +436,57 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
         const bool use_c = (p.C != nullptr) && (p.beta != 0.0f);
         // the bf16 C segment of this thread (up to 128 columns) is fetched before waiting on the MMAs
         uint4 cpre[16];
-        if (use_c && !p.c_fp32) {
+        if (use_c && !p.c_fp32 && row_ok) {
 #pragma unroll
-          for (int v = 0; v < 16; v++) {
-            const int col = cbeg + v * 8;
-            if (row_ok && col < cend && col < t.n_valid)
-              cpre[v] = *reinterpret_cast<const uint4 *>(static_cast<const __nv_bfloat16 *>(p.C) + base + col);
+          for (int vv = 0; vv < 8; vv++) {
+            const int col = cbeg + vv * 16;
+            if (col < cend && col < t.n_valid)
+              ld16(static_cast<const __nv_bfloat16 *>(p.C) + base + col, t.n_valid - col, cpre[2 * vv], cpre[2 * vv + 1]);
           }
         }
         bool ok = xwait(tfull_bar(acc), acc_phase, ST_EPILOGUE_TIMEOUT);
         if (!__all_sync(0xffffffffu, ok)) goto teardown;
         ptx::tc_fence_after();
 #pragma unroll
-        for (int ci = 0; ci < 4; ci++) {
-          const int c0 = cbeg + ci * 32;
+        for (int ch = 0; ch < 2; ch++) {  // 64 accumulator columns per TMEM round trip
+          const int c0 = cbeg + ch * 64;
           if (c0 < cend) {
-            uint32_t r[32];
+            uint32_t r[64];
             ptx::tmem_ld32(taddr + c0, r);
+            if (c0 + 32 < cend) ptx::tmem_ld32(taddr + c0 + 32, r + 32);
             ptx::tmem_ld_wait();
             if (row_ok) {
 #pragma unroll
-              for (int v = 0; v < 4; v++) {
-                const int col = c0 + v * 8;
-                if (col < t.n_valid) {
-                  float f[8];
+              for (int vv = 0; vv < 4; vv++) {
+                const int col = c0 + vv * 16;
+                if (col < cend && col < t.n_valid) {
+                  float f[16];
 #pragma unroll
-                  for (int q = 0; q < 8; q++) f[q] = p.alpha * __uint_as_float(r[v * 8 + q]);
+                  for (int q = 0; q < 16; q++) f[q] = p.alpha * __uint_as_float(r[vv * 16 + q]);
                   if (use_c) {
                     if (p.c_fp32) {
-                      const float4 *cp = reinterpret_cast<const float4 *>(static_cast<const float *>(p.C) + base + col);
-                      const float4 c_lo = cp[0], c_hi = cp[1];
-                      f[0] += p.beta * c_lo.x; f[1] += p.beta * c_lo.y; f[2] += p.beta * c_lo.z; f[3] += p.beta * c_lo.w;
-                      f[4] += p.beta * c_hi.x; f[5] += p.beta * c_hi.y; f[6] += p.beta * c_hi.z; f[7] += p.beta * c_hi.w;
-                    } else {
-                      float cf[8];
-                      unpack8(cpre[ci * 4 + v], cf);
+                      const float *cp = static_cast<const float *>(p.C) + base + col;
 #pragma unroll
-                      for (int q = 0; q < 8; q++) f[q] += p.beta * cf[q];
+                      for (int q = 0; q < 16; q++)
+                        if (col + q < t.n_valid) f[q] += p.beta * cp[q];
+                    } else {
+                      float cf[16];
+                      unpack8(cpre[ch * 8 + 2 * vv], cf);
+                      unpack8(cpre[ch * 8 + 2 * vv + 1], cf + 8);
+#pragma unroll
+                      for (int q = 0; q < 16; q++) f[q] += p.beta * cf[q];
                     }
                   }
                   if (p.out_fp32) {
                     float4 *dp = reinterpret_cast<float4 *>(static_cast<float *>(p.D) + base + col);
                     dp[0] = make_float4(f[0], f[1], f[2], f[3]);
                     dp[1] = make_float4(f[4], f[5], f[6], f[7]);
+                    if (col + 8 < t.n_valid) {
+                      dp[2] = make_float4(f[8], f[9], f[10], f[11]);
+                      dp[3] = make_float4(f[12], f[13], f[14], f[15]);
+                    }
                   } else {
-                    *reinterpret_cast<uint4 *>(static_cast<__nv_bfloat16 *>(p.D) + base + col) = pack8(f);
+                    st16(static_cast<__nv_bfloat16 *>(p.D) + base + col, t.n_valid - col, pack8(f), pack8(f + 8));
                   }
                 }
               }
@@ -474,26 +499,32 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
         if (!__all_sync(0xffffffffu, ok)) goto teardown;
         ptx::tc_fence_after();
         const int64_t base = orow * (int64_t)p.N + t.n0;
-        for (int c0 = cbeg; c0 < cend; c0 += 32) {
-          uint32_t r1[32], r3[32];
+        for (int c0 = cbeg; c0 < cend; c0 += 64) {
+          uint32_t r1[64], r3[64];
+          const bool two = c0 + 32 < cend;
           ptx::tmem_ld32(taddr + c0, r1);
           ptx::tmem_ld32(taddr + t.nw + c0, r3);
+          if (two) {
+            ptx::tmem_ld32(taddr + c0 + 32, r1 + 32);
+            ptx::tmem_ld32(taddr + t.nw + c0 + 32, r3 + 32);
+          }
           ptx::tmem_ld_wait();
           if (row_ok) {
 #pragma unroll
-            for (int v = 0; v < 4; v++) {
-              const int col = c0 + v * 8;
-              if (col < t.n_valid) {
-                float a[8], b[8], h[8];
+            for (int vv = 0; vv < 4; vv++) {
+              const int col = c0 + vv * 16;
+              if (col < cend && col < t.n_valid) {
+                float a[16], b[16], h[16];
 #pragma unroll
-                for (int q = 0; q < 8; q++) {
-                  a[q] = bf16_round(__uint_as_float(r1[v * 8 + q]));
-                  b[q] = bf16_round(__uint_as_float(r3[v * 8 + q]));
+                for (int q = 0; q < 16; q++) {
+                  a[q] = bf16_round(__uint_as_float(r1[vv * 16 + q]));
+                  b[q] = bf16_round(__uint_as_float(r3[vv * 16 + q]));
                   h[q] = silu_f(a[q]) * b[q];
                 }
-                *reinterpret_cast<uint4 *>(static_cast<__nv_bfloat16 *>(p.x1_out) + base + col) = pack8(a);
-                *reinterpret_cast<uint4 *>(static_cast<__nv_bfloat16 *>(p.x3_out) + base + col) = pack8(b);
-                *reinterpret_cast<uint4 *>(static_cast<__nv_bfloat16 *>(p.h_out) + base + col) = pack8(h);
+                const int left = t.n_valid - col;
+                st16(static_cast<__nv_bfloat16 *>(p.x1_out) + base + col, left, pack8(a), pack8(a + 8));
+                st16(static_cast<__nv_bfloat16 *>(p.x3_out) + base + col, left, pack8(b), pack8(b + 8));
+                st16(static_cast<__nv_bfloat16 *>(p.h_out) + base + col, left, pack8(h), pack8(h + 8));
               }
             }
           }
@@ -501,48 +532,61 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
       } else {
         // EPI_SWIGLU_BWD: accumulator = dh = (w * dOut) W2 for this row
         const int64_t base = orow * (int64_t)p.N + t.n0;
-        // x1 / x3 of the first 32 columns are requested before waiting on the MMAs
+        // x1 / x3 of the first 64 columns are requested before waiting on the MMAs, those of the second 64
+        // together with the second TMEM read
+        uint4 xa[8], xb[8];
+        auto load_x = [&](int c0) {
+          if (row_ok) {
+#pragma unroll
+            for (int vv = 0; vv < 4; vv++) {
+              const int col = c0 + vv * 16;
+              if (col < cend && col < t.n_valid) {
+                ld16(static_cast<const __nv_bfloat16 *>(p.x1_in) + base + col, t.n_valid - col, xa[2 * vv], xa[2 * vv + 1]);
+                ld16(static_cast<const __nv_bfloat16 *>(p.x3_in) + base + col, t.n_valid - col, xb[2 * vv], xb[2 * vv + 1]);
+              }
+            }
+          }
+        };
+        load_x(cbeg);
         bool ok = xwait(tfull_bar(acc), acc_phase, ST_EPILOGUE_TIMEOUT);
         if (!__all_sync(0xffffffffu, ok)) goto teardown;
         ptx::tc_fence_after();
         float dp_part = 0.f;
-        for (int c0 = cbeg; c0 < cend; c0 += 32) {
-          uint4 xa[4], xb[4];
-          if (row_ok) {
 #pragma unroll
-            for (int v = 0; v < 4; v++) {
-              const int col = c0 + v * 8;
-              if (col < t.n_valid) {
-                xa[v] = *reinterpret_cast<const uint4 *>(static_cast<const __nv_bfloat16 *>(p.x1_in) + base + col);
-                xb[v] = *reinterpret_cast<const uint4 *>(static_cast<const __nv_bfloat16 *>(p.x3_in) + base + col);
-              }
-            }
-          }
-          uint32_t r[32];
-          ptx::tmem_ld32(taddr + c0, r);
-          ptx::tmem_ld_wait();
-          if (row_ok) {
+        for (int ch = 0; ch < 2; ch++) {
+          const int c0 = cbeg + ch * 64;
+          if (c0 < cend) {
+            uint32_t r[64];
+            ptx::tmem_ld32(taddr + c0, r);
+            if (c0 + 32 < cend) ptx::tmem_ld32(taddr + c0 + 32, r + 32);
+            if (ch == 1) load_x(c0);
+            ptx::tmem_ld_wait();
+            if (row_ok) {
 #pragma unroll
-            for (int v = 0; v < 4; v++) {
-              const int col = c0 + v * 8;
-              if (col < t.n_valid) {
-                float a[8], b[8], o1[8], o3[8], hv[8];
-                unpack8(xa[v], a);
-                unpack8(xb[v], b);
+              for (int vv = 0; vv < 4; vv++) {
+                const int col = c0 + vv * 16;
+                if (col < cend && col < t.n_valid) {
+                  float a[16], b[16], o1[16], o3[16], hv[16];
+                  unpack8(xa[2 * vv], a);
+                  unpack8(xa[2 * vv + 1], a + 8);
+                  unpack8(xb[2 * vv], b);
+                  unpack8(xb[2 * vv + 1], b + 8);
+                  const int left = t.n_valid - col;
 #pragma unroll
-                for (int q = 0; q < 8; q++) {
-                  const float acc_dh = __uint_as_float(r[v * 8 + q]);
-                  const float s = 1.0f / (1.0f + __expf(-a[q]));
-                  const float silu = a[q] * s;
-                  hv[q] = silu * b[q];
-                  dp_part += bf16_round(hv[q]) * acc_dh;
-                  const float dh = bf16_round(acc_dh);  // the reference stores dh as bf16 before swiglu_bwd_x
-                  o3[q] = dh * silu;
-                  o1[q] = dh * b[q] * (s + a[q] * (s * (1.0f - s)));
+                  for (int q = 0; q < 16; q++) {
+                    const float acc_dh = (q < left) ? __uint_as_float(r[vv * 16 + q]) : 0.f;
+                    const float s = 1.0f / (1.0f + __expf(-a[q]));
+                    const float silu = a[q] * s;
+                    hv[q] = silu * b[q];
+                    if (q < left) dp_part += bf16_round(hv[q]) * acc_dh;
+                    const float dh = bf16_round(acc_dh);  // the reference stores dh as bf16 before swiglu_bwd_x
+                    o3[q] = dh * silu;
+                    o1[q] = dh * b[q] * (s + a[q] * (s * (1.0f - s)));
+                  }
+                  st16(static_cast<__nv_bfloat16 *>(p.dx1) + base + col, left, pack8(o1), pack8(o1 + 8));
+                  st16(static_cast<__nv_bfloat16 *>(p.dx3) + base + col, left, pack8(o3), pack8(o3 + 8));
+                  if (p.hs) st16(static_cast<__nv_bfloat16 *>(p.hs) + base + col, left, pack8(hv), pack8(hv + 8));
                 }
-                *reinterpret_cast<uint4 *>(static_cast<__nv_bfloat16 *>(p.dx1) + base + col) = pack8(o1);
-                *reinterpret_cast<uint4 *>(static_cast<__nv_bfloat16 *>(p.dx3) + base + col) = pack8(o3);
-                if (p.hs) *reinterpret_cast<uint4 *>(static_cast<__nv_bfloat16 *>(p.hs) + base + col) = pack8(hv);
               }
             }
           }
@@ -714,6 +758,18 @@ template <int EPI>
 static int launch_gemm(GemmParams &p, int64_t max_tiles, cudaStream_t s, bool pair_ok = true) {
   p.status = status_ptr();
   B200_REQUIRE(p.status != nullptr, "gemm: status word unavailable");
+  {
+    // 256-bit epilogue accesses need every bf16 row start to be 32-byte aligned
+    auto a32 = [](const void *q) { return (reinterpret_cast<uintptr_t>(q) & 31u) == 0; };
+    bool wide;
+    if (EPI == EPI_STORE)
+      wide = !p.out_fp32 && a32(p.D) && a32(p.C) && p.ldd % 16 == 0 && p.d_group_stride % 16 == 0;
+    else if (EPI == EPI_SWIGLU_FWD)
+      wide = a32(p.x1_out) && a32(p.x3_out) && a32(p.h_out) && p.N % 16 == 0;
+    else
+      wide = a32(p.x1_in) && a32(p.x3_in) && a32(p.dx1) && a32(p.dx3) && a32(p.hs) && p.N % 16 == 0;
+    p.wide = wide ? 1 : 0;
+  }
   if (pair_ok && pair_mode()) return launch_gemm_variant<EPI, true>(p, max_tiles, s);
   return launch_gemm_variant<EPI, false>(p, max_tiles, s);
 }

@@ -227,7 +227,8 @@ def run_gpu_arm(args, world):
     else:
         from ml_dataflow_b200.ep import ExpertParallelMoELayer
 
-        layer = ExpertParallelMoELayer(T, d, E, k, f, dist, device=dev)
+        layer = ExpertParallelMoELayer(T, d, E, k, f, dist, device=dev,
+                                       transport=os.environ.get("B200_EP_TRANSPORT", "p2p"))
         E_loc = E // world
     W1, W3, W2 = normal((E_loc, f, d), 0.02), normal((E_loc, f, d), 0.02), normal((E_loc, d, f), 0.02)
     out = torch.zeros((T, d), dtype=torch.bfloat16, device=dev)

@@ -282,6 +282,41 @@ int b200_scatter_row_weights(int num_tokens, int top_k, const int *token_mapping
 int b200_gather_router_grad(int num_tokens, int num_routed_experts, int top_k, const int *token_mapping,
                             const uint16_t *chosen_experts, const float *dP, void *dX_routed, void *stream);
 
+/* ---- expert parallelism over NVLink peer memory (no counterpart in the reference, which is single-GPU) ---- */
+
+/*
+ * Rank g of `world` owns experts [g*experts_per_rank, (g+1)*experts_per_rank). peer_buffers is a HOST array of
+ * `world` device addresses: entry h is rank h's receive buffer as mapped into this process (entry of this rank =
+ * its own buffer). In an owner's buffer the rows of an expert are grouped by source rank; dst_base[e] (device,
+ * int[num_experts]) is the first row, in the owner's buffer, of this rank's rows of expert e. A routed pair (t, j)
+ * with local row r = token_mapping[t, j] of expert e = chosen_experts[t, j] lives at row
+ * dst_base[e] + r - (expert_counts_cumsum[e] - expert_counts[e]) of rank e / experts_per_rank (inclusive cumsum).
+ * The kernels use plain peer loads / stores; the caller separates the phases with a barrier across the ranks.
+ */
+
+/* prepare_experts fused with the dispatch: row (t, j) = X[t, :] (times token_expert_weights[t, j] when that pointer
+ * is not NULL) is stored straight into its owner's buffer. */
+int b200_ep_dispatch_rows(int total_tokens, int model_dim, int top_k, const void *X, const float *token_expert_weights,
+                          const int *token_mapping, const uint16_t *chosen_experts, const int *expert_counts,
+                          const int *expert_counts_cumsum, const int *dst_base,
+                          const unsigned long long *peer_buffers, int world, int num_experts, int experts_per_rank,
+                          void *stream);
+
+/* merge_experts fused with the return: X_combined[t, :] += sum_j w[t, j] * row (t, j), every row loaded from its
+ * owner's buffer; token_expert_weights == NULL means 1.0 (backward un-permute). */
+int b200_ep_combine_rows(int num_tokens, int model_dim, int top_k, const float *token_expert_weights,
+                         const int *token_mapping, const uint16_t *chosen_experts, const int *expert_counts,
+                         const int *expert_counts_cumsum, const int *dst_base, const unsigned long long *peer_buffers,
+                         int world, int num_experts, int experts_per_rank, void *X_combined, void *stream);
+
+/* dX_routed[t, chosen[t, j]] = bf16(dP[row (t, j)] / w[t, j]) with dP (fp32 per routed row, holding w * <Y, dOut> as
+ * b200_moe_experts_bwd_x leaves it when row_weights are all 1) read from the owners' buffers. dX_routed pre-zeroed. */
+int b200_ep_gather_router_grad(int num_tokens, int top_k, const float *token_expert_weights, const int *token_mapping,
+                               const uint16_t *chosen_experts, const int *expert_counts,
+                               const int *expert_counts_cumsum, const int *dst_base,
+                               const unsigned long long *peer_dP_buffers, int world, int num_experts,
+                               int experts_per_rank, void *dX_routed, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

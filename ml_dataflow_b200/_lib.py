@@ -35,6 +35,9 @@ SIGNATURES = {
                                     _vp, _vp, _vp, _vp, _vp, _vp]),
     "b200_moe_experts_bwd_w": (_i, [_i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp,
                                     _vp]),
+    "b200_ep_dispatch_rows": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
+    "b200_ep_combine_rows": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp, _vp]),
+    "b200_ep_gather_router_grad": (_i, [_i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp, _vp]),
     "b200_scatter_row_weights": (_i, [_i, _i, _vp, _vp, _vp, _vp]),
     "b200_gather_router_grad": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp]),
 }

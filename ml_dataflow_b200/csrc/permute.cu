@@ -8,20 +8,6 @@ namespace b200 {
 
 constexpr int ROW_THREADS = 128;
 
-__device__ __forceinline__ uint4 ld_stream(const uint4 *p) {
-  uint4 v;
-  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "l"(p));
-  return v;
-}
-
-__device__ __forceinline__ void st_stream(uint4 *p, const uint4 &v) {
-  asm volatile("st.global.L1::no_allocate.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z),
-               "r"(v.w)
-               : "memory");
-}
-
 // ---------------------------------------------------------------------------------------
 // prepare_experts: zone[token_mapping[t,j], :] = X[t, :]   (moe/prepare_expert_zone.cu:69-117)
 // One block per token. Each thread keeps up to VPT 16-byte pieces of the row in registers

@@ -15,6 +15,13 @@ Per layer and direction there is one exchange each way:
      unchanged with per-expert counts summed over sources.
   -> grouped expert GEMMs on the received rows -> the reverse exchange -> local weighted combine.
 
+Two transports for the rows:
+  * "p2p" (default on GPUs): the receive buffers are NVLink-mapped into every rank (torch symmetric memory gives the
+    peer addresses). The gather kernel stores each row straight into its owner's buffer and the combine kernel loads
+    each expert output row straight from its owner (csrc/ep_p2p.cu): no staging copy, no collective on the data path,
+    only a stream-ordered barrier between the phases.
+  * "nccl": rows are first gathered locally and then moved with NCCL point-to-point batches.
+
 `RowExchange` holds only the bookkeeping and the point-to-point batches (torch.distributed
 `batch_isend_irecv`: one NCCL group per exchange over NVLink; also runs on gloo for the CPU tests).
 The row counts must be known on the host to size the messages, so `plan()` reads the exchanged
@@ -64,6 +71,11 @@ class RowExchange:
         self.rows_send = int(send_cnt.sum())
         self.local_counts = per_expert.to(torch.int32).to(self.device)
         self.local_cumsum = torch.cumsum(per_expert, 0).to(torch.int32).to(self.device)
+        # first row, in the OWNER's buffer, of this rank's rows of every global expert (used by the peer-memory kernels)
+        per_owner = all_counts.sum(dim=0)                               # [h][j] rows of owner h's expert j
+        owner_base = torch.cumsum(per_owner, 1) - per_owner             # [h][j]
+        before_me = all_counts[: self.rank].sum(dim=0)                  # rows of lower source ranks
+        self.dst_base = (owner_base + before_me).reshape(-1).to(torch.int32).to(self.device)
         return self
 
     # -------------------------------------------------------------------------------- transport
@@ -100,29 +112,52 @@ class RowExchange:
 class ExpertParallelMoELayer:
     """Same call surface as `MoELayer`, with W1/W3/W2 and their gradients holding only this rank's experts."""
 
-    def __init__(self, T, d, E, k, f, dist, device="cuda", recv_capacity_factor=1.5):
+    def __init__(self, T, d, E, k, f, dist, device="cuda", recv_capacity_factor=1.5, transport="p2p"):
         self.T, self.d, self.E, self.k, self.f = T, d, E, k, f
         self.dist = dist
         self.dev = torch.device(device)
+        self.transport = transport
         self.x = RowExchange(dist, E, self.dev)
         self.E_loc = self.x.E_loc
         self.R = T * k
-        self.home = _HomeSide(T, d, E, k, self.dev)
+        self.home = _HomeSide(T, d, E, k, self.dev, staging=(transport != "p2p"))
         self.cap = int(self.R * recv_capacity_factor) + 256
         bf, f32 = torch.bfloat16, torch.float32
 
         def buf(shape, dt):
             return torch.empty(shape, dtype=dt, device=self.dev)
 
-        self.zone_r = buf((self.cap, d), bf)   # received rows (kept for backward-w)
+        self.peers = {}
+        if transport == "p2p":
+            import torch.distributed._symmetric_memory as symm_mem
+
+            def shared(name, shape, dt):
+                t = symm_mem.empty(shape, dtype=dt, device=self.dev)
+                hdl = symm_mem.rendezvous(t, dist.group.WORLD)
+                self.peers[name] = [int(p) for p in hdl.buffer_ptrs]
+                self._handles = getattr(self, "_handles", []) + [hdl]
+                return t
+        else:
+            def shared(name, shape, dt):
+                return buf(shape, dt)
+
+        # buffers other ranks write into / read from
+        self.zone_r = shared("zone", (self.cap, d), bf)   # received rows (kept for backward-w)
+        self.Y_r = shared("Y", (self.cap, d), bf)
+        self.dY_r = shared("dY", (self.cap, d), bf)
+        self.dZ_r = shared("dZ", (self.cap, d), bf)
+        self.dP_r = shared("dP", (self.cap,), f32)
+        # local only
         self.x1, self.x3, self.h = buf((self.cap, f), bf), buf((self.cap, f), bf), buf((self.cap, f), bf)
-        self.Y_r = buf((self.cap, d), bf)
-        self.dY_r = buf((self.cap, d), bf)
         self.dx1, self.dx3 = buf((self.cap, f), bf), buf((self.cap, f), bf)
-        self.dZ_r = buf((self.cap, d), bf)
         self.ones = torch.ones(self.cap, dtype=f32, device=self.dev)
-        self.dP_r = buf((self.cap,), f32)
+        self._flag = torch.zeros(1, dtype=torch.int32, device=self.dev)
         self.profile = None
+
+    def _barrier(self):
+        """Stream-ordered barrier over all ranks: everything enqueued before it on every rank has finished (and its
+        peer stores have landed) before anything enqueued after it starts."""
+        self.dist.all_reduce(self._flag)
 
     def mark(self, name):
         if self.profile is not None:
@@ -137,21 +172,34 @@ class ExpertParallelMoELayer:
         T, d, E, k, f = self.T, self.d, self.E, self.k, self.f
         self.mark("router_gemm")
         hm.route(Xn, Wr)
-        self.mark("prepare_experts")
-        ops.prepare_experts(T, d, k, Xn, hm.token_mapping, hm.zone)
+        p2p = self.transport == "p2p"
+        if not p2p:
+            self.mark("prepare_experts")
+            ops.prepare_experts(T, d, k, Xn, hm.token_mapping, hm.zone)
         self.mark("dispatch")
+        # the counts exchange also orders this step after every rank's previous step (its buffers are free again)
         x.plan(hm.counts)
         if x.rows_recv > self.cap:
             raise RuntimeError(f"expert-parallel receive buffer too small: {x.rows_recv} rows > capacity {self.cap}")
         n = x.rows_recv
-        x.dispatch(hm.zone, self.zone_r)
+        if p2p:
+            ops.ep_dispatch_rows(T, d, k, Xn, None, hm.token_mapping, hm.chosen, hm.counts, hm.cumsum, x.dst_base,
+                                 self.peers["zone"], E, self.E_loc)
+            self._barrier()
+        else:
+            x.dispatch(hm.zone, self.zone_r)
         self.mark("experts_fwd_gemm")
         ops.moe_experts_fwd(n, d, f, self.E_loc, self.zone_r, W1, W3, W2, f * d, f * d, d * f, x.local_counts,
                             x.local_cumsum, self.x1, self.x3, self.h, self.Y_r)
         self.mark("return")
-        x.combine(self.Y_r, hm.Y)
-        self.mark("merge_experts")
-        ops.merge_experts(T, d, k, hm.Y, hm.token_mapping, hm.weights, out)
+        if p2p:
+            self._barrier()
+            ops.ep_combine_rows(T, d, k, hm.weights, hm.token_mapping, hm.chosen, hm.counts, hm.cumsum, x.dst_base,
+                                self.peers["Y"], E, self.E_loc, out)
+        else:
+            x.combine(self.Y_r, hm.Y)
+            self.mark("merge_experts")
+            ops.merge_experts(T, d, k, hm.Y, hm.token_mapping, hm.weights, out)
         self.mark("fwd_end")
         return out
 
@@ -161,11 +209,18 @@ class ExpertParallelMoELayer:
         hm, x = self.home, self.x
         T, d, E, k, f = self.T, self.d, self.E, self.k, self.f
         n = x.rows_recv
-        self.mark("prepare_experts_weighted")
-        ops.prepare_experts_weighted(T, d, k, dOut, hm.token_mapping, hm.weights, hm.dYz)
-        ops.scatter_row_weights(T, k, hm.token_mapping, hm.weights, hm.row_w)
-        self.mark("dispatch_bwd")
-        x.dispatch(hm.dYz, self.dY_r)
+        p2p = self.transport == "p2p"
+        if p2p:
+            self.mark("dispatch_bwd")
+            ops.ep_dispatch_rows(T, d, k, dOut, hm.weights, hm.token_mapping, hm.chosen, hm.counts, hm.cumsum,
+                                 x.dst_base, self.peers["dY"], E, self.E_loc)
+            self._barrier()
+        else:
+            self.mark("prepare_experts_weighted")
+            ops.prepare_experts_weighted(T, d, k, dOut, hm.token_mapping, hm.weights, hm.dYz)
+            ops.scatter_row_weights(T, k, hm.token_mapping, hm.weights, hm.row_w)
+            self.mark("dispatch_bwd")
+            x.dispatch(hm.dYz, self.dY_r)
         self.mark("experts_bwd_x_gemm")
         self.dP_r[:n].zero_()
         # the gate weight of a row lives on its home rank: accumulate w*<Y,dOut> here, divide there
@@ -175,15 +230,25 @@ class ExpertParallelMoELayer:
         ops.moe_experts_bwd_w(n, d, f, self.E_loc, self.dY_r, self.h, self.zone_r, self.dx1, self.dx3, dW1, dW3, dW2,
                               f * d, f * d, d * f, x.local_counts, x.local_cumsum)
         self.mark("return_bwd")
-        x.combine(self.dZ_r, hm.dZ)
-        x.combine(self.dP_r, hm.dP)
-        self.mark("unpermute")
-        hm.dP.div_(hm.row_w)
-        dXn.zero_()
-        ops.merge_experts(T, d, k, hm.dZ, hm.token_mapping, None, dXn)
-        self.mark("router_grad")
-        hm.dX_routed.zero_()
-        ops.gather_router_grad(T, E, k, hm.token_mapping, hm.chosen, hm.dP, hm.dX_routed)
+        if p2p:
+            self._barrier()
+            dXn.zero_()
+            ops.ep_combine_rows(T, d, k, None, hm.token_mapping, hm.chosen, hm.counts, hm.cumsum, x.dst_base,
+                                self.peers["dZ"], E, self.E_loc, dXn)
+            self.mark("router_grad")
+            hm.dX_routed.zero_()
+            ops.ep_gather_router_grad(T, k, hm.weights, hm.token_mapping, hm.chosen, hm.counts, hm.cumsum, x.dst_base,
+                                      self.peers["dP"], E, self.E_loc, hm.dX_routed)
+        else:
+            x.combine(self.dZ_r, hm.dZ)
+            x.combine(self.dP_r, hm.dP)
+            self.mark("unpermute")
+            hm.dP.div_(hm.row_w)
+            dXn.zero_()
+            ops.merge_experts(T, d, k, hm.dZ, hm.token_mapping, None, dXn)
+            self.mark("router_grad")
+            hm.dX_routed.zero_()
+            ops.gather_router_grad(T, E, k, hm.token_mapping, hm.chosen, hm.dP, hm.dX_routed)
         ops.router_gate_bwd_x(T, E, k, hm.chosen, hm.weights, hm.dX_routed)
         ops.matmul(0, 0, d, E, T, 1.0, 1.0, Wr, hm.dX_routed, dXn, dXn)
         hm.dWr_local.zero_()
@@ -197,7 +262,7 @@ class ExpertParallelMoELayer:
 class _HomeSide:
     """Token-side state of one rank: routing results, the expert-ordered zone and its backward twins."""
 
-    def __init__(self, T, d, E, k, dev):
+    def __init__(self, T, d, E, k, dev, staging=True):
         from . import ops
 
         self.T, self.d, self.E, self.k = T, d, E, k
@@ -215,8 +280,9 @@ class _HomeSide:
         self.expert_mapping = buf((R,), i32)
         self.token_mapping = buf((T, k), i32)
         self.map_ws = torch.empty(ops.build_expert_mapping_workspace_bytes(T, E, k), dtype=torch.uint8, device=dev)
-        self.zone, self.Y, self.dYz, self.dZ = (buf((R, d), bf) for _ in range(4))
-        self.row_w, self.dP = buf((R,), f32), buf((R,), f32)
+        if staging:  # local copies of the routed rows, only needed when rows travel through NCCL
+            self.zone, self.Y, self.dYz, self.dZ = (buf((R, d), bf) for _ in range(4))
+            self.row_w, self.dP = buf((R,), f32), buf((R,), f32)
         self.dX_routed = buf((T, E), bf)
         self.dWr_local = buf((E, d), bf)
 

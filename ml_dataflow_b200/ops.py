@@ -181,3 +181,34 @@ def gather_router_grad(num_tokens, num_routed_experts, top_k, token_mapping, cho
     _check(_lib.load().b200_gather_router_grad(num_tokens, num_routed_experts, top_k, _p(token_mapping),
                                                _p(chosen_experts), _p(dP), _p(dX_routed), _stream()),
            "gather_router_grad")
+
+
+def _peer_array(ptrs):
+    return (C.c_ulonglong * len(ptrs))(*[int(p) for p in ptrs])
+
+
+def ep_dispatch_rows(total_tokens, model_dim, top_k, X, token_expert_weights, token_mapping, chosen_experts,
+                     expert_counts, expert_counts_cumsum, dst_base, peer_buffers, num_experts, experts_per_rank):
+    """peer_buffers: list of device addresses, one per rank (this rank's own buffer included)."""
+    _check(_lib.load().b200_ep_dispatch_rows(total_tokens, model_dim, top_k, _p(X), _p(token_expert_weights),
+                                             _p(token_mapping), _p(chosen_experts), _p(expert_counts),
+                                             _p(expert_counts_cumsum), _p(dst_base), _peer_array(peer_buffers),
+                                             len(peer_buffers), num_experts, experts_per_rank, _stream()),
+           "ep_dispatch_rows")
+
+
+def ep_combine_rows(num_tokens, model_dim, top_k, token_expert_weights, token_mapping, chosen_experts, expert_counts,
+                    expert_counts_cumsum, dst_base, peer_buffers, num_experts, experts_per_rank, X_combined):
+    _check(_lib.load().b200_ep_combine_rows(num_tokens, model_dim, top_k, _p(token_expert_weights), _p(token_mapping),
+                                            _p(chosen_experts), _p(expert_counts), _p(expert_counts_cumsum),
+                                            _p(dst_base), _peer_array(peer_buffers), len(peer_buffers), num_experts,
+                                            experts_per_rank, _p(X_combined), _stream()), "ep_combine_rows")
+
+
+def ep_gather_router_grad(num_tokens, top_k, token_expert_weights, token_mapping, chosen_experts, expert_counts,
+                          expert_counts_cumsum, dst_base, peer_dP_buffers, num_experts, experts_per_rank, dX_routed):
+    _check(_lib.load().b200_ep_gather_router_grad(num_tokens, top_k, _p(token_expert_weights), _p(token_mapping),
+                                                  _p(chosen_experts), _p(expert_counts), _p(expert_counts_cumsum),
+                                                  _p(dst_base), _peer_array(peer_dP_buffers), len(peer_dP_buffers),
+                                                  num_experts, experts_per_rank, _p(dX_routed), _stream()),
+           "ep_gather_router_grad")

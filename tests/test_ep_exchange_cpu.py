@@ -51,6 +51,11 @@ def _worker(rank, world, port, E, d, seed, result_dir):
         assert x.rows_recv == len(expect_rows)
         assert x.local_counts.tolist() == [int(allc[:, rank * El + j].sum()) for j in range(El)]
         assert x.local_cumsum.tolist() == np.cumsum(x.local_counts.numpy()).tolist()
+        # dst_base: where THIS rank's rows of every expert start inside the owner's buffer == the owner's recv_off
+        offs = [None] * world
+        dist.all_gather_object(offs, x.recv_off)
+        for e in range(E):
+            assert int(x.dst_base[e]) == offs[e // El][rank][e % El], (rank, e)
         recv = torch.full((x.rows_recv + 3, d), -1.0)
         x.dispatch(zone, recv)
         got = [tuple(int(v) for v in recv[i, :3]) for i in range(x.rows_recv)]

@@ -3,6 +3,8 @@
 Tokens are independent, so rank r's outputs (out, dXn) must equal the oracle's single-GPU layer on rank r's batch
 with all experts; the expert weight gradients on the owning rank must equal the sum of the oracle's gradients over
 all ranks' batches; the per-expert row counts seen by the owner must equal the sum of the ranks' counts (bit-exact).
+Both transports are covered: rows written / read directly in the owner's NVLink-mapped buffer ("p2p") and rows moved
+by NCCL point-to-point batches ("nccl"). Two steps are run so that buffer reuse across steps is exercised.
 Skipped on a box with fewer than two GPUs.
 """
 import os
@@ -21,7 +23,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, result_dir):
+def _worker(rank, world, port, result_dir, transport):
     import torch.distributed as dist
 
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
@@ -47,7 +49,7 @@ def _worker(rank, world, port, result_dir):
             batches.append((rand_bf16(rng, (T, d)), rand_bf16(rng, (T, d))))
         X, dOut = batches[rank]
         sl = slice(rank * El, (rank + 1) * El)
-        layer = ExpertParallelMoELayer(T, d, E, k, f, dist, device=torch.device("cuda", rank))
+        layer = ExpertParallelMoELayer(T, d, E, k, f, dist, device=torch.device("cuda", rank), transport=transport)
         out = torch.zeros((T, d), dtype=torch.bfloat16, device="cuda")
         dXn = torch.empty_like(out)
         dWr = torch.zeros((E, d), dtype=torch.bfloat16, device="cuda")
@@ -55,8 +57,11 @@ def _worker(rank, world, port, result_dir):
         dW2 = torch.zeros((El, d, f), dtype=torch.bfloat16, device="cuda")
         Xd, dOd, Wrd = dev_bf16(X), dev_bf16(dOut), dev_bf16(Wr)
         W1d, W3d, W2d = dev_bf16(W1[sl]), dev_bf16(W3[sl]), dev_bf16(W2[sl])
-        layer.forward(Xd, Wrd, W1d, W3d, W2d, out)
-        layer.backward(Xd, Wrd, W1d, W3d, W2d, dOd, dXn, dWr, dW1, dW3, dW2)
+        for _ in range(2):  # the second pass reuses every buffer, local and remote
+            for t_ in (out, dWr, dW1, dW3, dW2):
+                t_.zero_()
+            layer.forward(Xd, Wrd, W1d, W3d, W2d, out)
+            layer.backward(Xd, Wrd, W1d, W3d, W2d, dOd, dXn, dWr, dW1, dW3, dW2)
         assert ops.gemm_status() == 0
 
         # oracle: every rank's batch through the single-GPU layer; this rank's logits come from its own GPU run
@@ -85,11 +90,12 @@ def _worker(rank, world, port, result_dir):
         dist.destroy_process_group()
 
 
-def test_expert_parallel_two_ranks(tmp_path):
+@pytest.mark.parametrize("transport", ["p2p", "nccl"])
+def test_expert_parallel_two_ranks(tmp_path, transport):
     if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     import torch.multiprocessing as mp
 
     world = 2
-    mp.spawn(_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, _free_port(), str(tmp_path), transport), nprocs=world, join=True)
     assert sorted(os.listdir(tmp_path)) == ["ok0", "ok1"]

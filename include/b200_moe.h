@@ -295,12 +295,14 @@ int b200_gather_router_grad(int num_tokens, int num_routed_experts, int top_k, c
  */
 
 /* prepare_experts fused with the dispatch: row (t, j) = X[t, :] (times token_expert_weights[t, j] when that pointer
- * is not NULL) is stored straight into its owner's buffer. */
+ * is not NULL) is stored straight into its owner's buffer. Only pairs whose expert has an index inside its owner
+ * (expert % experts_per_rank) in [local_expert_begin, local_expert_end) are moved, so that the exchange can run in
+ * slices under the GEMMs of the previous slice; pass 0 and experts_per_rank for all of them. */
 int b200_ep_dispatch_rows(int total_tokens, int model_dim, int top_k, const void *X, const float *token_expert_weights,
                           const int *token_mapping, const uint16_t *chosen_experts, const int *expert_counts,
                           const int *expert_counts_cumsum, const int *dst_base,
                           const unsigned long long *peer_buffers, int world, int num_experts, int experts_per_rank,
-                          void *stream);
+                          int local_expert_begin, int local_expert_end, void *stream);
 
 /* merge_experts fused with the return: X_combined[t, :] += sum_j w[t, j] * row (t, j), every row loaded from its
  * owner's buffer; token_expert_weights == NULL means 1.0 (backward un-permute). */
@@ -316,6 +318,38 @@ int b200_ep_gather_router_grad(int num_tokens, int top_k, const float *token_exp
                                const int *expert_counts_cumsum, const int *dst_base,
                                const unsigned long long *peer_dP_buffers, int world, int num_experts,
                                int experts_per_rank, void *dX_routed, void *stream);
+
+/*
+ * GEMM fused with the return exchange. A row tag is (rank << 40) | row. b200_ep_publish_row_tags writes, for every
+ * routed pair (t, j) of this rank, the tag (my_rank << 40) | token_mapping[t, j] into entry row (t, j) of the owner's
+ * tag array (peer_tag_buffers: host array of `world` device addresses of unsigned long long arrays, addressed like
+ * the row buffers above). After a barrier, the owner runs the *_scatter forms of the grouped passes: they are
+ * b200_moe_experts_fwd / b200_moe_experts_bwd_x except that the rows of the last GEMM (Y, resp. dZ) are not stored in
+ * place: the epilogue stores row r at row (row_tags[r] & (2^40 - 1)) of dest_buffers[row_tags[r] >> 40]
+ * ([rows_per_buffer, model_dim] bf16 each; plain stores, peer memory allowed), i.e. straight into the zone-ordered
+ * buffer of the token's home rank, where b200_merge_experts / b200_merge_expert_result then run locally. A tag
+ * outside (world, rows_per_buffer) is not stored and raises status 5 (b200_gemm_status). No counterpart in the
+ * reference, which runs on one GPU.
+ */
+int b200_ep_publish_row_tags(int num_tokens, int top_k, int my_rank, const int *token_mapping,
+                             const uint16_t *chosen_experts, const int *expert_counts, const int *expert_counts_cumsum,
+                             const int *dst_base, const unsigned long long *peer_tag_buffers, int world,
+                             int num_experts, int experts_per_rank, void *stream);
+
+int b200_moe_experts_fwd_scatter(int total_rows, int model_dim, int ffn_dim, int num_experts, const void *zone,
+                                 const void *W1, const void *W3, const void *W2, int64_t w1_stride_elems,
+                                 int64_t w3_stride_elems, int64_t w2_stride_elems, const int *expert_counts,
+                                 const int *expert_counts_cumsum, void *x1, void *x3, void *h,
+                                 const unsigned long long *row_tags, const unsigned long long *dest_buffers, int world,
+                                 int64_t rows_per_buffer, void *stream);
+
+int b200_moe_experts_bwd_x_scatter(int total_rows, int model_dim, int ffn_dim, int num_experts, const void *dY_zone,
+                                   const float *row_weights, const void *x1, const void *x3, const void *W1,
+                                   const void *W3, const void *W2, int64_t w1_stride_elems, int64_t w3_stride_elems,
+                                   int64_t w2_stride_elems, const int *expert_counts, const int *expert_counts_cumsum,
+                                   void *dx1, void *dx3, void *hs, float *dP, const unsigned long long *row_tags,
+                                   const unsigned long long *dest_buffers, int world, int64_t rows_per_buffer,
+                                   void *stream);
 
 #ifdef __cplusplus
 }

@@ -24,6 +24,7 @@ struct RouteView {
   const uint16_t *chosen;
   const int *counts, *cumsum_incl, *dst_base;
   int num_experts, experts_per_rank;
+  int local_begin, local_end;  // only pairs whose expert index inside its owner is in [local_begin, local_end)
 };
 
 __device__ __forceinline__ bool locate(const RouteView &rv, int64_t slot, int &owner, int64_t &row) {
@@ -31,6 +32,8 @@ __device__ __forceinline__ bool locate(const RouteView &rv, int64_t slot, int &o
   const int r = rv.token_mapping[slot];
   if (e >= rv.num_experts || r < 0) return false;
   owner = e / rv.experts_per_rank;
+  const int le = e - owner * rv.experts_per_rank;
+  if (le < rv.local_begin || le >= rv.local_end) return false;
   row = (int64_t)rv.dst_base[e] + (r - (rv.cumsum_incl[e] - rv.counts[e]));
   return true;
 }
@@ -143,6 +146,18 @@ __global__ void router_grad_p2p_kernel(int64_t n, int top_k, const float *__rest
   dX_routed[(i / top_k) * rv.num_experts + rv.chosen[i]] = __float2bfloat16_rn(w != 0.f ? v / w : 0.f);
 }
 
+// tags_owner[row(t,j)] = (my_rank << 40) | local zone row of (t, j): tells the owner's GEMM epilogue where the
+// output row of that routed pair has to go (b200_moe_experts_fwd_scatter / _bwd_x_scatter)
+__global__ void publish_row_tags_kernel(int64_t n, unsigned long long my_rank, RouteView rv, PeerTable peers) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  int owner;
+  int64_t row;
+  if (!locate(rv, i, owner, row)) return;
+  *(reinterpret_cast<unsigned long long *>(peers.base[owner]) + row) =
+      (my_rank << 40) | (unsigned long long)rv.token_mapping[i];
+}
+
 }  // namespace b200
 
 using namespace b200;
@@ -162,6 +177,8 @@ static int fill_views(const char *op, int num_experts, int experts_per_rank, int
   rv.dst_base = dst_base;
   rv.num_experts = num_experts;
   rv.experts_per_rank = experts_per_rank;
+  rv.local_begin = 0;
+  rv.local_end = experts_per_rank;
   for (int i = 0; i < P2P_MAX_RANKS; i++) pt.base[i] = i < world ? peer_ptrs[i] : 0ull;
   for (int i = 0; i < world; i++) B200_REQUIRE(pt.base[i] != 0 && (pt.base[i] & 15ull) == 0, "%s: bad peer pointer %d", op, i);
   return 0;
@@ -172,16 +189,22 @@ extern "C" int b200_ep_dispatch_rows(int total_tokens, int model_dim, int top_k,
                                      const uint16_t *chosen_experts, const int *expert_counts,
                                      const int *expert_counts_cumsum, const int *dst_base,
                                      const unsigned long long *peer_buffers, int world, int num_experts,
-                                     int experts_per_rank, void *stream) {
+                                     int experts_per_rank, int local_expert_begin, int local_expert_end,
+                                     void *stream) {
   B200_REQUIRE(total_tokens >= 0 && top_k >= 1 && top_k <= B200_MAX_TOP_K && model_dim > 0 && model_dim % 8 == 0 && X &&
                    b200_aligned16(X),
                "ep_dispatch_rows: bad arguments");
+  B200_REQUIRE(0 <= local_expert_begin && local_expert_begin <= local_expert_end && local_expert_end <= experts_per_rank,
+               "ep_dispatch_rows: local expert range [%d, %d) outside [0, %d)", local_expert_begin, local_expert_end,
+               experts_per_rank);
   RouteView rv;
   PeerTable pt;
   if (fill_views("ep_dispatch_rows", num_experts, experts_per_rank, world, token_mapping, chosen_experts, expert_counts,
                  expert_counts_cumsum, dst_base, peer_buffers, rv, pt))
     return -1;
-  if (total_tokens == 0) return 0;
+  rv.local_begin = local_expert_begin;
+  rv.local_end = local_expert_end;
+  if (total_tokens == 0 || local_expert_begin == local_expert_end) return 0;
   const int dv = model_dim / 8;
   cudaStream_t s = (cudaStream_t)stream;
   if (dv <= P2P_THREADS * 2)
@@ -236,5 +259,24 @@ extern "C" int b200_ep_gather_router_grad(int num_tokens, int top_k, const float
   router_grad_p2p_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
       n, top_k, token_expert_weights, rv, pt, (__nv_bfloat16 *)dX_routed);
   B200_CHECK_LAUNCH("ep_gather_router_grad");
+  return 0;
+}
+
+extern "C" int b200_ep_publish_row_tags(int num_tokens, int top_k, int my_rank, const int *token_mapping,
+                                        const uint16_t *chosen_experts, const int *expert_counts,
+                                        const int *expert_counts_cumsum, const int *dst_base,
+                                        const unsigned long long *peer_tag_buffers, int world, int num_experts,
+                                        int experts_per_rank, void *stream) {
+  B200_REQUIRE(num_tokens >= 0 && top_k >= 1 && my_rank >= 0 && my_rank < world, "ep_publish_row_tags: bad arguments");
+  RouteView rv;
+  PeerTable pt;
+  if (fill_views("ep_publish_row_tags", num_experts, experts_per_rank, world, token_mapping, chosen_experts,
+                 expert_counts, expert_counts_cumsum, dst_base, peer_tag_buffers, rv, pt))
+    return -1;
+  const int64_t n = (int64_t)num_tokens * top_k;
+  if (n == 0) return 0;
+  publish_row_tags_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(n, (unsigned long long)my_rank,
+                                                                                        rv, pt);
+  B200_CHECK_LAUNCH("ep_publish_row_tags");
   return 0;
 }

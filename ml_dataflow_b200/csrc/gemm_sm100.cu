@@ -48,8 +48,18 @@ struct Cfg {
 
 enum GroupMode { DENSE = 0, GROUPED_M = 1, GROUPED_K = 2 };
 enum Epilogue { EPI_STORE = 0, EPI_SWIGLU_FWD = 1, EPI_SWIGLU_BWD = 2 };
+constexpr int SCATTER_MAX_RANKS = 16;
+constexpr int TAG_RANK_SHIFT = 40;
+constexpr unsigned long long TAG_ROW_MASK = (1ull << TAG_RANK_SHIFT) - 1ull;
 
-enum StatusCode { ST_OK = 0, ST_PRODUCER_TIMEOUT = 1, ST_MMA_TIMEOUT = 2, ST_EPILOGUE_TIMEOUT = 3, ST_PEER_TIMEOUT = 4 };
+enum StatusCode {
+  ST_OK = 0,
+  ST_PRODUCER_TIMEOUT = 1,
+  ST_MMA_TIMEOUT = 2,
+  ST_EPILOGUE_TIMEOUT = 3,
+  ST_PEER_TIMEOUT = 4,
+  ST_BAD_ROW_TAG = 5  // a scatter tag named a rank or row outside the destination buffers; the row was not stored
+};
 
 __device__ int g_gemm_status = 0;
 
@@ -74,6 +84,12 @@ struct GemmParams {
   float *dP;
   int *status;
   int wide;  // every bf16 row the epilogue touches is 32-byte aligned: use 256-bit global accesses
+  // Row scatter (EPI_STORE, bf16, no C): output row r goes to row (tag & ROW_MASK) of the buffer of rank
+  // (tag >> RANK_SHIFT), tag = row_tags[r]; the buffers may be peer memory mapped over NVLink (plain stores).
+  const unsigned long long *row_tags;
+  unsigned long long scatter_base[SCATTER_MAX_RANKS];
+  int scatter_world;
+  int64_t scatter_rows;
 };
 
 struct Tile {
@@ -434,6 +450,19 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
         const int64_t goff = (p.group_mode == GROUPED_K) ? (int64_t)t.group * p.d_group_stride : 0;
         const int64_t base = goff + orow * p.ldd + t.n0;
         const bool use_c = (p.C != nullptr) && (p.beta != 0.0f);
+        // destination of this thread's row: D itself, or (row scatter) the row its tag names in some rank's buffer
+        __nv_bfloat16 *drow = static_cast<__nv_bfloat16 *>(p.D) + base;
+        bool store_ok = row_ok;
+        if (p.row_tags != nullptr && row_ok) {
+          const unsigned long long tag = p.row_tags[orow];
+          const unsigned long long rk = tag >> TAG_RANK_SHIFT, rr = tag & TAG_ROW_MASK;
+          if (rk < (unsigned long long)p.scatter_world && rr < (unsigned long long)p.scatter_rows) {
+            drow = reinterpret_cast<__nv_bfloat16 *>(p.scatter_base[rk]) + (int64_t)rr * p.ldd + t.n0;
+          } else {
+            store_ok = false;
+            atomicCAS(p.status, 0, (int)ST_BAD_ROW_TAG);
+          }
+        }
         // the bf16 C segment of this thread (up to 128 columns) is fetched before waiting on the MMAs
         uint4 cpre[16];
         if (use_c && !p.c_fp32 && row_ok) {
@@ -455,7 +484,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
             ptx::tmem_ld32(taddr + c0, r);
             if (c0 + 32 < cend) ptx::tmem_ld32(taddr + c0 + 32, r + 32);
             ptx::tmem_ld_wait();
-            if (row_ok) {
+            if (store_ok) {
 #pragma unroll
               for (int vv = 0; vv < 4; vv++) {
                 const int col = c0 + vv * 16;
@@ -486,7 +515,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
                       dp[3] = make_float4(f[12], f[13], f[14], f[15]);
                     }
                   } else {
-                    st16(static_cast<__nv_bfloat16 *>(p.D) + base + col, t.n_valid - col, pack8(f), pack8(f + 8));
+                    st16(drow + col, t.n_valid - col, pack8(f), pack8(f + 8));
                   }
                 }
               }
@@ -763,7 +792,10 @@ static int launch_gemm(GemmParams &p, int64_t max_tiles, cudaStream_t s, bool pa
     auto a32 = [](const void *q) { return (reinterpret_cast<uintptr_t>(q) & 31u) == 0; };
     bool wide;
     if (EPI == EPI_STORE)
+    {
       wide = !p.out_fp32 && a32(p.D) && a32(p.C) && p.ldd % 16 == 0 && p.d_group_stride % 16 == 0;
+      for (int i = 0; i < p.scatter_world; i++) wide = wide && (p.scatter_base[i] & 31ull) == 0;
+    }
     else if (EPI == EPI_SWIGLU_FWD)
       wide = a32(p.x1_out) && a32(p.x3_out) && a32(p.h_out) && p.N % 16 == 0;
     else
@@ -862,14 +894,36 @@ static int check_grouped(const char *op, int total_rows, int model_dim, int ffn_
   return 0;
 }
 
-extern "C" int b200_moe_experts_fwd(int total_rows, int model_dim, int ffn_dim, int num_experts, const void *zone,
-                                    const void *W1, const void *W3, const void *W2, int64_t w1_stride_elems,
-                                    int64_t w3_stride_elems, int64_t w2_stride_elems, const int *expert_counts,
-                                    const int *expert_counts_cumsum, void *x1, void *x3, void *h, void *Y,
-                                    void *stream) {
+// Where the rows of the last GEMM of a pass go when they are not stored in place: see GemmParams::row_tags.
+struct RowScatter {
+  const unsigned long long *row_tags;
+  const unsigned long long *buffers;  // host array, one device address per rank
+  int world;
+  int64_t rows_per_buffer;
+};
+
+static int apply_scatter(const char *op, GemmParams &p, const RowScatter *sc) {
+  if (!sc) return 0;
+  B200_REQUIRE(sc->row_tags && sc->buffers && sc->world >= 1 && sc->world <= SCATTER_MAX_RANKS && sc->rows_per_buffer >= 0,
+               "%s: bad scatter description (world %d, at most %d ranks)", op, sc->world, SCATTER_MAX_RANKS);
+  for (int i = 0; i < sc->world; i++)
+    B200_REQUIRE(sc->buffers[i] != 0 && (sc->buffers[i] & 15ull) == 0, "%s: destination buffer %d missing or unaligned", op, i);
+  p.row_tags = sc->row_tags;
+  p.scatter_world = sc->world;
+  p.scatter_rows = sc->rows_per_buffer;
+  for (int i = 0; i < sc->world; i++) p.scatter_base[i] = sc->buffers[i];
+  p.D = reinterpret_cast<void *>(sc->buffers[0]);  // never written through: only its alignment is looked at
+  return 0;
+}
+
+static int experts_fwd_impl(int total_rows, int model_dim, int ffn_dim, int num_experts, const void *zone,
+                            const void *W1, const void *W3, const void *W2, int64_t w1_stride_elems,
+                            int64_t w3_stride_elems, int64_t w2_stride_elems, const int *expert_counts,
+                            const int *expert_counts_cumsum, void *x1, void *x3, void *h, void *Y,
+                            const RowScatter *sc, void *stream) {
   if (check_grouped("moe_experts_fwd", total_rows, model_dim, ffn_dim, num_experts, expert_counts, expert_counts_cumsum))
     return -1;
-  B200_REQUIRE(zone && W1 && W3 && W2 && x1 && x3 && h && Y, "moe_experts_fwd: null buffer");
+  B200_REQUIRE(zone && W1 && W3 && W2 && x1 && x3 && h && (Y || sc), "moe_experts_fwd: null buffer");
   B200_REQUIRE(w1_stride_elems % 8 == 0 && w3_stride_elems % 8 == 0 && w2_stride_elems % 8 == 0,
                "moe_experts_fwd: expert strides must be multiples of 8 elements");
   B200_REQUIRE(b200_aligned16(x1) && b200_aligned16(x3) && b200_aligned16(h) && b200_aligned16(Y),
@@ -916,6 +970,7 @@ extern "C" int b200_moe_experts_fwd(int total_rows, int model_dim, int ffn_dim, 
     p.alpha = 1.0f;
     p.D = Y;
     p.ldd = model_dim;
+    if (apply_scatter("moe_experts_fwd_scatter", p, sc)) return -1;
     if (make_tmap(&p.tmA, h, 2, (uint64_t)ffn_dim, (uint64_t)total_rows, 1, (uint64_t)ffn_dim * 2, 0)) return -1;
     if (make_tmap(&p.tmB, W2, 3, (uint64_t)ffn_dim, (uint64_t)model_dim, (uint64_t)num_experts, (uint64_t)ffn_dim * 2,
                   (uint64_t)w2_stride_elems * 2))
@@ -927,16 +982,39 @@ extern "C" int b200_moe_experts_fwd(int total_rows, int model_dim, int ffn_dim, 
   return 0;
 }
 
-extern "C" int b200_moe_experts_bwd_x(int total_rows, int model_dim, int ffn_dim, int num_experts, const void *dY_zone,
-                                      const float *row_weights, const void *x1, const void *x3, const void *W1,
-                                      const void *W3, const void *W2, int64_t w1_stride_elems, int64_t w3_stride_elems,
-                                      int64_t w2_stride_elems, const int *expert_counts,
-                                      const int *expert_counts_cumsum, void *dx1, void *dx3, void *hs, float *dP,
-                                      void *dZ, void *stream) {
+extern "C" int b200_moe_experts_fwd(int total_rows, int model_dim, int ffn_dim, int num_experts, const void *zone,
+                                    const void *W1, const void *W3, const void *W2, int64_t w1_stride_elems,
+                                    int64_t w3_stride_elems, int64_t w2_stride_elems, const int *expert_counts,
+                                    const int *expert_counts_cumsum, void *x1, void *x3, void *h, void *Y,
+                                    void *stream) {
+  return experts_fwd_impl(total_rows, model_dim, ffn_dim, num_experts, zone, W1, W3, W2, w1_stride_elems,
+                          w3_stride_elems, w2_stride_elems, expert_counts, expert_counts_cumsum, x1, x3, h, Y, nullptr,
+                          stream);
+}
+
+extern "C" int b200_moe_experts_fwd_scatter(int total_rows, int model_dim, int ffn_dim, int num_experts,
+                                            const void *zone, const void *W1, const void *W3, const void *W2,
+                                            int64_t w1_stride_elems, int64_t w3_stride_elems, int64_t w2_stride_elems,
+                                            const int *expert_counts, const int *expert_counts_cumsum, void *x1,
+                                            void *x3, void *h, const unsigned long long *row_tags,
+                                            const unsigned long long *dest_buffers, int world,
+                                            int64_t rows_per_buffer, void *stream) {
+  RowScatter sc = {row_tags, dest_buffers, world, rows_per_buffer};
+  return experts_fwd_impl(total_rows, model_dim, ffn_dim, num_experts, zone, W1, W3, W2, w1_stride_elems,
+                          w3_stride_elems, w2_stride_elems, expert_counts, expert_counts_cumsum, x1, x3, h, nullptr,
+                          &sc, stream);
+}
+
+static int experts_bwd_x_impl(int total_rows, int model_dim, int ffn_dim, int num_experts, const void *dY_zone,
+                              const float *row_weights, const void *x1, const void *x3, const void *W1,
+                              const void *W3, const void *W2, int64_t w1_stride_elems, int64_t w3_stride_elems,
+                              int64_t w2_stride_elems, const int *expert_counts, const int *expert_counts_cumsum,
+                              void *dx1, void *dx3, void *hs, float *dP, void *dZ, const RowScatter *sc,
+                              void *stream) {
   if (check_grouped("moe_experts_bwd_x", total_rows, model_dim, ffn_dim, num_experts, expert_counts,
                     expert_counts_cumsum))
     return -1;
-  B200_REQUIRE(dY_zone && row_weights && x1 && x3 && W1 && W3 && W2 && dx1 && dx3 && dP && dZ,
+  B200_REQUIRE(dY_zone && row_weights && x1 && x3 && W1 && W3 && W2 && dx1 && dx3 && dP && (dZ || sc),
                "moe_experts_bwd_x: null buffer");
   B200_REQUIRE(w1_stride_elems % 8 == 0 && w3_stride_elems % 8 == 0 && w2_stride_elems % 8 == 0,
                "moe_experts_bwd_x: expert strides must be multiples of 8 elements");
@@ -989,6 +1067,7 @@ extern "C" int b200_moe_experts_bwd_x(int total_rows, int model_dim, int ffn_dim
     p.alpha = 1.0f;
     p.D = dZ;
     p.ldd = model_dim;
+    if (apply_scatter("moe_experts_bwd_x_scatter", p, sc)) return -1;
     if (make_tmap(&p.tmA, dx1, 2, (uint64_t)ffn_dim, (uint64_t)total_rows, 1, (uint64_t)ffn_dim * 2, 0)) return -1;
     if (make_tmap(&p.tmA2, dx3, 2, (uint64_t)ffn_dim, (uint64_t)total_rows, 1, (uint64_t)ffn_dim * 2, 0)) return -1;
     if (make_tmap(&p.tmB, W1, 3, (uint64_t)model_dim, (uint64_t)ffn_dim, (uint64_t)num_experts, (uint64_t)model_dim * 2,
@@ -1000,6 +1079,32 @@ extern "C" int b200_moe_experts_bwd_x(int total_rows, int model_dim, int ffn_dim
     if (launch_gemm<EPI_STORE>(p, m_tiles_max * ((model_dim + 255) / 256), s)) return -1;
   }
   return 0;
+}
+
+extern "C" int b200_moe_experts_bwd_x(int total_rows, int model_dim, int ffn_dim, int num_experts, const void *dY_zone,
+                                      const float *row_weights, const void *x1, const void *x3, const void *W1,
+                                      const void *W3, const void *W2, int64_t w1_stride_elems, int64_t w3_stride_elems,
+                                      int64_t w2_stride_elems, const int *expert_counts,
+                                      const int *expert_counts_cumsum, void *dx1, void *dx3, void *hs, float *dP,
+                                      void *dZ, void *stream) {
+  return experts_bwd_x_impl(total_rows, model_dim, ffn_dim, num_experts, dY_zone, row_weights, x1, x3, W1, W3, W2,
+                            w1_stride_elems, w3_stride_elems, w2_stride_elems, expert_counts, expert_counts_cumsum, dx1,
+                            dx3, hs, dP, dZ, nullptr, stream);
+}
+
+extern "C" int b200_moe_experts_bwd_x_scatter(int total_rows, int model_dim, int ffn_dim, int num_experts,
+                                              const void *dY_zone, const float *row_weights, const void *x1,
+                                              const void *x3, const void *W1, const void *W3, const void *W2,
+                                              int64_t w1_stride_elems, int64_t w3_stride_elems,
+                                              int64_t w2_stride_elems, const int *expert_counts,
+                                              const int *expert_counts_cumsum, void *dx1, void *dx3, void *hs,
+                                              float *dP, const unsigned long long *row_tags,
+                                              const unsigned long long *dest_buffers, int world,
+                                              int64_t rows_per_buffer, void *stream) {
+  RowScatter sc = {row_tags, dest_buffers, world, rows_per_buffer};
+  return experts_bwd_x_impl(total_rows, model_dim, ffn_dim, num_experts, dY_zone, row_weights, x1, x3, W1, W3, W2,
+                            w1_stride_elems, w3_stride_elems, w2_stride_elems, expert_counts, expert_counts_cumsum, dx1,
+                            dx3, hs, dP, nullptr, &sc, stream);
 }
 
 // One grouped wgrad: dW[e][Mrows][Ncols] += A[rows_e, Mrows]^T . B[rows_e, Ncols]

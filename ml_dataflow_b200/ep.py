@@ -15,8 +15,12 @@ Per layer and direction there is one exchange each way:
      unchanged with per-expert counts summed over sources.
   -> grouped expert GEMMs on the received rows -> the reverse exchange -> local weighted combine.
 
-Two transports for the rows:
-  * "p2p" (default on GPUs): the receive buffers are NVLink-mapped into every rank (torch symmetric memory gives the
+Three transports for the rows:
+  * "fused": as "p2p" on the way out; on the way back the LAST GEMM of each pass does the exchange itself: its
+    epilogue stores every output row (Y forward, dZ backward) straight into the zone-ordered buffer of the token's
+    home rank (peer stores, tile by tile under the MMAs of the next tile), guided by a per-row tag the home rank
+    published next to the row. After one barrier the combine / un-permute is a purely local kernel.
+  * "p2p": the receive buffers are NVLink-mapped into every rank (torch symmetric memory gives the
     peer addresses). The gather kernel stores each row straight into its owner's buffer and the combine kernel loads
     each expert output row straight from its owner (csrc/ep_p2p.cu): no staging copy, no collective on the data path,
     only a stream-ordered barrier between the phases.
@@ -112,7 +116,7 @@ class RowExchange:
 class ExpertParallelMoELayer:
     """Same call surface as `MoELayer`, with W1/W3/W2 and their gradients holding only this rank's experts."""
 
-    def __init__(self, T, d, E, k, f, dist, device="cuda", recv_capacity_factor=1.5, transport="p2p"):
+    def __init__(self, T, d, E, k, f, dist, device="cuda", recv_capacity_factor=1.5, transport="p2p", slices=1):
         self.T, self.d, self.E, self.k, self.f = T, d, E, k, f
         self.dist = dist
         self.dev = torch.device(device)
@@ -120,7 +124,9 @@ class ExpertParallelMoELayer:
         self.x = RowExchange(dist, E, self.dev)
         self.E_loc = self.x.E_loc
         self.R = T * k
-        self.home = _HomeSide(T, d, E, k, self.dev, staging=(transport != "p2p"))
+        if transport not in ("fused", "p2p", "nccl"):
+            raise ValueError(f"unknown expert-parallel transport {transport!r}")
+        self.home = _HomeSide(T, d, E, k, self.dev, staging=(transport == "nccl"))
         self.cap = int(self.R * recv_capacity_factor) + 256
         bf, f32 = torch.bfloat16, torch.float32
 
@@ -128,7 +134,7 @@ class ExpertParallelMoELayer:
             return torch.empty(shape, dtype=dt, device=self.dev)
 
         self.peers = {}
-        if transport == "p2p":
+        if transport in ("fused", "p2p"):
             import torch.distributed._symmetric_memory as symm_mem
 
             def shared(name, shape, dt):
@@ -143,21 +149,63 @@ class ExpertParallelMoELayer:
 
         # buffers other ranks write into / read from
         self.zone_r = shared("zone", (self.cap, d), bf)   # received rows (kept for backward-w)
-        self.Y_r = shared("Y", (self.cap, d), bf)
         self.dY_r = shared("dY", (self.cap, d), bf)
-        self.dZ_r = shared("dZ", (self.cap, d), bf)
         self.dP_r = shared("dP", (self.cap,), f32)
+        if transport == "fused":
+            # the GEMM epilogues store Y / dZ rows straight into the home rank's zone-ordered buffers
+            self.tags_r = shared("tags", (self.cap,), torch.int64)
+            self.Y_h = shared("Yh", (self.R, d), bf)
+            self.dZ_h = shared("dZh", (self.R, d), bf)
+        else:
+            self.Y_r = shared("Y", (self.cap, d), bf)
+            self.dZ_r = shared("dZ", (self.cap, d), bf)
         # local only
         self.x1, self.x3, self.h = buf((self.cap, f), bf), buf((self.cap, f), bf), buf((self.cap, f), bf)
         self.dx1, self.dx3 = buf((self.cap, f), bf), buf((self.cap, f), bf)
         self.ones = torch.ones(self.cap, dtype=f32, device=self.dev)
         self._flag = torch.zeros(1, dtype=torch.int32, device=self.dev)
         self.profile = None
+        # "fused": the outward exchange can run in slices of local experts on a side stream, slice c+1 under the GEMMs
+        # of slice c (the copy blocks are small enough to share the SMs with the persistent GEMM CTAs). Measured on
+        # 2 GPUs the copies are hidden but slow the GEMMs, which are bound by the same L2 paths, by as much as they
+        # hide (1 slice 36.8 ms/step, 4 slices 38.2, 8 slices 39.1), hence one slice by default.
+        n_sl = max(1, min(int(slices), self.E_loc))
+        edges = [round(i * self.E_loc / n_sl) for i in range(n_sl + 1)]
+        self.slices = [(a, b) for a, b in zip(edges[:-1], edges[1:]) if b > a]
+        if transport == "fused":
+            self.side = torch.cuda.Stream(device=self.dev)
+            self.side_group = dist.new_group()  # its own communicator: side-stream barriers never queue behind main's
+            self._flag_side = torch.zeros(1, dtype=torch.int32, device=self.dev)
 
     def _barrier(self):
         """Stream-ordered barrier over all ranks: everything enqueued before it on every rank has finished (and its
         peer stores have landed) before anything enqueued after it starts."""
         self.dist.all_reduce(self._flag)
+
+    def _sliced_dispatch(self, rows, row_weights, peer_buffers, publish_tags):
+        """Enqueues, on the side stream, the outward exchange slice by slice (each followed by a barrier) and
+        returns one event per slice: once it has fired, this rank's buffer holds every rank's rows of that slice."""
+        from . import ops
+
+        hm, x = self.home, self.x
+        T, d, E, k = self.T, self.d, self.E, self.k
+        main = torch.cuda.current_stream()
+        start = torch.cuda.Event()
+        start.record(main)
+        events = []
+        with torch.cuda.stream(self.side):
+            self.side.wait_event(start)
+            for i, (a, b) in enumerate(self.slices):
+                ops.ep_dispatch_rows(T, d, k, rows, row_weights, hm.token_mapping, hm.chosen, hm.counts, hm.cumsum,
+                                     x.dst_base, peer_buffers, E, self.E_loc, (a, b))
+                if publish_tags and i == 0:
+                    ops.ep_publish_row_tags(T, k, self.dist.get_rank(), hm.token_mapping, hm.chosen, hm.counts,
+                                            hm.cumsum, x.dst_base, self.peers["tags"], E, self.E_loc)
+                self.dist.all_reduce(self._flag_side, group=self.side_group)
+                ev = torch.cuda.Event()
+                ev.record(self.side)
+                events.append(ev)
+        return events
 
     def mark(self, name):
         if self.profile is not None:
@@ -172,7 +220,8 @@ class ExpertParallelMoELayer:
         T, d, E, k, f = self.T, self.d, self.E, self.k, self.f
         self.mark("router_gemm")
         hm.route(Xn, Wr)
-        p2p = self.transport == "p2p"
+        fused = self.transport == "fused"
+        p2p = fused or self.transport == "p2p"
         if not p2p:
             self.mark("prepare_experts")
             ops.prepare_experts(T, d, k, Xn, hm.token_mapping, hm.zone)
@@ -182,6 +231,21 @@ class ExpertParallelMoELayer:
         if x.rows_recv > self.cap:
             raise RuntimeError(f"expert-parallel receive buffer too small: {x.rows_recv} rows > capacity {self.cap}")
         n = x.rows_recv
+        if fused:
+            ready = self._sliced_dispatch(Xn, None, self.peers["zone"], publish_tags=True)
+            for (a, b), ev in zip(self.slices, ready):
+                self.mark("dispatch")
+                torch.cuda.current_stream().wait_event(ev)
+                self.mark("experts_fwd_gemm")
+                ops.moe_experts_fwd_scatter(n, d, f, b - a, self.zone_r, W1[a:b], W3[a:b], W2[a:b], f * d, f * d, d * f,
+                                            x.local_counts[a:b], x.local_cumsum[a:b], self.x1, self.x3, self.h,
+                                            self.tags_r, self.peers["Yh"], self.R)
+            self.mark("return")
+            self._barrier()  # every rank's epilogue stores into Y_h have landed
+            self.mark("merge_experts")
+            ops.merge_experts(T, d, k, self.Y_h, hm.token_mapping, hm.weights, out)
+            self.mark("fwd_end")
+            return out
         if p2p:
             ops.ep_dispatch_rows(T, d, k, Xn, None, hm.token_mapping, hm.chosen, hm.counts, hm.cumsum, x.dst_base,
                                  self.peers["zone"], E, self.E_loc)
@@ -209,7 +273,34 @@ class ExpertParallelMoELayer:
         hm, x = self.home, self.x
         T, d, E, k, f = self.T, self.d, self.E, self.k, self.f
         n = x.rows_recv
-        p2p = self.transport == "p2p"
+        fused = self.transport == "fused"
+        p2p = fused or self.transport == "p2p"
+        if fused:
+            self.dP_r[:n].zero_()
+            ready = self._sliced_dispatch(dOut, hm.weights, self.peers["dY"], publish_tags=False)
+            for (a, b), ev in zip(self.slices, ready):
+                self.mark("dispatch_bwd")
+                torch.cuda.current_stream().wait_event(ev)
+                self.mark("experts_bwd_x_gemm")
+                # the gate weight of a row lives on its home rank: accumulate w*<Y,dOut> here, divide there
+                ops.moe_experts_bwd_x_scatter(n, d, f, b - a, self.dY_r, self.ones, self.x1, self.x3, W1[a:b], W3[a:b],
+                                              W2[a:b], f * d, f * d, d * f, x.local_counts[a:b], x.local_cumsum[a:b],
+                                              self.dx1, self.dx3, None, self.dP_r, self.tags_r, self.peers["dZh"],
+                                              self.R)
+                self.mark("experts_bwd_w_gemm")
+                ops.moe_experts_bwd_w(n, d, f, b - a, self.dY_r, self.h, self.zone_r, self.dx1, self.dx3, dW1[a:b],
+                                      dW3[a:b], dW2[a:b], f * d, f * d, d * f, x.local_counts[a:b],
+                                      x.local_cumsum[a:b])
+            self.mark("return_bwd")
+            self._barrier()
+            self.mark("unpermute")
+            dXn.zero_()
+            ops.merge_experts(T, d, k, self.dZ_h, hm.token_mapping, None, dXn)
+            self.mark("router_grad")
+            hm.dX_routed.zero_()
+            ops.ep_gather_router_grad(T, k, hm.weights, hm.token_mapping, hm.chosen, hm.counts, hm.cumsum, x.dst_base,
+                                      self.peers["dP"], E, self.E_loc, hm.dX_routed)
+            return self._router_backward(Xn, Wr, dXn, dWr)
         if p2p:
             self.mark("dispatch_bwd")
             ops.ep_dispatch_rows(T, d, k, dOut, hm.weights, hm.token_mapping, hm.chosen, hm.counts, hm.cumsum,
@@ -249,6 +340,13 @@ class ExpertParallelMoELayer:
             self.mark("router_grad")
             hm.dX_routed.zero_()
             ops.gather_router_grad(T, E, k, hm.token_mapping, hm.chosen, hm.dP, hm.dX_routed)
+        return self._router_backward(Xn, Wr, dXn, dWr)
+
+    def _router_backward(self, Xn, Wr, dXn, dWr):
+        from . import ops
+
+        hm = self.home
+        T, d, E, k = self.T, self.d, self.E, self.k
         ops.router_gate_bwd_x(T, E, k, hm.chosen, hm.weights, hm.dX_routed)
         ops.matmul(0, 0, d, E, T, 1.0, 1.0, Wr, hm.dX_routed, dXn, dXn)
         hm.dWr_local.zero_()

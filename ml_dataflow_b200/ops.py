@@ -188,13 +188,16 @@ def _peer_array(ptrs):
 
 
 def ep_dispatch_rows(total_tokens, model_dim, top_k, X, token_expert_weights, token_mapping, chosen_experts,
-                     expert_counts, expert_counts_cumsum, dst_base, peer_buffers, num_experts, experts_per_rank):
-    """peer_buffers: list of device addresses, one per rank (this rank's own buffer included)."""
+                     expert_counts, expert_counts_cumsum, dst_base, peer_buffers, num_experts, experts_per_rank,
+                     local_expert_range=None):
+    """peer_buffers: list of device addresses, one per rank (this rank's own buffer included).
+    local_expert_range: (begin, end) of the owners' local expert indices to move; None = all."""
+    lo, hi = (0, experts_per_rank) if local_expert_range is None else local_expert_range
     _check(_lib.load().b200_ep_dispatch_rows(total_tokens, model_dim, top_k, _p(X), _p(token_expert_weights),
                                              _p(token_mapping), _p(chosen_experts), _p(expert_counts),
                                              _p(expert_counts_cumsum), _p(dst_base), _peer_array(peer_buffers),
-                                             len(peer_buffers), num_experts, experts_per_rank, _stream()),
-           "ep_dispatch_rows")
+                                             len(peer_buffers), num_experts, experts_per_rank, lo, hi, _stream()),
+           "ep_dispatch_rows", 1 if hi > lo else 0)
 
 
 def ep_combine_rows(num_tokens, model_dim, top_k, token_expert_weights, token_mapping, chosen_experts, expert_counts,
@@ -212,3 +215,35 @@ def ep_gather_router_grad(num_tokens, top_k, token_expert_weights, token_mapping
                                                   _p(dst_base), _peer_array(peer_dP_buffers), len(peer_dP_buffers),
                                                   num_experts, experts_per_rank, _p(dX_routed), _stream()),
            "ep_gather_router_grad")
+
+
+def ep_publish_row_tags(num_tokens, top_k, my_rank, token_mapping, chosen_experts, expert_counts, expert_counts_cumsum,
+                        dst_base, peer_tag_buffers, num_experts, experts_per_rank):
+    """Writes (my_rank << 40 | zone row) for every routed pair into the owner's tag array (peer stores)."""
+    _check(_lib.load().b200_ep_publish_row_tags(num_tokens, top_k, my_rank, _p(token_mapping), _p(chosen_experts),
+                                                _p(expert_counts), _p(expert_counts_cumsum), _p(dst_base),
+                                                _peer_array(peer_tag_buffers), len(peer_tag_buffers), num_experts,
+                                                experts_per_rank, _stream()), "ep_publish_row_tags")
+
+
+def moe_experts_fwd_scatter(total_rows, model_dim, ffn_dim, num_experts, zone, W1, W3, W2, w1_stride, w3_stride,
+                            w2_stride, expert_counts, expert_counts_cumsum, x1, x3, h, row_tags, dest_buffers,
+                            rows_per_buffer):
+    """moe_experts_fwd whose Y rows go to the rows of dest_buffers (device addresses, one per rank) their tags name."""
+    _check(_lib.load().b200_moe_experts_fwd_scatter(total_rows, model_dim, ffn_dim, num_experts, _p(zone), _p(W1),
+                                                    _p(W3), _p(W2), w1_stride, w3_stride, w2_stride,
+                                                    _p(expert_counts), _p(expert_counts_cumsum), _p(x1), _p(x3), _p(h),
+                                                    _p(row_tags), _peer_array(dest_buffers), len(dest_buffers),
+                                                    rows_per_buffer, _stream()), "moe_experts_fwd_scatter", 2)
+
+
+def moe_experts_bwd_x_scatter(total_rows, model_dim, ffn_dim, num_experts, dY_zone, row_weights, x1, x3, W1, W3, W2,
+                              w1_stride, w3_stride, w2_stride, expert_counts, expert_counts_cumsum, dx1, dx3, hs, dP,
+                              row_tags, dest_buffers, rows_per_buffer):
+    """moe_experts_bwd_x whose dZ rows go to the rows of dest_buffers their tags name."""
+    _check(_lib.load().b200_moe_experts_bwd_x_scatter(total_rows, model_dim, ffn_dim, num_experts, _p(dY_zone),
+                                                      _p(row_weights), _p(x1), _p(x3), _p(W1), _p(W3), _p(W2),
+                                                      w1_stride, w3_stride, w2_stride, _p(expert_counts),
+                                                      _p(expert_counts_cumsum), _p(dx1), _p(dx3), _p(hs), _p(dP),
+                                                      _p(row_tags), _peer_array(dest_buffers), len(dest_buffers),
+                                                      rows_per_buffer, _stream()), "moe_experts_bwd_x_scatter", 2)

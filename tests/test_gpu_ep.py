@@ -3,8 +3,9 @@
 Tokens are independent, so rank r's outputs (out, dXn) must equal the oracle's single-GPU layer on rank r's batch
 with all experts; the expert weight gradients on the owning rank must equal the sum of the oracle's gradients over
 all ranks' batches; the per-expert row counts seen by the owner must equal the sum of the ranks' counts (bit-exact).
-Both transports are covered: rows written / read directly in the owner's NVLink-mapped buffer ("p2p") and rows moved
-by NCCL point-to-point batches ("nccl"). Two steps are run so that buffer reuse across steps is exercised.
+All transports are covered: expert outputs stored into the home rank's buffer by the GEMM epilogue ("fused"), rows
+written / read directly in the owner's NVLink-mapped buffer ("p2p") and rows moved by NCCL point-to-point batches
+("nccl"). Two steps are run so that buffer reuse across steps is exercised.
 Skipped on a box with fewer than two GPUs.
 """
 import os
@@ -90,7 +91,7 @@ def _worker(rank, world, port, result_dir, transport):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("transport", ["p2p", "nccl"])
+@pytest.mark.parametrize("transport", ["fused", "p2p", "nccl"])
 def test_expert_parallel_two_ranks(tmp_path, transport):
     if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")

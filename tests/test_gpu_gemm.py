@@ -192,3 +192,76 @@ def test_grouped_backward(oracle, R, d, f, E, empty):
     assert_close(f32(host_bits(G2)), f32(g2r), what="dW2")
     assert_close(f32(host_bits(G1)), f32(g1r), what="dW1")
     assert_close(f32(host_bits(G3)), f32(g3r), what="dW3")
+
+
+def _tags(rank_of_row, dest_row):
+    return torch.from_numpy((rank_of_row.astype(np.int64) << 40) | dest_row.astype(np.int64)).cuda()
+
+
+@pytest.mark.parametrize("R,d,f,E", [(700, 256, 192, 4), (2100, 1024, 1408, 8)])
+def test_grouped_scatter_forms_match_in_place_forms(R, d, f, E):
+    """The *_scatter entry points store Y / dZ rows where their tags say (two destination buffers standing in for two
+    ranks); values must be bit-identical to the in-place entry points."""
+    require_b200()
+    from ml_dataflow_b200 import ops
+
+    rng = np.random.default_rng(R + 7)
+    counts, cincl = make_counts(rng, E, R, (1,))
+    Z, dYs = dev_bf16(rand_bf16(rng, (R, d))), dev_bf16(rand_bf16(rng, (R, d)))
+    W1, W3, W2 = (dev_bf16(rand_bf16(rng, s, 0.03)) for s in ((E, f, d), (E, f, d), (E, d, f)))
+    cd, cid = dev(counts), dev(cincl)
+    ones = torch.ones(R, dtype=torch.float32, device="cuda")
+    x1, x3, h, dx1, dx3 = (torch.zeros((R, f), dtype=torch.bfloat16, device="cuda") for _ in range(5))
+    Y, dZ = (torch.zeros((R, d), dtype=torch.bfloat16, device="cuda") for _ in range(2))
+    dP = torch.zeros(R, dtype=torch.float32, device="cuda")
+    ops.moe_experts_fwd(R, d, f, E, Z, W1, W3, W2, f * d, f * d, d * f, cd, cid, x1, x3, h, Y)
+    ops.moe_experts_bwd_x(R, d, f, E, dYs, ones, x1, x3, W1, W3, W2, f * d, f * d, d * f, cd, cid, dx1, dx3, None, dP, dZ)
+
+    # a random permutation of the rows over two buffers
+    perm = rng.permutation(R)
+    half = (R + 1) // 2
+    rank_of_row, dest_row = (perm >= half).astype(np.int64), np.where(perm >= half, perm - half, perm)
+    tags = _tags(rank_of_row, dest_row)
+    bufs = [torch.full((half, d), 7.0, dtype=torch.bfloat16, device="cuda") for _ in range(2)]
+    ptrs = [b.data_ptr() for b in bufs]
+    x1b, x3b, hb = (torch.zeros_like(x1) for _ in range(3))
+    ops.moe_experts_fwd_scatter(R, d, f, E, Z, W1, W3, W2, f * d, f * d, d * f, cd, cid, x1b, x3b, hb, tags, ptrs, half)
+    gemm_ok(ops)
+    got = torch.cat(bufs)[torch.from_numpy(perm).cuda()]
+    assert torch.equal(got.view(torch.int16), Y.view(torch.int16))
+    assert torch.equal(hb.view(torch.int16), h.view(torch.int16))
+
+    for b in bufs:
+        b.fill_(7.0)
+    dPb = torch.zeros_like(dP)
+    dx1b, dx3b = torch.zeros_like(dx1), torch.zeros_like(dx3)
+    ops.moe_experts_bwd_x_scatter(R, d, f, E, dYs, ones, x1, x3, W1, W3, W2, f * d, f * d, d * f, cd, cid, dx1b, dx3b,
+                                  None, dPb, tags, ptrs, half)
+    gemm_ok(ops)
+    got = torch.cat(bufs)[torch.from_numpy(perm).cuda()]
+    assert torch.equal(got.view(torch.int16), dZ.view(torch.int16))
+    assert torch.equal(dx1b.view(torch.int16), dx1.view(torch.int16))
+
+
+def test_scatter_refuses_a_tag_outside_the_destination():
+    """A tag naming a rank or a row outside the destination buffers is not stored; the status word reports it."""
+    require_b200()
+    from ml_dataflow_b200 import ops
+
+    R, d, f, E = 300, 128, 64, 2
+    rng = np.random.default_rng(5)
+    counts, cincl = make_counts(rng, E, R)
+    Z = dev_bf16(rand_bf16(rng, (R, d)))
+    W1, W3, W2 = (dev_bf16(rand_bf16(rng, s, 0.03)) for s in ((E, f, d), (E, f, d), (E, d, f)))
+    x1, x3, h = (torch.zeros((R, f), dtype=torch.bfloat16, device="cuda") for _ in range(3))
+    rank_of_row, dest_row = np.zeros(R, np.int64), np.arange(R, dtype=np.int64)
+    rank_of_row[10] = 3          # only one destination buffer is given
+    dest_row[20] = R + 5         # past the end of the buffer
+    guard = torch.full((R + 64, d), 7.0, dtype=torch.bfloat16, device="cuda")
+    ops.moe_experts_fwd_scatter(R, d, f, E, Z, W1, W3, W2, f * d, f * d, d * f, dev(counts), dev(cincl), x1, x3, h,
+                                _tags(rank_of_row, dest_row), [guard.data_ptr()], R)
+    assert ops.gemm_status() == 5
+    assert ops.gemm_status() == 0  # reading clears it
+    g = guard.float().cpu().numpy()
+    assert (g[10] == 7.0).all() and (g[20] == 7.0).all() and (g[R:] == 7.0).all()
+    assert (g[11] != 7.0).any()

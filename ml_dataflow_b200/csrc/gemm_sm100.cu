@@ -90,6 +90,9 @@ struct GemmParams {
   unsigned long long scatter_base[SCATTER_MAX_RANKS];
   int scatter_world;
   int64_t scatter_rows;
+  // scattered rows are first transposed through shared memory so that eight lanes store 128 contiguous bytes of one
+  // row (32-byte pieces of 32 different rows per instruction use a peer link poorly); set when the block fits
+  int stage_out;
 };
 
 struct Tile {
@@ -153,8 +156,13 @@ struct GemmSmemTail {
   uint64_t full[MAX_STAGES], empty[MAX_STAGES], peer_full[MAX_STAGES], tfull[2], tempty[2];
   uint32_t tmem_base;
   int abort_flag;
-  int cnt[MAX_GROUPS], base[MAX_GROUPS], tpre[MAX_GROUPS + 1];
+  int pad[2];
+  // followed in shared memory by the group tables (cnt[G], base[G], tpre[G + 1]; table_ints(G) ints) and, when
+  // GemmParams::stage_out is set, by one 4 KiB staging block per epilogue warp
 };
+
+__host__ __device__ constexpr int table_ints(int groups) { return ((3 * groups + 1) + 3) & ~3; }
+constexpr int STAGE_OUT_BYTES_PER_WARP = 32 * 128;  // 32 rows x 64 bf16 columns
 
 template <int EPI, bool PAIR>
 __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __grid_constant__ GemmParams p) {
@@ -166,6 +174,10 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
   unsigned char *smem = reinterpret_cast<unsigned char *>(
       (reinterpret_cast<uintptr_t>(gemm_smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   GemmSmemTail *st = reinterpret_cast<GemmSmemTail *>(smem + STAGES * STAGE_BYTES);
+  int *const tab_cnt = reinterpret_cast<int *>(st + 1);
+  int *const tab_base = tab_cnt + p.num_groups;
+  int *const tab_tpre = tab_base + p.num_groups;
+  uint4 *const stage_out = reinterpret_cast<uint4 *>(tab_cnt + table_ints(p.num_groups));
   volatile int *abort_flag = &st->abort_flag;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -213,8 +225,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
   if (p.group_mode != DENSE) {
     for (int e = tid; e < G; e += GEMM_THREADS) {
       const int c = p.counts[e];
-      st->cnt[e] = c;
-      st->base[e] = p.cumsum_incl[e] - c;
+      tab_cnt[e] = c;
+      tab_base[e] = p.cumsum_incl[e] - c;
     }
   }
   __syncthreads();
@@ -222,17 +234,17 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
     int running = 0;
     for (int e0 = 0; e0 < G; e0 += 32) {
       const int e = e0 + lane;
-      const int v = (e < G) ? (st->cnt[e] + CF::TILE_M - 1) / CF::TILE_M : 0;
+      const int v = (e < G) ? (tab_cnt[e] + CF::TILE_M - 1) / CF::TILE_M : 0;
       int incl = v;
 #pragma unroll
       for (int o = 1; o < 32; o <<= 1) {
         const int t = __shfl_up_sync(0xffffffffu, incl, o);
         if (lane >= o) incl += t;
       }
-      if (e < G) st->tpre[e] = running + incl - v;
+      if (e < G) tab_tpre[e] = running + incl - v;
       running += __shfl_sync(0xffffffffu, incl, 31);
     }
-    if (lane == 0) st->tpre[G] = running;
+    if (lane == 0) tab_tpre[G] = running;
   }
   ptx::tc_fence_before();
   if (PAIR) ptx::cluster_sync_all();  // the peer's barriers are initialised before anything arrives on them
@@ -250,12 +262,12 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
   sched.n_round = (PAIR && !p.dual_b) ? 128 : 64;
   sched.tiles_n = (p.N + sched.n_tile_w - 1) / sched.n_tile_w;
   sched.tiles_m = (p.M + CF::TILE_M - 1) / CF::TILE_M;
-  sched.s_cnt = st->cnt;
-  sched.s_base = st->base;
-  sched.s_tpre = st->tpre;
+  sched.s_cnt = tab_cnt;
+  sched.s_base = tab_base;
+  sched.s_tpre = tab_tpre;
   sched.cursor = 0;
   if (p.group_mode == DENSE) sched.total_tiles = sched.tiles_m * sched.tiles_n;
-  else if (p.group_mode == GROUPED_M) sched.total_tiles = st->tpre[G] * sched.tiles_n;
+  else if (p.group_mode == GROUPED_M) sched.total_tiles = tab_tpre[G] * sched.tiles_n;
   else sched.total_tiles = G * sched.tiles_m * sched.tiles_n;
   const int first_tile = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
   const int tile_step = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
@@ -484,7 +496,34 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
             ptx::tmem_ld32(taddr + c0, r);
             if (c0 + 32 < cend) ptx::tmem_ld32(taddr + c0 + 32, r + 32);
             ptx::tmem_ld_wait();
-            if (store_ok) {
+            if (p.stage_out) {
+              // lane = row writes its 64 columns as eight 16-byte chunks (XOR-swizzled: conflict-free both ways), then
+              // lanes 8i..8i+7 read back row 4*it + i and store its 128 bytes side by side
+              uint4 *sb = stage_out + (warp - 2) * (STAGE_OUT_BYTES_PER_WARP / 16);
+#pragma unroll
+              for (int vv = 0; vv < 4; vv++) {
+                if (c0 + vv * 16 < cend) {
+                  float f[16];
+#pragma unroll
+                  for (int q = 0; q < 16; q++) f[q] = p.alpha * __uint_as_float(r[vv * 16 + q]);
+                  sb[lane * 8 + ((2 * vv) ^ (lane & 7))] = pack8(f);
+                  sb[lane * 8 + ((2 * vv + 1) ^ (lane & 7))] = pack8(f + 8);
+                }
+              }
+              __syncwarp();
+              const unsigned long long dptr = reinterpret_cast<unsigned long long>(drow);
+              const int chunk = lane & 7;
+              const int col = c0 + chunk * 8;
+#pragma unroll
+              for (int it = 0; it < 8; it++) {
+                const int rr = it * 4 + (lane >> 3);
+                const unsigned long long rp = __shfl_sync(0xffffffffu, dptr, rr);
+                const int rok = __shfl_sync(0xffffffffu, (int)store_ok, rr);
+                const uint4 v = sb[rr * 8 + (chunk ^ (rr & 7))];
+                if (rok && col < cend && col < t.n_valid) *reinterpret_cast<uint4 *>(reinterpret_cast<__nv_bfloat16 *>(rp) + col) = v;
+              }
+              __syncwarp();
+            } else if (store_ok) {
 #pragma unroll
               for (int vv = 0; vv < 4; vv++) {
                 const int col = c0 + vv * 16;
@@ -656,9 +695,12 @@ teardown:
   }
 }
 
+constexpr size_t GEMM_SMEM_LIMIT = 232448;  // 227 KiB: the most one CTA can be given on sm_100
+
 template <bool PAIR>
-constexpr size_t gemm_smem_bytes() {
-  return 1024 + (size_t)Cfg<PAIR>::STAGES * Cfg<PAIR>::STAGE_BYTES + sizeof(GemmSmemTail);
+static size_t gemm_smem_bytes(int groups, bool stage_out) {
+  return 1024 + (size_t)Cfg<PAIR>::STAGES * Cfg<PAIR>::STAGE_BYTES + sizeof(GemmSmemTail) + 4 * (size_t)table_ints(groups) +
+         (stage_out ? (size_t)EPI_WARPS * STAGE_OUT_BYTES_PER_WARP : 0);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -732,16 +774,20 @@ static int pair_mode() {
 template <int EPI, bool PAIR>
 static int launch_gemm_variant(GemmParams &p, int64_t max_tiles, cudaStream_t s) {
   auto kern = gemm_sm100_kernel<EPI, PAIR>;
-  constexpr size_t smem = gemm_smem_bytes<PAIR>();
+  // staging of scattered rows is used whenever it fits beside the pipeline stages and the group tables
+  p.stage_out = (EPI == EPI_STORE && p.row_tags != nullptr && gemm_smem_bytes<PAIR>(p.num_groups, true) <= GEMM_SMEM_LIMIT) ? 1 : 0;
+  const size_t smem = gemm_smem_bytes<PAIR>(p.num_groups, p.stage_out != 0);
+  B200_REQUIRE(smem <= GEMM_SMEM_LIMIT, "gemm: %d groups need %zu bytes of shared memory (limit %zu)", p.num_groups, smem,
+               GEMM_SMEM_LIMIT);
   static bool configured = false;
   static int max_clusters = 0;
   if (!configured) {
-    B200_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    B200_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GEMM_SMEM_LIMIT));
     if (PAIR) {
       cudaLaunchConfig_t q = {};
       q.gridDim = dim3(2 * (unsigned)(sm_count_cached() / 2));
       q.blockDim = dim3(GEMM_THREADS);
-      q.dynamicSmemBytes = smem;
+      q.dynamicSmemBytes = GEMM_SMEM_LIMIT;
       cudaLaunchAttribute a[1];
       a[0].id = cudaLaunchAttributeClusterDimension;
       a[0].val.clusterDim.x = 2;

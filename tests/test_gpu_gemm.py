@@ -198,7 +198,7 @@ def _tags(rank_of_row, dest_row):
     return torch.from_numpy((rank_of_row.astype(np.int64) << 40) | dest_row.astype(np.int64)).cuda()
 
 
-@pytest.mark.parametrize("R,d,f,E", [(700, 256, 192, 4), (2100, 1024, 1408, 8)])
+@pytest.mark.parametrize("R,d,f,E", [(700, 256, 192, 4), (2100, 1024, 1408, 8), (3000, 128, 64, 200)])
 def test_grouped_scatter_forms_match_in_place_forms(R, d, f, E):
     """The *_scatter entry points store Y / dZ rows where their tags say (two destination buffers standing in for two
     ranks); values must be bit-identical to the in-place entry points."""

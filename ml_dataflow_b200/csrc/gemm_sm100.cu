@@ -34,15 +34,28 @@ constexpr int A_BLKS = 2;
 constexpr int ACC_COLS = 256;
 constexpr int TMEM_COLS = 512;
 constexpr int EPI_WARPS = 8;
-constexpr int GEMM_THREADS = 64 + EPI_WARPS * 32;  // TMA warp, MMA warp, 8 epilogue warps
+constexpr int TAIL_WARP = 2 + EPI_WARPS;                // clears the reduction tail of grouped weight-gradient slabs
+constexpr int GEMM_THREADS = (3 + EPI_WARPS) * 32;      // TMA warp, MMA warp, 8 epilogue warps, tail warp
 constexpr int MAX_GROUPS = 1024;
 constexpr int MAX_STAGES = 6;
+
+#ifndef B200_PAIR_STAGES
+#define B200_PAIR_STAGES 6
+#endif
+#ifndef B200_SINGLE_STAGES
+#define B200_SINGLE_STAGES 4
+#endif
+#ifndef B200_PAIR_KSLABS
+#define B200_PAIR_KSLABS 2
+#endif
 
 template <bool PAIR>
 struct Cfg {
   static constexpr int B_BLKS = PAIR ? 2 : 4;
-  static constexpr int STAGE_BYTES = (A_BLKS + B_BLKS) * BLK_BYTES;
-  static constexpr int STAGES = PAIR ? 6 : 4;
+  static constexpr int SLAB_BYTES = (A_BLKS + B_BLKS) * BLK_BYTES;  // one 64-deep slice of both operands
+  static constexpr int KSLABS = PAIR ? B200_PAIR_KSLABS : 1;        // slices per pipeline stage (one barrier round trip)
+  static constexpr int STAGE_BYTES = KSLABS * SLAB_BYTES;
+  static constexpr int STAGES = PAIR ? B200_PAIR_STAGES / KSLABS : B200_SINGLE_STAGES;
   static constexpr int TILE_M = PAIR ? 2 * BM : BM;
 };
 
@@ -58,6 +71,7 @@ enum StatusCode {
   ST_MMA_TIMEOUT = 2,
   ST_EPILOGUE_TIMEOUT = 3,
   ST_PEER_TIMEOUT = 4,
+  ST_TAIL_TIMEOUT = 6,
   ST_BAD_ROW_TAG = 5  // a scatter tag named a rank or row outside the destination buffers; the row was not stored
 };
 
@@ -153,7 +167,7 @@ __device__ __forceinline__ float silu_f(float a) { return a / (1.0f + __expf(-a)
 
 // shared-memory bookkeeping that follows the stage buffers
 struct GemmSmemTail {
-  uint64_t full[MAX_STAGES], empty[MAX_STAGES], peer_full[MAX_STAGES], tfull[2], tempty[2];
+  uint64_t full[MAX_STAGES], empty[MAX_STAGES], peer_full[MAX_STAGES], tail_done[MAX_STAGES], tfull[2], tempty[2];
   uint32_t tmem_base;
   int abort_flag;
   int pad[2];
@@ -187,14 +201,16 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
   auto full_bar = [&](int s) { return ptx::smem_u32(&st->full[s]); };
   auto empty_bar = [&](int s) { return ptx::smem_u32(&st->empty[s]); };
   auto peer_bar = [&](int s) { return ptx::smem_u32(&st->peer_full[s]); };
+  auto tail_bar = [&](int s) { return ptx::smem_u32(&st->tail_done[s]); };
   auto tfull_bar = [&](int s) { return ptx::smem_u32(&st->tfull[s]); };
   auto tempty_bar = [&](int s) { return ptx::smem_u32(&st->tempty[s]); };
 
   if (tid == 0) {
     for (int s = 0; s < STAGES; s++) {
       ptx::mbar_init(full_bar(s), 1);
-      ptx::mbar_init(empty_bar(s), 1);
+      ptx::mbar_init(empty_bar(s), p.group_mode == GROUPED_K ? 2 : 1);  // MMA commit (+ the tail warp)
       ptx::mbar_init(peer_bar(s), 1);
+      ptx::mbar_init(tail_bar(s), 1);
     }
     for (int s = 0; s < 2; s++) {
       ptx::mbar_init(tfull_bar(s), 1);
@@ -317,8 +333,6 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
       auto ld3 = [&](uint32_t dst, const CUtensorMap *m, int c0, int c1, int c2) {
         ptx::tma_load_3d(dst, m, bar, c0, c1, c2);
       };
-      const int nb_loaded = (p.dual_b && !PAIR) ? 2 * nb : nb;
-      ptx::mbar_arrive_expect_tx(bar, (uint32_t)((A_BLKS + nb_loaded) * BLK_BYTES));
       if (!p.a_mn_major) {
         ld2(sA, mA, kk, a_row);
         ld2(sA + BLK_BYTES, mA, kk, a_row + 64);
@@ -344,13 +358,19 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
     uint32_t phase = 0;
     for (int tile = first_tile; sched.get(tile, t); tile += tile_step) {
       const int ksteps = ((t.k_len + BK - 1) / BK) * p.k_segments;
-      for (int ks = 0; ks < ksteps; ks++) {
+      const int nb = p.dual_b ? (t.nw >> 6) : (PAIR ? (t.nw >> 7) : (t.nw >> 6));
+      const int nb_loaded = (p.dual_b && !PAIR) ? 2 * nb : nb;
+      for (int ks = 0; ks < ksteps; ks += CF::KSLABS) {
         bool ok = true;
         if (lane == 0) {
           ok = xwait(empty_bar(stage), phase ^ 1u, ST_PRODUCER_TIMEOUT);
           if (ok) {
-            const uint32_t sA = smem_base + stage * STAGE_BYTES;
-            slab(t, ks, sA, sA + A_BLKS * BLK_BYTES, full_bar(stage));
+            const int nsl = min(CF::KSLABS, ksteps - ks);
+            ptx::mbar_arrive_expect_tx(full_bar(stage), (uint32_t)(nsl * (A_BLKS + nb_loaded) * BLK_BYTES));
+            for (int j = 0; j < nsl; j++) {
+              const uint32_t sA = smem_base + stage * STAGE_BYTES + j * CF::SLAB_BYTES;
+              slab(t, ks + j, sA, sA + A_BLKS * BLK_BYTES, full_bar(stage));
+            }
           }
         }
         ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
@@ -367,12 +387,11 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
     uint32_t phase = 0;
     int acc = 0;
     uint32_t acc_phase = 0;
+    uint32_t tail_par = 0;  // parity of tail_done[stage], one bit per stage
     for (int tile = first_tile; sched.get(tile, t); tile += tile_step) {
       const int ksteps_seg = (t.k_len + BK - 1) / BK;
       const int ksteps = ksteps_seg * p.k_segments;
       if (ksteps == 0) continue;
-      const int nb = p.dual_b ? (t.nw >> 6) : (PAIR ? (t.nw >> 7) : (t.nw >> 6));
-      const int nb_loaded = (p.dual_b && !PAIR) ? 2 * nb : nb;
       const int mma_n = p.dual_b ? 2 * t.nw : t.nw;
       const uint32_t idesc = ptx::make_idesc_bf16(CF::TILE_M, mma_n, p.a_mn_major, p.b_mn_major);
       const uint32_t d_tmem = tmem_base + (uint32_t)(acc * ACC_COLS);
@@ -382,24 +401,21 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
         if (!__all_sync(0xffffffffu, ok)) goto teardown;
         ptx::tc_fence_after();
       }
-      for (int ks = 0; ks < ksteps; ks++) {
-        // every CTA watches its own slab land ...
-        ok = wait_local(full_bar(stage), phase, ST_MMA_TIMEOUT);
-        if (!__all_sync(0xffffffffu, ok)) goto teardown;
-        const int kv = (p.group_mode == GROUPED_K) ? t.k_len - (ks % ksteps_seg) * BK : BK;  // valid reduction rows
-        if (kv < BK) {
-          // rows kv..63 of every 64x64 block belong to the next expert (or lie past the end):
-          // clear them in both operands. A row is 128 contiguous bytes in the swizzled layout.
-          unsigned char *stA = smem + stage * STAGE_BYTES;
-          const int chunks_per_blk = (BK - kv) * 8;
-          const int nb_all = A_BLKS + nb_loaded;
-          for (int i = lane; i < nb_all * chunks_per_blk; i += 32) {
-            const int b = i / chunks_per_blk, c = i - b * chunks_per_blk;
-            *reinterpret_cast<uint4 *>(stA + b * BLK_BYTES + kv * 128 + c * 16) = make_uint4(0, 0, 0, 0);
-          }
-          ptx::fence_proxy_async_smem();
-          __syncwarp();
+      for (int ks = 0; ks < ksteps; ks += CF::KSLABS) {
+        const int nsl = min(CF::KSLABS, ksteps - ks);
+        // every CTA watches its own slabs land; a stage whose last slab runs past the expert's rows (grouped
+        // weight gradients) is handed over by the tail warp instead, once it has cleared those rows
+        // 16-row groups of the stage's last slab that hold rows of this expert (all four except at the ragged end)
+        int last_k16 = BK / 16;
+        if (p.group_mode == GROUPED_K && ks + nsl == ksteps && (t.k_len & (BK - 1)) != 0)
+          last_k16 = ((t.k_len & (BK - 1)) + 15) >> 4;
+        if (p.group_mode == GROUPED_K && ks + nsl == ksteps && (t.k_len & 15) != 0) {
+          ok = wait_local(tail_bar(stage), (tail_par >> stage) & 1u, ST_MMA_TIMEOUT);
+          tail_par ^= 1u << stage;
+        } else {
+          ok = wait_local(full_bar(stage), phase, ST_MMA_TIMEOUT);
         }
+        if (!__all_sync(0xffffffffu, ok)) goto teardown;
         if (PAIR && !leader) {
           // ... the odd CTA then tells the even one that its half is in place
           if (lane == 0) ptx::mbar_arrive_remote(peer_bar(stage), 0);
@@ -410,17 +426,21 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
           }
           ptx::tc_fence_after();
           if (lane == 0) {
-            const uint32_t sA = smem_base + stage * STAGE_BYTES;
-            const uint32_t sB = sA + A_BLKS * BLK_BYTES;
+            for (int j = 0; j < nsl; j++) {
+              const uint32_t sA = smem_base + stage * STAGE_BYTES + j * CF::SLAB_BYTES;
+              const uint32_t sB = sA + A_BLKS * BLK_BYTES;
+              const int n16 = (j == nsl - 1) ? last_k16 : BK / 16;
 #pragma unroll
-            for (int k16 = 0; k16 < BK / 16; k16++) {
-              const uint64_t adesc = p.a_mn_major ? ptx::make_smem_desc(sA + k16 * 2048, BLK_BYTES, 1024)
-                                                  : ptx::make_smem_desc(sA + k16 * 32, 0, 1024);
-              const uint64_t bdesc = p.b_mn_major ? ptx::make_smem_desc(sB + k16 * 2048, BLK_BYTES, 1024)
-                                                  : ptx::make_smem_desc(sB + k16 * 32, 0, 1024);
-              const uint32_t accum = (ks > 0 || k16 > 0) ? 1u : 0u;
-              if (PAIR) ptx::umma_bf16_pair(d_tmem, adesc, bdesc, idesc, accum);
-              else ptx::umma_bf16(d_tmem, adesc, bdesc, idesc, accum);
+              for (int k16 = 0; k16 < BK / 16; k16++) {
+                if (k16 >= n16) break;
+                const uint64_t adesc = p.a_mn_major ? ptx::make_smem_desc(sA + k16 * 2048, BLK_BYTES, 1024)
+                                                    : ptx::make_smem_desc(sA + k16 * 32, 0, 1024);
+                const uint64_t bdesc = p.b_mn_major ? ptx::make_smem_desc(sB + k16 * 2048, BLK_BYTES, 1024)
+                                                    : ptx::make_smem_desc(sB + k16 * 32, 0, 1024);
+                const uint32_t accum = (ks + j > 0 || k16 > 0) ? 1u : 0u;
+                if (PAIR) ptx::umma_bf16_pair(d_tmem, adesc, bdesc, idesc, accum);
+                else ptx::umma_bf16(d_tmem, adesc, bdesc, idesc, accum);
+              }
             }
             if (PAIR) ptx::umma_commit_pair(empty_bar(stage));
             else ptx::umma_commit(empty_bar(stage));
@@ -440,6 +460,45 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
       if (++acc == 2) {
         acc = 0;
         acc_phase ^= 1u;
+      }
+    }
+  } else if (warp == TAIL_WARP) {
+    // ================= tail warp (grouped weight gradients) =================
+    // The last 64-row slab of an expert's reduction range also holds rows of the next expert (or rows past the
+    // end). This warp follows the producer's schedule, waits for such a slab to land, clears the rows past the end
+    // in every 64x64 block of both operands (a row is 128 contiguous bytes in the swizzled layout) and passes the
+    // stage on through tail_done, so the clearing is off the MMA warp's issue path.
+    if (p.group_mode == GROUPED_K) {
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int tile = first_tile; sched.get(tile, t); tile += tile_step) {
+        const int ksteps = (t.k_len + BK - 1) / BK;
+        const int nb = PAIR ? (t.nw >> 7) : (t.nw >> 6);
+        const int kv = t.k_len & (BK - 1);
+        for (int ks = 0; ks < ksteps; ks += CF::KSLABS) {
+          const int nsl = min(CF::KSLABS, ksteps - ks);
+          // every use of a stage is observed, and the stage is not refilled before that (this warp is the second
+          // arrival on the empty barrier), so the parity this warp waits for always names the right fill
+          const bool ok = wait_local(full_bar(stage), phase, ST_TAIL_TIMEOUT);
+          if (!__all_sync(0xffffffffu, ok)) goto teardown;
+          if (ks + nsl == ksteps && (kv & 15) != 0) {
+            // only the 16-row group that straddles the end is multiplied at all (the MMA warp skips the groups past
+            // it), so rows kv .. roundup(kv, 16) - 1 of every block are all there is to clear
+            unsigned char *stA = smem + stage * STAGE_BYTES + (nsl - 1) * CF::SLAB_BYTES;
+            const int chunks_per_blk = (16 - (kv & 15)) * 8;
+            for (int b = 0; b < A_BLKS + nb; b++)
+              for (int c = lane; c < chunks_per_blk; c += 32)
+                *reinterpret_cast<uint4 *>(stA + b * BLK_BYTES + kv * 128 + c * 16) = make_uint4(0, 0, 0, 0);
+            ptx::fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(tail_bar(stage));
+          }
+          if (lane == 0) ptx::mbar_arrive(empty_bar(stage));
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
       }
     }
   } else {

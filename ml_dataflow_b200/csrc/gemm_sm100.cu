@@ -167,13 +167,15 @@ __device__ __forceinline__ float silu_f(float a) { return a / (1.0f + __expf(-a)
 
 // shared-memory bookkeeping that follows the stage buffers
 struct GemmSmemTail {
-  uint64_t full[MAX_STAGES], empty[MAX_STAGES], peer_full[MAX_STAGES], tail_done[MAX_STAGES], tfull[2], tempty[2];
+  uint64_t full[MAX_STAGES], empty[MAX_STAGES], tail_done[MAX_STAGES], tfull[2], tempty[2];
   uint32_t tmem_base;
   int abort_flag;
-  int pad[2];
+  int pad[2];  // keeps what follows 16-byte aligned
   // followed in shared memory by the group tables (cnt[G], base[G], tpre[G + 1]; table_ints(G) ints) and, when
   // GemmParams::stage_out is set, by one 4 KiB staging block per epilogue warp
 };
+
+static_assert(sizeof(GemmSmemTail) % 16 == 0, "the staging blocks after the tables need 16-byte alignment");
 
 __host__ __device__ constexpr int table_ints(int groups) { return ((3 * groups + 1) + 3) & ~3; }
 constexpr int STAGE_OUT_BYTES_PER_WARP = 32 * 128;  // 32 rows x 64 bf16 columns
@@ -200,16 +202,14 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
   const uint32_t smem_base = ptx::smem_u32(smem);
   auto full_bar = [&](int s) { return ptx::smem_u32(&st->full[s]); };
   auto empty_bar = [&](int s) { return ptx::smem_u32(&st->empty[s]); };
-  auto peer_bar = [&](int s) { return ptx::smem_u32(&st->peer_full[s]); };
   auto tail_bar = [&](int s) { return ptx::smem_u32(&st->tail_done[s]); };
   auto tfull_bar = [&](int s) { return ptx::smem_u32(&st->tfull[s]); };
   auto tempty_bar = [&](int s) { return ptx::smem_u32(&st->tempty[s]); };
 
   if (tid == 0) {
     for (int s = 0; s < STAGES; s++) {
-      ptx::mbar_init(full_bar(s), 1);
+      ptx::mbar_init(full_bar(s), (PAIR && leader) ? 2 : 1);  // own loads (+ the odd CTA's hand-over)
       ptx::mbar_init(empty_bar(s), p.group_mode == GROUPED_K ? 2 : 1);  // MMA commit (+ the tail warp)
-      ptx::mbar_init(peer_bar(s), 1);
       ptx::mbar_init(tail_bar(s), 1);
     }
     for (int s = 0; s < 2; s++) {
@@ -354,78 +354,84 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
         for (int i = 0; i < nb; i++) ld3(sB + i * BLK_BYTES, mB, n_start + 64 * i, tt.k_row0 + kk, g3);
       }
     };
-    int stage = 0;
-    uint32_t phase = 0;
-    for (int tile = first_tile; sched.get(tile, t); tile += tile_step) {
-      const int ksteps = ((t.k_len + BK - 1) / BK) * p.k_segments;
-      const int nb = p.dual_b ? (t.nw >> 6) : (PAIR ? (t.nw >> 7) : (t.nw >> 6));
-      const int nb_loaded = (p.dual_b && !PAIR) ? 2 * nb : nb;
-      for (int ks = 0; ks < ksteps; ks += CF::KSLABS) {
-        bool ok = true;
-        if (lane == 0) {
-          ok = xwait(empty_bar(stage), phase ^ 1u, ST_PRODUCER_TIMEOUT);
-          if (ok) {
-            const int nsl = min(CF::KSLABS, ksteps - ks);
-            ptx::mbar_arrive_expect_tx(full_bar(stage), (uint32_t)(nsl * (A_BLKS + nb_loaded) * BLK_BYTES));
-            for (int j = 0; j < nsl; j++) {
-              const uint32_t sA = smem_base + stage * STAGE_BYTES + j * CF::SLAB_BYTES;
-              slab(t, ks + j, sA, sA + A_BLKS * BLK_BYTES, full_bar(stage));
-            }
+    // one thread runs the whole loop: no warp-wide operation sits between two stages
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool alive = true;
+      for (int tile = first_tile; alive && sched.get(tile, t); tile += tile_step) {
+        const int ksteps = ((t.k_len + BK - 1) / BK) * p.k_segments;
+        const int nb = p.dual_b ? (t.nw >> 6) : (PAIR ? (t.nw >> 7) : (t.nw >> 6));
+        const int nb_loaded = (p.dual_b && !PAIR) ? 2 * nb : nb;
+        for (int ks = 0; ks < ksteps; ks += CF::KSLABS) {
+          if (!xwait(empty_bar(stage), phase ^ 1u, ST_PRODUCER_TIMEOUT)) {
+            alive = false;
+            break;
           }
-        }
-        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-        if (!ok) goto teardown;
-        if (++stage == STAGES) {
-          stage = 0;
-          phase ^= 1u;
+          const int nsl = min(CF::KSLABS, ksteps - ks);
+          ptx::mbar_arrive_expect_tx(full_bar(stage), (uint32_t)(nsl * (A_BLKS + nb_loaded) * BLK_BYTES));
+          for (int j = 0; j < nsl; j++) {
+            const uint32_t sA = smem_base + stage * STAGE_BYTES + j * CF::SLAB_BYTES;
+            slab(t, ks + j, sA, sA + A_BLKS * BLK_BYTES, full_bar(stage));
+          }
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
         }
       }
     }
+    __syncwarp();
   } else if (warp == 1) {
     // ================= MMA issuer (even CTA) / slab forwarder (odd CTA of a pair) =================
-    int stage = 0;
-    uint32_t phase = 0;
-    int acc = 0;
-    uint32_t acc_phase = 0;
-    uint32_t tail_par = 0;  // parity of tail_done[stage], one bit per stage
-    for (int tile = first_tile; sched.get(tile, t); tile += tile_step) {
-      const int ksteps_seg = (t.k_len + BK - 1) / BK;
-      const int ksteps = ksteps_seg * p.k_segments;
-      if (ksteps == 0) continue;
-      const int mma_n = p.dual_b ? 2 * t.nw : t.nw;
-      const uint32_t idesc = ptx::make_idesc_bf16(CF::TILE_M, mma_n, p.a_mn_major, p.b_mn_major);
-      const uint32_t d_tmem = tmem_base + (uint32_t)(acc * ACC_COLS);
-      bool ok = true;
-      if (leader) {
-        ok = xwait(tempty_bar(acc), acc_phase ^ 1u, ST_MMA_TIMEOUT);
-        if (!__all_sync(0xffffffffu, ok)) goto teardown;
-        ptx::tc_fence_after();
-      }
-      for (int ks = 0; ks < ksteps; ks += CF::KSLABS) {
-        const int nsl = min(CF::KSLABS, ksteps - ks);
-        // every CTA watches its own slabs land; a stage whose last slab runs past the expert's rows (grouped
-        // weight gradients) is handed over by the tail warp instead, once it has cleared those rows
-        // 16-row groups of the stage's last slab that hold rows of this expert (all four except at the ragged end)
-        int last_k16 = BK / 16;
-        if (p.group_mode == GROUPED_K && ks + nsl == ksteps && (t.k_len & (BK - 1)) != 0)
-          last_k16 = ((t.k_len & (BK - 1)) + 15) >> 4;
-        if (p.group_mode == GROUPED_K && ks + nsl == ksteps && (t.k_len & 15) != 0) {
-          ok = wait_local(tail_bar(stage), (tail_par >> stage) & 1u, ST_MMA_TIMEOUT);
-          tail_par ^= 1u << stage;
-        } else {
-          ok = wait_local(full_bar(stage), phase, ST_MMA_TIMEOUT);
-        }
-        if (!__all_sync(0xffffffffu, ok)) goto teardown;
-        if (PAIR && !leader) {
-          // ... the odd CTA then tells the even one that its half is in place
-          if (lane == 0) ptx::mbar_arrive_remote(peer_bar(stage), 0);
-        } else {
-          if (PAIR) {
-            ok = xwait(peer_bar(stage), phase, ST_PEER_TIMEOUT);
-            if (!__all_sync(0xffffffffu, ok)) goto teardown;
-          }
+    // again a single thread: wait, fence, issue, commit
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      uint32_t tail_par = 0;  // parity of tail_done[stage], one bit per stage
+      bool alive = true;
+      for (int tile = first_tile; alive && sched.get(tile, t); tile += tile_step) {
+        const int ksteps_seg = (t.k_len + BK - 1) / BK;
+        const int ksteps = ksteps_seg * p.k_segments;
+        if (ksteps == 0) continue;
+        const int mma_n = p.dual_b ? 2 * t.nw : t.nw;
+        const uint32_t idesc = ptx::make_idesc_bf16(CF::TILE_M, mma_n, p.a_mn_major, p.b_mn_major);
+        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * ACC_COLS);
+        if (leader) {
+          if (!xwait(tempty_bar(acc), acc_phase ^ 1u, ST_MMA_TIMEOUT)) break;
           ptx::tc_fence_after();
-          if (lane == 0) {
+        }
+        for (int ks = 0; ks < ksteps; ks += CF::KSLABS) {
+          const int nsl = min(CF::KSLABS, ksteps - ks);
+          const bool last = ks + nsl == ksteps;
+          // 16-row groups of the stage's last slab that hold rows of this expert (all four except at the ragged
+          // end of a grouped weight gradient)
+          int last_k16 = BK / 16;
+          if (p.group_mode == GROUPED_K && last && (t.k_len & (BK - 1)) != 0) last_k16 = ((t.k_len & (BK - 1)) + 15) >> 4;
+          // every CTA watches its own slabs land; a stage whose last slab straddles the end of the expert's rows is
+          // handed over by the tail warp instead, once it has cleared the rows past the end
+          bool ok;
+          if (p.group_mode == GROUPED_K && last && (t.k_len & 15) != 0) {
+            ok = wait_local(tail_bar(stage), (tail_par >> stage) & 1u, ST_MMA_TIMEOUT);
+            tail_par ^= 1u << stage;
+          } else if (!(PAIR && leader)) {
+            ok = wait_local(full_bar(stage), phase, ST_MMA_TIMEOUT);
+          } else {
+            ok = true;
+          }
+          // in a pair the even CTA's barrier also counts the odd CTA's hand-over: one cluster-scope wait covers both
+          if (ok && PAIR && leader) ok = xwait(full_bar(stage), phase, ST_PEER_TIMEOUT);
+          if (!ok) {
+            alive = false;
+            break;
+          }
+          if (PAIR && !leader) {
+            // ... the odd CTA then tells the even one that its half is in place
+            ptx::mbar_arrive_remote(full_bar(stage), 0);
+          } else {
+            ptx::tc_fence_after();
             for (int j = 0; j < nsl; j++) {
               const uint32_t sA = smem_base + stage * STAGE_BYTES + j * CF::SLAB_BYTES;
               const uint32_t sB = sA + A_BLKS * BLK_BYTES;
@@ -445,23 +451,23 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
             if (PAIR) ptx::umma_commit_pair(empty_bar(stage));
             else ptx::umma_commit(empty_bar(stage));
           }
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
         }
-        __syncwarp();
-        if (++stage == STAGES) {
-          stage = 0;
-          phase ^= 1u;
+        if (!alive) break;
+        if (leader) {
+          if (PAIR) ptx::umma_commit_pair(tfull_bar(acc));
+          else ptx::umma_commit(tfull_bar(acc));
         }
-      }
-      if (leader && lane == 0) {
-        if (PAIR) ptx::umma_commit_pair(tfull_bar(acc));
-        else ptx::umma_commit(tfull_bar(acc));
-      }
-      __syncwarp();
-      if (++acc == 2) {
-        acc = 0;
-        acc_phase ^= 1u;
+        if (++acc == 2) {
+          acc = 0;
+          acc_phase ^= 1u;
+        }
       }
     }
+    __syncwarp();
   } else if (warp == TAIL_WARP) {
     // ================= tail warp (grouped weight gradients) =================
     // The last 64-row slab of an expert's reduction range also holds rows of the next expert (or rows past the

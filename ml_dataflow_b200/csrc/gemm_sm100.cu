@@ -76,6 +76,14 @@ enum StatusCode {
 };
 
 __device__ int g_gemm_status = 0;
+#ifdef B200_GEMM_STATS
+__device__ unsigned long long g_gemm_stats[8];
+#define STAT_T0() const long long st_t0 = clock64()
+#define STAT_ADD(i) st_acc[i] += clock64() - st_t0
+#else
+#define STAT_T0()
+#define STAT_ADD(i)
+#endif
 
 struct GemmParams {
   CUtensorMap tmA, tmA2, tmB, tmB2;
@@ -356,6 +364,10 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
     };
     // one thread runs the whole loop: no warp-wide operation sits between two stages
     if (lane == 0) {
+#ifdef B200_GEMM_STATS
+      long long st_acc[4] = {0, 0, 0, 0};
+      const long long st_begin = clock64();
+#endif
       int stage = 0;
       uint32_t phase = 0;
       bool alive = true;
@@ -364,9 +376,13 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
         const int nb = p.dual_b ? (t.nw >> 6) : (PAIR ? (t.nw >> 7) : (t.nw >> 6));
         const int nb_loaded = (p.dual_b && !PAIR) ? 2 * nb : nb;
         for (int ks = 0; ks < ksteps; ks += CF::KSLABS) {
-          if (!xwait(empty_bar(stage), phase ^ 1u, ST_PRODUCER_TIMEOUT)) {
-            alive = false;
-            break;
+          {
+            STAT_T0();
+            if (!xwait(empty_bar(stage), phase ^ 1u, ST_PRODUCER_TIMEOUT)) {
+              alive = false;
+              break;
+            }
+            STAT_ADD(0);
           }
           const int nsl = min(CF::KSLABS, ksteps - ks);
           ptx::mbar_arrive_expect_tx(full_bar(stage), (uint32_t)(nsl * (A_BLKS + nb_loaded) * BLK_BYTES));
@@ -380,12 +396,20 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
           }
         }
       }
+#ifdef B200_GEMM_STATS
+      atomicAdd(&g_gemm_stats[0], (unsigned long long)st_acc[0]);
+      atomicAdd(&g_gemm_stats[1], (unsigned long long)(clock64() - st_begin));
+#endif
     }
     __syncwarp();
   } else if (warp == 1) {
     // ================= MMA issuer (even CTA) / slab forwarder (odd CTA of a pair) =================
     // again a single thread: wait, fence, issue, commit
     if (lane == 0) {
+#ifdef B200_GEMM_STATS
+      long long st_acc[4] = {0, 0, 0, 0};
+      const long long st_begin = clock64();
+#endif
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
@@ -400,7 +424,9 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
         const uint32_t idesc = ptx::make_idesc_bf16(CF::TILE_M, mma_n, p.a_mn_major, p.b_mn_major);
         const uint32_t d_tmem = tmem_base + (uint32_t)(acc * ACC_COLS);
         if (leader) {
+          STAT_T0();
           if (!xwait(tempty_bar(acc), acc_phase ^ 1u, ST_MMA_TIMEOUT)) break;
+          STAT_ADD(1);
           ptx::tc_fence_after();
         }
         for (int ks = 0; ks < ksteps; ks += CF::KSLABS) {
@@ -413,6 +439,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
           // every CTA watches its own slabs land; a stage whose last slab straddles the end of the expert's rows is
           // handed over by the tail warp instead, once it has cleared the rows past the end
           bool ok;
+          STAT_T0();
           if (p.group_mode == GROUPED_K && last && (t.k_len & 15) != 0) {
             ok = wait_local(tail_bar(stage), (tail_par >> stage) & 1u, ST_MMA_TIMEOUT);
             tail_par ^= 1u << stage;
@@ -427,6 +454,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
             alive = false;
             break;
           }
+          STAT_ADD(0);
           if (PAIR && !leader) {
             // ... the odd CTA then tells the even one that its half is in place
             ptx::mbar_arrive_remote(full_bar(stage), 0);
@@ -466,6 +494,16 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
           acc_phase ^= 1u;
         }
       }
+#ifdef B200_GEMM_STATS
+      if (leader) {
+        atomicAdd(&g_gemm_stats[2], (unsigned long long)st_acc[0]);
+        atomicAdd(&g_gemm_stats[3], (unsigned long long)st_acc[1]);
+        atomicAdd(&g_gemm_stats[4], (unsigned long long)(clock64() - st_begin));
+      } else {
+        atomicAdd(&g_gemm_stats[5], (unsigned long long)st_acc[0]);
+        atomicAdd(&g_gemm_stats[6], (unsigned long long)(clock64() - st_begin));
+      }
+#endif
     }
     __syncwarp();
   } else if (warp == TAIL_WARP) {
@@ -922,6 +960,18 @@ static void zero_params(GemmParams &p) { memset(&p, 0, sizeof(p)); }
 }  // namespace b200
 
 using namespace b200;
+
+#ifdef B200_GEMM_STATS
+// debugging build only: cycles summed over CTAs {producer wait-empty, producer total, leader wait-full, leader
+// wait-accumulator, leader total, odd-CTA wait-full, odd-CTA total}; reading clears
+extern "C" int b200_dbg_gemm_stats(unsigned long long *out) {
+  B200_CUDA(cudaDeviceSynchronize());
+  B200_CUDA(cudaMemcpyFromSymbol(out, g_gemm_stats, sizeof(unsigned long long) * 8));
+  unsigned long long z[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  B200_CUDA(cudaMemcpyToSymbol(g_gemm_stats, z, sizeof(z)));
+  return 0;
+}
+#endif
 
 extern "C" int b200_gemm_set_pair_mode(int on) {
   g_pair_mode = on ? 1 : 0;

@@ -175,7 +175,7 @@ def algorithmic_work(cfg):
 
 # dram__bytes_read.sum + dram__bytes_write.sum of the seven expert GEMM launches of one step, from one ncu pass on the
 # full-size 1-GPU workload (profiles/gemm_sm100_kernel__moe_layer_T8192_d4096_E64_k8_f1408.md, section 2)
-NCU_GEMM_DRAM_BYTES_PER_STEP = {(8192, 4096, 64, 8, 1408): 16.3e9}
+NCU_GEMM_DRAM_BYTES_PER_STEP = {(8192, 4096, 64, 8, 1408): 16.5e9}
 
 NVLINK_PEER_GBS = 770.0  # measured peer copy per direction on this pool (nominal 900)
 

@@ -34,8 +34,13 @@ constexpr int A_BLKS = 2;
 constexpr int ACC_COLS = 256;
 constexpr int TMEM_COLS = 512;
 constexpr int EPI_WARPS = 8;
+#ifndef B200_TWO_PRODUCERS
+#define B200_TWO_PRODUCERS 1
+#endif
 constexpr int TAIL_WARP = 2 + EPI_WARPS;                // clears the reduction tail of grouped weight-gradient slabs
-constexpr int GEMM_THREADS = (3 + EPI_WARPS) * 32;      // TMA warp, MMA warp, 8 epilogue warps, tail warp
+constexpr int PRODUCER_B_WARP = 3 + EPI_WARPS;          // second TMA thread: the B operand (warp 0 keeps A)
+constexpr int NUM_PRODUCERS = B200_TWO_PRODUCERS ? 2 : 1;
+constexpr int GEMM_THREADS = (3 + EPI_WARPS + (B200_TWO_PRODUCERS ? 1 : 0)) * 32;
 constexpr int MAX_GROUPS = 1024;
 constexpr int MAX_STAGES = 6;
 
@@ -216,7 +221,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
 
   if (tid == 0) {
     for (int s = 0; s < STAGES; s++) {
-      ptx::mbar_init(full_bar(s), (PAIR && leader) ? 2 : 1);  // own loads (+ the odd CTA's hand-over)
+      ptx::mbar_init(full_bar(s), NUM_PRODUCERS + ((PAIR && leader) ? 1 : 0));  // own loads (+ the odd CTA's hand-over)
       ptx::mbar_init(empty_bar(s), p.group_mode == GROUPED_K ? 2 : 1);  // MMA commit (+ the tail warp)
       ptx::mbar_init(tail_bar(s), 1);
     }
@@ -323,8 +328,12 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
     }
   };
   Tile t;
-  if (warp == 0) {
-    // ================= TMA producer (every CTA loads its own boxes) =================
+  if (warp == 0 || (NUM_PRODUCERS == 2 && warp == PRODUCER_B_WARP)) {
+    // ================= TMA producers (every CTA loads its own boxes) =================
+    // Two threads issue the loads, warp 0 those of A and PRODUCER_B_WARP those of B: one thread issuing all eight
+    // boxes of a stage spends 85 % of its time inside cp.async.bulk.tensor.
+    const bool do_a = (NUM_PRODUCERS == 1) || warp == 0;
+    const bool do_b = (NUM_PRODUCERS == 1) || warp != 0;
     // issue the loads of one slab into (sA, sB), counted on `bar`
     auto slab = [&](const Tile &tt, int ks, uint32_t sA, uint32_t sB, uint32_t bar) {
       const int ksteps_seg = (tt.k_len + BK - 1) / BK;
@@ -341,13 +350,16 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
       auto ld3 = [&](uint32_t dst, const CUtensorMap *m, int c0, int c1, int c2) {
         ptx::tma_load_3d(dst, m, bar, c0, c1, c2);
       };
-      if (!p.a_mn_major) {
-        ld2(sA, mA, kk, a_row);
-        ld2(sA + BLK_BYTES, mA, kk, a_row + 64);
-      } else {
-        ld2(sA, mA, a_row, tt.k_row0 + kk);
-        ld2(sA + BLK_BYTES, mA, a_row + 64, tt.k_row0 + kk);
+      if (do_a) {
+        if (!p.a_mn_major) {
+          ld2(sA, mA, kk, a_row);
+          ld2(sA + BLK_BYTES, mA, kk, a_row + 64);
+        } else {
+          ld2(sA, mA, a_row, tt.k_row0 + kk);
+          ld2(sA + BLK_BYTES, mA, a_row + 64, tt.k_row0 + kk);
+        }
       }
+      if (!do_b) return;
       if (p.dual_b) {
         if (PAIR) {  // even CTA holds the W1 columns, odd CTA the W3 columns
           const CUtensorMap *mine = cta_rank ? &p.tmB2 : &p.tmB;
@@ -385,7 +397,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
             STAT_ADD(0);
           }
           const int nsl = min(CF::KSLABS, ksteps - ks);
-          ptx::mbar_arrive_expect_tx(full_bar(stage), (uint32_t)(nsl * (A_BLKS + nb_loaded) * BLK_BYTES));
+          const int my_blks = (do_a ? A_BLKS : 0) + (do_b ? nb_loaded : 0);
+          ptx::mbar_arrive_expect_tx(full_bar(stage), (uint32_t)(nsl * my_blks * BLK_BYTES));
           for (int j = 0; j < nsl; j++) {
             const uint32_t sA = smem_base + stage * STAGE_BYTES + j * CF::SLAB_BYTES;
             slab(t, ks + j, sA, sA + A_BLKS * BLK_BYTES, full_bar(stage));
@@ -460,6 +473,9 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
             ptx::mbar_arrive_remote(full_bar(stage), 0);
           } else {
             ptx::tc_fence_after();
+#ifdef B200_GEMM_STATS
+            const long long st_issue0 = clock64();
+#endif
             for (int j = 0; j < nsl; j++) {
               const uint32_t sA = smem_base + stage * STAGE_BYTES + j * CF::SLAB_BYTES;
               const uint32_t sB = sA + A_BLKS * BLK_BYTES;
@@ -476,8 +492,15 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
                 else ptx::umma_bf16(d_tmem, adesc, bdesc, idesc, accum);
               }
             }
+#ifdef B200_GEMM_STATS
+            const long long st_issue1 = clock64();
+            st_acc[2] += st_issue1 - st_issue0;
+#endif
             if (PAIR) ptx::umma_commit_pair(empty_bar(stage));
             else ptx::umma_commit(empty_bar(stage));
+#ifdef B200_GEMM_STATS
+            st_acc[3] += clock64() - st_issue1;
+#endif
           }
           if (++stage == STAGES) {
             stage = 0;
@@ -499,7 +522,9 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
         atomicAdd(&g_gemm_stats[2], (unsigned long long)st_acc[0]);
         atomicAdd(&g_gemm_stats[3], (unsigned long long)st_acc[1]);
         atomicAdd(&g_gemm_stats[4], (unsigned long long)(clock64() - st_begin));
-      } else {
+        atomicAdd(&g_gemm_stats[7], (unsigned long long)st_acc[2]);
+        atomicAdd(&g_gemm_stats[5], (unsigned long long)st_acc[3]);
+      } else if (false) {
         atomicAdd(&g_gemm_stats[5], (unsigned long long)st_acc[0]);
         atomicAdd(&g_gemm_stats[6], (unsigned long long)(clock64() - st_begin));
       }

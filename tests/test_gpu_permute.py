@@ -131,3 +131,53 @@ def test_prepare_experts_weighted(oracle):
     ops.prepare_experts_weighted(T, d, k, dev_bf16(X), dev(tm), torch.from_numpy(w).cuda(), zone)
     torch.cuda.synchronize()
     np.testing.assert_array_equal(host_bits(zone), ref)
+
+
+def test_gather_combine_skewed_load_identity_experts_full_size():
+    """T=65536, d=4096, 64 experts, top-8, Zipf(1.1) expert popularity, identity experts (BASELINE config 3).
+
+    Size-independent properties: the gathered zone holds exactly the rows the mapping names (checked on sampled
+    rows and through a column checksum), counts add up, the heaviest expert is several times the mean, and the
+    weighted combine of the untouched zone returns every token row (gate weights sum to 1) within one bf16 ulp."""
+    require_b200()
+    from ml_dataflow_b200 import ops
+
+    T, d, E, k = 65536, 4096, 64, 8
+    gen = torch.Generator(device="cuda").manual_seed(0xB2000010)
+    logits = torch.randn((T, E), generator=gen, device="cuda")
+    rank = torch.randperm(E, generator=torch.Generator().manual_seed(0xB2000011)).float() + 1.0
+    logits += torch.log(rank.pow(-1.1) / rank.pow(-1.1).sum()).cuda()[None, :]
+    X = torch.randn((T, d), generator=gen, device="cuda").to(torch.bfloat16)
+    w = torch.empty((T, k), dtype=torch.float32, device="cuda")
+    ch = torch.empty((T, k), dtype=torch.int16, device="cuda")
+    counts = torch.zeros(E + 1, dtype=torch.int32, device="cuda")
+    cumsum = torch.zeros(E, dtype=torch.int32, device="cuda")
+    em = torch.empty(T * k, dtype=torch.int32, device="cuda")
+    tm = torch.empty((T, k), dtype=torch.int32, device="cuda")
+    ws = torch.empty(ops.build_expert_mapping_workspace_bytes(T, E, k), dtype=torch.uint8, device="cuda")
+    ops.select_experts(T, E, k, logits, w, ch, counts, cumsum, None)
+    ops.build_expert_mapping(T, E, k, ch, cumsum, em, tm, ws)
+    zone = torch.empty((T * k, d), dtype=torch.bfloat16, device="cuda")
+    ops.prepare_experts(T, d, k, X, tm, zone)
+    out = torch.zeros((T, d), dtype=torch.bfloat16, device="cuda")
+    ops.merge_experts(T, d, k, zone, tm, w, out)
+    torch.cuda.synchronize()
+
+    c = counts[:E].cpu().numpy().astype(np.int64)
+    assert c.sum() == T * k
+    np.testing.assert_array_equal(cumsum.cpu().numpy(), np.cumsum(c))
+    assert c.max() > 3 * c.mean() and c.min() < c.mean()  # the load really is skewed
+    # every zone row is the row of the token expert_mapping names
+    rows = torch.randint(0, T * k, (4096,), generator=torch.Generator().manual_seed(1)).cuda()
+    assert torch.equal(zone[rows], X[em[rows].long()])
+    # checksum over all rows: column sums of the zone == sum over tokens of k * X (fp64 on the device)
+    zs = torch.zeros(d, dtype=torch.float64, device="cuda")
+    for r0 in range(0, T * k, 32768):
+        zs += zone[r0:r0 + 32768].double().sum(dim=0)
+    xs = torch.zeros(d, dtype=torch.float64, device="cuda")
+    for r0 in range(0, T, 32768):
+        xs += X[r0:r0 + 32768].double().sum(dim=0) * k
+    assert torch.allclose(zs, xs, rtol=0, atol=1e-6)
+    # identity experts: sum_j w_j * x == x up to the rounding of the result
+    xf, of = X.float(), out.float()
+    assert ((of - xf).abs() <= xf.abs() * 2.0 ** -7 + 1e-30).all()

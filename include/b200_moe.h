@@ -282,6 +282,59 @@ int b200_scatter_row_weights(int num_tokens, int top_k, const int *token_mapping
 int b200_gather_router_grad(int num_tokens, int num_routed_experts, int top_k, const int *token_mapping,
                             const uint16_t *chosen_experts, const float *dP, void *dX_routed, void *stream);
 
+/* ---- the whole MoE feed-forward in one call --------------------------------------------------- */
+
+/*
+ * Buffers of one MoE feed-forward: the MoE fields of the reference's Seq_Batch_Saved_Activations
+ * (libdataflowmodels/include/seq_batch_structs.h:256-281) plus the workspace its block carves
+ * (Seq_Batch_Activation_Workspace, 369-395). R = total_tokens * top_k. All device memory, all the caller's.
+ */
+typedef struct B200MoeBlock {
+  int total_tokens, model_dim, num_experts, top_k, ffn_dim;
+  /* bf16 weights: Wr [E][d]; W1, W3 [E][f][d]; W2 [E][d][f]; strides between experts in elements */
+  const void *Wr, *W1, *W3, *W2;
+  int64_t w1_stride_elems, w3_stride_elems, w2_stride_elems;
+  /* written by the forward, read by the backward */
+  float *logits;               /* [T][E] fp32 */
+  float *token_expert_weights; /* [T][k] */
+  uint16_t *chosen_experts;    /* [T][k] */
+  int *expert_counts;          /* [E + 1] */
+  int *expert_counts_cumsum;   /* [E], inclusive after the forward */
+  int *host_expert_counts;     /* optional (NULL): mapped pinned host memory, valid after a stream sync */
+  int *expert_mapping;         /* [R] */
+  int *token_mapping;          /* [T][k] */
+  void *zone, *x1, *x3, *h;    /* bf16 [R][d], [R][f], [R][f], [R][f] */
+  void *Y;                     /* bf16 [R][d]: expert outputs before the combine */
+  void *mapping_workspace;     /* b200_build_expert_mapping_workspace_bytes(T, E, k) bytes */
+  size_t mapping_workspace_bytes;
+  /* backward workspace (may be NULL for forward-only use) */
+  void *dY_zone;               /* bf16 [R][d] */
+  float *row_weights, *dP;     /* [R] each */
+  void *dx1, *dx3;             /* bf16 [R][f] */
+  void *dZ;                    /* bf16 [R][d] (may be the same memory as Y) */
+  void *dX_routed;             /* bf16 [T][E] */
+} B200MoeBlock;
+
+/*
+ * Forward of the MoE part of dataflow_submit_transformer_moe_block
+ * (libdataflowmodels/src/transformer/src/dataflow_transformer.c:2710-2974): router GEMM (fp32 logits),
+ * select_experts, build_expert_mapping, prepare_experts, all experts' SwiGLU MLP in two grouped launches,
+ * merge_experts onto X_combined (which holds the residual). Zeroes the counters itself. Unlike the reference there
+ * is no stream synchronisation in the middle (2789) and no host loop over experts: the row counts stay on the
+ * device.
+ */
+int b200_moe_block_fwd(const B200MoeBlock *block, const void *Xn, void *X_combined, void *stream);
+
+/*
+ * Backward of the same: what dataflow_submit_transformer_moe_block_bwd_x (3399-3719) and
+ * dataflow_submit_transformer_moe_block_bwd_w (4062-4185) compute between them. dXn [T][d] is overwritten; dWr
+ * [E][d], dW1, dW3 [E][f][d], dW2 [E][d][f] (bf16) are accumulated into (beta = 1, one rounding), as the
+ * reference's gradient GEMMs do; dW1 / dW3 / dW2 may be NULL to skip the weight gradients. The expert output is not
+ * recomputed (3494-3516): the router's dot product comes out of the W2-dgrad epilogue.
+ */
+int b200_moe_block_bwd(const B200MoeBlock *block, const void *Xn, const void *dOut, void *dXn, void *dWr, void *dW1,
+                       void *dW3, void *dW2, void *stream);
+
 /* ---- expert parallelism over NVLink peer memory (no counterpart in the reference, which is single-GPU) ---- */
 
 /*

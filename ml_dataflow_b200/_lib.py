@@ -43,9 +43,28 @@ SIGNATURES = {
                                           _vp, _vp, _i, _i64, _vp]),
     "b200_moe_experts_bwd_x_scatter": (_i, [_i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp,
                                             _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i64, _vp]),
+    "b200_moe_block_fwd": (_i, [_vp, _vp, _vp, _vp]),
+    "b200_moe_block_bwd": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "b200_scatter_row_weights": (_i, [_i, _i, _vp, _vp, _vp, _vp]),
     "b200_gather_router_grad": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp]),
 }
+
+
+
+class MoeBlock(C.Structure):
+    """ctypes mirror of B200MoeBlock in include/b200_moe.h (same field order)."""
+    _fields_ = [
+        ("total_tokens", _i), ("model_dim", _i), ("num_experts", _i), ("top_k", _i), ("ffn_dim", _i),
+        ("Wr", _vp), ("W1", _vp), ("W3", _vp), ("W2", _vp),
+        ("w1_stride_elems", _i64), ("w3_stride_elems", _i64), ("w2_stride_elems", _i64),
+        ("logits", _vp), ("token_expert_weights", _vp), ("chosen_experts", _vp), ("expert_counts", _vp),
+        ("expert_counts_cumsum", _vp), ("host_expert_counts", _vp), ("expert_mapping", _vp), ("token_mapping", _vp),
+        ("zone", _vp), ("x1", _vp), ("x3", _vp), ("h", _vp), ("Y", _vp),
+        ("mapping_workspace", _vp), ("mapping_workspace_bytes", _sz),
+        ("dY_zone", _vp), ("row_weights", _vp), ("dP", _vp), ("dx1", _vp), ("dx3", _vp), ("dZ", _vp),
+        ("dX_routed", _vp),
+    ]
+
 
 _lib = None
 

@@ -67,6 +67,19 @@ class MoELayer:
             ev.record()
             self.profile.append((name, ev))
 
+    def block(self, Wr, W1, W3, W2):
+        """The layer's buffers as the C structure `b200_moe_block_fwd` / `b200_moe_block_bwd` take."""
+        from . import _lib
+
+        p = lambda t: None if t is None else t.data_ptr()
+        d, f = self.d, self.f
+        return _lib.MoeBlock(
+            self.T, self.d, self.E, self.k, self.f, p(Wr), p(W1), p(W3), p(W2), f * d, f * d, d * f,
+            p(self.logits), p(self.weights), p(self.chosen), p(self.counts), p(self.cumsum), None,
+            p(self.expert_mapping), p(self.token_mapping), p(self.zone), p(self.x1), p(self.x3), p(self.h), p(self.Y),
+            p(self.map_ws), self.map_ws.numel(), p(self.dYz), p(self.row_w), p(self.dP), p(self.dx1), p(self.dx3),
+            p(self.dZ), p(self.dX_routed))
+
     # ------------------------------------------------------------------ routing (shared)
     def route(self, Xn, Wr, logits=None):
         T, d, E, k = self.T, self.d, self.E, self.k

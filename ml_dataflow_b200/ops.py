@@ -247,3 +247,14 @@ def moe_experts_bwd_x_scatter(total_rows, model_dim, ffn_dim, num_experts, dY_zo
                                                       _p(expert_counts_cumsum), _p(dx1), _p(dx3), _p(hs), _p(dP),
                                                       _p(row_tags), _peer_array(dest_buffers), len(dest_buffers),
                                                       rows_per_buffer, _stream()), "moe_experts_bwd_x_scatter", 2)
+
+
+def moe_block_fwd(block, Xn, X_combined):
+    """block: a filled `_lib.MoeBlock` (see MoELayer.block). One C call issues the whole forward."""
+    _check(_lib.load().b200_moe_block_fwd(C.byref(block), _p(Xn), _p(X_combined), _stream()), "moe_block_fwd", 8)
+
+
+def moe_block_bwd(block, Xn, dOut, dXn, dWr, dW1, dW3, dW2):
+    _check(_lib.load().b200_moe_block_bwd(C.byref(block), _p(Xn), _p(dOut), _p(dXn), _p(dWr), _p(dW1), _p(dW3),
+                                          _p(dW2), _stream()), "moe_block_bwd",
+           10 + sum(g is not None for g in (dW1, dW3, dW2)))

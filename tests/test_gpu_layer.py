@@ -253,3 +253,50 @@ def test_layer_properties_full_size():
         got = layer.Y[base[e]:base[e] + n].float()
         err = (got - y).abs()
         assert (err <= 1e-3 + 2e-2 * y.abs()).float().mean() > 0.999, f"expert {e}"
+
+
+@pytest.mark.parametrize("T,d,E,k,f", [(512, 256, 16, 4, 192), (2048, 1024, 16, 2, 1024)])
+def test_c_block_driver_matches_fast_path(T, d, E, k, f):
+    """b200_moe_block_fwd / _bwd (one C call per direction) issue the same kernels in the same order as the Python
+    fast path, which the tests above hold to the oracle: everything that does not pass through the fp32 atomics of
+    the router dot product must be bit-identical, the router gradients equal to rounding."""
+    require_b200()
+    from ml_dataflow_b200 import ops
+    from ml_dataflow_b200.moe_layer import MoELayer
+
+    X, Wr, W1, W3, W2, dOut, g0 = make_case(T * 3 + f, T, d, E, k, f, wstd=0.05, grad_init=0.05)
+    Xd, Wrd, W1d, W3d, W2d, dOd = (dev_bf16(a) for a in (X, Wr, W1, W3, W2, dOut))
+    res = []
+    for use_block in (False, True):
+        layer = MoELayer(T, d, E, k, f)
+        out = dev_bf16(X.copy())  # the residual
+        dXn = torch.empty((T, d), dtype=torch.bfloat16, device="cuda")
+        G = {n: dev_bf16(g0[n].copy()) for n in ("dWr", "dW1", "dW3", "dW2")}
+        if use_block:
+            blk = layer.block(Wrd, W1d, W3d, W2d)
+            ops.moe_block_fwd(blk, Xd, out)
+            ops.moe_block_bwd(blk, Xd, dOd, dXn, G["dWr"], G["dW1"], G["dW3"], G["dW2"])
+        else:
+            layer.forward(Xd, Wrd, W1d, W3d, W2d, out)
+            layer.backward(Xd, Wrd, W1d, W3d, W2d, dOd, dXn, G["dWr"], G["dW1"], G["dW3"], G["dW2"])
+        assert ops.gemm_status() == 0
+        res.append((layer, out, dXn, G))
+    (la, oa, xa, ga), (lb, ob, xb, gb) = res
+    same = lambda p, q: torch.equal(p.view(torch.uint8), q.view(torch.uint8))
+    for name in ("logits", "weights", "chosen", "cumsum", "expert_mapping", "token_mapping", "zone", "x1", "x3", "h", "Y",
+                 "dYz", "dx1", "dx3", "dZ"):
+        assert same(getattr(la, name), getattr(lb, name)), name
+    assert same(la.counts[:E], lb.counts[:E])
+    assert same(oa, ob)
+    for n in ("dW1", "dW3", "dW2"):
+        assert same(ga[n], gb[n]), n
+    assert_close(f32(host_bits(xb)), f32(host_bits(xa)), rtol=2e-2, atol=1e-3, what="dXn")
+    assert_close(f32(host_bits(gb["dWr"])), f32(host_bits(ga["dWr"])), rtol=2e-2, atol=1e-3, what="dWr")
+    # forward-only use: no backward workspace, no weight gradients wanted
+    blk = lb.block(Wrd, W1d, W3d, W2d)
+    blk.dY_zone = None
+    out2 = dev_bf16(X.copy())
+    ops.moe_block_fwd(blk, Xd, out2)
+    assert same(out2, ob)
+    with pytest.raises(RuntimeError):
+        ops.moe_block_bwd(blk, Xd, dOd, xb, gb["dWr"], None, None, None)

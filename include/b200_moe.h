@@ -326,6 +326,16 @@ typedef struct B200MoeBlock {
 int b200_moe_block_fwd(const B200MoeBlock *block, const void *Xn, void *X_combined, void *stream);
 
 /*
+ * Stands in for the MoE part of dataflow_submit_transformer_moe_block_recompute (2989-3323) when the forward's
+ * workspace (zone, h - and x1, x3 unless they were saved) has been reused before the backward runs: re-gathers the
+ * zone from Xn with the saved token_mapping and re-forms h = silu(x1) * x3, from the saved x1, x3
+ * (recompute_x1_x3 == 0) or together with x1, x3 from the zone in one grouped launch (recompute_x1_x3 != 0). The W2
+ * product is never recomputed: b200_moe_block_bwd does not need it. Results are bit-identical to the forward's.
+ * b200_moe_experts_fwd with Y == NULL (and W2 == NULL) is the gate-up launch alone.
+ */
+int b200_moe_block_recompute(const B200MoeBlock *block, const void *Xn, int recompute_x1_x3, void *stream);
+
+/*
  * Backward of the same: what dataflow_submit_transformer_moe_block_bwd_x (3399-3719) and
  * dataflow_submit_transformer_moe_block_bwd_w (4062-4185) compute between them. dXn [T][d] is overwritten; dWr
  * [E][d], dW1, dW3 [E][f][d], dW2 [E][d][f] (bf16) are accumulated into (beta = 1, one rounding), as the

@@ -44,6 +44,7 @@ SIGNATURES = {
     "b200_moe_experts_bwd_x_scatter": (_i, [_i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp,
                                             _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i64, _vp]),
     "b200_moe_block_fwd": (_i, [_vp, _vp, _vp, _vp]),
+    "b200_moe_block_recompute": (_i, [_vp, _vp, _i, _vp]),
     "b200_moe_block_bwd": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "b200_scatter_row_weights": (_i, [_i, _i, _vp, _vp, _vp, _vp]),
     "b200_gather_router_grad": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp]),

@@ -1109,7 +1109,7 @@ static int experts_fwd_impl(int total_rows, int model_dim, int ffn_dim, int num_
                             const RowScatter *sc, void *stream) {
   if (check_grouped("moe_experts_fwd", total_rows, model_dim, ffn_dim, num_experts, expert_counts, expert_counts_cumsum))
     return -1;
-  B200_REQUIRE(zone && W1 && W3 && W2 && x1 && x3 && h && (Y || sc), "moe_experts_fwd: null buffer");
+  B200_REQUIRE(zone && W1 && W3 && x1 && x3 && h && (W2 || (!Y && !sc)), "moe_experts_fwd: null buffer");
   B200_REQUIRE(w1_stride_elems % 8 == 0 && w3_stride_elems % 8 == 0 && w2_stride_elems % 8 == 0,
                "moe_experts_fwd: expert strides must be multiples of 8 elements");
   B200_REQUIRE(b200_aligned16(x1) && b200_aligned16(x3) && b200_aligned16(h) && b200_aligned16(Y),
@@ -1142,6 +1142,7 @@ static int experts_fwd_impl(int total_rows, int model_dim, int ffn_dim, int num_
     p.tmA2 = p.tmA;
     if (launch_gemm<EPI_SWIGLU_FWD>(p, m_tiles_max * ((ffn_dim + 127) / 128), s)) return -1;
   }
+  if (Y == nullptr && sc == nullptr) return 0;  // gate-up only (recompute of x1, x3, h)
   {
     // Y = h W2^T
     GemmParams p;

@@ -51,6 +51,20 @@ extern "C" int b200_moe_block_fwd(const B200MoeBlock *b, const void *Xn, void *X
   return b200_merge_experts(T, d, k, b->Y, b->token_mapping, b->token_expert_weights, X_combined, stream);
 }
 
+extern "C" int b200_moe_block_recompute(const B200MoeBlock *b, const void *Xn, int recompute_x1_x3, void *stream) {
+  if (check_block("moe_block_recompute", b)) return -1;
+  B200_REQUIRE(Xn, "moe_block_recompute: Xn missing");
+  const int T = b->total_tokens, d = b->model_dim, E = b->num_experts, k = b->top_k, f = b->ffn_dim;
+  if (T == 0) return 0;
+  // the routing tables are small and always kept; the zone is re-gathered as the reference does (3202)
+  if (b200_prepare_experts(T, d, k, Xn, b->token_mapping, b->zone, stream)) return -1;
+  if (recompute_x1_x3)  // x1, x3 and h again from the zone (3252-3273), all experts in one launch, no W2 product
+    return b200_moe_experts_fwd(T * k, d, f, E, b->zone, b->W1, b->W3, nullptr, b->w1_stride_elems, b->w3_stride_elems,
+                                b->w2_stride_elems, b->expert_counts, b->expert_counts_cumsum, b->x1, b->x3, b->h,
+                                nullptr, stream);
+  return b200_swiglu(T * k, f, b->x1, b->x3, b->h, stream);  // x1, x3 were saved: only h is re-formed
+}
+
 extern "C" int b200_moe_block_bwd(const B200MoeBlock *b, const void *Xn, const void *dOut, void *dXn, void *dWr,
                                   void *dW1, void *dW3, void *dW2, void *stream) {
   if (check_block("moe_block_bwd", b)) return -1;

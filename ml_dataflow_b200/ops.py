@@ -258,3 +258,9 @@ def moe_block_bwd(block, Xn, dOut, dXn, dWr, dW1, dW3, dW2):
     _check(_lib.load().b200_moe_block_bwd(C.byref(block), _p(Xn), _p(dOut), _p(dXn), _p(dWr), _p(dW1), _p(dW3),
                                           _p(dW2), _stream()), "moe_block_bwd",
            10 + sum(g is not None for g in (dW1, dW3, dW2)))
+
+
+def moe_block_recompute(block, Xn, recompute_x1_x3):
+    """Re-forms zone and h (and x1, x3 when asked) after the forward's workspace has been reused."""
+    _check(_lib.load().b200_moe_block_recompute(C.byref(block), _p(Xn), int(bool(recompute_x1_x3)), _stream()),
+           "moe_block_recompute", 2)

@@ -292,6 +292,19 @@ def test_c_block_driver_matches_fast_path(T, d, E, k, f):
         assert same(ga[n], gb[n]), n
     assert_close(f32(host_bits(xb)), f32(host_bits(xa)), rtol=2e-2, atol=1e-3, what="dXn")
     assert_close(f32(host_bits(gb["dWr"])), f32(host_bits(ga["dWr"])), rtol=2e-2, atol=1e-3, what="dWr")
+    # recompute after the workspace has been clobbered: bit-identical zone / x1 / x3 / h, then the same backward
+    blk = lb.block(Wrd, W1d, W3d, W2d)
+    keep = {n: getattr(lb, n).clone() for n in ("zone", "x1", "x3", "h")}
+    for level, clobbered in ((0, ("zone", "h")), (1, ("zone", "h", "x1", "x3"))):
+        for n in clobbered:
+            getattr(lb, n).fill_(3.0)
+        ops.moe_block_recompute(blk, Xd, level)
+        for n in keep:
+            assert same(getattr(lb, n), keep[n]), (level, n)
+    G2 = {n: dev_bf16(g0[n].copy()) for n in ("dWr", "dW1", "dW3", "dW2")}
+    ops.moe_block_bwd(blk, Xd, dOd, xb, G2["dWr"], G2["dW1"], G2["dW3"], G2["dW2"])
+    for n in ("dW1", "dW3", "dW2"):
+        assert same(G2[n], gb[n]), n
     # forward-only use: no backward workspace, no weight gradients wanted
     blk = lb.block(Wrd, W1d, W3d, W2d)
     blk.dY_zone = None

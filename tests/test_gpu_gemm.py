@@ -265,3 +265,43 @@ def test_scatter_refuses_a_tag_outside_the_destination():
     g = guard.float().cpu().numpy()
     assert (g[10] == 7.0).all() and (g[20] == 7.0).all() and (g[R:] == 7.0).all()
     assert (g[11] != 7.0).any()
+
+
+def test_grouped_ops_on_the_reference_packed_expert_layout():
+    """The reference stores an expert's w1, w3, w2 back to back (prep_transformer.c:155-159), so each of the three
+    weight arrays is addressed as base + e * (3 f d). Forward, backward-x and backward-w on that layout must give the
+    bits they give on three separate arrays."""
+    require_b200()
+    from ml_dataflow_b200 import ops
+
+    R, d, f, E = 1500, 512, 320, 6
+    rng = np.random.default_rng(77)
+    counts, cincl = make_counts(rng, E, R, (3,))
+    Z, dYs = dev_bf16(rand_bf16(rng, (R, d))), dev_bf16(rand_bf16(rng, (R, d)))
+    W1, W3, W2 = (dev_bf16(rand_bf16(rng, s, 0.03)) for s in ((E, f, d), (E, f, d), (E, d, f)))
+    packed = torch.cat([W1.reshape(E, -1), W3.reshape(E, -1), W2.reshape(E, -1)], dim=1).contiguous()
+    stride = 3 * f * d
+    P1, P3, P2 = packed[0, 0:], packed[0, f * d:], packed[0, 2 * f * d:]  # views: only their addresses are used
+    gpacked = torch.zeros_like(packed)
+    Q1, Q3, Q2 = gpacked[0, 0:], gpacked[0, f * d:], gpacked[0, 2 * f * d:]
+    cd, cid = dev(counts), dev(cincl)
+    ones = torch.ones(R, dtype=torch.float32, device="cuda")
+
+    def run(w1, w3, w2, s1, s3, s2, g1, g3, g2):
+        x1, x3, h, dx1, dx3, hs = (torch.zeros((R, f), dtype=torch.bfloat16, device="cuda") for _ in range(6))
+        Y, dZ = (torch.zeros((R, d), dtype=torch.bfloat16, device="cuda") for _ in range(2))
+        dP = torch.zeros(R, dtype=torch.float32, device="cuda")
+        ops.moe_experts_fwd(R, d, f, E, Z, w1, w3, w2, s1, s3, s2, cd, cid, x1, x3, h, Y)
+        ops.moe_experts_bwd_x(R, d, f, E, dYs, ones, x1, x3, w1, w3, w2, s1, s3, s2, cd, cid, dx1, dx3, hs, dP, dZ)
+        ops.moe_experts_bwd_w(R, d, f, E, dYs, hs, Z, dx1, dx3, g1, g3, g2, s1, s3, s2, cd, cid)
+        gemm_ok(ops)
+        return Y, dZ
+
+    G1, G3, G2 = torch.zeros_like(W1), torch.zeros_like(W3), torch.zeros_like(W2)
+    Ya, dZa = run(W1, W3, W2, f * d, f * d, d * f, G1, G3, G2)
+    Yb, dZb = run(P1, P3, P2, stride, stride, stride, Q1, Q3, Q2)
+    eq = lambda a, b: torch.equal(a.contiguous().view(torch.int16), b.contiguous().view(torch.int16))
+    assert eq(Ya, Yb) and eq(dZa, dZb)
+    assert eq(gpacked[:, :f * d], G1.reshape(E, -1))
+    assert eq(gpacked[:, f * d:2 * f * d], G3.reshape(E, -1))
+    assert eq(gpacked[:, 2 * f * d:], G2.reshape(E, -1))

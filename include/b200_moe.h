@@ -194,7 +194,10 @@ int b200_swiglu_bwd_x(int num_rows, int num_cols, const void *x_w1, const void *
  * cores. a_dt = b_dt = B200_DT_BF16; d_dt (and c_dt when C is used) bf16 or
  * fp32; C may be NULL (beta ignored) or alias D. M must be a multiple of 8; so must K
  * unless (to_trans_a == 0 && to_trans_b == 1), and N when to_trans_b == 1 (16-byte rows for TMA).
- * workspace is unused and may be NULL.
+ * workspace (the reference's kernelWorkspace argument, matmul_op.c:33-53) may be NULL. When it is given, 16-byte
+ * aligned, and the product has too few output tiles to fill the GPU but a long reduction (the router's GEMMs), the
+ * reduction is cut into up to 16 ranges whose fp32 partial results (M * N * 4 bytes each) go to the workspace and
+ * are summed in a fixed order by a second kernel: same result up to fp32 summation order, deterministic.
  */
 int b200_matmul(int a_dt, int b_dt, int c_dt, int d_dt, int to_trans_a, int to_trans_b, int M, int K, int N,
                 float alpha, float beta, const void *A, const void *B, const void *C, void *D,
@@ -307,6 +310,8 @@ typedef struct B200MoeBlock {
   void *Y;                     /* bf16 [R][d]: expert outputs before the combine */
   void *mapping_workspace;     /* b200_build_expert_mapping_workspace_bytes(T, E, k) bytes */
   size_t mapping_workspace_bytes;
+  void *matmul_workspace;      /* optional (NULL): fp32 scratch for the router GEMMs' split reduction, see b200_matmul */
+  size_t matmul_workspace_bytes;
   /* backward workspace (may be NULL for forward-only use) */
   void *dY_zone;               /* bf16 [R][d] */
   float *row_weights, *dP;     /* [R] each */

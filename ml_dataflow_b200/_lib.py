@@ -62,6 +62,7 @@ class MoeBlock(C.Structure):
         ("expert_counts_cumsum", _vp), ("host_expert_counts", _vp), ("expert_mapping", _vp), ("token_mapping", _vp),
         ("zone", _vp), ("x1", _vp), ("x3", _vp), ("h", _vp), ("Y", _vp),
         ("mapping_workspace", _vp), ("mapping_workspace_bytes", _sz),
+        ("matmul_workspace", _vp), ("matmul_workspace_bytes", _sz),
         ("dY_zone", _vp), ("row_weights", _vp), ("dP", _vp), ("dx1", _vp), ("dx3", _vp), ("dZ", _vp),
         ("dX_routed", _vp),
     ]

@@ -21,6 +21,8 @@
 #include <stdlib.h>
 #include <string.h>
 
+#include <algorithm>
+
 #include "common.cuh"
 #include "sm100_ptx.cuh"
 #include "../../include/b200_moe.h"
@@ -120,6 +122,9 @@ struct GemmParams {
   // scattered rows are first transposed through shared memory so that eight lanes store 128 contiguous bytes of one
   // row (32-byte pieces of 32 different rows per instruction use a peer link poorly); set when the block fits
   int stage_out;
+  // DENSE only: the reduction is cut into k_splits ranges of k_split_len (a multiple of 64); range i is one more
+  // tile whose fp32 result goes to D + i * d_group_stride, summed afterwards by splitk_reduce_kernel
+  int k_splits, k_split_len;
 };
 
 struct Tile {
@@ -132,7 +137,7 @@ struct Tile {
 };
 
 struct Sched {
-  int mode, tiles_n, tiles_m, n_tile_w, n_round, tile_m, total_tiles, M, N, K;
+  int mode, tiles_n, tiles_m, n_tile_w, n_round, tile_m, total_tiles, M, N, K, k_splits, k_split_len;
   const int *s_cnt, *s_base, *s_tpre;
   int cursor;
 
@@ -140,13 +145,16 @@ struct Sched {
     if (tile_id >= total_tiles) return false;
     int nt;
     if (mode == DENSE) {
-      const int mt = tile_id / tiles_n;
-      nt = tile_id - mt * tiles_n;
-      t.group = 0;
+      const int per = tiles_m * tiles_n;
+      const int split = tile_id / per;  // 0 unless the reduction is split
+      const int rem = tile_id - split * per;
+      const int mt = rem / tiles_n;
+      nt = rem - mt * tiles_n;
+      t.group = split;
       t.a_row0 = t.out_row0 = mt * tile_m;
       t.m_valid = min(tile_m, M - mt * tile_m);
-      t.k_row0 = 0;
-      t.k_len = K;
+      t.k_row0 = split * k_split_len;
+      t.k_len = (k_splits > 1) ? min(k_split_len, K - t.k_row0) : K;
     } else if (mode == GROUPED_M) {
       const int mtg = tile_id / tiles_n;
       nt = tile_id - mtg * tiles_n;
@@ -295,7 +303,9 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
   sched.s_base = tab_base;
   sched.s_tpre = tab_tpre;
   sched.cursor = 0;
-  if (p.group_mode == DENSE) sched.total_tiles = sched.tiles_m * sched.tiles_n;
+  sched.k_splits = p.k_splits;
+  sched.k_split_len = p.k_split_len;
+  if (p.group_mode == DENSE) sched.total_tiles = sched.tiles_m * sched.tiles_n * max(1, p.k_splits);
   else if (p.group_mode == GROUPED_M) sched.total_tiles = tab_tpre[G] * sched.tiles_n;
   else sched.total_tiles = G * sched.tiles_m * sched.tiles_n;
   const int first_tile = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
@@ -352,8 +362,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
       };
       if (do_a) {
         if (!p.a_mn_major) {
-          ld2(sA, mA, kk, a_row);
-          ld2(sA + BLK_BYTES, mA, kk, a_row + 64);
+          ld2(sA, mA, tt.k_row0 + kk, a_row);
+          ld2(sA + BLK_BYTES, mA, tt.k_row0 + kk, a_row + 64);
         } else {
           ld2(sA, mA, a_row, tt.k_row0 + kk);
           ld2(sA + BLK_BYTES, mA, a_row + 64, tt.k_row0 + kk);
@@ -369,7 +379,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
           for (int i = 0; i < nb; i++) ld3(sB + (nb + i) * BLK_BYTES, &p.tmB2, kk, tt.n0 + 64 * i, g3);
         }
       } else if (!p.b_mn_major) {
-        for (int i = 0; i < nb; i++) ld3(sB + i * BLK_BYTES, mB, kk, n_start + 64 * i, g3);
+        for (int i = 0; i < nb; i++) ld3(sB + i * BLK_BYTES, mB, tt.k_row0 + kk, n_start + 64 * i, g3);
       } else {
         for (int i = 0; i < nb; i++) ld3(sB + i * BLK_BYTES, mB, n_start + 64 * i, tt.k_row0 + kk, g3);
       }
@@ -587,7 +597,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
       const int cbeg = chalf * (t.nw >> 1), cend = cbeg + (t.nw >> 1);
 
       if (EPI == EPI_STORE) {
-        const int64_t goff = (p.group_mode == GROUPED_K) ? (int64_t)t.group * p.d_group_stride : 0;
+        const int64_t goff = (p.group_mode == GROUPED_K || p.k_splits > 1) ? (int64_t)t.group * p.d_group_stride : 0;
         const int64_t base = goff + orow * p.ldd + t.n0;
         const bool use_c = (p.C != nullptr) && (p.beta != 0.0f);
         // destination of this thread's row: D itself, or (row scatter) the row its tag names in some rank's buffer
@@ -982,6 +992,33 @@ static int launch_gemm(GemmParams &p, int64_t max_tiles, cudaStream_t s, bool pa
 
 static void zero_params(GemmParams &p) { memset(&p, 0, sizeof(p)); }
 
+// D = alpha * sum_i partial[i] + beta * C over n elements (a multiple of 4); partial[i] = partials + i * n, fp32
+__global__ void splitk_reduce_kernel(int64_t n, int splits, const float *__restrict__ partials, float alpha, float beta,
+                                     const void *C, int c_fp32, void *D, int d_fp32) {
+  const int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  if (i >= n) return;
+  float4 acc = *reinterpret_cast<const float4 *>(partials + i);
+  for (int sidx = 1; sidx < splits; sidx++) {
+    const float4 v = *reinterpret_cast<const float4 *>(partials + (int64_t)sidx * n + i);
+    acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+  }
+  float f[4] = {alpha * acc.x, alpha * acc.y, alpha * acc.z, alpha * acc.w};
+  if (C != nullptr) {
+    if (c_fp32) {
+      const float4 c = *reinterpret_cast<const float4 *>(static_cast<const float *>(C) + i);
+      f[0] += beta * c.x; f[1] += beta * c.y; f[2] += beta * c.z; f[3] += beta * c.w;
+    } else {
+      const uint2 c = *reinterpret_cast<const uint2 *>(static_cast<const __nv_bfloat16 *>(C) + i);
+      f[0] += beta * bf16lo(c.x); f[1] += beta * bf16hi(c.x); f[2] += beta * bf16lo(c.y); f[3] += beta * bf16hi(c.y);
+    }
+  }
+  if (d_fp32) {
+    *reinterpret_cast<float4 *>(static_cast<float *>(D) + i) = make_float4(f[0], f[1], f[2], f[3]);
+  } else {
+    *reinterpret_cast<uint2 *>(static_cast<__nv_bfloat16 *>(D) + i) = make_uint2(pack_bf16(f[0], f[1]), pack_bf16(f[2], f[3]));
+  }
+}
+
 }  // namespace b200
 
 using namespace b200;
@@ -1020,8 +1057,6 @@ extern "C" int b200_gemm_status(int *status_out) {
 extern "C" int b200_matmul(int a_dt, int b_dt, int c_dt, int d_dt, int to_trans_a, int to_trans_b, int M, int K, int N,
                            float alpha, float beta, const void *A, const void *B, const void *C, void *D,
                            uint64_t workspaceBytes, void *workspace, void *stream) {
-  (void)workspaceBytes;
-  (void)workspace;
   B200_REQUIRE(a_dt == B200_DT_BF16 && b_dt == B200_DT_BF16, "matmul: A and B must be bf16 (got %d, %d)", a_dt, b_dt);
   B200_REQUIRE(d_dt == B200_DT_BF16 || d_dt == B200_DT_FP32, "matmul: D must be bf16 or fp32 (got %d)", d_dt);
   const bool use_c = (C != nullptr) && (c_dt != B200_DT_NONE) && (beta != 0.0f);
@@ -1066,7 +1101,36 @@ extern "C" int b200_matmul(int a_dt, int b_dt, int c_dt, int d_dt, int to_trans_
   p.tmB2 = p.tmB;
   const int64_t tiles = (int64_t)((N + BM - 1) / BM) * ((M + 255) / 256);
   // a 256-row pair tile only pays off when there are at least 256 output rows
-  return launch_gemm<EPI_STORE>(p, tiles, (cudaStream_t)stream, /*pair_ok=*/N >= 256);
+  const bool pair_ok = N >= 256;
+  // Few output tiles and a long reduction (the router's GEMMs): cut the reduction so that every SM gets a tile.
+  // Needs fp32 scratch for the partial results; without it (or when it is too small) the plain form runs.
+  const int64_t launched_tiles = (pair_ok && pair_mode()) ? (int64_t)((N + 255) / 256) * ((M + 255) / 256) : tiles;
+  const int sms = sm_count_cached();
+  const int64_t units = (pair_ok && pair_mode()) ? sms / 2 : sms;
+  int splits = 1;
+  if (workspace != nullptr && b200_aligned16(workspace) && launched_tiles * 2 <= units && K >= 2048 && M % 4 == 0) {
+    splits = (int)std::min<int64_t>(std::min<int64_t>(units / launched_tiles, K / 1024), 16);
+    const uint64_t per_split = (uint64_t)N * M * sizeof(float);
+    if ((uint64_t)splits * per_split > workspaceBytes) splits = (int)(workspaceBytes / per_split);
+  }
+  if (splits < 2) return launch_gemm<EPI_STORE>(p, tiles, (cudaStream_t)stream, pair_ok);
+  const int split_len = (((K + splits - 1) / splits) + BK - 1) / BK * BK;
+  splits = (K + split_len - 1) / split_len;
+  p.k_splits = splits;
+  p.k_split_len = split_len;
+  p.alpha = 1.0f;
+  p.beta = 0.0f;
+  p.C = nullptr;
+  p.out_fp32 = 1;
+  p.D = workspace;
+  p.d_group_stride = (int64_t)N * M;
+  if (launch_gemm<EPI_STORE>(p, tiles * splits, (cudaStream_t)stream, pair_ok)) return -1;
+  const int64_t n = (int64_t)N * M;
+  splitk_reduce_kernel<<<(unsigned)((n / 4 + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+      n, splits, static_cast<const float *>(workspace), alpha, use_c ? beta : 0.0f, use_c ? C : nullptr,
+      c_dt == B200_DT_FP32, D, d_dt == B200_DT_FP32);
+  B200_CHECK_LAUNCH("matmul split-k reduce");
+  return 0;
 }
 
 static int check_grouped(const char *op, int total_rows, int model_dim, int ffn_dim, int num_experts,

@@ -31,7 +31,7 @@ extern "C" int b200_moe_block_fwd(const B200MoeBlock *b, const void *Xn, void *X
   cudaStream_t s = (cudaStream_t)stream;
   // router logits, fp32: logits[T][E] = Xn . Wr^T (reference call: transa = 1, M = E, K = d, N = T)
   if (b200_matmul(B200_DT_BF16, B200_DT_BF16, B200_DT_NONE, B200_DT_FP32, 1, 0, E, d, T, 1.0f, 0.0f, b->Wr, Xn, nullptr,
-                  b->logits, 0, nullptr, stream))
+                  b->logits, b->matmul_workspace_bytes, b->matmul_workspace, stream))
     return -1;
   // the reference's caller zeroes the counters before select_experts (2737-2747)
   B200_CUDA(cudaMemsetAsync(b->expert_counts, 0, sizeof(int) * (size_t)(E + 1), s));
@@ -104,5 +104,5 @@ extern "C" int b200_moe_block_bwd(const B200MoeBlock *b, const void *Xn, const v
                   b->dX_routed, dXn, dXn, 0, nullptr, stream))
     return -1;
   return b200_matmul(B200_DT_BF16, B200_DT_BF16, B200_DT_BF16, B200_DT_BF16, 0, 1, d, T, E, 1.0f, 1.0f, Xn,
-                     b->dX_routed, dWr, dWr, 0, nullptr, stream);
+                     b->dX_routed, dWr, dWr, b->matmul_workspace_bytes, b->matmul_workspace, stream);
 }

@@ -350,7 +350,7 @@ class ExpertParallelMoELayer:
         ops.router_gate_bwd_x(T, E, k, hm.chosen, hm.weights, hm.dX_routed)
         ops.matmul(0, 0, d, E, T, 1.0, 1.0, Wr, hm.dX_routed, dXn, dXn)
         hm.dWr_local.zero_()
-        ops.matmul(0, 1, d, T, E, 1.0, 0.0, Xn, hm.dX_routed, None, hm.dWr_local)
+        ops.matmul(0, 1, d, T, E, 1.0, 0.0, Xn, hm.dX_routed, None, hm.dWr_local, hm.mm_ws)
         self.dist.all_reduce(hm.dWr_local)  # the replicated router weight sees every rank's tokens
         dWr.add_(hm.dWr_local)
         self.mark("bwd_end")
@@ -378,6 +378,7 @@ class _HomeSide:
         self.expert_mapping = buf((R,), i32)
         self.token_mapping = buf((T, k), i32)
         self.map_ws = torch.empty(ops.build_expert_mapping_workspace_bytes(T, E, k), dtype=torch.uint8, device=dev)
+        self.mm_ws = torch.empty(16 << 20, dtype=torch.uint8, device=dev)  # split-K scratch of the router GEMMs
         if staging:  # local copies of the routed rows, only needed when rows travel through NCCL
             self.zone, self.Y, self.dYz, self.dZ = (buf((R, d), bf) for _ in range(4))
             self.row_w, self.dP = buf((R,), f32), buf((R,), f32)
@@ -388,7 +389,7 @@ class _HomeSide:
         from . import ops
 
         T, d, E, k = self.T, self.d, self.E, self.k
-        ops.matmul(1, 0, E, d, T, 1.0, 0.0, Wr, Xn, None, self.logits)
+        ops.matmul(1, 0, E, d, T, 1.0, 0.0, Wr, Xn, None, self.logits, self.mm_ws)
         self.counts.zero_()
         self.cumsum.zero_()
         ops.select_experts(T, E, k, self.logits, self.weights, self.chosen, self.counts, self.cumsum, None)

@@ -41,6 +41,7 @@ class MoELayer:
         self.expert_mapping = buf((R,), i32)
         self.token_mapping = buf((T, k), i32)
         self.map_ws = torch.empty(ops.build_expert_mapping_workspace_bytes(T, E, k), dtype=torch.uint8, device=dev)
+        self.mm_ws = torch.empty(16 << 20, dtype=torch.uint8, device=dev)  # split-K scratch of the router GEMMs
         self.zone = buf((R, d), bf)
         self.x1 = buf((R, f), bf)
         self.x3 = buf((R, f), bf)
@@ -77,7 +78,7 @@ class MoELayer:
             self.T, self.d, self.E, self.k, self.f, p(Wr), p(W1), p(W3), p(W2), f * d, f * d, d * f,
             p(self.logits), p(self.weights), p(self.chosen), p(self.counts), p(self.cumsum), None,
             p(self.expert_mapping), p(self.token_mapping), p(self.zone), p(self.x1), p(self.x3), p(self.h), p(self.Y),
-            p(self.map_ws), self.map_ws.numel(), p(self.dYz), p(self.row_w), p(self.dP), p(self.dx1), p(self.dx3),
+            p(self.map_ws), self.map_ws.numel(), p(self.mm_ws), self.mm_ws.numel(), p(self.dYz), p(self.row_w), p(self.dP), p(self.dx1), p(self.dx3),
             p(self.dZ), p(self.dX_routed))
 
     # ------------------------------------------------------------------ routing (shared)
@@ -86,7 +87,7 @@ class MoELayer:
         self.mark("router_gemm")
         if logits is None:
             # logits[T,E] = Xn . Wr^T, fp32 out (reference call: transa=1, M=E, K=d, N=T)
-            ops.matmul(1, 0, E, d, T, 1.0, 0.0, Wr, Xn, None, self.logits)
+            ops.matmul(1, 0, E, d, T, 1.0, 0.0, Wr, Xn, None, self.logits, self.mm_ws)
         else:
             self.logits.copy_(logits)
         self.mark("select_experts")
@@ -140,7 +141,7 @@ class MoELayer:
         # dXn += dL . Wr   (reference: transa=0, transb=0, M=d, K=E, N=T, beta=1, C=D)
         ops.matmul(0, 0, d, E, T, 1.0, 1.0, Wr, self.dX_routed, dXn, dXn)
         # dWr += dL^T . Xn (reference: transa=0, transb=1, M=d, K=T, N=E, beta=1, C=D)
-        ops.matmul(0, 1, d, T, E, 1.0, 1.0, Xn, self.dX_routed, dWr, dWr)
+        ops.matmul(0, 1, d, T, E, 1.0, 1.0, Xn, self.dX_routed, dWr, dWr, self.mm_ws)
         self.mark("bwd_end")
         return dXn
 
@@ -206,5 +207,5 @@ class MoELayer:
             ops.matmul(0, 1, d, n, f, 1.0, 1.0, self.zone[sl], self.dx1[sl], dW1[e], dW1[e])
             ops.matmul(0, 1, d, n, f, 1.0, 1.0, self.zone[sl], self.dx3[sl], dW3[e], dW3[e])
             base += n
-        ops.matmul(0, 1, d, T, E, 1.0, 1.0, Xn, self.dX_routed, dWr, dWr)
+        ops.matmul(0, 1, d, T, E, 1.0, 1.0, Xn, self.dX_routed, dWr, dWr, self.mm_ws)
         return dXn

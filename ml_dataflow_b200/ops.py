@@ -140,10 +140,13 @@ def swiglu_bwd_x(num_rows, num_cols, x_w1, x_w3, upstream_dX, dX_w1, dX_w3):
                                          _p(dX_w3), _stream()), "swiglu_bwd_x")
 
 
-def matmul(to_trans_a, to_trans_b, M, K, N, alpha, beta, A, B, Cm, D):
-    """Column-major D[MxN] = alpha * op(A) * op(B) + beta * C, the reference's matmul op."""
+def matmul(to_trans_a, to_trans_b, M, K, N, alpha, beta, A, B, Cm, D, workspace=None):
+    """Column-major D[MxN] = alpha * op(A) * op(B) + beta * C, the reference's matmul op.
+    workspace (a uint8 tensor, optional): fp32 scratch that lets a GEMM with few output tiles and a long reduction
+    split the reduction over the SMs."""
+    wbytes = 0 if workspace is None else workspace.numel() * workspace.element_size()
     _check(_lib.load().b200_matmul(_dt(A), _dt(B), _dt(Cm), _dt(D), to_trans_a, to_trans_b, M, K, N, alpha, beta,
-                                   _p(A), _p(B), _p(Cm), _p(D), 0, None, _stream()), "matmul")
+                                   _p(A), _p(B), _p(Cm), _p(D), wbytes, _p(workspace), _stream()), "matmul")
 
 
 def moe_experts_fwd(total_rows, model_dim, ffn_dim, num_experts, zone, W1, W3, W2, w1_stride, w3_stride, w2_stride,

@@ -305,3 +305,42 @@ def test_grouped_ops_on_the_reference_packed_expert_layout():
     assert eq(gpacked[:, :f * d], G1.reshape(E, -1))
     assert eq(gpacked[:, f * d:2 * f * d], G3.reshape(E, -1))
     assert eq(gpacked[:, 2 * f * d:], G2.reshape(E, -1))
+
+
+@pytest.mark.parametrize("ta,tb", [(1, 0), (0, 0), (0, 1), (1, 1)])
+@pytest.mark.parametrize("M,K,N,d_fp32", [(64, 4096, 1024, True), (4096, 8192, 64, False), (256, 5000 // 8 * 8, 264, False)])
+def test_matmul_with_split_reduction(oracle, ta, tb, M, K, N, d_fp32):
+    """Few output tiles + long reduction + a workspace: the reduction is split over the SMs and summed by a second
+    kernel. Same answer as the oracle (router logits and router weight-gradient shapes among the cases), also with
+    alpha, beta and C aliasing D, and the same bits on a second run (the partial sums are added in a fixed order)."""
+    require_b200()
+    from ml_dataflow_b200 import ops
+
+    rng = np.random.default_rng(M + K + N + 2 * ta + tb)
+    A = rand_bf16(rng, (M, K) if ta else (K, M), std=0.5)
+    B = rand_bf16(rng, (K, N) if tb else (N, K), std=0.5)
+    ws = torch.empty(16 << 20, dtype=torch.uint8, device="cuda")
+    Ad, Bd = dev_bf16(A), dev_bf16(B)
+    if d_fp32:
+        D_ref = np.zeros((N, M), np.float32)
+        oracle.matmul(ta, tb, M, K, N, 1.0, 0.0, A, B, None, D_ref)
+        D = torch.zeros((N, M), dtype=torch.float32, device="cuda")
+        ops.matmul(ta, tb, M, K, N, 1.0, 0.0, Ad, Bd, None, D, ws)
+        gemm_ok(ops)
+        assert_close(D.cpu().numpy(), D_ref, rtol=1e-3, atol=1e-3 * np.sqrt(K) * 0.25, what="split-k fp32")
+        return
+    C0 = rand_bf16(rng, (N, M), std=2.0)
+    D_ref = C0.copy()
+    oracle.matmul(ta, tb, M, K, N, 0.5, 1.0, A, B, C0, D_ref)
+    D = dev_bf16(C0.copy())
+    ops.matmul(ta, tb, M, K, N, 0.5, 1.0, Ad, Bd, D, D, ws)     # C aliases D
+    gemm_ok(ops)
+    assert_close(bf16_bits_to_f32(host_bits(D)), bf16_bits_to_f32(D_ref), what=f"split-k ta={ta} tb={tb}")
+    D2 = dev_bf16(C0.copy())
+    ops.matmul(ta, tb, M, K, N, 0.5, 1.0, Ad, Bd, D2, D2, ws)
+    assert torch.equal(D.view(torch.int16), D2.view(torch.int16))
+    # without a workspace the plain form runs and agrees to rounding
+    D3 = dev_bf16(C0.copy())
+    ops.matmul(ta, tb, M, K, N, 0.5, 1.0, Ad, Bd, D3, D3)
+    gemm_ok(ops)
+    assert_close(bf16_bits_to_f32(host_bits(D3)), bf16_bits_to_f32(host_bits(D)), what="split vs plain")

@@ -62,9 +62,23 @@ select_experts_kernel(int total_tokens, int n_experts, int top_k, const T *__res
   for (int e0 = 0; e0 < n_experts; e0 += SEL_EC) {
     const int ec = min(SEL_EC, n_experts - e0);
     __syncthreads();  // previous chunk fully consumed (and block_counts zeroed on first pass)
-    for (int i = tid; i < rows_here * ec; i += SEL_TOKENS) {
-      int r = i / ec, c = i - r * ec;
-      tile[r * SEL_PITCH + c] = load_logit<T>(X_routed + (tok0 + r) * n_experts + e0 + c);
+    // sixteen independent loads in flight per thread before the first store (one load per trip leaves the whole
+    // staging loop waiting on memory latency, trip after trip)
+    const int n_stage = rows_here * ec;
+    for (int i0 = tid; i0 < n_stage; i0 += SEL_TOKENS * 16) {
+      float v[16];
+#pragma unroll
+      for (int u = 0; u < 16; u++) {
+        const int i = i0 + u * SEL_TOKENS;
+        const int r = i / ec, c = i - r * ec;
+        v[u] = (i < n_stage) ? load_logit<T>(X_routed + (tok0 + r) * n_experts + e0 + c) : 0.f;
+      }
+#pragma unroll
+      for (int u = 0; u < 16; u++) {
+        const int i = i0 + u * SEL_TOKENS;
+        const int r = i / ec, c = i - r * ec;
+        if (i < n_stage) tile[r * SEL_PITCH + c] = v[u];
+      }
     }
     __syncthreads();
     if (active) {

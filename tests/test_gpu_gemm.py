@@ -344,3 +344,40 @@ def test_matmul_with_split_reduction(oracle, ta, tb, M, K, N, d_fp32):
     ops.matmul(ta, tb, M, K, N, 0.5, 1.0, Ad, Bd, D3, D3)
     gemm_ok(ops)
     assert_close(bf16_bits_to_f32(host_bits(D3)), bf16_bits_to_f32(host_bits(D)), what="split vs plain")
+
+
+def test_weight_gradients_at_every_kind_of_reduction_tail(oracle):
+    """Per-expert row counts chosen to end a reduction slab at every interesting place: empty, a single row, one short
+    of / exactly / one past a 16-row group and a 64-row slab, two slabs (one pipeline stage) and a bit more. The rows
+    of the next expert that share the last slab must not leak into the gradient."""
+    require_b200()
+    from ml_dataflow_b200 import ops
+
+    counts = np.array([0, 1, 15, 16, 17, 63, 64, 65, 127, 128, 129, 0, 200, 3], np.int32)
+    E, R = len(counts), int(counts.sum())
+    cincl = np.cumsum(counts).astype(np.int32)
+    d, f = 256, 320
+    rng = np.random.default_rng(4242)
+    dY, Z = rand_bf16(rng, (R, d), 2.0), rand_bf16(rng, (R, d), 2.0)
+    hs, dx1, dx3 = rand_bf16(rng, (R, f), 2.0), rand_bf16(rng, (R, f), 2.0), rand_bf16(rng, (R, f), 2.0)
+    g1, g3, g2 = rand_bf16(rng, (E, f, d), 0.1), rand_bf16(rng, (E, f, d), 0.1), rand_bf16(rng, (E, d, f), 0.1)
+    G1, G3, G2 = dev_bf16(g1.copy()), dev_bf16(g3.copy()), dev_bf16(g2.copy())
+    ops.moe_experts_bwd_w(R, d, f, E, dev_bf16(dY), dev_bf16(hs), dev_bf16(Z), dev_bf16(dx1), dev_bf16(dx3), G1, G3, G2,
+                          f * d, f * d, d * f, dev(counts), dev(cincl))
+    gemm_ok(ops)
+    b = 0
+    for e in range(E):
+        n = int(counts[e])
+        sl = slice(b, b + n)
+        if n:
+            oracle.linear_wgrad(np.ascontiguousarray(hs[sl]), np.ascontiguousarray(dY[sl]), g2[e])
+            oracle.linear_wgrad(np.ascontiguousarray(Z[sl]), np.ascontiguousarray(dx1[sl]), g1[e])
+            oracle.linear_wgrad(np.ascontiguousarray(Z[sl]), np.ascontiguousarray(dx3[sl]), g3[e])
+        b += n
+    for got, ref, what in ((G1, g1, "dW1"), (G3, g3, "dW3"), (G2, g2, "dW2")):
+        gb = host_bits(got)
+        for e in range(E):
+            if counts[e] == 0:
+                np.testing.assert_array_equal(gb[e], ref[e], err_msg=f"{what}[{e}] of an empty expert changed")
+            else:
+                assert_close(bf16_bits_to_f32(gb[e]), bf16_bits_to_f32(ref[e]), what=f"{what}[{e}] ({counts[e]} rows)")

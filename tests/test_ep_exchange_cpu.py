@@ -61,6 +61,29 @@ def _worker(rank, world, port, E, d, seed, result_dir):
         got = [tuple(int(v) for v in recv[i, :3]) for i in range(x.rows_recv)]
         assert got == expect_rows, (rank, got[:8], expect_rows[:8])
         assert (recv[x.rows_recv:] == -1).all()
+        # the peer-memory kernels address rows without any message: a routed row r of expert e sits at row
+        # dst_base[e] + (r - first_row[e]) of rank e // El (csrc/ep_p2p.cu, locate()). Check that arithmetic
+        # against what the message transport delivered, and the row tags the fused return path relies on:
+        # tag (home rank << 40 | home row) stored at that position must name every home row exactly once.
+        first_row = np.concatenate([[0], np.cumsum(counts)[:-1]])
+        recvs = [None] * world
+        dist.all_gather_object(recvs, recv[:x.rows_recv, :3].numpy().copy())
+        tags_here = {}
+        r = 0
+        for e in range(E):
+            for i in range(counts[e]):
+                owner, row = e // El, int(x.dst_base[e]) + (r - int(first_row[e]))
+                assert tuple(int(v) for v in recvs[owner][row]) == (rank, e, i)
+                tags_here[(owner, row)] = (rank << 40) | r
+                r += 1
+        all_tags = [None] * world
+        dist.all_gather_object(all_tags, tags_here)
+        mine = sorted(t for tg in all_tags for (owner, _), t in tg.items() if owner == rank)
+        assert len(mine) == x.rows_recv                      # every received row has a tag
+        positions = sorted(row for tg in all_tags for (owner, row) in tg if owner == rank)
+        assert positions == list(range(x.rows_recv))         # at distinct, dense positions
+        homes = sorted((t >> 40, t & ((1 << 40) - 1)) for t in tags_here.values())
+        assert homes == [(rank, i) for i in range(R)]        # and this rank's rows each get exactly one way back
         # identity experts, then the way back
         back = torch.full((R, d), -5.0)
         x.combine(recv, back)

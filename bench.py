@@ -292,6 +292,8 @@ def run_gpu_arm(args, world):
     status = ops.gemm_status()
     if status != 0:
         raise RuntimeError(f"a GEMM kernel gave up waiting (status {status}); the timing is void")
+    if world > 1:
+        layer.check()  # raises if a receive buffer overflowed (rows dropped): the timing would be void
     value = world * T / (ms_step * 1e-3)
     if args.quick:
         if rank == 0:

@@ -360,6 +360,9 @@ int b200_moe_block_bwd(const B200MoeBlock *block, const void *Xn, const void *dO
  * with local row r = token_mapping[t, j] of expert e = chosen_experts[t, j] lives at row
  * dst_base[e] + r - (expert_counts_cumsum[e] - expert_counts[e]) of rank e / experts_per_rank (inclusive cumsum).
  * The kernels use plain peer loads / stores; the caller separates the phases with a barrier across the ranks.
+ * capacity_rows is the number of rows every rank's buffer holds: a routed pair whose row would lie past it is
+ * skipped (never written or read), so a receive buffer that turns out too small loses rows but is not overrun; the
+ * caller compares the received row total with the capacity (on the device, without a host round trip, if it likes).
  */
 
 /* prepare_experts fused with the dispatch: row (t, j) = X[t, :] (times token_expert_weights[t, j] when that pointer
@@ -370,14 +373,15 @@ int b200_ep_dispatch_rows(int total_tokens, int model_dim, int top_k, const void
                           const int *token_mapping, const uint16_t *chosen_experts, const int *expert_counts,
                           const int *expert_counts_cumsum, const int *dst_base,
                           const unsigned long long *peer_buffers, int world, int num_experts, int experts_per_rank,
-                          int local_expert_begin, int local_expert_end, void *stream);
+                          int64_t capacity_rows, int local_expert_begin, int local_expert_end, void *stream);
 
 /* merge_experts fused with the return: X_combined[t, :] += sum_j w[t, j] * row (t, j), every row loaded from its
  * owner's buffer; token_expert_weights == NULL means 1.0 (backward un-permute). */
 int b200_ep_combine_rows(int num_tokens, int model_dim, int top_k, const float *token_expert_weights,
                          const int *token_mapping, const uint16_t *chosen_experts, const int *expert_counts,
                          const int *expert_counts_cumsum, const int *dst_base, const unsigned long long *peer_buffers,
-                         int world, int num_experts, int experts_per_rank, void *X_combined, void *stream);
+                         int world, int num_experts, int experts_per_rank, int64_t capacity_rows, void *X_combined,
+                         void *stream);
 
 /* dX_routed[t, chosen[t, j]] = bf16(dP[row (t, j)] / w[t, j]) with dP (fp32 per routed row, holding w * <Y, dOut> as
  * b200_moe_experts_bwd_x leaves it when row_weights are all 1) read from the owners' buffers. dX_routed pre-zeroed. */
@@ -385,7 +389,7 @@ int b200_ep_gather_router_grad(int num_tokens, int top_k, const float *token_exp
                                const uint16_t *chosen_experts, const int *expert_counts,
                                const int *expert_counts_cumsum, const int *dst_base,
                                const unsigned long long *peer_dP_buffers, int world, int num_experts,
-                               int experts_per_rank, void *dX_routed, void *stream);
+                               int experts_per_rank, int64_t capacity_rows, void *dX_routed, void *stream);
 
 /*
  * GEMM fused with the return exchange. A row tag is (rank << 40) | row. b200_ep_publish_row_tags writes, for every
@@ -402,7 +406,7 @@ int b200_ep_gather_router_grad(int num_tokens, int top_k, const float *token_exp
 int b200_ep_publish_row_tags(int num_tokens, int top_k, int my_rank, const int *token_mapping,
                              const uint16_t *chosen_experts, const int *expert_counts, const int *expert_counts_cumsum,
                              const int *dst_base, const unsigned long long *peer_tag_buffers, int world,
-                             int num_experts, int experts_per_rank, void *stream);
+                             int num_experts, int experts_per_rank, int64_t capacity_rows, void *stream);
 
 int b200_moe_experts_fwd_scatter(int total_rows, int model_dim, int ffn_dim, int num_experts, const void *zone,
                                  const void *W1, const void *W3, const void *W2, int64_t w1_stride_elems,

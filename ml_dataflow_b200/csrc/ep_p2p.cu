@@ -25,6 +25,7 @@ struct RouteView {
   const int *counts, *cumsum_incl, *dst_base;
   int num_experts, experts_per_rank;
   int local_begin, local_end;  // only pairs whose expert index inside its owner is in [local_begin, local_end)
+  int64_t capacity_rows;       // rows every rank's buffer holds: a pair whose row would lie past it is skipped
 };
 
 __device__ __forceinline__ bool locate(const RouteView &rv, int64_t slot, int &owner, int64_t &row) {
@@ -35,7 +36,7 @@ __device__ __forceinline__ bool locate(const RouteView &rv, int64_t slot, int &o
   const int le = e - owner * rv.experts_per_rank;
   if (le < rv.local_begin || le >= rv.local_end) return false;
   row = (int64_t)rv.dst_base[e] + (r - (rv.cumsum_incl[e] - rv.counts[e]));
-  return true;
+  return row >= 0 && row < rv.capacity_rows;
 }
 
 // X[t, :] (optionally scaled by the gate weight) -> row (t, j) in its owner's buffer
@@ -164,7 +165,8 @@ using namespace b200;
 
 static int fill_views(const char *op, int num_experts, int experts_per_rank, int world, const int *token_mapping,
                       const uint16_t *chosen, const int *counts, const int *cumsum, const int *dst_base,
-                      const unsigned long long *peer_ptrs, RouteView &rv, PeerTable &pt) {
+                      const unsigned long long *peer_ptrs, int64_t capacity_rows, RouteView &rv, PeerTable &pt) {
+  B200_REQUIRE(capacity_rows >= 0, "%s: negative buffer capacity", op);
   B200_REQUIRE(num_experts >= 1 && experts_per_rank >= 1 && world >= 1 && world <= P2P_MAX_RANKS &&
                    experts_per_rank * world == num_experts,
                "%s: need experts_per_rank * world == num_experts and world <= %d (got %d, %d, %d)", op, P2P_MAX_RANKS,
@@ -179,6 +181,7 @@ static int fill_views(const char *op, int num_experts, int experts_per_rank, int
   rv.experts_per_rank = experts_per_rank;
   rv.local_begin = 0;
   rv.local_end = experts_per_rank;
+  rv.capacity_rows = capacity_rows;
   for (int i = 0; i < P2P_MAX_RANKS; i++) pt.base[i] = i < world ? peer_ptrs[i] : 0ull;
   for (int i = 0; i < world; i++) B200_REQUIRE(pt.base[i] != 0 && (pt.base[i] & 15ull) == 0, "%s: bad peer pointer %d", op, i);
   return 0;
@@ -189,8 +192,8 @@ extern "C" int b200_ep_dispatch_rows(int total_tokens, int model_dim, int top_k,
                                      const uint16_t *chosen_experts, const int *expert_counts,
                                      const int *expert_counts_cumsum, const int *dst_base,
                                      const unsigned long long *peer_buffers, int world, int num_experts,
-                                     int experts_per_rank, int local_expert_begin, int local_expert_end,
-                                     void *stream) {
+                                     int experts_per_rank, int64_t capacity_rows, int local_expert_begin,
+                                     int local_expert_end, void *stream) {
   B200_REQUIRE(total_tokens >= 0 && top_k >= 1 && top_k <= B200_MAX_TOP_K && model_dim > 0 && model_dim % 8 == 0 && X &&
                    b200_aligned16(X),
                "ep_dispatch_rows: bad arguments");
@@ -200,7 +203,7 @@ extern "C" int b200_ep_dispatch_rows(int total_tokens, int model_dim, int top_k,
   RouteView rv;
   PeerTable pt;
   if (fill_views("ep_dispatch_rows", num_experts, experts_per_rank, world, token_mapping, chosen_experts, expert_counts,
-                 expert_counts_cumsum, dst_base, peer_buffers, rv, pt))
+                 expert_counts_cumsum, dst_base, peer_buffers, capacity_rows, rv, pt))
     return -1;
   rv.local_begin = local_expert_begin;
   rv.local_end = local_expert_end;
@@ -221,14 +224,14 @@ extern "C" int b200_ep_combine_rows(int num_tokens, int model_dim, int top_k, co
                                     const int *token_mapping, const uint16_t *chosen_experts, const int *expert_counts,
                                     const int *expert_counts_cumsum, const int *dst_base,
                                     const unsigned long long *peer_buffers, int world, int num_experts,
-                                    int experts_per_rank, void *X_combined, void *stream) {
+                                    int experts_per_rank, int64_t capacity_rows, void *X_combined, void *stream) {
   B200_REQUIRE(num_tokens >= 0 && top_k >= 1 && top_k <= B200_MAX_TOP_K && model_dim > 0 && model_dim % 8 == 0 &&
                    X_combined && b200_aligned16(X_combined),
                "ep_combine_rows: bad arguments");
   RouteView rv;
   PeerTable pt;
   if (fill_views("ep_combine_rows", num_experts, experts_per_rank, world, token_mapping, chosen_experts, expert_counts,
-                 expert_counts_cumsum, dst_base, peer_buffers, rv, pt))
+                 expert_counts_cumsum, dst_base, peer_buffers, capacity_rows, rv, pt))
     return -1;
   if (num_tokens == 0) return 0;
   const int dv = model_dim / 8;
@@ -247,12 +250,13 @@ extern "C" int b200_ep_gather_router_grad(int num_tokens, int top_k, const float
                                           const int *token_mapping, const uint16_t *chosen_experts,
                                           const int *expert_counts, const int *expert_counts_cumsum, const int *dst_base,
                                           const unsigned long long *peer_dP_buffers, int world, int num_experts,
-                                          int experts_per_rank, void *dX_routed, void *stream) {
+                                          int experts_per_rank, int64_t capacity_rows, void *dX_routed,
+                                          void *stream) {
   B200_REQUIRE(num_tokens >= 0 && top_k >= 1 && token_expert_weights && dX_routed, "ep_gather_router_grad: bad arguments");
   RouteView rv;
   PeerTable pt;
   if (fill_views("ep_gather_router_grad", num_experts, experts_per_rank, world, token_mapping, chosen_experts,
-                 expert_counts, expert_counts_cumsum, dst_base, peer_dP_buffers, rv, pt))
+                 expert_counts, expert_counts_cumsum, dst_base, peer_dP_buffers, capacity_rows, rv, pt))
     return -1;
   const int64_t n = (int64_t)num_tokens * top_k;
   if (n == 0) return 0;
@@ -266,12 +270,12 @@ extern "C" int b200_ep_publish_row_tags(int num_tokens, int top_k, int my_rank, 
                                         const uint16_t *chosen_experts, const int *expert_counts,
                                         const int *expert_counts_cumsum, const int *dst_base,
                                         const unsigned long long *peer_tag_buffers, int world, int num_experts,
-                                        int experts_per_rank, void *stream) {
+                                        int experts_per_rank, int64_t capacity_rows, void *stream) {
   B200_REQUIRE(num_tokens >= 0 && top_k >= 1 && my_rank >= 0 && my_rank < world, "ep_publish_row_tags: bad arguments");
   RouteView rv;
   PeerTable pt;
   if (fill_views("ep_publish_row_tags", num_experts, experts_per_rank, world, token_mapping, chosen_experts,
-                 expert_counts, expert_counts_cumsum, dst_base, peer_tag_buffers, rv, pt))
+                 expert_counts, expert_counts_cumsum, dst_base, peer_tag_buffers, capacity_rows, rv, pt))
     return -1;
   const int64_t n = (int64_t)num_tokens * top_k;
   if (n == 0) return 0;

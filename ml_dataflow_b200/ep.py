@@ -82,6 +82,29 @@ class RowExchange:
         self.dst_base = (owner_base + before_me).reshape(-1).to(torch.int32).to(self.device)
         return self
 
+    def plan_on_device(self, counts_dev, capacity_rows):
+        """The part of `plan` the peer-memory transports need, computed on the device with no host read:
+        `local_counts`, `local_cumsum` (int32 [E_loc], clipped to `capacity_rows`), `dst_base` (int32 [E]) and
+        `rows_recv_dev` (0-dim int64 tensor, unclipped). The layer then launches everything with its buffer capacity as the row bound; the kernels take the
+        real per-expert counts from these tensors."""
+        G, El = self.world, self.E_loc
+        mine = counts_dev[: self.E].to(torch.int32).contiguous()
+        gathered = torch.empty(G * self.E, dtype=torch.int32, device=mine.device)
+        self.dist.all_gather_into_tensor(gathered, mine)
+        all_counts = gathered.view(G, G, El).to(torch.int64)  # [source rank][destination rank][local expert]
+        per_expert = all_counts[:, self.rank, :].sum(dim=0)
+        self.rows_recv_dev = per_expert.sum()
+        # what the GEMMs are told never reaches past the buffer: rows that do not fit are dropped by the senders
+        # (capacity bound of the peer-memory kernels) and by these clipped counts alike
+        cum = torch.cumsum(per_expert, 0).clamp(max=int(capacity_rows))
+        self.local_cumsum = cum.to(torch.int32)
+        self.local_counts = (cum - torch.cat([cum.new_zeros(1), cum[:-1]])).to(torch.int32)
+        per_owner = all_counts.sum(dim=0)
+        owner_base = torch.cumsum(per_owner, 1) - per_owner
+        before_me = all_counts[: self.rank].sum(dim=0)
+        self.dst_base = (owner_base + before_me).reshape(-1).to(torch.int32)
+        return self
+
     # -------------------------------------------------------------------------------- transport
     def _exchange(self, src, dst, out_cnt, out_off, in_cnt, in_off):
         """Rows src[out_off[p][j] : +out_cnt[p][j]] go to rank p; rows from rank p land in dst[in_off[p][j] : ...]."""
@@ -164,6 +187,8 @@ class ExpertParallelMoELayer:
         self.dx1, self.dx3 = buf((self.cap, f), bf), buf((self.cap, f), bf)
         self.ones = torch.ones(self.cap, dtype=f32, device=self.dev)
         self._flag = torch.zeros(1, dtype=torch.int32, device=self.dev)
+        self.overflowed = torch.zeros((), dtype=torch.bool, device=self.dev)
+        self.rows = 0
         self.profile = None
         # "fused": the outward exchange can run in slices of local experts on a side stream, slice c+1 under the GEMMs
         # of slice c (the copy blocks are small enough to share the SMs with the persistent GEMM CTAs). Measured on
@@ -176,6 +201,17 @@ class ExpertParallelMoELayer:
             self.side = torch.cuda.Stream(device=self.dev)
             self.side_group = dist.new_group()  # its own communicator: side-stream barriers never queue behind main's
             self._flag_side = torch.zeros(1, dtype=torch.int32, device=self.dev)
+
+    def check(self):
+        """Synchronises and raises if a step received more rows than the buffers hold (the extra rows were dropped,
+        never written out of bounds) or if a GEMM kernel gave up a bounded wait."""
+        from . import ops
+
+        if bool(self.overflowed.item()):
+            raise RuntimeError(f"expert-parallel receive buffer too small (capacity {self.cap} rows): rows were dropped")
+        st = ops.gemm_status()
+        if st:
+            raise RuntimeError(f"a GEMM kernel gave up waiting (status {st})")
 
     def _barrier(self):
         """Stream-ordered barrier over all ranks: everything enqueued before it on every rank has finished (and its
@@ -197,10 +233,10 @@ class ExpertParallelMoELayer:
             self.side.wait_event(start)
             for i, (a, b) in enumerate(self.slices):
                 ops.ep_dispatch_rows(T, d, k, rows, row_weights, hm.token_mapping, hm.chosen, hm.counts, hm.cumsum,
-                                     x.dst_base, peer_buffers, E, self.E_loc, (a, b))
+                                     x.dst_base, peer_buffers, E, self.E_loc, self.cap, (a, b))
                 if publish_tags and i == 0:
                     ops.ep_publish_row_tags(T, k, self.dist.get_rank(), hm.token_mapping, hm.chosen, hm.counts,
-                                            hm.cumsum, x.dst_base, self.peers["tags"], E, self.E_loc)
+                                            hm.cumsum, x.dst_base, self.peers["tags"], E, self.E_loc, self.cap)
                 self.dist.all_reduce(self._flag_side, group=self.side_group)
                 ev = torch.cuda.Event()
                 ev.record(self.side)
@@ -227,10 +263,18 @@ class ExpertParallelMoELayer:
             ops.prepare_experts(T, d, k, Xn, hm.token_mapping, hm.zone)
         self.mark("dispatch")
         # the counts exchange also orders this step after every rank's previous step (its buffers are free again)
-        x.plan(hm.counts)
-        if x.rows_recv > self.cap:
-            raise RuntimeError(f"expert-parallel receive buffer too small: {x.rows_recv} rows > capacity {self.cap}")
-        n = x.rows_recv
+        if p2p:
+            # no host read of the counts: every launch below is bounded by the buffer capacity and reads the real
+            # counts on the device; an overflow is recorded in self.overflowed and raised by check()
+            x.plan_on_device(hm.counts, self.cap)
+            self.overflowed |= x.rows_recv_dev > self.cap
+            n = self.cap
+        else:
+            x.plan(hm.counts)
+            if x.rows_recv > self.cap:
+                raise RuntimeError(f"expert-parallel receive buffer too small: {x.rows_recv} rows > capacity {self.cap}")
+            n = x.rows_recv
+        self.rows = n
         if fused:
             ready = self._sliced_dispatch(Xn, None, self.peers["zone"], publish_tags=True)
             for (a, b), ev in zip(self.slices, ready):
@@ -248,7 +292,7 @@ class ExpertParallelMoELayer:
             return out
         if p2p:
             ops.ep_dispatch_rows(T, d, k, Xn, None, hm.token_mapping, hm.chosen, hm.counts, hm.cumsum, x.dst_base,
-                                 self.peers["zone"], E, self.E_loc)
+                                 self.peers["zone"], E, self.E_loc, self.cap)
             self._barrier()
         else:
             x.dispatch(hm.zone, self.zone_r)
@@ -259,7 +303,7 @@ class ExpertParallelMoELayer:
         if p2p:
             self._barrier()
             ops.ep_combine_rows(T, d, k, hm.weights, hm.token_mapping, hm.chosen, hm.counts, hm.cumsum, x.dst_base,
-                                self.peers["Y"], E, self.E_loc, out)
+                                self.peers["Y"], E, self.E_loc, self.cap, out)
         else:
             x.combine(self.Y_r, hm.Y)
             self.mark("merge_experts")
@@ -272,7 +316,7 @@ class ExpertParallelMoELayer:
 
         hm, x = self.home, self.x
         T, d, E, k, f = self.T, self.d, self.E, self.k, self.f
-        n = x.rows_recv
+        n = self.rows
         fused = self.transport == "fused"
         p2p = fused or self.transport == "p2p"
         if fused:
@@ -299,12 +343,12 @@ class ExpertParallelMoELayer:
             self.mark("router_grad")
             hm.dX_routed.zero_()
             ops.ep_gather_router_grad(T, k, hm.weights, hm.token_mapping, hm.chosen, hm.counts, hm.cumsum, x.dst_base,
-                                      self.peers["dP"], E, self.E_loc, hm.dX_routed)
+                                      self.peers["dP"], E, self.E_loc, self.cap, hm.dX_routed)
             return self._router_backward(Xn, Wr, dXn, dWr)
         if p2p:
             self.mark("dispatch_bwd")
             ops.ep_dispatch_rows(T, d, k, dOut, hm.weights, hm.token_mapping, hm.chosen, hm.counts, hm.cumsum,
-                                 x.dst_base, self.peers["dY"], E, self.E_loc)
+                                 x.dst_base, self.peers["dY"], E, self.E_loc, self.cap)
             self._barrier()
         else:
             self.mark("prepare_experts_weighted")
@@ -325,11 +369,11 @@ class ExpertParallelMoELayer:
             self._barrier()
             dXn.zero_()
             ops.ep_combine_rows(T, d, k, None, hm.token_mapping, hm.chosen, hm.counts, hm.cumsum, x.dst_base,
-                                self.peers["dZ"], E, self.E_loc, dXn)
+                                self.peers["dZ"], E, self.E_loc, self.cap, dXn)
             self.mark("router_grad")
             hm.dX_routed.zero_()
             ops.ep_gather_router_grad(T, k, hm.weights, hm.token_mapping, hm.chosen, hm.counts, hm.cumsum, x.dst_base,
-                                      self.peers["dP"], E, self.E_loc, hm.dX_routed)
+                                      self.peers["dP"], E, self.E_loc, self.cap, hm.dX_routed)
         else:
             x.combine(self.dZ_r, hm.dZ)
             x.combine(self.dP_r, hm.dP)

@@ -192,41 +192,45 @@ def _peer_array(ptrs):
 
 def ep_dispatch_rows(total_tokens, model_dim, top_k, X, token_expert_weights, token_mapping, chosen_experts,
                      expert_counts, expert_counts_cumsum, dst_base, peer_buffers, num_experts, experts_per_rank,
-                     local_expert_range=None):
+                     capacity_rows, local_expert_range=None):
     """peer_buffers: list of device addresses, one per rank (this rank's own buffer included).
     local_expert_range: (begin, end) of the owners' local expert indices to move; None = all."""
     lo, hi = (0, experts_per_rank) if local_expert_range is None else local_expert_range
     _check(_lib.load().b200_ep_dispatch_rows(total_tokens, model_dim, top_k, _p(X), _p(token_expert_weights),
                                              _p(token_mapping), _p(chosen_experts), _p(expert_counts),
                                              _p(expert_counts_cumsum), _p(dst_base), _peer_array(peer_buffers),
-                                             len(peer_buffers), num_experts, experts_per_rank, lo, hi, _stream()),
+                                             len(peer_buffers), num_experts, experts_per_rank, capacity_rows, lo, hi,
+                                             _stream()),
            "ep_dispatch_rows", 1 if hi > lo else 0)
 
 
 def ep_combine_rows(num_tokens, model_dim, top_k, token_expert_weights, token_mapping, chosen_experts, expert_counts,
-                    expert_counts_cumsum, dst_base, peer_buffers, num_experts, experts_per_rank, X_combined):
+                    expert_counts_cumsum, dst_base, peer_buffers, num_experts, experts_per_rank, capacity_rows,
+                    X_combined):
     _check(_lib.load().b200_ep_combine_rows(num_tokens, model_dim, top_k, _p(token_expert_weights), _p(token_mapping),
                                             _p(chosen_experts), _p(expert_counts), _p(expert_counts_cumsum),
                                             _p(dst_base), _peer_array(peer_buffers), len(peer_buffers), num_experts,
-                                            experts_per_rank, _p(X_combined), _stream()), "ep_combine_rows")
+                                            experts_per_rank, capacity_rows, _p(X_combined), _stream()),
+           "ep_combine_rows")
 
 
 def ep_gather_router_grad(num_tokens, top_k, token_expert_weights, token_mapping, chosen_experts, expert_counts,
-                          expert_counts_cumsum, dst_base, peer_dP_buffers, num_experts, experts_per_rank, dX_routed):
+                          expert_counts_cumsum, dst_base, peer_dP_buffers, num_experts, experts_per_rank, capacity_rows,
+                          dX_routed):
     _check(_lib.load().b200_ep_gather_router_grad(num_tokens, top_k, _p(token_expert_weights), _p(token_mapping),
                                                   _p(chosen_experts), _p(expert_counts), _p(expert_counts_cumsum),
                                                   _p(dst_base), _peer_array(peer_dP_buffers), len(peer_dP_buffers),
-                                                  num_experts, experts_per_rank, _p(dX_routed), _stream()),
+                                                  num_experts, experts_per_rank, capacity_rows, _p(dX_routed), _stream()),
            "ep_gather_router_grad")
 
 
 def ep_publish_row_tags(num_tokens, top_k, my_rank, token_mapping, chosen_experts, expert_counts, expert_counts_cumsum,
-                        dst_base, peer_tag_buffers, num_experts, experts_per_rank):
+                        dst_base, peer_tag_buffers, num_experts, experts_per_rank, capacity_rows):
     """Writes (my_rank << 40 | zone row) for every routed pair into the owner's tag array (peer stores)."""
     _check(_lib.load().b200_ep_publish_row_tags(num_tokens, top_k, my_rank, _p(token_mapping), _p(chosen_experts),
                                                 _p(expert_counts), _p(expert_counts_cumsum), _p(dst_base),
                                                 _peer_array(peer_tag_buffers), len(peer_tag_buffers), num_experts,
-                                                experts_per_rank, _stream()), "ep_publish_row_tags")
+                                                experts_per_rank, capacity_rows, _stream()), "ep_publish_row_tags")
 
 
 def moe_experts_fwd_scatter(total_rows, model_dim, ffn_dim, num_experts, zone, W1, W3, W2, w1_stride, w3_stride,

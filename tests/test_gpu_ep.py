@@ -63,7 +63,7 @@ def _worker(rank, world, port, result_dir, transport):
                 t_.zero_()
             layer.forward(Xd, Wrd, W1d, W3d, W2d, out)
             layer.backward(Xd, Wrd, W1d, W3d, W2d, dOd, dXn, dWr, dW1, dW3, dW2)
-        assert ops.gemm_status() == 0
+        layer.check()  # no GEMM wait gave up, no receive buffer overflowed
 
         # oracle: every rank's batch through the single-GPU layer; this rank's logits come from its own GPU run
         grads = dict(dW1=np.zeros_like(W1), dW3=np.zeros_like(W3), dW2=np.zeros_like(W2), dWr=np.zeros_like(Wr))
@@ -89,6 +89,63 @@ def _worker(rank, world, port, result_dir, transport):
         open(os.path.join(result_dir, f"ok{rank}"), "w").close()
     finally:
         dist.destroy_process_group()
+
+
+def _overflow_worker(rank, world, port, result_dir):
+    import torch.distributed as dist
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        import sys
+        sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+        from gpu_util import dev_bf16, rand_bf16
+        from ml_dataflow_b200.ep import ExpertParallelMoELayer
+
+        T, d, E, k, f = 384, 256, 8, 2, 128
+        El = E // world
+        rng = np.random.default_rng(5 + rank)
+        X, dOut = dev_bf16(rand_bf16(rng, (T, d))), dev_bf16(rand_bf16(rng, (T, d)))
+        wr = np.random.default_rng(1)
+        Wr = dev_bf16(rand_bf16(wr, (E, d), 0.06))
+        W1, W3 = (dev_bf16(rand_bf16(rng, (El, f, d), 0.06)) for _ in range(2))
+        W2 = dev_bf16(rand_bf16(rng, (El, d, f), 0.06))
+        # receive buffers of 64 rows where about 768 arrive: the step must run to the end, touch nothing outside
+        # its buffers, and report the overflow when asked
+        layer = ExpertParallelMoELayer(T, d, E, k, f, dist, device=torch.device("cuda", rank), transport="fused",
+                                       recv_capacity_factor=0.0)
+        assert layer.cap < 400
+        out = torch.zeros((T, d), dtype=torch.bfloat16, device="cuda")
+        dXn = torch.empty_like(out)
+        dWr = torch.zeros((E, d), dtype=torch.bfloat16, device="cuda")
+        dW1, dW3 = (torch.zeros((El, f, d), dtype=torch.bfloat16, device="cuda") for _ in range(2))
+        dW2 = torch.zeros((El, d, f), dtype=torch.bfloat16, device="cuda")
+        layer.forward(X, Wr, W1, W3, W2, out)
+        layer.backward(X, Wr, W1, W3, W2, dOut, dXn, dWr, dW1, dW3, dW2)
+        torch.cuda.synchronize()
+        assert int(layer.x.local_counts.sum()) <= layer.cap
+        raised = False
+        try:
+            layer.check()
+        except RuntimeError as e:
+            raised = "too small" in str(e)
+        assert raised
+        open(os.path.join(result_dir, f"ok{rank}"), "w").close()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_receive_buffer_overflow_is_reported_not_overrun(tmp_path):
+    """A failure made on the host side (buffers sized far too small): rows that do not fit are dropped by the senders
+    and by the clipped counts, the kernels stay inside their buffers, `check()` raises."""
+    if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+
+    world = 2
+    mp.spawn(_overflow_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    assert sorted(os.listdir(tmp_path)) == ["ok0", "ok1"]
 
 
 @pytest.mark.parametrize("transport", ["fused", "p2p", "nccl"])

@@ -28,9 +28,10 @@ Three transports for the rows:
 
 `RowExchange` holds only the bookkeeping and the point-to-point batches (torch.distributed
 `batch_isend_irecv`: one NCCL group per exchange over NVLink; also runs on gloo for the CPU tests).
-The row counts must be known on the host to size the messages, so `plan()` reads the exchanged
-counts back once per layer - the same place where the reference's block synchronises to read
-`host_expert_counts` (dataflow_transformer.c:2789).
+Only the "nccl" transport needs the row counts on the host (to size its messages): its `plan()` reads
+the exchanged counts back once per layer - the same place where the reference's block synchronises to
+read `host_expert_counts` (dataflow_transformer.c:2789). The peer-memory transports use
+`plan_on_device()` and never leave the stream.
 """
 import torch
 

@@ -1,23 +1,29 @@
-// bf16 GEMM for sm_100a on tcgen05 tensor cores: operands staged in shared memory by TMA
-// (128-byte swizzle, 64x64 boxes), fp32 accumulators in tensor memory, one persistent CTA per
-// SM with three roles - a TMA producer warp, an MMA-issuing warp, four epilogue warps.
+// bf16 GEMM for sm_100a on tcgen05 tensor cores: operands staged in shared memory by TMA (128-byte swizzle,
+// 64x64 boxes), fp32 accumulators in tensor memory, one persistent CTA per SM of twelve warps with these roles:
+//   warp 0            one thread issues the TMA loads of operand A
+//   warp 1            one thread issues the MMAs (in a pair: the even CTA; the odd CTA's thread hands its slabs over)
+//   warps 2..9        epilogue: tcgen05.ld, convert, fused SwiGLU forward / backward or plain store / accumulate
+//   warp 10           grouped weight gradients only: clears the reduction tail of an expert's last slab
+//   warp 11           one thread issues the TMA loads of operand B
+// The producer and MMA loops run on a single thread each, with no warp-wide operation between two stages.
 //
 // One kernel body serves
-//   * the dense matmul op (any combination of K-major / MN-major operands),
-//   * the expert-grouped forward / dgrad GEMMs (groups along the rows, weights picked by the
-//     third TMA coordinate), with fused SwiGLU forward or backward epilogues,
-//   * the expert-grouped wgrad GEMMs (groups along the reduction; the rows of the last 64-row
-//     slab that belong to the next expert are zeroed in shared memory before the MMA).
+//   * the dense matmul op (any combination of K-major / MN-major operands), optionally with the reduction cut into
+//     ranges whose fp32 partial results a second kernel adds (few output tiles, long reduction: the router GEMMs),
+//   * the expert-grouped forward / dgrad GEMMs (groups along the rows, weights picked by the third TMA coordinate),
+//     with fused SwiGLU forward or backward epilogues and, for expert parallelism, output rows stored wherever a
+//     per-row tag says (another GPU's buffer included),
+//   * the expert-grouped wgrad GEMMs (groups along the reduction).
 //
-// Tile per CTA: 128 rows x up to 256 columns x 64 deep per stage; two 256-column accumulator
-// buffers in tensor memory so the epilogue of one tile overlaps the next tile's MMAs.
-// Two variants of the same body:
-//   single (cta_group::1): 4 stages of 48 KiB (A 128x64 + B 256x64);
-//   pair   (cta_group::2): two CTAs of a cluster share one 256 x 256 MMA; each loads its 128 rows of
-//           A and HALF the columns of B (32 KiB per stage, 6 stages), so the same tensor work needs
-//           two thirds of the shared-memory fill bandwidth and tolerates more load latency. No TMA
-//           multicast is used: every CTA fetches its own boxes, the even CTA issues the MMAs, and
-//           tcgen05.commit tells both CTAs when a stage or an accumulator is done.
+// Tile per CTA: 128 rows x up to 256 columns; two 256-column accumulator buffers in tensor memory so the epilogue
+// of one tile overlaps the next tile's MMAs. Two variants of the same body:
+//   single (cta_group::1): 4 stages of one 64-deep slab, 48 KiB each (A 128x64 + B 256x64);
+//   pair   (cta_group::2): two CTAs of a cluster share one 256 x 256 MMA; each loads its 128 rows of A and HALF
+//           the columns of B; a stage holds two 64-deep slabs (64 KiB, 3 stages), so one barrier round trip covers
+//           eight MMAs. No TMA multicast is used: every CTA fetches its own boxes, the odd CTA reports its slabs
+//           with a remote arrive on the even CTA's full barrier, and tcgen05.commit (multicast to both CTAs) says
+//           when a stage or an accumulator is done.
+// Every wait on a barrier is bounded; a wait that runs out raises a status word and the CTA leaves in order.
 #include <stdlib.h>
 #include <string.h>
 

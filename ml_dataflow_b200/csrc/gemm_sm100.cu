@@ -540,9 +540,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
         atomicAdd(&g_gemm_stats[4], (unsigned long long)(clock64() - st_begin));
         atomicAdd(&g_gemm_stats[7], (unsigned long long)st_acc[2]);
         atomicAdd(&g_gemm_stats[5], (unsigned long long)st_acc[3]);
-      } else if (false) {
-        atomicAdd(&g_gemm_stats[5], (unsigned long long)st_acc[0]);
-        atomicAdd(&g_gemm_stats[6], (unsigned long long)(clock64() - st_begin));
+      } else {
+        atomicAdd(&g_gemm_stats[6], (unsigned long long)st_acc[0]);
       }
 #endif
     }
@@ -1030,8 +1029,9 @@ __global__ void splitk_reduce_kernel(int64_t n, int splits, const float *__restr
 using namespace b200;
 
 #ifdef B200_GEMM_STATS
-// debugging build only: cycles summed over CTAs {producer wait-empty, producer total, leader wait-full, leader
-// wait-accumulator, leader total, odd-CTA wait-full, odd-CTA total}; reading clears
+// debugging build only: cycles summed over CTAs {0 producers waiting for a free stage, 1 producers' lifetime,
+// 2 MMA thread waiting for data, 3 waiting for a free accumulator, 4 MMA thread's lifetime, 5 in tcgen05.commit,
+// 6 odd CTA's thread waiting for its slabs, 7 issuing the MMAs}; reading clears
 extern "C" int b200_dbg_gemm_stats(unsigned long long *out) {
   B200_CUDA(cudaDeviceSynchronize());
   B200_CUDA(cudaMemcpyFromSymbol(out, g_gemm_stats, sizeof(unsigned long long) * 8));

@@ -12,6 +12,10 @@
  * Each declaration names the reference interface it stands in for
  * (paths are relative to the reference project root).
  *
+ * Threading: like the reference's op table (libdataflow/include/dataflow_table.h:6) the entry points expect one
+ * submitting host thread per process and device; the library keeps small per-process caches (kernel attributes,
+ * the address of its status word) that are filled on first use without locking.
+ *
  * Element types use the reference's DataflowDatatype numbering
  * (libdataflow/include/dataflow_common.h:46-74).
  */

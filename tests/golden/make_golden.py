@@ -24,6 +24,7 @@ CASES = {
     # name: (T, d, E, k, f, seed)
     "moe_mlp_small": (96, 128, 8, 2, 64, 1234),
     "moe_mlp_k4": (80, 64, 16, 4, 96, 4321),
+    "moe_mlp_e64k8": (72, 64, 64, 8, 32, 777),   # the benchmark's routing shape: 64 experts, top-8 (9 rows per expert)
 }
 
 

@@ -173,7 +173,7 @@ def test_layer_config1_fast_path(oracle):
     compare_with_oracle(oracle, layer, out, dXn, G, X, Wr, W1, W3, W2, dOut, g0, k, "fast")
 
 
-@pytest.mark.parametrize("name", ["moe_mlp_small", "moe_mlp_k4"])
+@pytest.mark.parametrize("name", ["moe_mlp_small", "moe_mlp_k4", "moe_mlp_e64k8"])
 def test_layer_against_reference_pytorch_golden(name):
     """The CUDA layer against tensors produced by the reference's own PyTorch MoE layer (tests/golden)."""
     require_b200()

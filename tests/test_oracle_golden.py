@@ -27,7 +27,7 @@ def rel_fro(a, b):
     return float(np.linalg.norm(a - b) / (np.linalg.norm(b) + 1e-30))
 
 
-@pytest.mark.parametrize("name", ["moe_mlp_small", "moe_mlp_k4"])
+@pytest.mark.parametrize("name", ["moe_mlp_small", "moe_mlp_k4", "moe_mlp_e64k8"])
 def test_oracle_matches_reference_pytorch_layer(oracle, name):
     g = np.load(os.path.join(GOLD, name + ".npz"))
     T, d, E, k, f = [int(v) for v in g["shape"]]

@@ -223,6 +223,21 @@ int b200_gemm_status(int *status_out);
  */
 int b200_gemm_set_pair_mode(int on);
 
+/*
+ * Runs the GEMM kernels' tile scheduler on the HOST (the same code the device runs) and lists the tiles one launch
+ * would process, in processing order: for checking the index arithmetic where there is no GPU. group_mode 0 = dense,
+ * 1 = groups along the rows (forward / dgrad), 2 = groups along the reduction (wgrad); pair as in
+ * b200_gemm_set_pair_mode; M = output rows (dense, wgrad), N = output columns, K = reduction length; dual_b = 1 for
+ * the fused W1 | W3 launch; counts / cumsum_incl are host arrays of num_groups ints (unused when dense);
+ * k_splits / k_split_len describe a split reduction (dense only, 0 = none). Writes up to max_tiles records of nine
+ * ints {group, first A row, first output row, valid rows, first column, valid columns, loaded columns, first
+ * reduction row, reduction length} to out and returns the number of tiles (-1 on bad arguments). No counterpart in
+ * the reference.
+ */
+int b200_gemm_enumerate_tiles(int group_mode, int pair, int M, int N, int K, int dual_b, int num_groups,
+                              const int *counts, const int *cumsum_incl, int k_splits, int k_split_len, int max_tiles,
+                              int *out);
+
 /* ---- grouped expert GEMMs (additive ops; the reference loops experts on the host) ----------- */
 
 /*

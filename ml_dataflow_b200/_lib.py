@@ -43,6 +43,7 @@ SIGNATURES = {
                                           _vp, _vp, _i, _i64, _vp]),
     "b200_moe_experts_bwd_x_scatter": (_i, [_i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp,
                                             _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i64, _vp]),
+    "b200_gemm_enumerate_tiles": (_i, [_i, _i, _i, _i, _i, _i, _i, _vp, _vp, _i, _i, _i, _vp]),
     "b200_moe_block_fwd": (_i, [_vp, _vp, _vp, _vp]),
     "b200_moe_block_recompute": (_i, [_vp, _vp, _i, _vp]),
     "b200_moe_block_bwd": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),

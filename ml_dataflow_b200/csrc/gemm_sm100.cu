@@ -28,6 +28,7 @@
 #include <string.h>
 
 #include <algorithm>
+#include <vector>
 
 #include "common.cuh"
 #include "sm100_ptx.cuh"
@@ -147,7 +148,31 @@ struct Sched {
   const int *s_cnt, *s_base, *s_tpre;
   int cursor;
 
-  __device__ __forceinline__ bool get(int tile_id, Tile &t) {
+  // s_cnt[g] rows of group g, s_base[g] its first row, s_tpre[g] row tiles of the groups before it (GROUPED_M)
+  __host__ __device__ __forceinline__ void init(int group_mode, int M_, int N_, int K_, int dual_b, bool pair,
+                                                int tile_rows, int splits, int split_len, const int *cnt,
+                                                const int *base, const int *tpre, int groups) {
+    mode = group_mode;
+    M = M_;
+    N = N_;
+    K = K_;
+    tile_m = tile_rows;
+    n_tile_w = dual_b ? 128 : 256;
+    n_round = (pair && !dual_b) ? 128 : 64;
+    tiles_n = (N + n_tile_w - 1) / n_tile_w;
+    tiles_m = (M + tile_m - 1) / tile_m;
+    s_cnt = cnt;
+    s_base = base;
+    s_tpre = tpre;
+    cursor = 0;
+    k_splits = splits;
+    k_split_len = split_len;
+    if (mode == DENSE) total_tiles = tiles_m * tiles_n * (splits > 1 ? splits : 1);
+    else if (mode == GROUPED_M) total_tiles = tpre[groups] * tiles_n;
+    else total_tiles = groups * tiles_m * tiles_n;
+  }
+
+  __host__ __device__ __forceinline__ bool get(int tile_id, Tile &t) {
     if (tile_id >= total_tiles) return false;
     int nt;
     if (mode == DENSE) {
@@ -296,24 +321,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
   const uint32_t tmem_base = st->tmem_base;
 
   Sched sched;
-  sched.mode = p.group_mode;
-  sched.M = p.M;
-  sched.N = p.N;
-  sched.K = p.K;
-  sched.tile_m = CF::TILE_M;
-  sched.n_tile_w = p.dual_b ? 128 : 256;
-  sched.n_round = (PAIR && !p.dual_b) ? 128 : 64;
-  sched.tiles_n = (p.N + sched.n_tile_w - 1) / sched.n_tile_w;
-  sched.tiles_m = (p.M + CF::TILE_M - 1) / CF::TILE_M;
-  sched.s_cnt = tab_cnt;
-  sched.s_base = tab_base;
-  sched.s_tpre = tab_tpre;
-  sched.cursor = 0;
-  sched.k_splits = p.k_splits;
-  sched.k_split_len = p.k_split_len;
-  if (p.group_mode == DENSE) sched.total_tiles = sched.tiles_m * sched.tiles_n * max(1, p.k_splits);
-  else if (p.group_mode == GROUPED_M) sched.total_tiles = tab_tpre[G] * sched.tiles_n;
-  else sched.total_tiles = G * sched.tiles_m * sched.tiles_n;
+  sched.init(p.group_mode, p.M, p.N, p.K, p.dual_b, PAIR, CF::TILE_M, p.k_splits, p.k_split_len, tab_cnt, tab_base,
+             tab_tpre, G);
   const int first_tile = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
   const int tile_step = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
   const int row_off = (int)cta_rank * BM;  // this CTA's rows inside a pair tile
@@ -1040,6 +1049,38 @@ extern "C" int b200_dbg_gemm_stats(unsigned long long *out) {
   return 0;
 }
 #endif
+
+// Host run of the kernels' tile scheduler (same Sched code as the device uses): lists the tiles a launch would
+// process, in order. counts / cumsum_incl are HOST arrays here. Nothing touches a GPU.
+extern "C" int b200_gemm_enumerate_tiles(int group_mode, int pair, int M, int N, int K, int dual_b, int num_groups,
+                                         const int *counts, const int *cumsum_incl, int k_splits, int k_split_len,
+                                         int max_tiles, int *out) {
+  B200_REQUIRE(group_mode >= DENSE && group_mode <= GROUPED_K && num_groups >= 1 && num_groups <= MAX_GROUPS && out,
+               "gemm_enumerate_tiles: bad arguments");
+  B200_REQUIRE(group_mode == DENSE || (counts && cumsum_incl), "gemm_enumerate_tiles: group tables missing");
+  const int tile_rows = pair ? 2 * BM : BM;
+  std::vector<int> cnt(num_groups, 0), base(num_groups, 0), tpre(num_groups + 1, 0);
+  if (group_mode != DENSE) {
+    for (int e = 0; e < num_groups; e++) {
+      cnt[e] = counts[e];
+      base[e] = cumsum_incl[e] - counts[e];
+      tpre[e + 1] = tpre[e] + (cnt[e] + tile_rows - 1) / tile_rows;
+    }
+  }
+  Sched sc;
+  sc.init(group_mode, M, N, K, dual_b, pair != 0, tile_rows, k_splits, k_split_len, cnt.data(), base.data(), tpre.data(),
+          num_groups);
+  Tile t;
+  int n = 0;
+  for (int id = 0; sc.get(id, t); id++) {
+    if (n < max_tiles) {
+      const int rec[9] = {t.group, t.a_row0, t.out_row0, t.m_valid, t.n0, t.n_valid, t.nw, t.k_row0, t.k_len};
+      memcpy(out + (size_t)n * 9, rec, sizeof(rec));
+    }
+    n++;
+  }
+  return n;
+}
 
 extern "C" int b200_gemm_set_pair_mode(int on) {
   g_pair_mode = on ? 1 : 0;

@@ -84,6 +84,17 @@ def _worker(rank, world, port, E, d, seed, result_dir):
         assert positions == list(range(x.rows_recv))         # at distinct, dense positions
         homes = sorted((t >> 40, t & ((1 << 40) - 1)) for t in tags_here.values())
         assert homes == [(rank, i) for i in range(R)]        # and this rank's rows each get exactly one way back
+        # the device-side plan (no host read of the counts) must agree with the host plan, and clip to a capacity
+        y = RowExchange(dist, E, torch.device("cpu")).plan_on_device(torch.from_numpy(counts), 1 << 30)
+        assert y.local_counts.tolist() == x.local_counts.tolist()
+        assert y.local_cumsum.tolist() == x.local_cumsum.tolist()
+        assert y.dst_base.tolist() == x.dst_base.tolist()
+        assert int(y.rows_recv_dev) == x.rows_recv
+        small = max(1, x.rows_recv // 2)
+        z = RowExchange(dist, E, torch.device("cpu")).plan_on_device(torch.from_numpy(counts), small)
+        assert int(z.rows_recv_dev) == x.rows_recv                     # the true total is still reported
+        assert z.local_cumsum.tolist() == [min(c, small) for c in x.local_cumsum.tolist()]
+        assert int(z.local_counts.sum()) == min(small, x.rows_recv) and (z.local_counts >= 0).all()
         # identity experts, then the way back
         back = torch.full((R, d), -5.0)
         x.combine(recv, back)

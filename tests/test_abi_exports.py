@@ -56,3 +56,22 @@ def test_block_structure_mirror_matches_the_header():
     assert fields == [f[0] for f in _lib.MoeBlock._fields_]
     # 5 ints (+4 pad), then only 8-byte members
     assert ctypes.sizeof(_lib.MoeBlock) == 24 + 8 * (len(fields) - 5)
+
+
+def test_host_only_entry_points_answer_without_a_gpu():
+    """Sizing functions run on the host: scratch for the mapping grows with the problem and stays 16-byte granular;
+    the built-in scratch of the no-allocation variant is 4 MiB and holds the benchmark's shapes."""
+    from ml_dataflow_b200 import _lib
+
+    lib = _lib.load()
+    ws = lib.b200_build_expert_mapping_workspace_bytes
+    cap = lib.b200_build_expert_mapping_static_capacity_bytes()
+    assert cap == 4 << 20
+    prev = 0
+    for T in (1, 1000, 8192, 32768, 65536, 1 << 20):
+        n = ws(T, 64, 8)
+        assert n >= prev and n > 0 and n % 4 == 0
+        prev = n
+        assert n <= cap                      # 64 experts fit the built-in scratch at any token count
+    assert ws(1 << 20, 4096, 8) > cap        # a problem the no-allocation variant must refuse
+    assert ws(8192, 64, 8) <= ws(8192, 256, 8)

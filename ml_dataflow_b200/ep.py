@@ -16,7 +16,7 @@ Per layer and direction there is one exchange each way:
   -> grouped expert GEMMs on the received rows -> the reverse exchange -> local weighted combine.
 
 Three transports for the rows:
-  * "fused": as "p2p" on the way out; on the way back the LAST GEMM of each pass does the exchange itself: its
+  * "fused" (default): as "p2p" on the way out; on the way back the LAST GEMM of each pass does the exchange itself: its
     epilogue stores every output row (Y forward, dZ backward) straight into the zone-ordered buffer of the token's
     home rank (peer stores, tile by tile under the MMAs of the next tile), guided by a per-row tag the home rank
     published next to the row. After one barrier the combine / un-permute is a purely local kernel.
@@ -140,7 +140,7 @@ class RowExchange:
 class ExpertParallelMoELayer:
     """Same call surface as `MoELayer`, with W1/W3/W2 and their gradients holding only this rank's experts."""
 
-    def __init__(self, T, d, E, k, f, dist, device="cuda", recv_capacity_factor=1.5, transport="p2p", slices=1):
+    def __init__(self, T, d, E, k, f, dist, device="cuda", recv_capacity_factor=1.5, transport="fused", slices=1):
         self.T, self.d, self.E, self.k, self.f = T, d, E, k, f
         self.dist = dist
         self.dev = torch.device(device)

@@ -4,16 +4,23 @@
 
 N = 1: one MoE layer fwd+bwd at T=8192, d=4096, 64 experts, top-8, ffn 1408 (bf16 weights N(0,0.02),
 activations / upstream gradient N(0,1), fp32 router logits from a bf16 router weight); synthetic seeded data.
+The line also carries `ns_shape`: the same layer at T=32768 on the one GPU (device-timed, with its GEMM fractions).
 N > 1 (launched with torch.distributed.run, one rank per GPU): the expert-parallel layer, 64 experts sharded
 over the ranks, T=32768 tokens per GPU (weak scaling); rows travel over NVLink peer memory, out through the gather
-kernel and back through the epilogue of the last GEMM of each pass (B200_EP_TRANSPORT=fused|p2p|nccl).
+kernel and back through the epilogue of the last GEMM of each pass (B200_EP_TRANSPORT=fused|p2p|nccl). After the
+timed regions every rank runs one small expert-parallel layer against the CPU oracle (`ep_parity`; a mismatch
+replaces the line by an error and exit code 1), and rank 0 runs the same per-GPU batch on one GPU with all experts
+(`same_batch_1gpu`), from which `efficiency_same_batch` = value / (N x that value).
 
 Prints ONE JSON line on rank 0. `value` is device-timed with inputs resident in HBM; `e2e` is the same step
-driven from pinned host buffers with the host<->device copies inside the timed region; `roofline` covers the
-grouped tcgen05 GEMM launches (the dominant kernel) and `kernels` lists every op group with its own bound;
-`cpu_baseline` is the CPU oracle timed on a bounded token sample of the same shape on this box's host cores.
+driven from pinned host buffers with the host<->device copies inside the timed region (`host_link` gives what the
+host path delivers per GPU for those copies alone); `roofline` covers the grouped tcgen05 GEMM launches (the dominant
+kernel) and `kernels` lists every op group with its own bound; `cpu_baseline` is the CPU oracle timed on a bounded
+token sample of the same shape, and on the CPU-runnable configuration (T=2048, d=1024, 16 experts, top-2) in full,
+on this box's host cores.
 `--impl reference` times that CPU restatement of the reference's algorithm only (the reference has no CPU
-implementation of this path of its own, and its CUDA kernels are what this repository replaces).
+implementation of this path of its own, and its CUDA kernels are what this repository replaces); under
+torch.distributed.run rank 0 alone runs it, on all host cores.
 """
 import argparse
 import json
@@ -29,9 +36,11 @@ if ROOT not in sys.path:
 
 METRIC = "moe_layer_fwd_bwd_tokens_per_s"
 UNIT = "tokens/s"
-CFG_1GPU = dict(T=8192, d=4096, E=64, k=8, f=1408)       # BASELINE configs[1]
-CFG_EP = dict(T=32768, d=4096, E=64, k=8, f=1408)        # BASELINE configs[4], T per GPU
-CPU_SAMPLE_TOKENS = 512
+CFG_1GPU = dict(T=8192, d=4096, E=64, k=8, f=1408)       # the 1-GPU configuration the metric is quoted on
+CFG_NS = dict(T=32768, d=4096, E=64, k=8, f=1408)        # the target shape: T=32768 on one GPU
+CFG_EP = dict(T=32768, d=4096, E=64, k=8, f=1408)        # expert-parallel configuration, T per GPU
+CFG_CPU_FULL = dict(T=2048, d=1024, E=16, k=2, f=1024)   # the CPU-runnable configuration, run in full on the host
+CPU_SAMPLE_TOKENS = 1024
 
 
 def read_peaks():
@@ -104,13 +113,15 @@ class ClockSampler:
 
 
 # ------------------------------------------------------------------------------------------ CPU arm
-def cpu_reference_run(cfg, steps, warmup):
-    """Times the CPU oracle (fwd+bwd) on CPU_SAMPLE_TOKENS tokens of the workload's shape. Returns tokens/s."""
+def cpu_reference_run(cfg, tokens, steps, warmup):
+    """Times the CPU oracle (fwd+bwd) on `tokens` tokens of the shape `cfg`, on every host core this process may use.
+    Returns (tokens/s, seconds per pass, threads)."""
     import numpy as np
     from oracle import oracle as orc
 
     orc.build()
-    Ts, d, E, k, f = CPU_SAMPLE_TOKENS, cfg["d"], cfg["E"], cfg["k"], cfg["f"]
+    threads = orc.use_all_cores()  # process launchers export OMP_NUM_THREADS=1
+    Ts, d, E, k, f = tokens, cfg["d"], cfg["E"], cfg["k"], cfg["f"]
     X, dOut = orc.normal_bf16((Ts, d), 0xB2000001), orc.normal_bf16((Ts, d), 0xB2000002)
     Wr = orc.normal_bf16((E, d), 0xB2000003, std=0.02)
     W1 = orc.normal_bf16((E, f, d), 0xB2000004, std=0.02)
@@ -125,24 +136,36 @@ def cpu_reference_run(cfg, steps, warmup):
         if i >= warmup:
             times.append(time.perf_counter() - t0)
     sec = sum(times) / len(times)
-    return Ts / sec, sec, orc.num_threads()
+    return Ts / sec, sec, threads
+
+
+def cpu_baseline_record(cfg, steps, warmup):
+    """The CPU legs: a bounded token sample of the workload `cfg` (the value that sits beside the GPU number) and the
+    CPU-runnable configuration in full."""
+    tps, sec, threads = cpu_reference_run(cfg, CPU_SAMPLE_TOKENS, steps, warmup)
+    full_tps, full_sec, _ = cpu_reference_run(CFG_CPU_FULL, CFG_CPU_FULL["T"], 2, 1)
+    c = CFG_CPU_FULL
+    return dict(
+        value=tps, unit=UNIT, cores=threads, kind="port",
+        sample=(f"{CPU_SAMPLE_TOKENS} tokens of the workload shape (d={cfg['d']}, E={cfg['E']}, top-{cfg['k']}, ffn "
+                f"{cfg['f']}), fwd+bwd through the CPU restatement of the reference kernels, OpenMP, {sec:.1f} s per pass"),
+        cpu_config_in_full=dict(workload=workload_name(c, 1), value=full_tps, unit=UNIT, ms_per_step=full_sec * 1e3,
+                                steps=2, warmup=1)), sec
 
 
 def run_reference_arm(args, cfg, world):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    steps, warmup = max(1, args.steps), max(0, args.warmup)
-    # keep the whole run within a few minutes: one sample step costs a few seconds of CPU
-    steps, warmup = min(steps, 5), min(warmup, 1)
-    tps, sec, threads = cpu_reference_run(cfg, steps, warmup)
-    sample = (f"{CPU_SAMPLE_TOKENS} tokens of the workload shape (d={cfg['d']}, E={cfg['E']}, top-{cfg['k']}, "
-              f"ffn {cfg['f']}); fwd+bwd through the CPU restatement of the reference kernels, OpenMP")
-    line = dict(metric=METRIC, value=tps, unit=UNIT, n_gpus=world, steps=steps, warmup=warmup, ms_per_step=sec * 1e3,
+    # one sample pass costs a few seconds of CPU: the step count is bounded so the run ends within minutes
+    steps, warmup = min(max(1, args.steps), 3), min(max(0, args.warmup), 1)
+    rec, sec = cpu_baseline_record(cfg, steps, warmup)
+    line = dict(metric=METRIC, value=rec["value"], unit=UNIT, n_gpus=world, steps=steps, warmup=warmup,
+                steps_requested=args.steps, warmup_requested=args.warmup, ms_per_step=sec * 1e3,
                 higher_is_better=True, scaling="weak", vs_baseline=None, dtype="bf16", data="synthetic", impl="reference",
                 config=dict(workload=workload_name(cfg, world), T_sample=CPU_SAMPLE_TOKENS),
-                cpu_baseline=dict(value=tps, unit=UNIT, cores=threads, kind="port", sample=sample),
-                e2e=dict(value=tps, unit=UNIT, h2d_bytes_per_step=0, d2h_bytes_per_step=0), gpu_launches=0)
+                cpu_baseline=rec,
+                e2e=dict(value=rec["value"], unit=UNIT, h2d_bytes_per_step=0, d2h_bytes_per_step=0), gpu_launches=0)
     print(json.dumps(line), flush=True)
 
 
@@ -173,11 +196,13 @@ def algorithmic_work(cfg):
     }
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum of the seven expert GEMM launches of one step, from one ncu pass on the
-# full-size 1-GPU workload (profiles/gemm_sm100_kernel__moe_layer_T8192_d4096_E64_k8_f1408.md, section 2)
+# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of the seven expert GEMM launches of one step, from an
+# ncu pass over the same workload. It is a recorded profile figure, not a measurement of the present run.
 NCU_GEMM_DRAM_BYTES_PER_STEP = {(8192, 4096, 64, 8, 1408): 16.5e9}
+NCU_TRAFFIC_SOURCE = ("ncu dram__bytes_read.sum + dram__bytes_write.sum over the 7 launches of one step, one pass, "
+                      "recorded from a profiler run of this workload (not measured by this run)")
 
-NVLINK_PEER_GBS = 770.0  # measured peer copy per direction on this pool (nominal 900)
+NVLINK_PEER_GBS_RECORDED = 770.0  # peer copy per direction recorded for this machine type (nominal 900)
 
 
 def exchange_work(cfg, world):
@@ -185,6 +210,139 @@ def exchange_work(cfg, world):
     R = cfg["T"] * cfg["k"]
     rows = 2 * R * cfg["d"] * (world - 1) / world
     return {"dispatch": rows, "return": rows, "dispatch_bwd": rows, "return_bwd": rows + 4 * R * (world - 1) / world}
+
+
+def gpu_numa_cpus(index):
+    """(numa node, cpu list) of the GPU `index`, read from sysfs; (None, None) when it cannot be told."""
+    try:
+        import torch
+
+        pr = torch.cuda.get_device_properties(index)
+        addr = f"{pr.pci_domain_id:04x}:{pr.pci_bus_id:02x}:{pr.pci_device_id:02x}.0"
+        with open(f"/sys/bus/pci/devices/{addr}/numa_node") as fh:
+            node = int(fh.read().strip())
+        if node < 0:
+            return None, None
+        with open(f"/sys/devices/system/node/node{node}/cpulist") as fh:
+            cpus = set()
+            for part in fh.read().strip().split(","):
+                lo, _, hi = part.partition("-")
+                cpus.update(range(int(lo), int(hi or lo) + 1))
+        return node, cpus
+    except Exception:
+        return None, None
+
+
+def measure_peer_copy_gbs(dev_from, dev_to, mib=256, reps=5):
+    """Device-to-device copy rate between two GPUs of this node (GB/s, one direction), timed with CUDA events."""
+    import torch
+
+    n = mib << 20
+    a = torch.empty(n, dtype=torch.uint8, device=f"cuda:{dev_from}")
+    b = torch.empty(n, dtype=torch.uint8, device=f"cuda:{dev_to}")
+    b.copy_(a)
+    torch.cuda.synchronize(dev_from)
+    torch.cuda.synchronize(dev_to)
+    with torch.cuda.device(dev_from):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            b.copy_(a, non_blocking=True)
+        e1.record()
+        e1.synchronize()
+        ms = e0.elapsed_time(e1) / reps
+    del a, b
+    return n / (ms * 1e-3) / 1e9
+
+
+def per_op_profile(layer, step, work, peaks, reps):
+    """Runs `step` with an event between the ops and returns ({group: record}, GEMM ms, GEMM flop, raw ms per mark)."""
+    import torch
+
+    acc = {}
+    for _ in range(reps):
+        layer.profile = []
+        step()
+        layer.mark("end")
+        torch.cuda.synchronize()
+        marks = layer.profile
+        layer.profile = None
+        per_step = {}  # a phase that runs in slices is marked once per slice: sum inside the step
+        for (name, ev), (_, nxt) in zip(marks[:-1], marks[1:]):
+            per_step[name] = per_step.get(name, 0.0) + ev.elapsed_time(nxt)
+        for name, ms in per_step.items():
+            acc.setdefault(name, []).append(ms)
+    kernels = {}
+    gemm_ms, gemm_flops = 0.0, 0
+    for name, (bound, amount) in work.items():
+        if name not in acc:
+            continue
+        ms = sum(acc[name]) / len(acc[name])
+        if bound == "tensor":
+            ach = amount / (ms * 1e-3) / 1e12
+            kernels[name] = dict(ms=round(ms, 4), bound="tensor", achieved=round(ach, 1), unit="TFLOP/s",
+                                 frac=round(ach / peaks["bf16_tflops_sustained"], 4),
+                                 frac_of_burst_peak=round(ach / peaks["bf16_tflops"], 4))
+            gemm_ms += ms
+            gemm_flops += amount
+        else:
+            ach = amount / (ms * 1e-3) / 1e9
+            kernels[name] = dict(ms=round(ms, 4), bound="hbm", achieved=round(ach, 1), unit="GB/s",
+                                 frac=round(ach / peaks["hbm_gbs"], 4))
+    return kernels, gemm_ms, gemm_flops, {n: sum(v) / len(v) for n, v in acc.items()}
+
+
+def single_gpu_layer_run(cfg, dev, steps, warmup, peaks, seed):
+    """One GPU, one MoE layer of shape `cfg`, inputs resident: device-timed ms/step through b200_moe_block_fwd / _bwd
+    and the per-op roofline. Used for the target shape beside the headline and as the same-batch base of the
+    multi-GPU lines. Frees what it allocated."""
+    import torch
+
+    from ml_dataflow_b200 import ops
+    from ml_dataflow_b200.moe_layer import MoELayer
+
+    T, d, E, k, f = cfg["T"], cfg["d"], cfg["E"], cfg["k"], cfg["f"]
+    gen = torch.Generator(device=dev).manual_seed(seed)
+
+    def normal(shape, std):
+        return (torch.randn(shape, generator=gen, device=dev) * std).to(torch.bfloat16)
+
+    X, dOut, Wr = normal((T, d), 1.0), normal((T, d), 1.0), normal((E, d), 0.02)
+    W1, W3, W2 = normal((E, f, d), 0.02), normal((E, f, d), 0.02), normal((E, d, f), 0.02)
+    out, dXn, dWr = torch.zeros_like(X), torch.empty_like(X), torch.zeros_like(Wr)
+    dW1, dW3, dW2 = torch.zeros_like(W1), torch.zeros_like(W3), torch.zeros_like(W2)
+    layer = MoELayer(T, d, E, k, f, device=dev)
+    block = layer.block(Wr, W1, W3, W2)
+
+    def step():
+        out.zero_()
+        if layer.profile is None:
+            ops.moe_block_fwd(block, X, out)
+            ops.moe_block_bwd(block, X, dOut, dXn, dWr, dW1, dW3, dW2)
+        else:
+            layer.forward(X, Wr, W1, W3, W2, out)
+            layer.backward(X, Wr, W1, W3, W2, dOut, dXn, dWr, dW1, dW3, dW2)
+
+    for _ in range(max(3, warmup)):
+        step()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    if ops.gemm_status() != 0:
+        raise RuntimeError("a GEMM kernel gave up waiting; the timing is void")
+    kernels, gemm_ms, gemm_flops, _ = per_op_profile(layer, step, algorithmic_work(cfg), peaks, 3)
+    ach = gemm_flops / (gemm_ms * 1e-3) / 1e12 if gemm_ms else 0.0
+    rec = dict(workload=workload_name(cfg, 1), ms_per_step=round(ms, 4), value=T / (ms * 1e-3), unit=UNIT, steps=steps,
+               gemm_tflops=round(ach, 1), gemm_frac_of_sustained_peak=round(ach / peaks["bf16_tflops_sustained"], 4),
+               gemm_frac_of_burst_peak=round(ach / peaks["bf16_tflops"], 4), gemm_ms_per_step=round(gemm_ms, 4))
+    del layer, block, X, dOut, Wr, W1, W3, W2, out, dXn, dWr, dW1, dW3, dW2
+    torch.cuda.empty_cache()
+    return rec
 
 
 def run_gpu_arm(args, world):
@@ -200,9 +358,9 @@ def run_gpu_arm(args, world):
         dist = dist_mod
         import datetime
 
-        # a short collective timeout: a rank that falls out of step ends the run in minutes, not in ten
+        # a bounded collective timeout: a rank that falls out of step ends the run in minutes, not in ten
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank),
-                                timeout=datetime.timedelta(seconds=180))
+                                timeout=datetime.timedelta(seconds=300))
     from ml_dataflow_b200 import ops
     from ml_dataflow_b200.moe_layer import MoELayer
 
@@ -222,6 +380,7 @@ def run_gpu_arm(args, world):
     wgen = torch.Generator(device=dev).manual_seed(0xB2000003)  # router weight identical on every rank
     Wr = (torch.randn((E, d), generator=wgen, device=dev) * 0.02).to(torch.bfloat16)
 
+    transport = None
     if world == 1:
         layer = MoELayer(T, d, E, k, f, device=dev)
         E_loc = E
@@ -305,9 +464,28 @@ def run_gpu_arm(args, world):
         return
 
     # ---------------- end to end: pinned host buffers, copies inside the timed region, double buffered
-    Xh, dOh = X.cpu().pin_memory(), dOut.cpu().pin_memory()
-    outh = [torch.empty((T, d), dtype=torch.bfloat16).pin_memory() for _ in range(2)]
-    dXh = [torch.empty((T, d), dtype=torch.bfloat16).pin_memory() for _ in range(2)]
+    # The pinned buffers are first touched while this process is confined to the CPUs of the GPU's own NUMA node, so
+    # that the pages sit on the memory that node's PCIe root reaches directly (eight ranks that all pin on one node
+    # share one memory controller and the inter-socket link).
+    numa_node, numa_cpus = gpu_numa_cpus(local_rank)
+    old_aff = None
+    if numa_cpus and hasattr(os, "sched_setaffinity"):
+        try:
+            old_aff = os.sched_getaffinity(0)
+            os.sched_setaffinity(0, numa_cpus & old_aff or old_aff)
+        except OSError:
+            old_aff = None
+
+    def pinned_like(t):
+        return torch.empty(t.shape, dtype=t.dtype).pin_memory()
+
+    Xh, dOh = pinned_like(X), pinned_like(dOut)
+    Xh.copy_(X)
+    dOh.copy_(dOut)
+    outh = [pinned_like(X).zero_() for _ in range(2)]
+    dXh = [pinned_like(X).zero_() for _ in range(2)]
+    if old_aff is not None:
+        os.sched_setaffinity(0, old_aff)
     Xd, dOd = [torch.empty_like(X) for _ in range(2)], [torch.empty_like(X) for _ in range(2)]
     outd, dXd = [torch.empty_like(X) for _ in range(2)], [torch.empty_like(X) for _ in range(2)]
     main = torch.cuda.current_stream()
@@ -353,75 +531,125 @@ def run_gpu_arm(args, world):
     e2e_value = world * T / (ms_e2e * 1e-3)
     io_bytes = 2 * T * d * 2
 
+    # host link alone: the step's H2D and D2H copies with nothing else running, every rank at once (what the host
+    # path delivers per GPU when all N share it)
+    def copies_only(n):
+        for _ in range(n):
+            with torch.cuda.stream(s_in):
+                Xd[0].copy_(Xh, non_blocking=True)
+                dOd[0].copy_(dOh, non_blocking=True)
+            with torch.cuda.stream(s_out):
+                outh[0].copy_(outd[0], non_blocking=True)
+                dXh[0].copy_(dXd[0], non_blocking=True)
+
+    copies_only(1)
+    barrier()
+    h0, h1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    o0, o1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    h0.record(s_in)
+    o0.record(s_out)
+    copies_only(4)
+    h1.record(s_in)
+    o1.record(s_out)
+    barrier()
+    h2d_gbs = 4 * io_bytes / (h0.elapsed_time(h1) * 1e-3) / 1e9
+    d2h_gbs = 4 * io_bytes / (o0.elapsed_time(o1) * 1e-3) / 1e9
+    if dist is not None:
+        tmin = torch.tensor([h2d_gbs, d2h_gbs], dtype=torch.float64, device=dev)
+        dist.all_reduce(tmin, op=dist.ReduceOp.MIN)
+        h2d_gbs, d2h_gbs = float(tmin[0]), float(tmin[1])
+    del Xd, dOd, outd, dXd, Xh, dOh, outh, dXh
+
     # ---------------- per-op timing for the roofline (separate pass, events between ops)
-    work = algorithmic_work(cfg)
-    acc = {}
-    for _ in range(max(3, min(steps, 10))):
-        layer.profile = []
-        step(X, dOut, out, dXn)
-        layer.mark("end")
-        torch.cuda.synchronize()
-        marks = layer.profile
-        layer.profile = None
-        per_step = {}  # a phase that runs in slices is marked once per slice: sum inside the step
-        for (name, ev), (_, nxt) in zip(marks[:-1], marks[1:]):
-            per_step[name] = per_step.get(name, 0.0) + ev.elapsed_time(nxt)
-        for name, ms in per_step.items():
-            acc.setdefault(name, []).append(ms)
-    kernels = {}
-    gemm_ms, gemm_flops = 0.0, 0
-    for name, (bound, amount) in work.items():
-        if name not in acc:
-            continue
-        ms = sum(acc[name]) / len(acc[name])
-        if bound == "tensor":
-            ach = amount / (ms * 1e-3) / 1e12
-            kernels[name] = dict(ms=round(ms, 4), bound="tensor", achieved=round(ach, 1), unit="TFLOP/s",
-                                 frac=round(ach / peaks["bf16_tflops_sustained"], 4))
-            gemm_ms += ms
-            gemm_flops += amount
-        else:
-            ach = amount / (ms * 1e-3) / 1e9
-            kernels[name] = dict(ms=round(ms, 4), bound="hbm", achieved=round(ach, 1), unit="GB/s",
-                                 frac=round(ach / peaks["hbm_gbs"], 4))
+    kernels, gemm_ms, gemm_flops, raw_ms = per_op_profile(layer, lambda: step(X, dOut, out, dXn), algorithmic_work(cfg),
+                                                          peaks, max(3, min(steps, 10)))
+    peer_gbs = None
     if world > 1:
+        if rank == 0:
+            try:
+                peer_gbs = measure_peer_copy_gbs(0, 1)
+            except Exception:
+                peer_gbs = None
+        link = peer_gbs or NVLINK_PEER_GBS_RECORDED
+        t_link = torch.tensor([link], dtype=torch.float64, device=dev)
+        dist.broadcast(t_link, 0)
+        link = float(t_link.item())
         for name, amount in exchange_work(cfg, world).items():
-            if name in acc:
-                ms = sum(acc[name]) / len(acc[name])
+            if name in raw_ms:
+                ms = raw_ms[name]
                 if transport == "fused" and name.startswith("return"):
                     # the rows went home inside the GEMM epilogues; what is left of this phase is the barrier
                     kernels[name] = dict(ms=round(ms, 4), bound="barrier (rows are stored by the GEMM epilogue)")
                     continue
                 ach_x = amount / (ms * 1e-3) / 1e9
                 kernels[name] = dict(ms=round(ms, 4), bound="nvlink", achieved=round(ach_x, 1), unit="GB/s per direction",
-                                     frac=round(ach_x / NVLINK_PEER_GBS, 4))
+                                     peak=round(link, 1), frac=round(ach_x / link, 4),
+                                     peak_source=("peer copy GPU 0 -> GPU 1 timed by this run" if peer_gbs else
+                                                  "recorded peer-copy rate for this machine type (not measured by this run)"))
     ach = gemm_flops / (gemm_ms * 1e-3) / 1e12 if gemm_ms else 0.0
+    traffic = NCU_GEMM_DRAM_BYTES_PER_STEP.get((T, d, E, k, f)) if world == 1 else None
     roofline = dict(kernel="gemm_sm100_kernel (grouped expert GEMMs: 7 launches per step, 18*R*d*f flop)",
                     bound="tensor", achieved=round(ach, 1), peak=peaks["bf16_tflops_sustained"], unit="TFLOP/s",
                     frac=round(ach / peaks["bf16_tflops_sustained"], 4),
                     frac_of_burst_peak=round(ach / peaks["bf16_tflops"], 4), peak_source=peaks["source"] +
                     " (sustained cuBLAS bf16, the kernel is timed inside a long step)",
-                    traffic=NCU_GEMM_DRAM_BYTES_PER_STEP.get((T, d, E, k, f)) if world == 1 else None,
-                    traffic_unit="bytes per step over the 7 launches (ncu, one pass)", algorithmic_flop=gemm_flops,
+                    traffic=traffic, traffic_unit="bytes per step over the 7 launches",
+                    traffic_source=NCU_TRAFFIC_SOURCE if traffic else None, algorithmic_flop=gemm_flops,
                     ms_per_step_in_kernel=round(gemm_ms, 4))
+
+    # ---------------- after the timed regions: the target shape / the same-batch base on one GPU, EP parity
+    extra = {}
+    del layer, block
+    torch.cuda.empty_cache()
+    if world == 1 and args.tokens <= 0:
+        # the target shape (T=32768 on one GPU) beside the headline configuration
+        extra["ns_shape"] = single_gpu_layer_run(CFG_NS, dev, 10, 3, peaks, 0xB200)
+    if world > 1:
+        ep_parity = "ok"
+        try:
+            sys.path.insert(0, os.path.join(ROOT, "tests"))
+            from ep_parity import check_expert_parallel
+
+            check_expert_parallel(dist, rank, world, transport, num_experts=max(8, world))
+        except Exception as exc:  # reported below, after every rank has voted
+            ep_parity = f"rank {rank}: {type(exc).__name__}: {str(exc)[:300]}"
+        votes = [None] * world
+        dist.all_gather_object(votes, ep_parity)
+        bad = [v for v in votes if v != "ok"]
+        extra["ep_parity"] = "ok" if not bad else bad[0]
+        extra["ep_parity_case"] = (f"{world} ranks, T=384 per rank, d=256, {max(8, world)} experts, top-2, ffn 128, two "
+                                   "steps, every rank against the CPU oracle (counts and mappings bit-exact)")
+        # the same per-GPU batch on ONE GPU with all 64 experts (no exchange): the base for weak-scaling efficiency
+        if rank == 0:
+            base = single_gpu_layer_run(dict(cfg), dev, 5, 3, peaks, 0xB200)
+            extra["same_batch_1gpu"] = base
+            extra["efficiency_same_batch"] = round(value / (world * base["value"]), 4)
+        dist.barrier()
+        if bad:
+            if rank == 0:
+                print(json.dumps(dict(metric=METRIC, impl="ours", n_gpus=world, error="expert-parallel parity failed",
+                                      ep_parity=bad[0])), flush=True)
+            dist.destroy_process_group()
+            sys.exit(1)
 
     if rank != 0:
         if dist is not None:
             dist.destroy_process_group()
         return
-    cpu_tps, cpu_sec, threads = cpu_reference_run(cfg, 2, 1) if world == 1 else (None, None, None)
     line = dict(metric=METRIC, value=value, unit=UNIT, n_gpus=world, steps=steps, warmup=warmup, ms_per_step=ms_step,
                 higher_is_better=True, scaling="weak", vs_baseline=None, dtype="bf16", data="synthetic", impl="ours",
                 config=dict(workload=workload_name(cfg, world), T=T, d_model=d, experts=E, top_k=k, ffn=f,
                             **({"exchange": transport} if world > 1 else {}),
                             l2="inputs exceed L2 (zone 2*T*k*d bytes per pass)"),
                 e2e=dict(value=e2e_value, unit=UNIT, h2d_bytes_per_step=io_bytes, d2h_bytes_per_step=io_bytes,
-                         ms_per_step=ms_e2e),
-                gpu_launches=launches, clocks=clocks, roofline=roofline, kernels=kernels)
-    if cpu_tps is not None:
-        line["cpu_baseline"] = dict(
-            value=cpu_tps, unit=UNIT, cores=threads, kind="port",
-            sample=f"{CPU_SAMPLE_TOKENS} tokens of the same shape, fwd+bwd, {cpu_sec:.1f} s per pass")
+                         ms_per_step=ms_e2e, ratio_to_device_timed=round(e2e_value / value, 4),
+                         host_link=dict(h2d_gbs_per_gpu=round(h2d_gbs, 2), d2h_gbs_per_gpu=round(d2h_gbs, 2),
+                                        note="copies of one step alone, all ranks at once, slowest rank",
+                                        needed_gbs_per_gpu=round(io_bytes / (ms_step * 1e-3) / 1e9, 2),
+                                        pinned_on_numa_node=numa_node)),
+                gpu_launches=launches, clocks=clocks, roofline=roofline, kernels=kernels, **extra)
+    if world == 1:
+        line["cpu_baseline"], _ = cpu_baseline_record(cfg, 1, 1)
     print(json.dumps(line), flush=True)
     if dist is not None:
         dist.destroy_process_group()

@@ -224,10 +224,21 @@ int b200_gemm_status(int *status_out);
 int b200_gemm_set_pair_mode(int on);
 
 /*
+ * Work unit of the CTA-pair GEMMs: which kinds of launch let one fetch of the A rows feed two adjacent column tiles
+ * (a 256 x 512 output block per CTA pair, a quarter fewer bytes staged per flop) - bit 0 the expert forward / dgrad
+ * launches, bit 1 the expert weight gradients, bit 2 the dense matmul. A launch with too few units to fill the GPU
+ * that way keeps one column tile per unit unless bit 3 is set. The environment variable B200_GEMM_WIDE=<0..15> sets the mask at
+ * start-up. Results are identical either way (same MMAs per output element, same order). No counterpart in the
+ * reference.
+ */
+int b200_gemm_set_wide_mode(int mask);
+
+/*
  * Runs the GEMM kernels' tile scheduler on the HOST (the same code the device runs) and lists the tiles one launch
  * would process, in processing order: for checking the index arithmetic where there is no GPU. group_mode 0 = dense,
  * 1 = groups along the rows (forward / dgrad), 2 = groups along the reduction (wgrad); pair as in
- * b200_gemm_set_pair_mode; M = output rows (dense, wgrad), N = output columns, K = reduction length; dual_b = 1 for
+ * b200_gemm_set_pair_mode, or 2 = CTA pairs with two column tiles per unit (b200_gemm_set_wide_mode);
+ * M = output rows (dense, wgrad), N = output columns, K = reduction length; dual_b = 1 for
  * the fused W1 | W3 launch; counts / cumsum_incl are host arrays of num_groups ints (unused when dense);
  * k_splits / k_split_len describe a split reduction (dense only, 0 = none). Writes up to max_tiles records of nine
  * ints {group, first A row, first output row, valid rows, first column, valid columns, loaded columns, first

@@ -30,6 +30,7 @@ SIGNATURES = {
     "b200_matmul": (_i, [_i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _f, _vp, _vp, _vp, _vp, _u64, _vp, _vp]),
     "b200_gemm_status": (_i, [_vp]),
     "b200_gemm_set_pair_mode": (_i, [_i]),
+    "b200_gemm_set_wide_mode": (_i, [_i]),
     "b200_moe_experts_fwd": (_i, [_i, _i, _i, _i, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "b200_moe_experts_bwd_x": (_i, [_i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp,
                                     _vp, _vp, _vp, _vp, _vp, _vp]),

@@ -47,7 +47,8 @@ def build_adapter(reference_root=None, force=False):
 
     Returns the path of the .so, or None when the reference tree is not present on this machine.
     """
-    reference_root = reference_root or os.environ.get("REFERENCE_ROOT", "/root/reference")
+    reference_root = (reference_root or os.environ.get("REFERENCE_ROOT")
+                      or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference"))
     if not os.path.isdir(os.path.join(reference_root, "libdataflowops", "include")):
         return ADAPTER_PATH if os.path.exists(ADAPTER_PATH) else None
     build(force=False)

@@ -63,13 +63,16 @@ constexpr int MAX_STAGES = 6;
 #define B200_PAIR_KSLABS 2
 #endif
 
-template <bool PAIR>
+template <bool PAIR, int SUP>
 struct Cfg {
-  static constexpr int B_BLKS = PAIR ? 2 : 4;
+  static_assert(SUP == 1 || (SUP == 2 && PAIR), "two column tiles per row tile exist for CTA pairs only");
+  static constexpr int B_BLKS_SUB = PAIR ? 2 : 4;                   // 64-column boxes of B per column tile and CTA
+  static constexpr int B_BLKS = B_BLKS_SUB * SUP;
   static constexpr int SLAB_BYTES = (A_BLKS + B_BLKS) * BLK_BYTES;  // one 64-deep slice of both operands
-  static constexpr int KSLABS = PAIR ? B200_PAIR_KSLABS : 1;        // slices per pipeline stage (one barrier round trip)
+  // slices per pipeline stage (one barrier round trip): a stage always feeds eight MMAs in pair mode
+  static constexpr int KSLABS = (PAIR && SUP == 1) ? B200_PAIR_KSLABS : 1;
   static constexpr int STAGE_BYTES = KSLABS * SLAB_BYTES;
-  static constexpr int STAGES = PAIR ? B200_PAIR_STAGES / KSLABS : B200_SINGLE_STAGES;
+  static constexpr int STAGES = PAIR ? (SUP == 2 ? 4 : B200_PAIR_STAGES / KSLABS) : B200_SINGLE_STAGES;
   static constexpr int TILE_M = PAIR ? 2 * BM : BM;
 };
 
@@ -90,13 +93,16 @@ enum StatusCode {
 };
 
 __device__ int g_gemm_status = 0;
-#ifdef B200_GEMM_STATS
-__device__ unsigned long long g_gemm_stats[8];
-#define STAT_T0() const long long st_t0 = clock64()
-#define STAT_ADD(i) st_acc[i] += clock64() - st_t0
+#ifdef B200_GEMM_DEBUG
+// timing experiments only; cycles summed over CTAs: 0 MMA thread waiting for operands, 1 waiting for a drained
+// accumulator, 2 MMA thread's lifetime, 3 epilogue warp 2 busy (accumulator ready -> released), 4 its sub-tiles,
+// 5 producer A waiting for a free stage, 6 producer A lifetime, 7 MMA thread inside the issue loop
+__device__ unsigned long long g_dbg_stats[8];
+#define DBG_CLK() clock64()
+#define DBG_ADD(i, v) atomicAdd(&g_dbg_stats[i], (unsigned long long)(v))
 #else
-#define STAT_T0()
-#define STAT_ADD(i)
+#define DBG_CLK() 0ll
+#define DBG_ADD(i, v)
 #endif
 
 struct GemmParams {
@@ -132,6 +138,10 @@ struct GemmParams {
   // DENSE only: the reduction is cut into k_splits ranges of k_split_len (a multiple of 64); range i is one more
   // tile whose fp32 result goes to D + i * d_group_stride, summed afterwards by splitk_reduce_kernel
   int k_splits, k_split_len;
+#ifdef B200_GEMM_DEBUG
+  int dbg;  // timing experiments only: bit 0 = the epilogue touches no global memory, bit 1 = every load fetches the
+            // same (cache-resident) boxes; results are garbage
+#endif
 };
 
 struct Tile {
@@ -139,27 +149,33 @@ struct Tile {
   int a_row0;    // first row of the tile in A (GROUPED_K: first column of the [R, M] array)
   int out_row0;  // first output row of the tile
   int m_valid;   // valid rows in the tile (up to TILE_M)
-  int n0, n_valid, nw;  // first column, valid columns, columns rounded up to the load granule
+  int nt0, nsub;        // first column tile and how many column tiles share these rows (1 or 2)
+  int n0, n_valid, nw;  // of the column tile picked by Sched::set_sub: first column, valid columns, columns rounded
+                        // up to the load granule
   int k_row0, k_len;    // GROUPED_K: reduction range inside the [R, *] arrays
 };
 
+// Work units are row tiles times groups of `sup` adjacent column tiles: with sup == 2 one fetch of the A rows feeds
+// two accumulators (a 256 x 512 output block per CTA pair), which cuts the bytes staged per flop by a quarter.
 struct Sched {
-  int mode, tiles_n, tiles_m, n_tile_w, n_round, tile_m, total_tiles, M, N, K, k_splits, k_split_len;
+  int mode, tiles_n, stiles_n, sup, tiles_m, n_tile_w, n_round, tile_m, total_tiles, M, N, K, k_splits, k_split_len;
   const int *s_cnt, *s_base, *s_tpre;
   int cursor;
 
   // s_cnt[g] rows of group g, s_base[g] its first row, s_tpre[g] row tiles of the groups before it (GROUPED_M)
   __host__ __device__ __forceinline__ void init(int group_mode, int M_, int N_, int K_, int dual_b, bool pair,
-                                                int tile_rows, int splits, int split_len, const int *cnt,
+                                                int tile_rows, int sup_, int splits, int split_len, const int *cnt,
                                                 const int *base, const int *tpre, int groups) {
     mode = group_mode;
     M = M_;
     N = N_;
     K = K_;
     tile_m = tile_rows;
+    sup = sup_;
     n_tile_w = dual_b ? 128 : 256;
     n_round = (pair && !dual_b) ? 128 : 64;
     tiles_n = (N + n_tile_w - 1) / n_tile_w;
+    stiles_n = (tiles_n + sup - 1) / sup;
     tiles_m = (M + tile_m - 1) / tile_m;
     s_cnt = cnt;
     s_base = base;
@@ -167,28 +183,35 @@ struct Sched {
     cursor = 0;
     k_splits = splits;
     k_split_len = split_len;
-    if (mode == DENSE) total_tiles = tiles_m * tiles_n * (splits > 1 ? splits : 1);
-    else if (mode == GROUPED_M) total_tiles = tpre[groups] * tiles_n;
-    else total_tiles = groups * tiles_m * tiles_n;
+    if (mode == DENSE) total_tiles = tiles_m * stiles_n * (splits > 1 ? splits : 1);
+    else if (mode == GROUPED_M) total_tiles = tpre[groups] * stiles_n;
+    else total_tiles = groups * tiles_m * stiles_n;
+  }
+
+  // column tile `sub` (0 .. t.nsub - 1) of the unit
+  __host__ __device__ __forceinline__ void set_sub(Tile &t, int sub) const {
+    t.n0 = (t.nt0 + sub) * n_tile_w;
+    t.n_valid = min(n_tile_w, N - t.n0);
+    t.nw = (t.n_valid + n_round - 1) & ~(n_round - 1);
   }
 
   __host__ __device__ __forceinline__ bool get(int tile_id, Tile &t) {
     if (tile_id >= total_tiles) return false;
-    int nt;
+    int snt;
     if (mode == DENSE) {
-      const int per = tiles_m * tiles_n;
+      const int per = tiles_m * stiles_n;
       const int split = tile_id / per;  // 0 unless the reduction is split
       const int rem = tile_id - split * per;
-      const int mt = rem / tiles_n;
-      nt = rem - mt * tiles_n;
+      const int mt = rem / stiles_n;
+      snt = rem - mt * stiles_n;
       t.group = split;
       t.a_row0 = t.out_row0 = mt * tile_m;
       t.m_valid = min(tile_m, M - mt * tile_m);
       t.k_row0 = split * k_split_len;
       t.k_len = (k_splits > 1) ? min(k_split_len, K - t.k_row0) : K;
     } else if (mode == GROUPED_M) {
-      const int mtg = tile_id / tiles_n;
-      nt = tile_id - mtg * tiles_n;
+      const int mtg = tile_id / stiles_n;
+      snt = tile_id - mtg * stiles_n;
       while (s_tpre[cursor + 1] <= mtg) cursor++;
       const int ml = mtg - s_tpre[cursor];
       t.group = cursor;
@@ -197,20 +220,20 @@ struct Sched {
       t.k_row0 = 0;
       t.k_len = K;
     } else {
-      const int per = tiles_m * tiles_n;
+      const int per = tiles_m * stiles_n;
       const int e = tile_id / per;
       const int rem = tile_id - e * per;
-      const int mt = rem / tiles_n;
-      nt = rem - mt * tiles_n;
+      const int mt = rem / stiles_n;
+      snt = rem - mt * stiles_n;
       t.group = e;
       t.a_row0 = t.out_row0 = mt * tile_m;
       t.m_valid = min(tile_m, M - mt * tile_m);
       t.k_row0 = s_base[e];
       t.k_len = s_cnt[e];
     }
-    t.n0 = nt * n_tile_w;
-    t.n_valid = min(n_tile_w, N - t.n0);
-    t.nw = (t.n_valid + n_round - 1) & ~(n_round - 1);
+    t.nt0 = snt * sup;
+    t.nsub = min(sup, tiles_n - t.nt0);
+    set_sub(t, 0);
     return true;
   }
 };
@@ -232,9 +255,9 @@ static_assert(sizeof(GemmSmemTail) % 16 == 0, "the staging blocks after the tabl
 __host__ __device__ constexpr int table_ints(int groups) { return ((3 * groups + 1) + 3) & ~3; }
 constexpr int STAGE_OUT_BYTES_PER_WARP = 32 * 128;  // 32 rows x 64 bf16 columns
 
-template <int EPI, bool PAIR>
+template <int EPI, bool PAIR, int SUP>
 __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __grid_constant__ GemmParams p) {
-  using CF = Cfg<PAIR>;
+  using CF = Cfg<PAIR, SUP>;
   constexpr int STAGES = CF::STAGES;
   constexpr int STAGE_BYTES = CF::STAGE_BYTES;
   extern __shared__ unsigned char gemm_smem_raw[];
@@ -321,7 +344,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
   const uint32_t tmem_base = st->tmem_base;
 
   Sched sched;
-  sched.init(p.group_mode, p.M, p.N, p.K, p.dual_b, PAIR, CF::TILE_M, p.k_splits, p.k_split_len, tab_cnt, tab_base,
+  sched.init(p.group_mode, p.M, p.N, p.K, p.dual_b, PAIR, CF::TILE_M, SUP, p.k_splits, p.k_split_len, tab_cnt, tab_base,
              tab_tpre, G);
   const int first_tile = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
   const int tile_step = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
@@ -337,6 +360,9 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
   // 16 bf16 columns of a row at `ptr` (n_left valid columns remain, a multiple of 8): one 32-byte access when
   // the launch allows it, else one or two 16-byte accesses
   auto ld16 = [&](const __nv_bfloat16 *ptr, int n_left, uint4 &lo, uint4 &hi) {
+#ifdef B200_GEMM_DEBUG
+    if (p.dbg & 1) return;
+#endif
     if (p.wide && n_left >= 16) {
       ld_global_256(ptr, lo, hi);
     } else {
@@ -345,6 +371,9 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
     }
   };
   auto st16 = [&](__nv_bfloat16 *ptr, int n_left, const uint4 &lo, const uint4 &hi) {
+#ifdef B200_GEMM_DEBUG
+    if (p.dbg & 1) return;
+#endif
     if (p.wide && n_left >= 16) {
       st_global_256(ptr, lo, hi);
     } else {
@@ -352,23 +381,35 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
       if (n_left > 8) *reinterpret_cast<uint4 *>(ptr + 8) = hi;
     }
   };
+  // 64-column boxes of B that ONE CTA fetches per slab for a column tile of (rounded) width nw
+  auto b_boxes = [&](int nw) { return p.dual_b ? ((PAIR ? 1 : 2) * (nw >> 6)) : (PAIR ? (nw >> 7) : (nw >> 6)); };
   Tile t;
   if (warp == 0 || (NUM_PRODUCERS == 2 && warp == PRODUCER_B_WARP)) {
     // ================= TMA producers (every CTA loads its own boxes) =================
-    // Two threads issue the loads, warp 0 those of A and PRODUCER_B_WARP those of B: one thread issuing all eight
+    // Two threads issue the loads, warp 0 those of A and PRODUCER_B_WARP those of B: one thread issuing all the
     // boxes of a stage spends 85 % of its time inside cp.async.bulk.tensor.
     const bool do_a = (NUM_PRODUCERS == 1) || warp == 0;
     const bool do_b = (NUM_PRODUCERS == 1) || warp != 0;
-    // issue the loads of one slab into (sA, sB), counted on `bar`
-    auto slab = [&](const Tile &tt, int ks, uint32_t sA, uint32_t sB, uint32_t bar) {
+    // issue the loads of one slab into (sA, sB), counted on `bar`; sB holds the B boxes of column tile 0, then
+    // (at the fixed offset B_BLKS_SUB boxes) those of column tile 1
+    auto slab = [&](Tile &tt, int ks, uint32_t sA, uint32_t sB, uint32_t bar) {
+#ifdef B200_GEMM_DEBUG
+      if (p.dbg & 2) ks &= 3;
+#endif
       const int ksteps_seg = (tt.k_len + BK - 1) / BK;
       const int seg = ks / ksteps_seg;
       const int kk = (ks - seg * ksteps_seg) * BK;
       const CUtensorMap *mA = seg ? &p.tmA2 : &p.tmA;
       const CUtensorMap *mB = seg ? &p.tmB2 : &p.tmB;
-      // 64-column boxes of B this CTA fetches per slab, and where they start
-      const int nb = p.dual_b ? (tt.nw >> 6) : (PAIR ? (tt.nw >> 7) : (tt.nw >> 6));
-      const int n_start = tt.n0 + ((PAIR && !p.dual_b) ? (int)cta_rank * (tt.nw >> 1) : 0);
+#ifdef B200_GEMM_DEBUG
+      if (p.dbg & 2) {
+        tt.a_row0 = 0;
+        tt.k_row0 = 0;
+        tt.nt0 = 0;
+        tt.group = 0;
+        ks = ks & 3;
+      }
+#endif
       const int a_row = tt.a_row0 + row_off;
       const int g3 = (p.group_mode == GROUPED_M) ? tt.group : 0;
       auto ld2 = [&](uint32_t dst, const CUtensorMap *m, int c0, int c1) { ptx::tma_load_2d(dst, m, bar, c0, c1); };
@@ -385,44 +426,50 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
         }
       }
       if (!do_b) return;
-      if (p.dual_b) {
-        if (PAIR) {  // even CTA holds the W1 columns, odd CTA the W3 columns
-          const CUtensorMap *mine = cta_rank ? &p.tmB2 : &p.tmB;
-          for (int i = 0; i < nb; i++) ld3(sB + i * BLK_BYTES, mine, kk, tt.n0 + 64 * i, g3);
+      for (int sub = 0; sub < tt.nsub; sub++) {
+        sched.set_sub(tt, sub);
+        const uint32_t sBs = sB + sub * CF::B_BLKS_SUB * BLK_BYTES;
+        // boxes of one map, and where this CTA's columns start
+        const int nb = p.dual_b ? (tt.nw >> 6) : (PAIR ? (tt.nw >> 7) : (tt.nw >> 6));
+        const int n_start = tt.n0 + ((PAIR && !p.dual_b) ? (int)cta_rank * (tt.nw >> 1) : 0);
+        if (p.dual_b) {
+          if (PAIR) {  // even CTA holds the W1 columns, odd CTA the W3 columns
+            const CUtensorMap *mine = cta_rank ? &p.tmB2 : &p.tmB;
+            for (int i = 0; i < nb; i++) ld3(sBs + i * BLK_BYTES, mine, kk, tt.n0 + 64 * i, g3);
+          } else {
+            for (int i = 0; i < nb; i++) ld3(sBs + i * BLK_BYTES, &p.tmB, kk, tt.n0 + 64 * i, g3);
+            for (int i = 0; i < nb; i++) ld3(sBs + (nb + i) * BLK_BYTES, &p.tmB2, kk, tt.n0 + 64 * i, g3);
+          }
+        } else if (!p.b_mn_major) {
+          for (int i = 0; i < nb; i++) ld3(sBs + i * BLK_BYTES, mB, tt.k_row0 + kk, n_start + 64 * i, g3);
         } else {
-          for (int i = 0; i < nb; i++) ld3(sB + i * BLK_BYTES, &p.tmB, kk, tt.n0 + 64 * i, g3);
-          for (int i = 0; i < nb; i++) ld3(sB + (nb + i) * BLK_BYTES, &p.tmB2, kk, tt.n0 + 64 * i, g3);
+          for (int i = 0; i < nb; i++) ld3(sBs + i * BLK_BYTES, mB, n_start + 64 * i, tt.k_row0 + kk, g3);
         }
-      } else if (!p.b_mn_major) {
-        for (int i = 0; i < nb; i++) ld3(sB + i * BLK_BYTES, mB, tt.k_row0 + kk, n_start + 64 * i, g3);
-      } else {
-        for (int i = 0; i < nb; i++) ld3(sB + i * BLK_BYTES, mB, n_start + 64 * i, tt.k_row0 + kk, g3);
       }
     };
     // one thread runs the whole loop: no warp-wide operation sits between two stages
     if (lane == 0) {
-#ifdef B200_GEMM_STATS
-      long long st_acc[4] = {0, 0, 0, 0};
-      const long long st_begin = clock64();
-#endif
       int stage = 0;
       uint32_t phase = 0;
       bool alive = true;
+      [[maybe_unused]] long long dbg_wait = 0;
+      [[maybe_unused]] const long long dbg_begin = DBG_CLK();
       for (int tile = first_tile; alive && sched.get(tile, t); tile += tile_step) {
         const int ksteps = ((t.k_len + BK - 1) / BK) * p.k_segments;
-        const int nb = p.dual_b ? (t.nw >> 6) : (PAIR ? (t.nw >> 7) : (t.nw >> 6));
-        const int nb_loaded = (p.dual_b && !PAIR) ? 2 * nb : nb;
+        int b_loaded = 0;
+        for (int sub = 0; sub < t.nsub; sub++) {
+          sched.set_sub(t, sub);
+          b_loaded += b_boxes(t.nw);
+        }
+        const int my_blks = (do_a ? A_BLKS : 0) + (do_b ? b_loaded : 0);
         for (int ks = 0; ks < ksteps; ks += CF::KSLABS) {
-          {
-            STAT_T0();
-            if (!xwait(empty_bar(stage), phase ^ 1u, ST_PRODUCER_TIMEOUT)) {
-              alive = false;
-              break;
-            }
-            STAT_ADD(0);
+          [[maybe_unused]] const long long dbg_t0 = DBG_CLK();
+          if (!xwait(empty_bar(stage), phase ^ 1u, ST_PRODUCER_TIMEOUT)) {
+            alive = false;
+            break;
           }
+          dbg_wait += DBG_CLK() - dbg_t0;
           const int nsl = min(CF::KSLABS, ksteps - ks);
-          const int my_blks = (do_a ? A_BLKS : 0) + (do_b ? nb_loaded : 0);
           ptx::mbar_arrive_expect_tx(full_bar(stage), (uint32_t)(nsl * my_blks * BLK_BYTES));
           for (int j = 0; j < nsl; j++) {
             const uint32_t sA = smem_base + stage * STAGE_BYTES + j * CF::SLAB_BYTES;
@@ -434,38 +481,37 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
           }
         }
       }
-#ifdef B200_GEMM_STATS
-      atomicAdd(&g_gemm_stats[0], (unsigned long long)st_acc[0]);
-      atomicAdd(&g_gemm_stats[1], (unsigned long long)(clock64() - st_begin));
-#endif
+      if (do_a) {
+        DBG_ADD(5, dbg_wait);
+        DBG_ADD(6, DBG_CLK() - dbg_begin);
+      }
     }
     __syncwarp();
   } else if (warp == 1) {
     // ================= MMA issuer (even CTA) / slab forwarder (odd CTA of a pair) =================
     // again a single thread: wait, fence, issue, commit
     if (lane == 0) {
-#ifdef B200_GEMM_STATS
-      long long st_acc[4] = {0, 0, 0, 0};
-      const long long st_begin = clock64();
-#endif
       int stage = 0;
       uint32_t phase = 0;
-      int acc = 0;
-      uint32_t acc_phase = 0;
+      uint32_t acc_par = 0;  // bit a: parity of the next completion of accumulator a (as seen by the epilogue)
+      int seq = 0;
       uint32_t tail_par = 0;  // parity of tail_done[stage], one bit per stage
       bool alive = true;
+      [[maybe_unused]] long long dbg_w_full = 0, dbg_w_acc = 0, dbg_issue = 0;
+      [[maybe_unused]] const long long dbg_begin = DBG_CLK();
       for (int tile = first_tile; alive && sched.get(tile, t); tile += tile_step) {
         const int ksteps_seg = (t.k_len + BK - 1) / BK;
         const int ksteps = ksteps_seg * p.k_segments;
         if (ksteps == 0) continue;
-        const int mma_n = p.dual_b ? 2 * t.nw : t.nw;
-        const uint32_t idesc = ptx::make_idesc_bf16(CF::TILE_M, mma_n, p.a_mn_major, p.b_mn_major);
-        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * ACC_COLS);
-        if (leader) {
-          STAT_T0();
-          if (!xwait(tempty_bar(acc), acc_phase ^ 1u, ST_MMA_TIMEOUT)) break;
-          STAT_ADD(1);
-          ptx::tc_fence_after();
+        // per column tile: its accumulator and its instruction descriptor
+        uint32_t idesc[SUP], d_tmem[SUP];
+        int accs[SUP];
+#pragma unroll
+        for (int sub = 0; sub < SUP; sub++) {
+          if (sub < t.nsub) sched.set_sub(t, sub);
+          accs[sub] = (SUP == 2) ? sub : (seq & 1);
+          idesc[sub] = ptx::make_idesc_bf16(CF::TILE_M, p.dual_b ? 2 * t.nw : t.nw, p.a_mn_major, p.b_mn_major);
+          d_tmem[sub] = tmem_base + (uint32_t)(accs[sub] * ACC_COLS);
         }
         for (int ks = 0; ks < ksteps; ks += CF::KSLABS) {
           const int nsl = min(CF::KSLABS, ksteps - ks);
@@ -477,7 +523,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
           // every CTA watches its own slabs land; a stage whose last slab straddles the end of the expert's rows is
           // handed over by the tail warp instead, once it has cleared the rows past the end
           bool ok;
-          STAT_T0();
+          [[maybe_unused]] const long long dbg_t0 = DBG_CLK();
           if (p.group_mode == GROUPED_K && last && (t.k_len & 15) != 0) {
             ok = wait_local(tail_bar(stage), (tail_par >> stage) & 1u, ST_MMA_TIMEOUT);
             tail_par ^= 1u << stage;
@@ -492,40 +538,48 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
             alive = false;
             break;
           }
-          STAT_ADD(0);
+          dbg_w_full += DBG_CLK() - dbg_t0;
+          [[maybe_unused]] const long long dbg_t1 = DBG_CLK();
           if (PAIR && !leader) {
             // ... the odd CTA then tells the even one that its half is in place
             ptx::mbar_arrive_remote(full_bar(stage), 0);
           } else {
             ptx::tc_fence_after();
-#ifdef B200_GEMM_STATS
-            const long long st_issue0 = clock64();
-#endif
-            for (int j = 0; j < nsl; j++) {
+            for (int j = 0; j < nsl && alive; j++) {
               const uint32_t sA = smem_base + stage * STAGE_BYTES + j * CF::SLAB_BYTES;
-              const uint32_t sB = sA + A_BLKS * BLK_BYTES;
               const int n16 = (j == nsl - 1) ? last_k16 : BK / 16;
 #pragma unroll
-              for (int k16 = 0; k16 < BK / 16; k16++) {
-                if (k16 >= n16) break;
-                const uint64_t adesc = p.a_mn_major ? ptx::make_smem_desc(sA + k16 * 2048, BLK_BYTES, 1024)
-                                                    : ptx::make_smem_desc(sA + k16 * 32, 0, 1024);
-                const uint64_t bdesc = p.b_mn_major ? ptx::make_smem_desc(sB + k16 * 2048, BLK_BYTES, 1024)
-                                                    : ptx::make_smem_desc(sB + k16 * 32, 0, 1024);
-                const uint32_t accum = (ks + j > 0 || k16 > 0) ? 1u : 0u;
-                if (PAIR) ptx::umma_bf16_pair(d_tmem, adesc, bdesc, idesc, accum);
-                else ptx::umma_bf16(d_tmem, adesc, bdesc, idesc, accum);
+              for (int sub = 0; sub < SUP; sub++) {
+                if (sub >= t.nsub) break;
+                if (ks + j == 0) {
+                  // the accumulator must have been drained by the epilogue of the unit before; column tile 1 is
+                  // waited for only now, after the first MMAs of column tile 0 are on their way
+                  [[maybe_unused]] const long long dbg_t2 = DBG_CLK();
+                  if (!xwait(tempty_bar(accs[sub]), ((acc_par >> accs[sub]) & 1u) ^ 1u, ST_MMA_TIMEOUT)) {
+                    alive = false;
+                    break;
+                  }
+                  dbg_w_acc += DBG_CLK() - dbg_t2;
+                  ptx::tc_fence_after();
+                }
+                const uint32_t sB = sA + (A_BLKS + sub * CF::B_BLKS_SUB) * BLK_BYTES;
+#pragma unroll
+                for (int k16 = 0; k16 < BK / 16; k16++) {
+                  if (k16 >= n16) break;
+                  const uint64_t adesc = p.a_mn_major ? ptx::make_smem_desc(sA + k16 * 2048, BLK_BYTES, 1024)
+                                                      : ptx::make_smem_desc(sA + k16 * 32, 0, 1024);
+                  const uint64_t bdesc = p.b_mn_major ? ptx::make_smem_desc(sB + k16 * 2048, BLK_BYTES, 1024)
+                                                      : ptx::make_smem_desc(sB + k16 * 32, 0, 1024);
+                  const uint32_t accum = (ks + j > 0 || k16 > 0) ? 1u : 0u;
+                  if (PAIR) ptx::umma_bf16_pair(d_tmem[sub], adesc, bdesc, idesc[sub], accum);
+                  else ptx::umma_bf16(d_tmem[sub], adesc, bdesc, idesc[sub], accum);
+                }
               }
             }
-#ifdef B200_GEMM_STATS
-            const long long st_issue1 = clock64();
-            st_acc[2] += st_issue1 - st_issue0;
-#endif
+            if (!alive) break;
             if (PAIR) ptx::umma_commit_pair(empty_bar(stage));
             else ptx::umma_commit(empty_bar(stage));
-#ifdef B200_GEMM_STATS
-            st_acc[3] += clock64() - st_issue1;
-#endif
+            dbg_issue += DBG_CLK() - dbg_t1;
           }
           if (++stage == STAGES) {
             stage = 0;
@@ -533,26 +587,23 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
           }
         }
         if (!alive) break;
-        if (leader) {
-          if (PAIR) ptx::umma_commit_pair(tfull_bar(acc));
-          else ptx::umma_commit(tfull_bar(acc));
+#pragma unroll
+        for (int sub = 0; sub < SUP; sub++) {
+          if (sub >= t.nsub) break;
+          if (leader) {
+            if (PAIR) ptx::umma_commit_pair(tfull_bar(accs[sub]));
+            else ptx::umma_commit(tfull_bar(accs[sub]));
+          }
+          acc_par ^= 1u << accs[sub];
         }
-        if (++acc == 2) {
-          acc = 0;
-          acc_phase ^= 1u;
-        }
+        seq++;
       }
-#ifdef B200_GEMM_STATS
       if (leader) {
-        atomicAdd(&g_gemm_stats[2], (unsigned long long)st_acc[0]);
-        atomicAdd(&g_gemm_stats[3], (unsigned long long)st_acc[1]);
-        atomicAdd(&g_gemm_stats[4], (unsigned long long)(clock64() - st_begin));
-        atomicAdd(&g_gemm_stats[7], (unsigned long long)st_acc[2]);
-        atomicAdd(&g_gemm_stats[5], (unsigned long long)st_acc[3]);
-      } else {
-        atomicAdd(&g_gemm_stats[6], (unsigned long long)st_acc[0]);
+        DBG_ADD(0, dbg_w_full);
+        DBG_ADD(1, dbg_w_acc);
+        DBG_ADD(2, DBG_CLK() - dbg_begin);
+        DBG_ADD(7, dbg_issue - dbg_w_acc);
       }
-#endif
     }
     __syncwarp();
   } else if (warp == TAIL_WARP) {
@@ -566,7 +617,15 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
       uint32_t phase = 0;
       for (int tile = first_tile; sched.get(tile, t); tile += tile_step) {
         const int ksteps = (t.k_len + BK - 1) / BK;
-        const int nb = PAIR ? (t.nw >> 7) : (t.nw >> 6);
+        int nbs[SUP];
+#pragma unroll
+        for (int sub = 0; sub < SUP; sub++) {
+          nbs[sub] = 0;
+          if (sub < t.nsub) {
+            sched.set_sub(t, sub);
+            nbs[sub] = PAIR ? (t.nw >> 7) : (t.nw >> 6);
+          }
+        }
         const int kv = t.k_len & (BK - 1);
         for (int ks = 0; ks < ksteps; ks += CF::KSLABS) {
           const int nsl = min(CF::KSLABS, ksteps - ks);
@@ -579,9 +638,15 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
             // it), so rows kv .. roundup(kv, 16) - 1 of every block are all there is to clear
             unsigned char *stA = smem + stage * STAGE_BYTES + (nsl - 1) * CF::SLAB_BYTES;
             const int chunks_per_blk = (16 - (kv & 15)) * 8;
-            for (int b = 0; b < A_BLKS + nb; b++)
-              for (int c = lane; c < chunks_per_blk; c += 32)
-                *reinterpret_cast<uint4 *>(stA + b * BLK_BYTES + kv * 128 + c * 16) = make_uint4(0, 0, 0, 0);
+            auto clear_blocks = [&](unsigned char *first, int blocks) {
+              for (int b = 0; b < blocks; b++)
+                for (int c = lane; c < chunks_per_blk; c += 32)
+                  *reinterpret_cast<uint4 *>(first + b * BLK_BYTES + kv * 128 + c * 16) = make_uint4(0, 0, 0, 0);
+            };
+            clear_blocks(stA, A_BLKS);
+#pragma unroll
+            for (int sub = 0; sub < SUP; sub++)
+              clear_blocks(stA + (A_BLKS + sub * CF::B_BLKS_SUB) * BLK_BYTES, nbs[sub]);
             ptx::fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(tail_bar(stage));
@@ -599,237 +664,250 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
     // TMEM lanes a warp may read are fixed by warp_id % 4; two warps share a lane quarter and split the columns.
     const int quarter = warp & 3;
     const int chalf = (warp - 2) >> 2;
-    int acc = 0;
-    uint32_t acc_phase = 0;
+    uint32_t acc_par = 0;  // bit a: parity of the next completion of accumulator a
+    int seq = 0;
     for (int tile = first_tile; sched.get(tile, t); tile += tile_step) {
       if (t.k_len == 0) continue;
       const int row_in_cta = quarter * 32 + lane;
       const bool row_ok = row_in_cta + row_off < t.m_valid;
       const int64_t orow = (int64_t)t.out_row0 + row_off + row_in_cta;
-      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * ACC_COLS);
-      // t.nw is the logical width (per part when the accumulator holds x1 | x3); each warp takes half of it
-      const int cbeg = chalf * (t.nw >> 1), cend = cbeg + (t.nw >> 1);
+      for (int sub = 0; sub < t.nsub; sub++) {
+        // the column tiles of a unit finish together; they are drained in order, each freeing its accumulator
+        sched.set_sub(t, sub);
+        const int acc = (SUP == 2) ? sub : (seq & 1);
+        const uint32_t acc_phase = (acc_par >> acc) & 1u;
+        const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * ACC_COLS);
+        [[maybe_unused]] long long dbg_e0 = 0;
+        // t.nw is the logical width (per part when the accumulator holds x1 | x3); each warp takes half of it
+        const int cbeg = chalf * (t.nw >> 1), cend = cbeg + (t.nw >> 1);
 
-      if (EPI == EPI_STORE) {
-        const int64_t goff = (p.group_mode == GROUPED_K || p.k_splits > 1) ? (int64_t)t.group * p.d_group_stride : 0;
-        const int64_t base = goff + orow * p.ldd + t.n0;
-        const bool use_c = (p.C != nullptr) && (p.beta != 0.0f);
-        // destination of this thread's row: D itself, or (row scatter) the row its tag names in some rank's buffer
-        __nv_bfloat16 *drow = static_cast<__nv_bfloat16 *>(p.D) + base;
-        bool store_ok = row_ok;
-        if (p.row_tags != nullptr && row_ok) {
-          const unsigned long long tag = p.row_tags[orow];
-          const unsigned long long rk = tag >> TAG_RANK_SHIFT, rr = tag & TAG_ROW_MASK;
-          if (rk < (unsigned long long)p.scatter_world && rr < (unsigned long long)p.scatter_rows) {
-            drow = reinterpret_cast<__nv_bfloat16 *>(p.scatter_base[rk]) + (int64_t)rr * p.ldd + t.n0;
-          } else {
-            store_ok = false;
-            atomicCAS(p.status, 0, (int)ST_BAD_ROW_TAG);
+        if (EPI == EPI_STORE) {
+          const int64_t goff = (p.group_mode == GROUPED_K || p.k_splits > 1) ? (int64_t)t.group * p.d_group_stride : 0;
+          const int64_t base = goff + orow * p.ldd + t.n0;
+          const bool use_c = (p.C != nullptr) && (p.beta != 0.0f);
+          // destination of this thread's row: D itself, or (row scatter) the row its tag names in some rank's buffer
+          __nv_bfloat16 *drow = static_cast<__nv_bfloat16 *>(p.D) + base;
+          bool store_ok = row_ok;
+          if (p.row_tags != nullptr && row_ok) {
+            const unsigned long long tag = p.row_tags[orow];
+            const unsigned long long rk = tag >> TAG_RANK_SHIFT, rr = tag & TAG_ROW_MASK;
+            if (rk < (unsigned long long)p.scatter_world && rr < (unsigned long long)p.scatter_rows) {
+              drow = reinterpret_cast<__nv_bfloat16 *>(p.scatter_base[rk]) + (int64_t)rr * p.ldd + t.n0;
+            } else {
+              store_ok = false;
+              atomicCAS(p.status, 0, (int)ST_BAD_ROW_TAG);
+            }
           }
-        }
-        // the bf16 C segment of this thread (up to 128 columns) is fetched before waiting on the MMAs
-        uint4 cpre[16];
-        if (use_c && !p.c_fp32 && row_ok) {
+          // the bf16 C segment of this thread (up to 128 columns) is fetched before waiting on the MMAs
+          uint4 cpre[16];
+          if (use_c && !p.c_fp32 && row_ok) {
 #pragma unroll
-          for (int vv = 0; vv < 8; vv++) {
-            const int col = cbeg + vv * 16;
-            if (col < cend && col < t.n_valid)
-              ld16(static_cast<const __nv_bfloat16 *>(p.C) + base + col, t.n_valid - col, cpre[2 * vv], cpre[2 * vv + 1]);
+            for (int vv = 0; vv < 8; vv++) {
+              const int col = cbeg + vv * 16;
+              if (col < cend && col < t.n_valid)
+                ld16(static_cast<const __nv_bfloat16 *>(p.C) + base + col, t.n_valid - col, cpre[2 * vv], cpre[2 * vv + 1]);
+            }
           }
-        }
-        bool ok = xwait(tfull_bar(acc), acc_phase, ST_EPILOGUE_TIMEOUT);
-        if (!__all_sync(0xffffffffu, ok)) goto teardown;
-        ptx::tc_fence_after();
+          bool ok = xwait(tfull_bar(acc), acc_phase, ST_EPILOGUE_TIMEOUT);
+          if (!__all_sync(0xffffffffu, ok)) goto teardown;
+          ptx::tc_fence_after();
+          dbg_e0 = DBG_CLK();
 #pragma unroll
-        for (int ch = 0; ch < 2; ch++) {  // 64 accumulator columns per TMEM round trip
-          const int c0 = cbeg + ch * 64;
-          if (c0 < cend) {
-            uint32_t r[64];
-            ptx::tmem_ld32(taddr + c0, r);
-            if (c0 + 32 < cend) ptx::tmem_ld32(taddr + c0 + 32, r + 32);
-            ptx::tmem_ld_wait();
-            if (p.stage_out) {
-              // lane = row writes its 64 columns as eight 16-byte chunks (XOR-swizzled: conflict-free both ways), then
-              // lanes 8i..8i+7 read back row 4*it + i and store its 128 bytes side by side
-              uint4 *sb = stage_out + (warp - 2) * (STAGE_OUT_BYTES_PER_WARP / 16);
+          for (int ch = 0; ch < 2; ch++) {  // 64 accumulator columns per TMEM round trip
+            const int c0 = cbeg + ch * 64;
+            if (c0 < cend) {
+              uint32_t r[64];
+              ptx::tmem_ld32(taddr + c0, r);
+              if (c0 + 32 < cend) ptx::tmem_ld32(taddr + c0 + 32, r + 32);
+              ptx::tmem_ld_wait();
+              if (p.stage_out) {
+                // lane = row writes its 64 columns as eight 16-byte chunks (XOR-swizzled: conflict-free both ways), then
+                // lanes 8i..8i+7 read back row 4*it + i and store its 128 bytes side by side
+                uint4 *sb = stage_out + (warp - 2) * (STAGE_OUT_BYTES_PER_WARP / 16);
 #pragma unroll
-              for (int vv = 0; vv < 4; vv++) {
-                if (c0 + vv * 16 < cend) {
-                  float f[16];
+                for (int vv = 0; vv < 4; vv++) {
+                  if (c0 + vv * 16 < cend) {
+                    float f[16];
 #pragma unroll
-                  for (int q = 0; q < 16; q++) f[q] = p.alpha * __uint_as_float(r[vv * 16 + q]);
-                  sb[lane * 8 + ((2 * vv) ^ (lane & 7))] = pack8(f);
-                  sb[lane * 8 + ((2 * vv + 1) ^ (lane & 7))] = pack8(f + 8);
+                    for (int q = 0; q < 16; q++) f[q] = p.alpha * __uint_as_float(r[vv * 16 + q]);
+                    sb[lane * 8 + ((2 * vv) ^ (lane & 7))] = pack8(f);
+                    sb[lane * 8 + ((2 * vv + 1) ^ (lane & 7))] = pack8(f + 8);
+                  }
                 }
-              }
-              __syncwarp();
-              const unsigned long long dptr = reinterpret_cast<unsigned long long>(drow);
-              const int chunk = lane & 7;
-              const int col = c0 + chunk * 8;
+                __syncwarp();
+                const unsigned long long dptr = reinterpret_cast<unsigned long long>(drow);
+                const int chunk = lane & 7;
+                const int col = c0 + chunk * 8;
 #pragma unroll
-              for (int it = 0; it < 8; it++) {
-                const int rr = it * 4 + (lane >> 3);
-                const unsigned long long rp = __shfl_sync(0xffffffffu, dptr, rr);
-                const int rok = __shfl_sync(0xffffffffu, (int)store_ok, rr);
-                const uint4 v = sb[rr * 8 + (chunk ^ (rr & 7))];
-                if (rok && col < cend && col < t.n_valid) *reinterpret_cast<uint4 *>(reinterpret_cast<__nv_bfloat16 *>(rp) + col) = v;
-              }
-              __syncwarp();
-            } else if (store_ok) {
+                for (int it = 0; it < 8; it++) {
+                  const int rr = it * 4 + (lane >> 3);
+                  const unsigned long long rp = __shfl_sync(0xffffffffu, dptr, rr);
+                  const int rok = __shfl_sync(0xffffffffu, (int)store_ok, rr);
+                  const uint4 v = sb[rr * 8 + (chunk ^ (rr & 7))];
+                  if (rok && col < cend && col < t.n_valid) *reinterpret_cast<uint4 *>(reinterpret_cast<__nv_bfloat16 *>(rp) + col) = v;
+                }
+                __syncwarp();
+              } else if (store_ok) {
 #pragma unroll
-              for (int vv = 0; vv < 4; vv++) {
-                const int col = c0 + vv * 16;
-                if (col < cend && col < t.n_valid) {
-                  float f[16];
+                for (int vv = 0; vv < 4; vv++) {
+                  const int col = c0 + vv * 16;
+                  if (col < cend && col < t.n_valid) {
+                    float f[16];
 #pragma unroll
-                  for (int q = 0; q < 16; q++) f[q] = p.alpha * __uint_as_float(r[vv * 16 + q]);
-                  if (use_c) {
-                    if (p.c_fp32) {
-                      const float *cp = static_cast<const float *>(p.C) + base + col;
+                    for (int q = 0; q < 16; q++) f[q] = p.alpha * __uint_as_float(r[vv * 16 + q]);
+                    if (use_c) {
+                      if (p.c_fp32) {
+                        const float *cp = static_cast<const float *>(p.C) + base + col;
 #pragma unroll
-                      for (int q = 0; q < 16; q++)
-                        if (col + q < t.n_valid) f[q] += p.beta * cp[q];
+                        for (int q = 0; q < 16; q++)
+                          if (col + q < t.n_valid) f[q] += p.beta * cp[q];
+                      } else {
+                        float cf[16];
+                        unpack8(cpre[ch * 8 + 2 * vv], cf);
+                        unpack8(cpre[ch * 8 + 2 * vv + 1], cf + 8);
+#pragma unroll
+                        for (int q = 0; q < 16; q++) f[q] += p.beta * cf[q];
+                      }
+                    }
+                    if (p.out_fp32) {
+                      float4 *dp = reinterpret_cast<float4 *>(static_cast<float *>(p.D) + base + col);
+                      dp[0] = make_float4(f[0], f[1], f[2], f[3]);
+                      dp[1] = make_float4(f[4], f[5], f[6], f[7]);
+                      if (col + 8 < t.n_valid) {
+                        dp[2] = make_float4(f[8], f[9], f[10], f[11]);
+                        dp[3] = make_float4(f[12], f[13], f[14], f[15]);
+                      }
                     } else {
-                      float cf[16];
-                      unpack8(cpre[ch * 8 + 2 * vv], cf);
-                      unpack8(cpre[ch * 8 + 2 * vv + 1], cf + 8);
-#pragma unroll
-                      for (int q = 0; q < 16; q++) f[q] += p.beta * cf[q];
+                      st16(drow + col, t.n_valid - col, pack8(f), pack8(f + 8));
                     }
-                  }
-                  if (p.out_fp32) {
-                    float4 *dp = reinterpret_cast<float4 *>(static_cast<float *>(p.D) + base + col);
-                    dp[0] = make_float4(f[0], f[1], f[2], f[3]);
-                    dp[1] = make_float4(f[4], f[5], f[6], f[7]);
-                    if (col + 8 < t.n_valid) {
-                      dp[2] = make_float4(f[8], f[9], f[10], f[11]);
-                      dp[3] = make_float4(f[12], f[13], f[14], f[15]);
-                    }
-                  } else {
-                    st16(drow + col, t.n_valid - col, pack8(f), pack8(f + 8));
                   }
                 }
               }
             }
           }
-        }
-      } else if (EPI == EPI_SWIGLU_FWD) {
-        // accumulator columns [0, nw) = x1 tile, [nw, 2 nw) = x3 tile
-        bool ok = xwait(tfull_bar(acc), acc_phase, ST_EPILOGUE_TIMEOUT);
-        if (!__all_sync(0xffffffffu, ok)) goto teardown;
-        ptx::tc_fence_after();
-        const int64_t base = orow * (int64_t)p.N + t.n0;
-        for (int c0 = cbeg; c0 < cend; c0 += 64) {
-          uint32_t r1[64], r3[64];
-          const bool two = c0 + 32 < cend;
-          ptx::tmem_ld32(taddr + c0, r1);
-          ptx::tmem_ld32(taddr + t.nw + c0, r3);
-          if (two) {
-            ptx::tmem_ld32(taddr + c0 + 32, r1 + 32);
-            ptx::tmem_ld32(taddr + t.nw + c0 + 32, r3 + 32);
-          }
-          ptx::tmem_ld_wait();
-          if (row_ok) {
-#pragma unroll
-            for (int vv = 0; vv < 4; vv++) {
-              const int col = c0 + vv * 16;
-              if (col < cend && col < t.n_valid) {
-                float a[16], b[16], h[16];
-#pragma unroll
-                for (int q = 0; q < 16; q++) {
-                  a[q] = bf16_round(__uint_as_float(r1[vv * 16 + q]));
-                  b[q] = bf16_round(__uint_as_float(r3[vv * 16 + q]));
-                  h[q] = silu_f(a[q]) * b[q];
-                }
-                const int left = t.n_valid - col;
-                st16(static_cast<__nv_bfloat16 *>(p.x1_out) + base + col, left, pack8(a), pack8(a + 8));
-                st16(static_cast<__nv_bfloat16 *>(p.x3_out) + base + col, left, pack8(b), pack8(b + 8));
-                st16(static_cast<__nv_bfloat16 *>(p.h_out) + base + col, left, pack8(h), pack8(h + 8));
-              }
+        } else if (EPI == EPI_SWIGLU_FWD) {
+          // accumulator columns [0, nw) = x1 tile, [nw, 2 nw) = x3 tile
+          bool ok = xwait(tfull_bar(acc), acc_phase, ST_EPILOGUE_TIMEOUT);
+          if (!__all_sync(0xffffffffu, ok)) goto teardown;
+          ptx::tc_fence_after();
+          dbg_e0 = DBG_CLK();
+          const int64_t base = orow * (int64_t)p.N + t.n0;
+          for (int c0 = cbeg; c0 < cend; c0 += 64) {
+            uint32_t r1[64], r3[64];
+            const bool two = c0 + 32 < cend;
+            ptx::tmem_ld32(taddr + c0, r1);
+            ptx::tmem_ld32(taddr + t.nw + c0, r3);
+            if (two) {
+              ptx::tmem_ld32(taddr + c0 + 32, r1 + 32);
+              ptx::tmem_ld32(taddr + t.nw + c0 + 32, r3 + 32);
             }
-          }
-        }
-      } else {
-        // EPI_SWIGLU_BWD: accumulator = dh = (w * dOut) W2 for this row
-        const int64_t base = orow * (int64_t)p.N + t.n0;
-        // x1 / x3 of the first 64 columns are requested before waiting on the MMAs, those of the second 64
-        // together with the second TMEM read
-        uint4 xa[8], xb[8];
-        auto load_x = [&](int c0) {
-          if (row_ok) {
-#pragma unroll
-            for (int vv = 0; vv < 4; vv++) {
-              const int col = c0 + vv * 16;
-              if (col < cend && col < t.n_valid) {
-                ld16(static_cast<const __nv_bfloat16 *>(p.x1_in) + base + col, t.n_valid - col, xa[2 * vv], xa[2 * vv + 1]);
-                ld16(static_cast<const __nv_bfloat16 *>(p.x3_in) + base + col, t.n_valid - col, xb[2 * vv], xb[2 * vv + 1]);
-              }
-            }
-          }
-        };
-        load_x(cbeg);
-        bool ok = xwait(tfull_bar(acc), acc_phase, ST_EPILOGUE_TIMEOUT);
-        if (!__all_sync(0xffffffffu, ok)) goto teardown;
-        ptx::tc_fence_after();
-        float dp_part = 0.f;
-#pragma unroll
-        for (int ch = 0; ch < 2; ch++) {
-          const int c0 = cbeg + ch * 64;
-          if (c0 < cend) {
-            uint32_t r[64];
-            ptx::tmem_ld32(taddr + c0, r);
-            if (c0 + 32 < cend) ptx::tmem_ld32(taddr + c0 + 32, r + 32);
-            if (ch == 1) load_x(c0);
             ptx::tmem_ld_wait();
             if (row_ok) {
 #pragma unroll
               for (int vv = 0; vv < 4; vv++) {
                 const int col = c0 + vv * 16;
                 if (col < cend && col < t.n_valid) {
-                  float a[16], b[16], o1[16], o3[16], hv[16];
-                  unpack8(xa[2 * vv], a);
-                  unpack8(xa[2 * vv + 1], a + 8);
-                  unpack8(xb[2 * vv], b);
-                  unpack8(xb[2 * vv + 1], b + 8);
-                  const int left = t.n_valid - col;
+                  float a[16], b[16], h[16];
 #pragma unroll
                   for (int q = 0; q < 16; q++) {
-                    const float acc_dh = (q < left) ? __uint_as_float(r[vv * 16 + q]) : 0.f;
-                    const float s = 1.0f / (1.0f + __expf(-a[q]));
-                    const float silu = a[q] * s;
-                    hv[q] = silu * b[q];
-                    if (q < left) dp_part += bf16_round(hv[q]) * acc_dh;
-                    const float dh = bf16_round(acc_dh);  // the reference stores dh as bf16 before swiglu_bwd_x
-                    o3[q] = dh * silu;
-                    o1[q] = dh * b[q] * (s + a[q] * (s * (1.0f - s)));
+                    a[q] = bf16_round(__uint_as_float(r1[vv * 16 + q]));
+                    b[q] = bf16_round(__uint_as_float(r3[vv * 16 + q]));
+                    h[q] = silu_f(a[q]) * b[q];
                   }
-                  st16(static_cast<__nv_bfloat16 *>(p.dx1) + base + col, left, pack8(o1), pack8(o1 + 8));
-                  st16(static_cast<__nv_bfloat16 *>(p.dx3) + base + col, left, pack8(o3), pack8(o3 + 8));
-                  if (p.hs) st16(static_cast<__nv_bfloat16 *>(p.hs) + base + col, left, pack8(hv), pack8(hv + 8));
+                  const int left = t.n_valid - col;
+                  st16(static_cast<__nv_bfloat16 *>(p.x1_out) + base + col, left, pack8(a), pack8(a + 8));
+                  st16(static_cast<__nv_bfloat16 *>(p.x3_out) + base + col, left, pack8(b), pack8(b + 8));
+                  st16(static_cast<__nv_bfloat16 *>(p.h_out) + base + col, left, pack8(h), pack8(h + 8));
                 }
               }
             }
           }
+        } else {
+          // EPI_SWIGLU_BWD: accumulator = dh = (w * dOut) W2 for this row
+          const int64_t base = orow * (int64_t)p.N + t.n0;
+          // x1 / x3 of the first 64 columns are requested before waiting on the MMAs, those of the second 64
+          // together with the second TMEM read
+          uint4 xa[8], xb[8];
+          auto load_x = [&](int c0) {
+            if (row_ok) {
+#pragma unroll
+              for (int vv = 0; vv < 4; vv++) {
+                const int col = c0 + vv * 16;
+                if (col < cend && col < t.n_valid) {
+                  ld16(static_cast<const __nv_bfloat16 *>(p.x1_in) + base + col, t.n_valid - col, xa[2 * vv], xa[2 * vv + 1]);
+                  ld16(static_cast<const __nv_bfloat16 *>(p.x3_in) + base + col, t.n_valid - col, xb[2 * vv], xb[2 * vv + 1]);
+                }
+              }
+            }
+          };
+          load_x(cbeg);
+          bool ok = xwait(tfull_bar(acc), acc_phase, ST_EPILOGUE_TIMEOUT);
+          if (!__all_sync(0xffffffffu, ok)) goto teardown;
+          ptx::tc_fence_after();
+          dbg_e0 = DBG_CLK();
+          float dp_part = 0.f;
+#pragma unroll
+          for (int ch = 0; ch < 2; ch++) {
+            const int c0 = cbeg + ch * 64;
+            if (c0 < cend) {
+              uint32_t r[64];
+              ptx::tmem_ld32(taddr + c0, r);
+              if (c0 + 32 < cend) ptx::tmem_ld32(taddr + c0 + 32, r + 32);
+              if (ch == 1) load_x(c0);
+              ptx::tmem_ld_wait();
+              if (row_ok) {
+#pragma unroll
+                for (int vv = 0; vv < 4; vv++) {
+                  const int col = c0 + vv * 16;
+                  if (col < cend && col < t.n_valid) {
+                    float a[16], b[16], o1[16], o3[16], hv[16];
+                    unpack8(xa[2 * vv], a);
+                    unpack8(xa[2 * vv + 1], a + 8);
+                    unpack8(xb[2 * vv], b);
+                    unpack8(xb[2 * vv + 1], b + 8);
+                    const int left = t.n_valid - col;
+#pragma unroll
+                    for (int q = 0; q < 16; q++) {
+                      const float acc_dh = (q < left) ? __uint_as_float(r[vv * 16 + q]) : 0.f;
+                      const float s = 1.0f / (1.0f + __expf(-a[q]));
+                      const float silu = a[q] * s;
+                      hv[q] = silu * b[q];
+                      if (q < left) dp_part += bf16_round(hv[q]) * acc_dh;
+                      const float dh = bf16_round(acc_dh);  // the reference stores dh as bf16 before swiglu_bwd_x
+                      o3[q] = dh * silu;
+                      o1[q] = dh * b[q] * (s + a[q] * (s * (1.0f - s)));
+                    }
+                    st16(static_cast<__nv_bfloat16 *>(p.dx1) + base + col, left, pack8(o1), pack8(o1 + 8));
+                    st16(static_cast<__nv_bfloat16 *>(p.dx3) + base + col, left, pack8(o3), pack8(o3 + 8));
+                    if (p.hs) st16(static_cast<__nv_bfloat16 *>(p.hs) + base + col, left, pack8(hv), pack8(hv + 8));
+                  }
+                }
+              }
+            }
+          }
+          if (row_ok) {
+            // <h, (w dOut) W2> = w <Y, dOut>: divide the gate weight back out (w == 0 contributes nothing downstream)
+            const float w = p.row_w[orow];
+            if (w != 0.f) atomicAdd(p.dP + orow, dp_part / w);
+          }
         }
-        if (row_ok) {
-          // <h, (w dOut) W2> = w <Y, dOut>: divide the gate weight back out (w == 0 contributes nothing downstream)
-          const float w = p.row_w[orow];
-          if (w != 0.f) atomicAdd(p.dP + orow, dp_part / w);
-        }
-      }
 
-      ptx::tc_fence_before();
-      __syncwarp();
-      if (lane == 0) {
-        if (PAIR && !leader) ptx::mbar_arrive_remote(tempty_bar(acc), 0);
-        else ptx::mbar_arrive(tempty_bar(acc));
+        ptx::tc_fence_before();
+        __syncwarp();
+        if (lane == 0) {
+          if (PAIR && !leader) ptx::mbar_arrive_remote(tempty_bar(acc), 0);
+          else ptx::mbar_arrive(tempty_bar(acc));
+          if (warp == 2 && leader) {
+            DBG_ADD(3, DBG_CLK() - dbg_e0);
+            DBG_ADD(4, 1);
+          }
+        }
+        acc_par ^= 1u << acc;
       }
-      if (++acc == 2) {
-        acc = 0;
-        acc_phase ^= 1u;
-      }
+      seq++;
     }
   }
+
 
 teardown:
   if (*abort_flag) {
@@ -849,9 +927,10 @@ teardown:
 
 constexpr size_t GEMM_SMEM_LIMIT = 232448;  // 227 KiB: the most one CTA can be given on sm_100
 
-template <bool PAIR>
+template <bool PAIR, int SUP>
 static size_t gemm_smem_bytes(int groups, bool stage_out) {
-  return 1024 + (size_t)Cfg<PAIR>::STAGES * Cfg<PAIR>::STAGE_BYTES + sizeof(GemmSmemTail) + 4 * (size_t)table_ints(groups) +
+  using CF = Cfg<PAIR, SUP>;
+  return 1024 + (size_t)CF::STAGES * CF::STAGE_BYTES + sizeof(GemmSmemTail) + 4 * (size_t)table_ints(groups) +
          (stage_out ? (size_t)EPI_WARPS * STAGE_OUT_BYTES_PER_WARP : 0);
 }
 
@@ -894,21 +973,35 @@ static int make_tmap(CUtensorMap *m, const void *base, int rank, uint64_t d0, ui
   return 0;
 }
 
+// Per-device host state. One process may drive several GPUs (cudaSetDevice between calls), so everything that is a
+// property of a device - its SM count, the address of its copy of the status word, whether a kernel variant has been
+// given its shared-memory attribute there - is kept per device ordinal.
+constexpr int MAX_DEVICES = 64;
+
+static int current_device() {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) return -1;
+  return dev;
+}
+
 static int sm_count_cached() {
-  static int sms = 0;
-  if (!sms) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    if (sms <= 0) sms = 148;
+  static int sms[MAX_DEVICES];
+  const int dev = current_device();
+  if (dev < 0) return 148;
+  if (!sms[dev]) {
+    int v = 0;
+    cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev);
+    sms[dev] = v > 0 ? v : 148;
   }
-  return sms;
+  return sms[dev];
 }
 
 static int *status_ptr() {
-  static int *ptr = nullptr;
-  if (!ptr) cudaGetSymbolAddress((void **)&ptr, g_gemm_status);
-  return ptr;
+  static int *ptr[MAX_DEVICES];
+  const int dev = current_device();
+  if (dev < 0) return nullptr;
+  if (!ptr[dev] && cudaGetSymbolAddress((void **)&ptr[dev], g_gemm_status) != cudaSuccess) ptr[dev] = nullptr;
+  return ptr[dev];
 }
 
 // 0 = one CTA per tile (cta_group::1), 1 = CTA pairs (cta_group::2) wherever a launch allows it.
@@ -923,17 +1016,37 @@ static int pair_mode() {
   return g_pair_mode;
 }
 
-template <int EPI, bool PAIR>
+// Which kinds of launch let one fetch of the A rows feed two column tiles (256 x 512 per CTA pair): bit 0 the
+// row-grouped expert GEMMs (forward, dgrad), bit 1 the reduction-grouped weight gradients, bit 2 the dense matmul,
+// bit 3 = also when the launch then has too few units to fill the GPU (for tests on small shapes).
+// Environment variable B200_GEMM_WIDE on first use; b200_gemm_set_wide_mode overrides it.
+constexpr int WIDE_GROUPED_M = 1, WIDE_GROUPED_K = 2, WIDE_DENSE = 4, WIDE_ALWAYS = 8;
+#ifndef B200_GEMM_WIDE_DEFAULT
+#define B200_GEMM_WIDE_DEFAULT WIDE_DENSE
+#endif
+static int g_wide_mode = -1;
+
+static int wide_mode() {
+  if (g_wide_mode < 0) {
+    const char *e = getenv("B200_GEMM_WIDE");
+    g_wide_mode = (e && e[0] >= '0' && e[0] <= '9') ? (atoi(e) & 15) : B200_GEMM_WIDE_DEFAULT;
+  }
+  return g_wide_mode;
+}
+
+template <int EPI, bool PAIR, int SUP>
 static int launch_gemm_variant(GemmParams &p, int64_t max_tiles, cudaStream_t s) {
-  auto kern = gemm_sm100_kernel<EPI, PAIR>;
+  auto kern = gemm_sm100_kernel<EPI, PAIR, SUP>;
   // staging of scattered rows is used whenever it fits beside the pipeline stages and the group tables
-  p.stage_out = (EPI == EPI_STORE && p.row_tags != nullptr && gemm_smem_bytes<PAIR>(p.num_groups, true) <= GEMM_SMEM_LIMIT) ? 1 : 0;
-  const size_t smem = gemm_smem_bytes<PAIR>(p.num_groups, p.stage_out != 0);
+  p.stage_out = (EPI == EPI_STORE && p.row_tags != nullptr && gemm_smem_bytes<PAIR, SUP>(p.num_groups, true) <= GEMM_SMEM_LIMIT) ? 1 : 0;
+  const size_t smem = gemm_smem_bytes<PAIR, SUP>(p.num_groups, p.stage_out != 0);
   B200_REQUIRE(smem <= GEMM_SMEM_LIMIT, "gemm: %d groups need %zu bytes of shared memory (limit %zu)", p.num_groups, smem,
                GEMM_SMEM_LIMIT);
-  static bool configured = false;
-  static int max_clusters = 0;
-  if (!configured) {
+  const int dev = current_device();
+  B200_REQUIRE(dev >= 0, "gemm: no current device (or its ordinal is %d or more)", MAX_DEVICES);
+  static bool configured[MAX_DEVICES];
+  static int max_clusters[MAX_DEVICES];
+  if (!configured[dev]) {
     B200_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GEMM_SMEM_LIMIT));
     if (PAIR) {
       cudaLaunchConfig_t q = {};
@@ -947,12 +1060,12 @@ static int launch_gemm_variant(GemmParams &p, int64_t max_tiles, cudaStream_t s)
       a[0].val.clusterDim.z = 1;
       q.attrs = a;
       q.numAttrs = 1;
-      if (cudaOccupancyMaxActiveClusters(&max_clusters, kern, &q) != cudaSuccess || max_clusters <= 0) {
+      if (cudaOccupancyMaxActiveClusters(&max_clusters[dev], kern, &q) != cudaSuccess || max_clusters[dev] <= 0) {
         cudaGetLastError();
-        max_clusters = sm_count_cached() / 2;
+        max_clusters[dev] = sm_count_cached() / 2;
       }
     }
-    configured = true;
+    configured[dev] = true;
   }
   if (max_tiles < 1) return 0;
   if (!PAIR) {
@@ -962,7 +1075,7 @@ static int launch_gemm_variant(GemmParams &p, int64_t max_tiles, cudaStream_t s)
     B200_CHECK_LAUNCH("gemm_sm100");
     return 0;
   }
-  int64_t pairs = max_clusters;
+  int64_t pairs = max_clusters[dev];
   if (max_tiles < pairs) pairs = max_tiles;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)(2 * pairs));
@@ -980,11 +1093,18 @@ static int launch_gemm_variant(GemmParams &p, int64_t max_tiles, cudaStream_t s)
   return 0;
 }
 
-// max_tiles: an upper bound on the number of 128-row tiles (pair tiles are never more numerous).
+// max_tiles: an upper bound on the number of 128-row x one-column-tile units (pair and wide units are never more
+// numerous). row_tiles_hint: about how many 256-row tiles the launch has (decides whether wide units still fill the GPU).
 template <int EPI>
-static int launch_gemm(GemmParams &p, int64_t max_tiles, cudaStream_t s, bool pair_ok = true) {
+static int launch_gemm(GemmParams &p, int64_t max_tiles, cudaStream_t s, bool pair_ok = true, int64_t row_tiles_hint = 0) {
   p.status = status_ptr();
   B200_REQUIRE(p.status != nullptr, "gemm: status word unavailable");
+#ifdef B200_GEMM_DEBUG
+  {
+    const char *e = getenv("B200_GEMM_DBG");
+    p.dbg = e ? atoi(e) : 0;
+  }
+#endif
   {
     // 256-bit epilogue accesses need every bf16 row start to be 32-byte aligned
     auto a32 = [](const void *q) { return (reinterpret_cast<uintptr_t>(q) & 31u) == 0; };
@@ -1000,8 +1120,20 @@ static int launch_gemm(GemmParams &p, int64_t max_tiles, cudaStream_t s, bool pa
       wide = a32(p.x1_in) && a32(p.x3_in) && a32(p.dx1) && a32(p.dx3) && a32(p.hs) && p.N % 16 == 0;
     p.wide = wide ? 1 : 0;
   }
-  if (pair_ok && pair_mode()) return launch_gemm_variant<EPI, true>(p, max_tiles, s);
-  return launch_gemm_variant<EPI, false>(p, max_tiles, s);
+  if (pair_ok && pair_mode()) {
+    // two column tiles per unit: when the kind of launch is enabled, there are at least two column tiles, the units
+    // still outnumber the CTA pairs a few times over, and the deeper stages fit beside the group tables
+    const int kind = p.group_mode == GROUPED_M ? WIDE_GROUPED_M : (p.group_mode == GROUPED_K ? WIDE_GROUPED_K : WIDE_DENSE);
+    const int col_tiles = (p.N + (p.dual_b ? 127 : 255)) / (p.dual_b ? 128 : 256);
+    const int64_t units2 = row_tiles_hint * ((col_tiles + 1) / 2);
+    const bool long_reduction = p.group_mode == GROUPED_K || (int64_t)p.K * p.k_segments >= 1024;  // else the epilogue is all
+    if ((wide_mode() & kind) && col_tiles >= 2 && (long_reduction || (wide_mode() & WIDE_ALWAYS)) &&
+        ((wide_mode() & WIDE_ALWAYS) || units2 >= 2 * (int64_t)(sm_count_cached() / 2)) &&
+        gemm_smem_bytes<true, 2>(p.num_groups, false) <= GEMM_SMEM_LIMIT)
+      return launch_gemm_variant<EPI, true, 2>(p, max_tiles, s);
+    return launch_gemm_variant<EPI, true, 1>(p, max_tiles, s);
+  }
+  return launch_gemm_variant<EPI, false, 1>(p, max_tiles, s);
 }
 
 static void zero_params(GemmParams &p) { memset(&p, 0, sizeof(p)); }
@@ -1037,18 +1169,6 @@ __global__ void splitk_reduce_kernel(int64_t n, int splits, const float *__restr
 
 using namespace b200;
 
-#ifdef B200_GEMM_STATS
-// debugging build only: cycles summed over CTAs {0 producers waiting for a free stage, 1 producers' lifetime,
-// 2 MMA thread waiting for data, 3 waiting for a free accumulator, 4 MMA thread's lifetime, 5 in tcgen05.commit,
-// 6 odd CTA's thread waiting for its slabs, 7 issuing the MMAs}; reading clears
-extern "C" int b200_dbg_gemm_stats(unsigned long long *out) {
-  B200_CUDA(cudaDeviceSynchronize());
-  B200_CUDA(cudaMemcpyFromSymbol(out, g_gemm_stats, sizeof(unsigned long long) * 8));
-  unsigned long long z[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-  B200_CUDA(cudaMemcpyToSymbol(g_gemm_stats, z, sizeof(z)));
-  return 0;
-}
-#endif
 
 // Host run of the kernels' tile scheduler (same Sched code as the device uses): lists the tiles a launch would
 // process, in order. counts / cumsum_incl are HOST arrays here. Nothing touches a GPU.
@@ -1068,22 +1188,41 @@ extern "C" int b200_gemm_enumerate_tiles(int group_mode, int pair, int M, int N,
     }
   }
   Sched sc;
-  sc.init(group_mode, M, N, K, dual_b, pair != 0, tile_rows, k_splits, k_split_len, cnt.data(), base.data(), tpre.data(),
-          num_groups);
+  sc.init(group_mode, M, N, K, dual_b, pair != 0, tile_rows, pair == 2 ? 2 : 1, k_splits, k_split_len, cnt.data(),
+          base.data(), tpre.data(), num_groups);
   Tile t;
   int n = 0;
   for (int id = 0; sc.get(id, t); id++) {
-    if (n < max_tiles) {
-      const int rec[9] = {t.group, t.a_row0, t.out_row0, t.m_valid, t.n0, t.n_valid, t.nw, t.k_row0, t.k_len};
-      memcpy(out + (size_t)n * 9, rec, sizeof(rec));
+    for (int sub = 0; sub < t.nsub; sub++) {
+      sc.set_sub(t, sub);
+      if (n < max_tiles) {
+        const int rec[9] = {t.group, t.a_row0, t.out_row0, t.m_valid, t.n0, t.n_valid, t.nw, t.k_row0, t.k_len};
+        memcpy(out + (size_t)n * 9, rec, sizeof(rec));
+      }
+      n++;
     }
-    n++;
   }
   return n;
 }
 
+#ifdef B200_GEMM_DEBUG
+// timing experiments only: reads and clears the cycle counters
+extern "C" int b200_dbg_gemm_stats(unsigned long long *out) {
+  B200_CUDA(cudaDeviceSynchronize());
+  B200_CUDA(cudaMemcpyFromSymbol(out, g_dbg_stats, sizeof(unsigned long long) * 8));
+  unsigned long long z[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  B200_CUDA(cudaMemcpyToSymbol(g_dbg_stats, z, sizeof(z)));
+  return 0;
+}
+#endif
+
 extern "C" int b200_gemm_set_pair_mode(int on) {
   g_pair_mode = on ? 1 : 0;
+  return 0;
+}
+
+extern "C" int b200_gemm_set_wide_mode(int mask) {
+  g_wide_mode = mask & 15;
   return 0;
 }
 
@@ -1160,7 +1299,7 @@ extern "C" int b200_matmul(int a_dt, int b_dt, int c_dt, int d_dt, int to_trans_
     const uint64_t per_split = (uint64_t)N * M * sizeof(float);
     if ((uint64_t)splits * per_split > workspaceBytes) splits = (int)(workspaceBytes / per_split);
   }
-  if (splits < 2) return launch_gemm<EPI_STORE>(p, tiles, (cudaStream_t)stream, pair_ok);
+  if (splits < 2) return launch_gemm<EPI_STORE>(p, tiles, (cudaStream_t)stream, pair_ok, (N + 255) / 256);
   const int split_len = (((K + splits - 1) / splits) + BK - 1) / BK * BK;
   splits = (K + split_len - 1) / split_len;
   p.k_splits = splits;
@@ -1171,7 +1310,7 @@ extern "C" int b200_matmul(int a_dt, int b_dt, int c_dt, int d_dt, int to_trans_
   p.out_fp32 = 1;
   p.D = workspace;
   p.d_group_stride = (int64_t)N * M;
-  if (launch_gemm<EPI_STORE>(p, tiles * splits, (cudaStream_t)stream, pair_ok)) return -1;
+  if (launch_gemm<EPI_STORE>(p, tiles * splits, (cudaStream_t)stream, pair_ok, (int64_t)((N + 255) / 256) * splits)) return -1;
   const int64_t n = (int64_t)N * M;
   splitk_reduce_kernel<<<(unsigned)((n / 4 + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
       n, splits, static_cast<const float *>(workspace), alpha, use_c ? beta : 0.0f, use_c ? C : nullptr,
@@ -1251,7 +1390,7 @@ static int experts_fwd_impl(int total_rows, int model_dim, int ffn_dim, int num_
                   (uint64_t)model_dim * 2, (uint64_t)w3_stride_elems * 2))
       return -1;
     p.tmA2 = p.tmA;
-    if (launch_gemm<EPI_SWIGLU_FWD>(p, m_tiles_max * ((ffn_dim + 127) / 128), s)) return -1;
+    if (launch_gemm<EPI_SWIGLU_FWD>(p, m_tiles_max * ((ffn_dim + 127) / 128), s, true, total_rows / 256)) return -1;
   }
   if (Y == nullptr && sc == nullptr) return 0;  // gate-up only (recompute of x1, x3, h)
   {
@@ -1275,7 +1414,7 @@ static int experts_fwd_impl(int total_rows, int model_dim, int ffn_dim, int num_
       return -1;
     p.tmA2 = p.tmA;
     p.tmB2 = p.tmB;
-    if (launch_gemm<EPI_STORE>(p, m_tiles_max * ((model_dim + 255) / 256), s)) return -1;
+    if (launch_gemm<EPI_STORE>(p, m_tiles_max * ((model_dim + 255) / 256), s, true, total_rows / 256)) return -1;
   }
   return 0;
 }
@@ -1348,7 +1487,7 @@ static int experts_bwd_x_impl(int total_rows, int model_dim, int ffn_dim, int nu
       return -1;
     p.tmA2 = p.tmA;
     p.tmB2 = p.tmB;
-    if (launch_gemm<EPI_SWIGLU_BWD>(p, m_tiles_max * ((ffn_dim + 255) / 256), s)) return -1;
+    if (launch_gemm<EPI_SWIGLU_BWD>(p, m_tiles_max * ((ffn_dim + 255) / 256), s, true, total_rows / 256)) return -1;
   }
   {
     // dZ = dx1 W1 + dx3 W3: one accumulator, two reduction segments
@@ -1374,7 +1513,7 @@ static int experts_bwd_x_impl(int total_rows, int model_dim, int ffn_dim, int nu
     if (make_tmap(&p.tmB2, W3, 3, (uint64_t)model_dim, (uint64_t)ffn_dim, (uint64_t)num_experts,
                   (uint64_t)model_dim * 2, (uint64_t)w3_stride_elems * 2))
       return -1;
-    if (launch_gemm<EPI_STORE>(p, m_tiles_max * ((model_dim + 255) / 256), s)) return -1;
+    if (launch_gemm<EPI_STORE>(p, m_tiles_max * ((model_dim + 255) / 256), s, true, total_rows / 256)) return -1;
   }
   return 0;
 }
@@ -1433,7 +1572,7 @@ static int launch_wgrad(int total_rows, int Mrows, int Ncols, int num_experts, c
   p.tmA2 = p.tmA;
   p.tmB2 = p.tmB;
   const int64_t tiles = (int64_t)num_experts * ((Mrows + BM - 1) / BM) * ((Ncols + 255) / 256);
-  return launch_gemm<EPI_STORE>(p, tiles, s);
+  return launch_gemm<EPI_STORE>(p, tiles, s, true, (int64_t)num_experts * ((Mrows + 255) / 256));
 }
 
 extern "C" int b200_moe_experts_bwd_w(int total_rows, int model_dim, int ffn_dim, int num_experts, const void *dY_zone,

@@ -62,6 +62,12 @@ def gemm_set_pair_mode(on):
     _check(_lib.load().b200_gemm_set_pair_mode(int(bool(on))), "b200_gemm_set_pair_mode", 0)
 
 
+def gemm_set_wide_mode(mask):
+    """Bit 0 / 1 / 2: forward+dgrad / weight-gradient / dense launches use 256 x 512 units per CTA pair; bit 3: even
+    when that leaves too few units to fill the GPU (tests on small shapes)."""
+    _check(_lib.load().b200_gemm_set_wide_mode(int(mask)), "b200_gemm_set_wide_mode", 0)
+
+
 def select_experts(total_tokens, n_experts, top_k_experts, X_routed, token_expert_weights, chosen_experts,
                    expert_counts, expert_counts_cumsum, host_expert_counts=None):
     _check(_lib.load().b200_select_experts(_dt(X_routed), total_tokens, n_experts, top_k_experts, _p(X_routed),

@@ -61,6 +61,15 @@ int orc_num_threads(void) {
 #endif
 }
 
+/* Sets the OpenMP team size (a launcher such as torch.distributed.run exports OMP_NUM_THREADS=1). */
+void orc_set_num_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
+}
+
 void orc_f32_to_bf16(const float *src, uint16_t *dst, int64_t n) {
 #pragma omp parallel for schedule(static)
   for (int64_t i = 0; i < n; i++) dst[i] = f32_to_bf16(src[i]);

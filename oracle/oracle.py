@@ -19,14 +19,20 @@ _LIB_PATH = os.path.join(_HERE, "liboracle.so")
 DT_FP32, DT_BF16 = 3, 5
 
 
+def reference_root():
+    """The reference checkout: $REFERENCE_ROOT, else a directory named `reference` beside this repository."""
+    return os.environ.get("REFERENCE_ROOT") or os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")
+
+
 def build(force=False):
     if force or not os.path.exists(_LIB_PATH) or (
         os.path.getmtime(_LIB_PATH) < os.path.getmtime(os.path.join(_HERE, "moe_oracle.c"))
     ):
         subprocess.check_call(["make", "-C", _HERE, "liboracle.so"], stdout=subprocess.DEVNULL)
-    if os.path.isdir(os.environ.get("REFERENCE_ROOT", "/root/reference")):
+    if os.path.isdir(reference_root()):
         # the reference's own kernels (cubins) and host submitters, compiled from its sources in place
-        subprocess.call(["make", "-C", _HERE, "ref", "dropin"], stdout=subprocess.DEVNULL)
+        subprocess.call(["make", "-C", _HERE, "ref", "dropin", "REFERENCE_ROOT=" + reference_root()],
+                        stdout=subprocess.DEVNULL)
 
 
 _lib = None
@@ -51,6 +57,14 @@ def _p(a):
 
 def num_threads():
     return lib().orc_num_threads()
+
+
+def use_all_cores():
+    """Makes the oracle's OpenMP loops use every core this process may run on, whatever OMP_NUM_THREADS says (process
+    launchers set it to 1). Returns the thread count now in use."""
+    n = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    lib().orc_set_num_threads(C.c_int(n))
+    return num_threads()
 
 
 # ---- bf16 helpers -----------------------------------------------------------

@@ -33,7 +33,9 @@ def bits(t):
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2 and not os.environ.get("REFERENCE_ROOT"):
+        sys.exit("usage: make_golden.py <path of the reference checkout>   (or set REFERENCE_ROOT)")
+    ref_root = sys.argv[1] if len(sys.argv) > 1 else os.environ["REFERENCE_ROOT"]
     sys.path.insert(0, os.path.join(ref_root, "test/dataflow_models/correctness_compare/test_moe"))
     import moe_model_flash2 as ref  # noqa: E402
 

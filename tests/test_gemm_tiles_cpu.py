@@ -17,7 +17,7 @@ def tiles(mode, pair, M, N, K, dual_b=0, counts=None, splits=0, split_len=0):
     G = 1 if counts is None else len(counts)
     c = None if counts is None else np.ascontiguousarray(counts, np.int32)
     ci = None if counts is None else np.cumsum(c).astype(np.int32)
-    cap = 1 << 16
+    cap = 1 << 16  # pair: 0 = single-CTA tiles, 1 = CTA pairs, 2 = CTA pairs with two column tiles per unit
     out = np.zeros((cap, 9), np.int32)
     p = lambda a: None if a is None else a.ctypes.data_as(ctypes.c_void_p)
     n = lib.b200_gemm_enumerate_tiles(mode, pair, M, N, K, dual_b, G, p(c), p(ci), splits, split_len, cap, p(out))
@@ -25,7 +25,7 @@ def tiles(mode, pair, M, N, K, dual_b=0, counts=None, splits=0, split_len=0):
     return out[:n]
 
 
-@pytest.mark.parametrize("pair", [0, 1])
+@pytest.mark.parametrize("pair", [0, 1, 2])
 @pytest.mark.parametrize("N,dual_b", [(1408, 1), (4096, 0), (1408, 0), (72, 0), (200, 1)])
 def test_row_grouped_tiles_cover_every_expert_exactly(pair, N, dual_b):
     rng = np.random.default_rng(N + pair)
@@ -52,7 +52,7 @@ def test_row_grouped_tiles_cover_every_expert_exactly(pair, N, dual_b):
     assert key == sorted(key)
 
 
-@pytest.mark.parametrize("pair", [0, 1])
+@pytest.mark.parametrize("pair", [0, 1, 2])
 def test_reduction_grouped_tiles(pair):
     counts = np.array([0, 1, 63, 64, 65, 130, 0, 1000], np.int32)
     M, N = 1408, 4096
@@ -70,7 +70,7 @@ def test_reduction_grouped_tiles(pair):
         assert (cover == 1).all()
 
 
-@pytest.mark.parametrize("pair", [0, 1])
+@pytest.mark.parametrize("pair", [0, 1, 2])
 @pytest.mark.parametrize("K,splits,split_len", [(8192, 8, 1024), (5000, 4, 1280), (4096, 0, 0)])
 def test_dense_tiles_and_split_reduction(pair, K, splits, split_len):
     M, N = 300, 520          # output rows, output columns in the kernel's row-major view

@@ -13,15 +13,21 @@ from helpers import assert_close, assert_close_with_slack, bf16_bits_to_f32
 pytestmark = pytest.mark.gpu
 
 
-@pytest.fixture(params=["pair", "single"], autouse=True)
+DEFAULT_WIDE_MASK = 4  # the library default: dense launches only, when the launch is large enough
+
+
+@pytest.fixture(params=["pair", "wide", "single"], autouse=True)
 def gemm_tile_mode(request):
-    """Every test runs with CTA-pair tiles (cta_group::2, the default) and with single-CTA tiles."""
+    """Every test runs with CTA-pair tiles of one column tile per unit (cta_group::2), with CTA pairs and two column
+    tiles per unit forced on for every kind of launch however small ("wide"), and with single-CTA tiles."""
     if torch.cuda.is_available():
         from ml_dataflow_b200 import ops
 
-        ops.gemm_set_pair_mode(request.param == "pair")
+        ops.gemm_set_pair_mode(request.param != "single")
+        ops.gemm_set_wide_mode(15 if request.param == "wide" else 0)
         yield request.param
         ops.gemm_set_pair_mode(True)
+        ops.gemm_set_wide_mode(DEFAULT_WIDE_MASK)
     else:
         yield request.param
 

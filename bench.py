@@ -233,28 +233,6 @@ def gpu_numa_cpus(index):
         return None, None
 
 
-def measure_peer_copy_gbs(dev_from, dev_to, mib=256, reps=5):
-    """Device-to-device copy rate between two GPUs of this node (GB/s, one direction), timed with CUDA events."""
-    import torch
-
-    n = mib << 20
-    a = torch.empty(n, dtype=torch.uint8, device=f"cuda:{dev_from}")
-    b = torch.empty(n, dtype=torch.uint8, device=f"cuda:{dev_to}")
-    b.copy_(a)
-    torch.cuda.synchronize(dev_from)
-    torch.cuda.synchronize(dev_to)
-    with torch.cuda.device(dev_from):
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(reps):
-            b.copy_(a, non_blocking=True)
-        e1.record()
-        e1.synchronize()
-        ms = e0.elapsed_time(e1) / reps
-    del a, b
-    return n / (ms * 1e-3) / 1e9
-
-
 def per_op_profile(layer, step, work, peaks, reps):
     """Runs `step` with an event between the ops and returns ({group: record}, GEMM ms, GEMM flop, raw ms per mark)."""
     import torch
@@ -563,17 +541,8 @@ def run_gpu_arm(args, world):
     # ---------------- per-op timing for the roofline (separate pass, events between ops)
     kernels, gemm_ms, gemm_flops, raw_ms = per_op_profile(layer, lambda: step(X, dOut, out, dXn), algorithmic_work(cfg),
                                                           peaks, max(3, min(steps, 10)))
-    peer_gbs = None
     if world > 1:
-        if rank == 0:
-            try:
-                peer_gbs = measure_peer_copy_gbs(0, 1)
-            except Exception:
-                peer_gbs = None
-        link = peer_gbs or NVLINK_PEER_GBS_RECORDED
-        t_link = torch.tensor([link], dtype=torch.float64, device=dev)
-        dist.broadcast(t_link, 0)
-        link = float(t_link.item())
+        link = NVLINK_PEER_GBS_RECORDED
         for name, amount in exchange_work(cfg, world).items():
             if name in raw_ms:
                 ms = raw_ms[name]
@@ -584,8 +553,8 @@ def run_gpu_arm(args, world):
                 ach_x = amount / (ms * 1e-3) / 1e9
                 kernels[name] = dict(ms=round(ms, 4), bound="nvlink", achieved=round(ach_x, 1), unit="GB/s per direction",
                                      peak=round(link, 1), frac=round(ach_x / link, 4),
-                                     peak_source=("peer copy GPU 0 -> GPU 1 timed by this run" if peer_gbs else
-                                                  "recorded peer-copy rate for this machine type (not measured by this run)"))
+                                     peak_source="recorded peer-copy rate per direction for this machine type (nominal "
+                                                 "900 GB/s); a constant, not measured by this run")
     ach = gemm_flops / (gemm_ms * 1e-3) / 1e12 if gemm_ms else 0.0
     traffic = NCU_GEMM_DRAM_BYTES_PER_STEP.get((T, d, E, k, f)) if world == 1 else None
     roofline = dict(kernel="gemm_sm100_kernel (grouped expert GEMMs: 7 launches per step, 18*R*d*f flop)",

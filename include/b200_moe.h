@@ -380,6 +380,55 @@ int b200_moe_block_recompute(const B200MoeBlock *block, const void *Xn, int reco
 int b200_moe_block_bwd(const B200MoeBlock *block, const void *Xn, const void *dOut, void *dXn, void *dWr, void *dW1,
                        void *dW3, void *dW2, void *stream);
 
+/* ---- the reference's model directory -------------------------------------------------------------------- */
+
+/*
+ * config.txt of a model directory: the twenty "Name: value" lines the reference parses with one sscanf
+ * (libdataflowmodels/src/transformer/src/prep_seq_batch.c:84-130; struct in
+ * libdataflowmodels/include/dataflow_models.h:69-90; writer models/init_model.py:153-156). Same fields, same order.
+ */
+typedef struct B200ModelConfig {
+  char embed_dtype[16], attn_dtype[16], router_dtype[16], expert_dtype[16], head_dtype[16];
+  int vocab_size, num_layers, model_dim, head_dim, num_q_heads, num_kv_heads;
+  char qk_norm_type[16], qk_norm_weight_type[16];
+  int num_shared_experts, num_routed_experts, top_k_routed_experts, expert_dim;
+  char expert_mlp_type[16];
+  int rope_theta;
+  float rms_norm_epsilon;
+} B200ModelConfig;
+
+int b200_parse_model_config(const char *config_txt_path, B200ModelConfig *out);
+
+/*
+ * Byte offsets inside layers/<i>/combined_layer.weight, computed as set_transformer_block_weight_offsets does
+ * (libdataflowmodels/src/transformer/src/prep_transformer.c:24-165): attention norm, q, k, v, o, ffn norm, router,
+ * then per expert w1, w3, w2, every tensor starting at the running size rounded up to pointer_alignment (0 = packed;
+ * the reference's drivers use 256). Experts are equally spaced: expert e's w1 starts at w1_first + e *
+ * expert_stride_bytes, likewise w3, w2. Shared experts, if any, precede the routed ones in the file.
+ */
+typedef struct B200MoeLayerLayout {
+  uint64_t attn_norm, w_q, w_k, w_v, w_o, ffn_norm, router;
+  uint64_t w1_first, w3_first, w2_first, expert_stride_bytes;
+  int num_experts_in_file, first_routed_expert;
+  uint64_t raw_bytes, aligned_bytes; /* sum of the tensor sizes; size of the laid-out block = size of the file */
+} B200MoeLayerLayout;
+
+int b200_moe_layer_file_layout(const B200ModelConfig *config, int pointer_alignment, B200MoeLayerLayout *out);
+
+/*
+ * load_transformer_block (prep_transformer.c:368-388): reads exactly `bytes` (= layout.aligned_bytes) from the file
+ * into host_buffer; a file that is shorter or longer is refused. The caller copies the buffer to the device.
+ */
+int b200_read_layer_file(const char *path, void *host_buffer, uint64_t bytes);
+
+/*
+ * bind_transformer_block for the MoE part (prep_transformer.c:316-366): points block->Wr, W1, W3, W2 and the expert
+ * strides at the tensors of a layer laid out at layer_base (device memory, a copy of the file), and sets model_dim,
+ * num_experts, top_k, ffn_dim from the configuration. bf16 router and expert weights only.
+ */
+int b200_moe_block_bind_weights(B200MoeBlock *block, const B200ModelConfig *config, const B200MoeLayerLayout *layout,
+                                const void *layer_base);
+
 /* ---- expert parallelism over NVLink peer memory (no counterpart in the reference, which is single-GPU) ---- */
 
 /*

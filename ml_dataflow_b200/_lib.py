@@ -48,6 +48,10 @@ SIGNATURES = {
     "b200_moe_block_fwd": (_i, [_vp, _vp, _vp, _vp]),
     "b200_moe_block_recompute": (_i, [_vp, _vp, _i, _vp]),
     "b200_moe_block_bwd": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "b200_parse_model_config": (_i, [C.c_char_p, _vp]),
+    "b200_moe_layer_file_layout": (_i, [_vp, _i, _vp]),
+    "b200_read_layer_file": (_i, [C.c_char_p, _vp, _u64]),
+    "b200_moe_block_bind_weights": (_i, [_vp, _vp, _vp, _vp]),
     "b200_scatter_row_weights": (_i, [_i, _i, _vp, _vp, _vp, _vp]),
     "b200_gather_router_grad": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp]),
 }
@@ -67,6 +71,27 @@ class MoeBlock(C.Structure):
         ("matmul_workspace", _vp), ("matmul_workspace_bytes", _sz),
         ("dY_zone", _vp), ("row_weights", _vp), ("dP", _vp), ("dx1", _vp), ("dx3", _vp), ("dZ", _vp),
         ("dX_routed", _vp),
+    ]
+
+
+class ModelConfig(C.Structure):
+    """ctypes mirror of B200ModelConfig (config.txt of a reference model directory)."""
+    _fields_ = [
+        ("embed_dtype", C.c_char * 16), ("attn_dtype", C.c_char * 16), ("router_dtype", C.c_char * 16),
+        ("expert_dtype", C.c_char * 16), ("head_dtype", C.c_char * 16),
+        ("vocab_size", _i), ("num_layers", _i), ("model_dim", _i), ("head_dim", _i), ("num_q_heads", _i),
+        ("num_kv_heads", _i), ("qk_norm_type", C.c_char * 16), ("qk_norm_weight_type", C.c_char * 16),
+        ("num_shared_experts", _i), ("num_routed_experts", _i), ("top_k_routed_experts", _i), ("expert_dim", _i),
+        ("expert_mlp_type", C.c_char * 16), ("rope_theta", _i), ("rms_norm_epsilon", _f),
+    ]
+
+
+class MoeLayerLayout(C.Structure):
+    """ctypes mirror of B200MoeLayerLayout (byte offsets inside combined_layer.weight)."""
+    _fields_ = [
+        ("attn_norm", _u64), ("w_q", _u64), ("w_k", _u64), ("w_v", _u64), ("w_o", _u64), ("ffn_norm", _u64),
+        ("router", _u64), ("w1_first", _u64), ("w3_first", _u64), ("w2_first", _u64), ("expert_stride_bytes", _u64),
+        ("num_experts_in_file", _i), ("first_routed_expert", _i), ("raw_bytes", _u64), ("aligned_bytes", _u64),
     ]
 
 

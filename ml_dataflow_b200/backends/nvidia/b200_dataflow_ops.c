@@ -9,6 +9,7 @@
  * dataflow_submit_* function (libdataflowops/src/submit_ops/moe_ops.c, matmul_op.c, mlp_misc_ops.c) -
  * into the C ABI of include/b200_moe.h. dataflow_register_b200_moe_ops() registers them under the same
  * op skeletons the submitters build, so libdataflowmodels' MoE block reaches these kernels unchanged.
+ * Three additive ops (all experts of one pass per call) come with their own skeleton setters and submitters.
  */
 #include "dataflow_ops.h"
 #include "cuda_dataflow_handle.h"
@@ -121,7 +122,132 @@ int b200_ext_matmul(Dataflow_Handle * handle, int stream_id, Op * op, void * op_
 		ARG(uint64_t, 17), ARG(void *, 18), s);
 }
 
-#define B200_NUM_EXT_OPS 12
+/* ------------------------------------------------------------------------------------------------------------
+ * Additive grouped ops. The reference expresses the experts as a host loop of single matmuls around a stream
+ * sync (libdataflowmodels/src/transformer/src/dataflow_transformer.c:2789, 2848-2940, 3460-3641, 4101-4148); these
+ * three ops run all experts of one pass in two or three launches and read the per-expert row counts on the device.
+ * They are new skeletons in the reference's own style (libdataflowops/src/set_ops/set_op_skeletons.c:1087-1122):
+ * nickname "<op>_<dtype>", scalar and buffer argument dtypes, SHA-256 fingerprint of the header - and new
+ * submitters in the style of libdataflowops/src/submit_ops/moe_ops.c, so a caller reaches them through
+ * handle->submit_op like every other op.
+ * ------------------------------------------------------------------------------------------------------------ */
+
+static void set_grouped_skeleton(Op_Skeleton * skeleton, const char * name, DataflowDatatype dt, int num_args,
+									const DataflowDatatype * dtypes) {
+	Op_Skeleton_Header * header = &(skeleton -> header);
+	memset(header, 0, sizeof(Op_Skeleton_Header));
+	snprintf(header -> op_nickname, MAX_OP_NICKNAME_SIZE, "%s_%s", name, dataflow_datatype_as_string(dt));
+	header -> num_args = num_args;
+	for (int i = 0; i < MAX_OP_ARGS; i++) {
+		(header -> arg_dtypes)[i] = i < num_args ? dtypes[i] : DATAFLOW_NONE;
+	}
+	dataflow_do_fingerprinting(header, sizeof(Op_Skeleton_Header), (skeleton -> identifier).fingerprint);
+}
+
+#define I_S DATAFLOW_INT_SCALAR
+#define L_S DATAFLOW_LONG_SCALAR
+
+/* args: total_rows, model_dim, ffn_dim, num_experts, zone, W1, W3, W2, w1/w3/w2 expert strides (elements),
+ * expert_counts, expert_counts_cumsum (inclusive), x1, x3, h, Y */
+void dataflow_set_b200_moe_experts_fwd_skeleton(Op_Skeleton * skeleton, DataflowDatatype dt) {
+	DataflowDatatype a[17] = {I_S, I_S, I_S, I_S, dt, dt, dt, dt, L_S, L_S, L_S, DATAFLOW_INT, DATAFLOW_INT, dt, dt, dt, dt};
+	set_grouped_skeleton(skeleton, "b200_moe_experts_fwd", dt, 17, a);
+}
+
+/* args: total_rows, model_dim, ffn_dim, num_experts, dY_zone, row_weights, x1, x3, W1, W3, W2, strides x3,
+ * expert_counts, expert_counts_cumsum, dx1, dx3, hs (may be NULL), dP (fp32, caller zeroes), dZ */
+void dataflow_set_b200_moe_experts_bwd_x_skeleton(Op_Skeleton * skeleton, DataflowDatatype dt) {
+	DataflowDatatype a[21] = {I_S, I_S, I_S, I_S, dt, DATAFLOW_FP32, dt, dt, dt, dt, dt, L_S, L_S, L_S, DATAFLOW_INT,
+								DATAFLOW_INT, dt, dt, dt, DATAFLOW_FP32, dt};
+	set_grouped_skeleton(skeleton, "b200_moe_experts_bwd_x", dt, 21, a);
+}
+
+/* args: total_rows, model_dim, ffn_dim, num_experts, dY_zone, hs, zone_x, dx1, dx3, dW1, dW3, dW2 (each may be
+ * NULL), strides x3, expert_counts, expert_counts_cumsum */
+void dataflow_set_b200_moe_experts_bwd_w_skeleton(Op_Skeleton * skeleton, DataflowDatatype dt) {
+	DataflowDatatype a[17] = {I_S, I_S, I_S, I_S, dt, dt, dt, dt, dt, dt, dt, dt, L_S, L_S, L_S, DATAFLOW_INT, DATAFLOW_INT};
+	set_grouped_skeleton(skeleton, "b200_moe_experts_bwd_w", dt, 17, a);
+}
+
+int b200_ext_moe_experts_fwd(Dataflow_Handle * handle, int stream_id, Op * op, void * op_extra) {
+	void * s;
+	if (stream_of(handle, stream_id, &s, "moe_experts_fwd") || require_bf16(op, 4, "moe_experts_fwd")) return -1;
+	return b200_moe_experts_fwd(ARG(int, 0), ARG(int, 1), ARG(int, 2), ARG(int, 3), ARG(void *, 4), ARG(void *, 5),
+		ARG(void *, 6), ARG(void *, 7), ARG(int64_t, 8), ARG(int64_t, 9), ARG(int64_t, 10), ARG(int *, 11), ARG(int *, 12),
+		ARG(void *, 13), ARG(void *, 14), ARG(void *, 15), ARG(void *, 16), s);
+}
+
+int b200_ext_moe_experts_bwd_x(Dataflow_Handle * handle, int stream_id, Op * op, void * op_extra) {
+	void * s;
+	if (stream_of(handle, stream_id, &s, "moe_experts_bwd_x") || require_bf16(op, 4, "moe_experts_bwd_x")) return -1;
+	return b200_moe_experts_bwd_x(ARG(int, 0), ARG(int, 1), ARG(int, 2), ARG(int, 3), ARG(void *, 4), ARG(float *, 5),
+		ARG(void *, 6), ARG(void *, 7), ARG(void *, 8), ARG(void *, 9), ARG(void *, 10), ARG(int64_t, 11), ARG(int64_t, 12),
+		ARG(int64_t, 13), ARG(int *, 14), ARG(int *, 15), ARG(void *, 16), ARG(void *, 17), ARG(void *, 18), ARG(float *, 19),
+		ARG(void *, 20), s);
+}
+
+int b200_ext_moe_experts_bwd_w(Dataflow_Handle * handle, int stream_id, Op * op, void * op_extra) {
+	void * s;
+	if (stream_of(handle, stream_id, &s, "moe_experts_bwd_w") || require_bf16(op, 4, "moe_experts_bwd_w")) return -1;
+	return b200_moe_experts_bwd_w(ARG(int, 0), ARG(int, 1), ARG(int, 2), ARG(int, 3), ARG(void *, 4), ARG(void *, 5),
+		ARG(void *, 6), ARG(void *, 7), ARG(void *, 8), ARG(void *, 9), ARG(void *, 10), ARG(void *, 11), ARG(int64_t, 12),
+		ARG(int64_t, 13), ARG(int64_t, 14), ARG(int *, 15), ARG(int *, 16), s);
+}
+
+int dataflow_submit_b200_moe_experts_fwd(Dataflow_Handle * handle, int stream_id, DataflowDatatype dt,
+		int total_rows, int model_dim, int ffn_dim, int num_experts, void * zone, void * W1, void * W3, void * W2,
+		int64_t w1_stride_elems, int64_t w3_stride_elems, int64_t w2_stride_elems, int * expert_counts,
+		int * expert_counts_cumsum, void * x1, void * x3, void * h, void * Y) {
+	Op op;
+	dataflow_set_b200_moe_experts_fwd_skeleton(&op.op_skeleton, dt);
+	void ** a = op.op_args;
+	a[0] = &total_rows; a[1] = &model_dim; a[2] = &ffn_dim; a[3] = &num_experts; a[4] = &zone; a[5] = &W1; a[6] = &W3;
+	a[7] = &W2; a[8] = &w1_stride_elems; a[9] = &w3_stride_elems; a[10] = &w2_stride_elems; a[11] = &expert_counts;
+	a[12] = &expert_counts_cumsum; a[13] = &x1; a[14] = &x3; a[15] = &h; a[16] = &Y;
+	if ((handle -> submit_op)(handle, &op, stream_id)) {
+		fprintf(stderr, "Error: failed to submit b200 moe experts fwd op...\n");
+		return -1;
+	}
+	return 0;
+}
+
+int dataflow_submit_b200_moe_experts_bwd_x(Dataflow_Handle * handle, int stream_id, DataflowDatatype dt,
+		int total_rows, int model_dim, int ffn_dim, int num_experts, void * dY_zone, float * row_weights, void * x1,
+		void * x3, void * W1, void * W3, void * W2, int64_t w1_stride_elems, int64_t w3_stride_elems,
+		int64_t w2_stride_elems, int * expert_counts, int * expert_counts_cumsum, void * dx1, void * dx3, void * hs,
+		float * dP, void * dZ) {
+	Op op;
+	dataflow_set_b200_moe_experts_bwd_x_skeleton(&op.op_skeleton, dt);
+	void ** a = op.op_args;
+	a[0] = &total_rows; a[1] = &model_dim; a[2] = &ffn_dim; a[3] = &num_experts; a[4] = &dY_zone; a[5] = &row_weights;
+	a[6] = &x1; a[7] = &x3; a[8] = &W1; a[9] = &W3; a[10] = &W2; a[11] = &w1_stride_elems; a[12] = &w3_stride_elems;
+	a[13] = &w2_stride_elems; a[14] = &expert_counts; a[15] = &expert_counts_cumsum; a[16] = &dx1; a[17] = &dx3;
+	a[18] = &hs; a[19] = &dP; a[20] = &dZ;
+	if ((handle -> submit_op)(handle, &op, stream_id)) {
+		fprintf(stderr, "Error: failed to submit b200 moe experts bwd_x op...\n");
+		return -1;
+	}
+	return 0;
+}
+
+int dataflow_submit_b200_moe_experts_bwd_w(Dataflow_Handle * handle, int stream_id, DataflowDatatype dt,
+		int total_rows, int model_dim, int ffn_dim, int num_experts, void * dY_zone, void * hs, void * zone_x, void * dx1,
+		void * dx3, void * dW1, void * dW3, void * dW2, int64_t dw1_stride_elems, int64_t dw3_stride_elems,
+		int64_t dw2_stride_elems, int * expert_counts, int * expert_counts_cumsum) {
+	Op op;
+	dataflow_set_b200_moe_experts_bwd_w_skeleton(&op.op_skeleton, dt);
+	void ** a = op.op_args;
+	a[0] = &total_rows; a[1] = &model_dim; a[2] = &ffn_dim; a[3] = &num_experts; a[4] = &dY_zone; a[5] = &hs;
+	a[6] = &zone_x; a[7] = &dx1; a[8] = &dx3; a[9] = &dW1; a[10] = &dW3; a[11] = &dW2; a[12] = &dw1_stride_elems;
+	a[13] = &dw3_stride_elems; a[14] = &dw2_stride_elems; a[15] = &expert_counts; a[16] = &expert_counts_cumsum;
+	if ((handle -> submit_op)(handle, &op, stream_id)) {
+		fprintf(stderr, "Error: failed to submit b200 moe experts bwd_w op...\n");
+		return -1;
+	}
+	return 0;
+}
+
+#define B200_NUM_EXT_OPS 15
 
 /*
  * Registers the external ops above with `handle` from the shared library at `adapter_so_path` (this file's
@@ -147,6 +273,9 @@ int dataflow_register_b200_moe_ops(Dataflow_Handle * handle, char * adapter_so_p
 	dataflow_set_default_swiglu_skeleton(&sk[n], DATAFLOW_BF16); syms[n++] = "b200_ext_swiglu";
 	dataflow_set_default_swiglu_bwd_x_skeleton(&sk[n], DATAFLOW_BF16, DATAFLOW_BF16); syms[n++] = "b200_ext_swiglu_bwd_x";
 	dataflow_set_matmul_skeleton(&sk[n]); syms[n++] = "b200_ext_matmul";
+	dataflow_set_b200_moe_experts_fwd_skeleton(&sk[n], DATAFLOW_BF16); syms[n++] = "b200_ext_moe_experts_fwd";
+	dataflow_set_b200_moe_experts_bwd_x_skeleton(&sk[n], DATAFLOW_BF16); syms[n++] = "b200_ext_moe_experts_bwd_x";
+	dataflow_set_b200_moe_experts_bwd_w_skeleton(&sk[n], DATAFLOW_BF16); syms[n++] = "b200_ext_moe_experts_bwd_w";
 
 	for (int i = 0; i < n; i++) {
 		inits[i] = NULL;

@@ -138,6 +138,7 @@ struct GemmParams {
   // DENSE only: the reduction is cut into k_splits ranges of k_split_len (a multiple of 64); range i is one more
   // tile whose fp32 result goes to D + i * d_group_stride, summed afterwards by splitk_reduce_kernel
   int k_splits, k_split_len;
+  int k_hint;  // host only, GROUPED_K: average reduction length per group (rows / groups), for choosing the unit shape
 #ifdef B200_GEMM_DEBUG
   int dbg;  // timing experiments only: bit 0 = the epilogue touches no global memory, bit 1 = every load fetches the
             // same (cache-resident) boxes; results are garbage
@@ -1022,7 +1023,7 @@ static int pair_mode() {
 // Environment variable B200_GEMM_WIDE on first use; b200_gemm_set_wide_mode overrides it.
 constexpr int WIDE_GROUPED_M = 1, WIDE_GROUPED_K = 2, WIDE_DENSE = 4, WIDE_ALWAYS = 8;
 #ifndef B200_GEMM_WIDE_DEFAULT
-#define B200_GEMM_WIDE_DEFAULT WIDE_DENSE
+#define B200_GEMM_WIDE_DEFAULT (WIDE_GROUPED_K | WIDE_DENSE)
 #endif
 static int g_wide_mode = -1;
 
@@ -1126,7 +1127,9 @@ static int launch_gemm(GemmParams &p, int64_t max_tiles, cudaStream_t s, bool pa
     const int kind = p.group_mode == GROUPED_M ? WIDE_GROUPED_M : (p.group_mode == GROUPED_K ? WIDE_GROUPED_K : WIDE_DENSE);
     const int col_tiles = (p.N + (p.dual_b ? 127 : 255)) / (p.dual_b ? 128 : 256);
     const int64_t units2 = row_tiles_hint * ((col_tiles + 1) / 2);
-    const bool long_reduction = p.group_mode == GROUPED_K || (int64_t)p.K * p.k_segments >= 1024;  // else the epilogue is all
+    // the two accumulators of a wide unit finish together, so their epilogues are not hidden behind the next unit's
+    // MMAs: it pays only where the reduction is long (measured: weight gradients from about 2048 rows per expert)
+    const bool long_reduction = p.group_mode == GROUPED_K ? p.k_hint >= 2048 : (int64_t)p.K * p.k_segments >= 1024;
     if ((wide_mode() & kind) && col_tiles >= 2 && (long_reduction || (wide_mode() & WIDE_ALWAYS)) &&
         ((wide_mode() & WIDE_ALWAYS) || units2 >= 2 * (int64_t)(sm_count_cached() / 2)) &&
         gemm_smem_bytes<true, 2>(p.num_groups, false) <= GEMM_SMEM_LIMIT)
@@ -1565,6 +1568,7 @@ static int launch_wgrad(int total_rows, int Mrows, int Ncols, int num_experts, c
   p.C = dW;
   p.ldd = Ncols;
   p.d_group_stride = dw_stride;
+  p.k_hint = total_rows / num_experts;
   if (make_tmap(&p.tmA, A, 2, (uint64_t)Mrows, (uint64_t)total_rows, 1, (uint64_t)Mrows * 2, 0)) return -1;
   if (make_tmap(&p.tmB, B, 3, (uint64_t)Ncols, (uint64_t)total_rows, 1, (uint64_t)Ncols * 2,
                 (uint64_t)Ncols * 2 * (uint64_t)total_rows))

@@ -371,6 +371,41 @@ int b200_moe_block_fwd(const B200MoeBlock *block, const void *Xn, void *X_combin
 int b200_moe_block_recompute(const B200MoeBlock *block, const void *Xn, int recompute_x1_x3, void *stream);
 
 /*
+ * The reference's saved-activation levels (libdataflowmodels/include/transformer/seq_batch_structs.h:199-204), for
+ * the MoE part of a block. At every level from INP_ONLY up the routing results are kept (router logits, chosen
+ * experts, gate weights, counts, cumsum, both mappings: they sit before the "input only" cut-off of the reference's
+ * saved-activations buffer, libdataflowmodels/src/transformer/src/prep_seq_batch.c:230-283); x1 and x3 are kept only
+ * at FULL (prep_seq_batch.c:320-365); the zone and h are workspace at every level. NONE keeps nothing: no backward.
+ */
+#define B200_SAVED_ACTIVATION_LEVEL_NONE 0
+#define B200_SAVED_ACTIVATION_LEVEL_INP_ONLY 1
+#define B200_SAVED_ACTIVATION_LEVEL_INP_ATTN_ONLY 2
+#define B200_SAVED_ACTIVATION_LEVEL_FULL 3
+
+/* Bytes of the MoE part of a saved-activations buffer at `level` (0 for NONE or an unknown level): the tensors
+ * above in the reference's order, each starting on a 256-byte boundary as in prep_seq_batch.c:230-283. */
+uint64_t b200_moe_saved_activations_bytes(int total_tokens, int num_experts, int top_k, int ffn_dim, int level);
+
+/*
+ * Copies what `level` keeps out of the block's buffers into `buffer` (device memory, or pinned host memory for the
+ * host offload the reference's drivers do between forward and backward) and back. Asynchronous on `stream`, one
+ * cudaMemcpyAsync per tensor; the layout is that of b200_moe_saved_activations_bytes. -1 at level NONE.
+ */
+int b200_moe_block_save_activations(const B200MoeBlock *block, int level, void *buffer, uint64_t buffer_bytes,
+                                    void *stream);
+int b200_moe_block_restore_activations(const B200MoeBlock *block, int level, const void *buffer, uint64_t buffer_bytes,
+                                       void *stream);
+
+/*
+ * dataflow_submit_transformer_moe_block_recompute by level (dataflow_transformer.c:2989-3006, 3199-3315): at FULL the
+ * reference has nothing to recompute; here the zone is gathered and h formed again from the kept x1, x3 (the
+ * backward of this library reads both, the reference re-forms h inside its backward). Below FULL the zone, x1, x3 and
+ * h are all formed again from Xn and the kept token_mapping; the router is not re-run. NONE is an error, as in the
+ * reference ("cannot recompute with no block input").
+ */
+int b200_moe_block_recompute_level(const B200MoeBlock *block, const void *Xn, int level, void *stream);
+
+/*
  * Backward of the same: what dataflow_submit_transformer_moe_block_bwd_x (3399-3719) and
  * dataflow_submit_transformer_moe_block_bwd_w (4062-4185) compute between them. dXn [T][d] is overwritten; dWr
  * [E][d], dW1, dW3 [E][f][d], dW2 [E][d][f] (bf16) are accumulated into (beta = 1, one rounding), as the
@@ -501,6 +536,104 @@ int b200_moe_experts_bwd_x_scatter(int total_rows, int model_dim, int ffn_dim, i
                                    void *dx1, void *dx3, void *hs, float *dP, const unsigned long long *row_tags,
                                    const unsigned long long *dest_buffers, int world, int64_t rows_per_buffer,
                                    void *stream);
+
+/*
+ * ---- the expert-parallel layer as one C call per direction (no counterpart in the reference) ----
+ *
+ * Stream-ordered barrier over the ranks of one node, as a kernel: every rank stores a rising epoch number into its
+ * slot of every peer's flag array (peer_flags: host array of `world` device addresses of unsigned int[world] arrays,
+ * NVLink-mapped, zeroed once before the first barrier) and waits until all slots of its own array have reached that
+ * epoch. `epoch` is a device word of this rank (zeroed once) that the kernel advances. payload (optional): payload_ints
+ * ints that are stored into entry [rank][.] of every peer's payload array (peer_payload: int[world][payload_ints]
+ * each) before the flag is raised - the counts exchange of the layer rides on its first barrier. The wait is bounded
+ * (10 s unless b200_ep_set_barrier_timeout_ms says otherwise): a rank that never arrives raises status 1
+ * (b200_ep_status, which synchronises the device and clears the word) and the kernel returns; nothing hangs.
+ * Every rank must issue the same sequence of barriers, and the ranks must be synchronised on the host once after
+ * the flag arrays were zeroed.
+ */
+int b200_ep_barrier(const unsigned long long *peer_flags, int world, int rank, unsigned int *epoch, const int *payload,
+                    int payload_ints, const unsigned long long *peer_payload, void *stream);
+int b200_ep_set_barrier_timeout_ms(int ms);
+int b200_ep_status(int *status_out);
+
+/*
+ * Exchange plan of one rank from the gathered counts (int[world][num_experts]: row s = per-expert row counts of rank
+ * s's tokens, global expert ids), in one launch: local_counts / local_cumsum [experts_per_rank] = rows this rank
+ * receives per local expert and their inclusive prefix sums, clipped to capacity_rows; dst_base[num_experts] as the
+ * b200_ep_* kernels take it; overflow[0] is set to 1 (never cleared) when the unclipped total exceeds the capacity.
+ */
+int b200_ep_plan(const int *gathered_counts, int world, int rank, int experts_per_rank, int64_t capacity_rows,
+                 int *local_counts, int *local_cumsum, int *dst_base, int *overflow, void *stream);
+
+/* dWr[i] = bf16(f32(dWr[i]) + sum over ranks, in rank order, of partial_r[i]); peer_partials: host array of `world`
+ * device addresses of bf16 arrays of num_elements (a multiple of 8) elements; call it after a barrier. */
+int b200_ep_reduce_router_grad(const unsigned long long *peer_partials, int world, int64_t num_elements, void *dWr,
+                               void *stream);
+
+/*
+ * One rank's share of the expert-parallel layer. Rank g of `world` owns experts [g*E/world, (g+1)*E/world) with
+ * their W1 / W3 / W2 (and gradients); tokens are data-parallel (total_tokens per rank); Wr is replicated. The peer_*
+ * members are HOST arrays of `world` device addresses: entry h = the named buffer of rank h as mapped into this
+ * process (entry `rank` = this rank's own buffer, which is also given as a plain pointer). Receive-side buffers hold
+ * capacity_rows rows (1.5 * T * k is ample for balanced routing); rows that would not fit are dropped and
+ * overflow[0] is raised, nothing is overrun. R = total_tokens * top_k.
+ */
+typedef struct B200EpMoeBlock {
+  int world, rank;
+  int total_tokens, model_dim, num_experts, top_k, ffn_dim;
+  int64_t capacity_rows;
+  const void *Wr;               /* [E][d], replicated */
+  const void *W1, *W3, *W2;     /* this rank's experts: [E/world][f][d], [E/world][f][d], [E/world][d][f] */
+  int64_t w1_stride_elems, w3_stride_elems, w2_stride_elems;
+  /* token side (this rank's tokens, all E experts) */
+  float *logits;                /* [T][E] */
+  float *token_expert_weights;  /* [T][k] */
+  uint16_t *chosen_experts;     /* [T][k] */
+  int *expert_counts;           /* [E + 1] */
+  int *expert_counts_cumsum;    /* [E] */
+  int *expert_mapping, *token_mapping; /* [R] each */
+  void *mapping_workspace;
+  size_t mapping_workspace_bytes;
+  void *matmul_workspace;       /* optional */
+  size_t matmul_workspace_bytes;
+  void *dX_routed;              /* bf16 [T][E] (backward) */
+  /* exchange plan */
+  int *gathered_counts;         /* int [world][E], this rank's copy of peer_counts */
+  int *local_counts, *local_cumsum; /* [E/world] */
+  int *dst_base;                /* [E] */
+  int *overflow;                /* [1], zeroed by the caller */
+  unsigned int *barrier_epoch;  /* [1], zeroed once */
+  const unsigned long long *peer_flags;  /* unsigned int [world] per rank, zeroed once */
+  const unsigned long long *peer_counts; /* = gathered_counts of every rank */
+  /* expert side: rows received from every rank, expert-contiguous */
+  void *zone_recv;              /* bf16 [capacity][d] */
+  unsigned long long *tags_recv; /* [capacity] */
+  void *x1, *x3, *h;            /* bf16 [capacity][f] */
+  const unsigned long long *peer_zone, *peer_tags;
+  /* home side: expert outputs of this rank's routed pairs, in its own zone order */
+  void *Y_home;                 /* bf16 [R][d] */
+  const unsigned long long *peer_Y_home;
+  /* backward (may be NULL for forward-only use) */
+  void *dY_recv;                /* bf16 [capacity][d] */
+  float *dP_recv;               /* [capacity] */
+  void *dx1, *dx3;              /* bf16 [capacity][f] */
+  const float *ones;            /* [capacity] of 1.0f */
+  void *dZ_home;                /* bf16 [R][d] */
+  void *dWr_partial;            /* bf16 [E][d] */
+  const unsigned long long *peer_dY, *peer_dP, *peer_dZ_home, *peer_dWr;
+} B200EpMoeBlock;
+
+/*
+ * Forward: route locally, counts to every rank on the first barrier, plan, rows and row tags into the owners'
+ * buffers (peer stores), barrier, this rank's experts over everything it received with the W2 GEMM's epilogue storing
+ * each Y row straight into its home rank's buffer, barrier, local weighted combine onto X_combined. 13 launches, three
+ * of them barriers; no host synchronisation, no collective library. Backward mirrors it and ends with the sum of
+ * the router weight gradient over the ranks; dXn is overwritten, dWr / dW1 / dW3 / dW2 are accumulated into (dW*
+ * cover this rank's experts and may be NULL).
+ */
+int b200_ep_moe_block_fwd(const B200EpMoeBlock *block, const void *Xn, void *X_combined, void *stream);
+int b200_ep_moe_block_bwd(const B200EpMoeBlock *block, const void *Xn, const void *dOut, void *dXn, void *dWr, void *dW1,
+                          void *dW3, void *dW2, void *stream);
 
 #ifdef __cplusplus
 }

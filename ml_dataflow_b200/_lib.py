@@ -48,10 +48,21 @@ SIGNATURES = {
     "b200_moe_block_fwd": (_i, [_vp, _vp, _vp, _vp]),
     "b200_moe_block_recompute": (_i, [_vp, _vp, _i, _vp]),
     "b200_moe_block_bwd": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "b200_moe_saved_activations_bytes": (_u64, [_i, _i, _i, _i, _i]),
+    "b200_moe_block_save_activations": (_i, [_vp, _i, _vp, _u64, _vp]),
+    "b200_moe_block_restore_activations": (_i, [_vp, _i, _vp, _u64, _vp]),
+    "b200_moe_block_recompute_level": (_i, [_vp, _vp, _i, _vp]),
     "b200_parse_model_config": (_i, [C.c_char_p, _vp]),
     "b200_moe_layer_file_layout": (_i, [_vp, _i, _vp]),
     "b200_read_layer_file": (_i, [C.c_char_p, _vp, _u64]),
     "b200_moe_block_bind_weights": (_i, [_vp, _vp, _vp, _vp]),
+    "b200_ep_barrier": (_i, [_vp, _i, _i, _vp, _vp, _i, _vp, _vp]),
+    "b200_ep_set_barrier_timeout_ms": (_i, [_i]),
+    "b200_ep_status": (_i, [_vp]),
+    "b200_ep_plan": (_i, [_vp, _i, _i, _i, _i64, _vp, _vp, _vp, _vp, _vp]),
+    "b200_ep_reduce_router_grad": (_i, [_vp, _i, _i64, _vp, _vp]),
+    "b200_ep_moe_block_fwd": (_i, [_vp, _vp, _vp, _vp]),
+    "b200_ep_moe_block_bwd": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "b200_scatter_row_weights": (_i, [_i, _i, _vp, _vp, _vp, _vp]),
     "b200_gather_router_grad": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp]),
 }
@@ -71,6 +82,30 @@ class MoeBlock(C.Structure):
         ("matmul_workspace", _vp), ("matmul_workspace_bytes", _sz),
         ("dY_zone", _vp), ("row_weights", _vp), ("dP", _vp), ("dx1", _vp), ("dx3", _vp), ("dZ", _vp),
         ("dX_routed", _vp),
+    ]
+
+
+class EpMoeBlock(C.Structure):
+    """ctypes mirror of B200EpMoeBlock in include/b200_moe.h (same field order)."""
+    _fields_ = [
+        ("world", _i), ("rank", _i),
+        ("total_tokens", _i), ("model_dim", _i), ("num_experts", _i), ("top_k", _i), ("ffn_dim", _i),
+        ("capacity_rows", _i64),
+        ("Wr", _vp), ("W1", _vp), ("W3", _vp), ("W2", _vp),
+        ("w1_stride_elems", _i64), ("w3_stride_elems", _i64), ("w2_stride_elems", _i64),
+        ("logits", _vp), ("token_expert_weights", _vp), ("chosen_experts", _vp), ("expert_counts", _vp),
+        ("expert_counts_cumsum", _vp), ("expert_mapping", _vp), ("token_mapping", _vp),
+        ("mapping_workspace", _vp), ("mapping_workspace_bytes", _sz),
+        ("matmul_workspace", _vp), ("matmul_workspace_bytes", _sz),
+        ("dX_routed", _vp),
+        ("gathered_counts", _vp), ("local_counts", _vp), ("local_cumsum", _vp), ("dst_base", _vp), ("overflow", _vp),
+        ("barrier_epoch", _vp), ("peer_flags", _vp), ("peer_counts", _vp),
+        ("zone_recv", _vp), ("tags_recv", _vp), ("x1", _vp), ("x3", _vp), ("h", _vp),
+        ("peer_zone", _vp), ("peer_tags", _vp),
+        ("Y_home", _vp), ("peer_Y_home", _vp),
+        ("dY_recv", _vp), ("dP_recv", _vp), ("dx1", _vp), ("dx3", _vp), ("ones", _vp), ("dZ_home", _vp),
+        ("dWr_partial", _vp),
+        ("peer_dY", _vp), ("peer_dP", _vp), ("peer_dZ_home", _vp), ("peer_dWr", _vp),
     ]
 
 

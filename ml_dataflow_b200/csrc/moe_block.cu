@@ -106,3 +106,111 @@ extern "C" int b200_moe_block_bwd(const B200MoeBlock *b, const void *Xn, const v
   return b200_matmul(B200_DT_BF16, B200_DT_BF16, B200_DT_BF16, B200_DT_BF16, 0, 1, d, T, E, 1.0f, 1.0f, Xn,
                      b->dX_routed, dWr, dWr, b->matmul_workspace_bytes, b->matmul_workspace, stream);
 }
+
+// ---------------------------------------------------------------------------------------------------------------
+// Saved-activation contract of the MoE part (libdataflowmodels/include/transformer/seq_batch_structs.h:199-286).
+// What the reference keeps per level: the routing results (x_routed, chosen_experts, token_expert_weights,
+// expert_counts, expert_counts_cumsum, expert_mapping, token_mapping) at every level that can run a backward - they
+// sit before `inp_only_cutoff` in its saved-activations buffer (prep_seq_batch.c:230-283) - and x_1, x_3 only at
+// SAVED_ACTIVATION_LEVEL_FULL (prep_seq_batch.c:320-365). The zone and h are workspace at every level. The layout
+// below is the reference's: that order, each tensor starting on a 256-byte boundary.
+// ---------------------------------------------------------------------------------------------------------------
+
+namespace {
+
+struct SavedPiece {
+  void *dev;       // where the tensor lives in the block
+  uint64_t bytes;
+  uint64_t offset;  // in the saved-activations buffer
+};
+
+// fills `pieces` (at most 9) and returns how many; *total = bytes of the buffer
+int saved_pieces(const B200MoeBlock *b, int level, SavedPiece *pieces, uint64_t *total) {
+  const uint64_t T = (uint64_t)b->total_tokens, E = (uint64_t)b->num_experts, k = (uint64_t)b->top_k,
+                 f = (uint64_t)b->ffn_dim;
+  const uint64_t R = T * k;
+  int n = 0;
+  uint64_t at = 0;
+  auto add = [&](void *p, uint64_t bytes) {
+    at = (at + 255) & ~255ull;
+    pieces[n].dev = p;
+    pieces[n].bytes = bytes;
+    pieces[n].offset = at;
+    at += bytes;
+    n++;
+  };
+  add(b->logits, T * E * sizeof(float));
+  add(b->chosen_experts, R * sizeof(uint16_t));
+  add(b->token_expert_weights, R * sizeof(float));
+  add(b->expert_counts, (E + 1) * sizeof(int));
+  add(b->expert_counts_cumsum, E * sizeof(int));
+  add(b->expert_mapping, R * sizeof(int));
+  add(b->token_mapping, R * sizeof(int));
+  if (level == B200_SAVED_ACTIVATION_LEVEL_FULL) {
+    add(b->x1, R * f * 2);
+    add(b->x3, R * f * 2);
+  }
+  *total = at;
+  return n;
+}
+
+int check_level(const char *op, int level) {
+  B200_REQUIRE(level >= B200_SAVED_ACTIVATION_LEVEL_NONE && level <= B200_SAVED_ACTIVATION_LEVEL_FULL,
+               "%s: unknown saved-activation level %d", op, level);
+  B200_REQUIRE(level != B200_SAVED_ACTIVATION_LEVEL_NONE, "%s: nothing is saved at level NONE, no backward can follow", op);
+  return 0;
+}
+
+}  // namespace
+
+extern "C" uint64_t b200_moe_saved_activations_bytes(int total_tokens, int num_experts, int top_k, int ffn_dim,
+                                                     int level) {
+  if (level <= B200_SAVED_ACTIVATION_LEVEL_NONE || level > B200_SAVED_ACTIVATION_LEVEL_FULL) return 0;
+  B200MoeBlock b;
+  memset(&b, 0, sizeof(b));
+  b.total_tokens = total_tokens;
+  b.num_experts = num_experts;
+  b.top_k = top_k;
+  b.ffn_dim = ffn_dim;
+  SavedPiece pieces[9];
+  uint64_t total = 0;
+  saved_pieces(&b, level, pieces, &total);
+  return total;
+}
+
+static int copy_saved(const char *op, const B200MoeBlock *b, int level, void *buffer, uint64_t buffer_bytes, bool save,
+                      void *stream) {
+  if (check_block(op, b) || check_level(op, level)) return -1;
+  B200_REQUIRE(buffer != nullptr, "%s: null buffer", op);
+  SavedPiece pieces[9];
+  uint64_t total = 0;
+  const int n = saved_pieces(b, level, pieces, &total);
+  B200_REQUIRE(buffer_bytes >= total, "%s: the buffer holds %llu bytes, level %d needs %llu", op,
+               (unsigned long long)buffer_bytes, level, (unsigned long long)total);
+  unsigned char *base = static_cast<unsigned char *>(buffer);
+  for (int i = 0; i < n; i++) {
+    if (pieces[i].bytes == 0) continue;
+    // the buffer may be device memory or pinned host memory: the copy kind is taken from the pointers
+    if (save)
+      B200_CUDA(cudaMemcpyAsync(base + pieces[i].offset, pieces[i].dev, pieces[i].bytes, cudaMemcpyDefault, (cudaStream_t)stream));
+    else
+      B200_CUDA(cudaMemcpyAsync(pieces[i].dev, base + pieces[i].offset, pieces[i].bytes, cudaMemcpyDefault, (cudaStream_t)stream));
+  }
+  return 0;
+}
+
+extern "C" int b200_moe_block_save_activations(const B200MoeBlock *block, int level, void *buffer, uint64_t buffer_bytes,
+                                               void *stream) {
+  return copy_saved("moe_block_save_activations", block, level, buffer, buffer_bytes, true, stream);
+}
+
+extern "C" int b200_moe_block_restore_activations(const B200MoeBlock *block, int level, const void *buffer,
+                                                  uint64_t buffer_bytes, void *stream) {
+  return copy_saved("moe_block_restore_activations", block, level, const_cast<void *>(buffer), buffer_bytes, false, stream);
+}
+
+extern "C" int b200_moe_block_recompute_level(const B200MoeBlock *block, const void *Xn, int level, void *stream) {
+  if (check_level("moe_block_recompute_level", level)) return -1;
+  // FULL: x1 and x3 were kept, only the zone and h are formed again; below FULL they come back from the zone too
+  return b200_moe_block_recompute(block, Xn, level == B200_SAVED_ACTIVATION_LEVEL_FULL ? 0 : 1, stream);
+}

@@ -203,11 +203,78 @@ class ExpertParallelMoELayer:
             self.side_group = dist.new_group()  # its own communicator: side-stream barriers never queue behind main's
             self._flag_side = torch.zeros(1, dtype=torch.int32, device=self.dev)
 
+    def c_block(self, Wr, W1, W3, W2):
+        """Fills a `B200EpMoeBlock` for b200_ep_moe_block_fwd / _bwd over this layer's buffers ("fused" transport
+        only): the same step with the barriers, the counts exchange, the plan and the router-gradient sum done by
+        the library's own kernels over peer memory instead of torch.distributed. Collective: every rank calls it."""
+        import ctypes as C
+
+        from . import _lib
+
+        if self.transport != "fused":
+            raise ValueError("the C block runs on the buffers of the 'fused' transport")
+        if not hasattr(self, "_c_shared"):
+            import torch.distributed._symmetric_memory as symm_mem
+
+            def shared(name, shape, dt):
+                t = symm_mem.empty(shape, dtype=dt, device=self.dev)
+                t.zero_()
+                hdl = symm_mem.rendezvous(t, self.dist.group.WORLD)
+                self.peers[name] = [int(p) for p in hdl.buffer_ptrs]
+                self._handles.append(hdl)
+                return t
+
+            G = self.x.world
+            self._c_shared = dict(flags=shared("flags", (max(G, 4),), torch.int32),
+                                  gathered=shared("gathered", (G, self.E), torch.int32),
+                                  dWr_part=shared("dWr_part", (self.E, self.d), torch.bfloat16))
+            self._c_local = dict(
+                local_counts=torch.zeros(self.E_loc, dtype=torch.int32, device=self.dev),
+                local_cumsum=torch.zeros(self.E_loc, dtype=torch.int32, device=self.dev),
+                dst_base=torch.zeros(self.E, dtype=torch.int32, device=self.dev),
+                overflow=torch.zeros(1, dtype=torch.int32, device=self.dev),
+                epoch=torch.zeros(1, dtype=torch.int32, device=self.dev))
+            torch.cuda.synchronize(self.dev)
+            self.dist.barrier()  # every rank's flag array is zero before the first barrier kernel runs
+        hm, sh, lo = self.home, self._c_shared, self._c_local
+        ptr = lambda t: t.data_ptr()
+        self._c_tables = {n: (C.c_ulonglong * len(v))(*v) for n, v in self.peers.items()}
+        tab = lambda n: C.cast(self._c_tables[n], C.c_void_p)
+        b = _lib.EpMoeBlock()
+        b.world, b.rank = self.x.world, self.x.rank
+        b.total_tokens, b.model_dim, b.num_experts, b.top_k, b.ffn_dim = self.T, self.d, self.E, self.k, self.f
+        b.capacity_rows = self.cap
+        b.Wr, b.W1, b.W3, b.W2 = ptr(Wr), ptr(W1), ptr(W3), ptr(W2)
+        b.w1_stride_elems = b.w3_stride_elems = self.f * self.d
+        b.w2_stride_elems = self.d * self.f
+        b.logits, b.token_expert_weights, b.chosen_experts = ptr(hm.logits), ptr(hm.weights), ptr(hm.chosen)
+        b.expert_counts, b.expert_counts_cumsum = ptr(hm.counts), ptr(hm.cumsum)
+        b.expert_mapping, b.token_mapping = ptr(hm.expert_mapping), ptr(hm.token_mapping)
+        b.mapping_workspace, b.mapping_workspace_bytes = ptr(hm.map_ws), hm.map_ws.numel()
+        b.matmul_workspace, b.matmul_workspace_bytes = ptr(hm.mm_ws), hm.mm_ws.numel()
+        b.dX_routed = ptr(hm.dX_routed)
+        b.gathered_counts = ptr(sh["gathered"])
+        b.local_counts, b.local_cumsum, b.dst_base = ptr(lo["local_counts"]), ptr(lo["local_cumsum"]), ptr(lo["dst_base"])
+        b.overflow, b.barrier_epoch = ptr(lo["overflow"]), ptr(lo["epoch"])
+        b.peer_flags, b.peer_counts = tab("flags"), tab("gathered")
+        b.zone_recv, b.tags_recv = ptr(self.zone_r), ptr(self.tags_r)
+        b.x1, b.x3, b.h = ptr(self.x1), ptr(self.x3), ptr(self.h)
+        b.peer_zone, b.peer_tags = tab("zone"), tab("tags")
+        b.Y_home, b.peer_Y_home = ptr(self.Y_h), tab("Yh")
+        b.dY_recv, b.dP_recv, b.dx1, b.dx3, b.ones = ptr(self.dY_r), ptr(self.dP_r), ptr(self.dx1), ptr(self.dx3), ptr(self.ones)
+        b.dZ_home, b.dWr_partial = ptr(self.dZ_h), ptr(sh["dWr_part"])
+        b.peer_dY, b.peer_dP, b.peer_dZ_home, b.peer_dWr = tab("dY"), tab("dP"), tab("dZh"), tab("dWr_part")
+        return b
+
     def check(self):
         """Synchronises and raises if a step received more rows than the buffers hold (the extra rows were dropped,
         never written out of bounds) or if a GEMM kernel gave up a bounded wait."""
         from . import ops
 
+        if hasattr(self, "_c_local") and int(self._c_local["overflow"].item()):
+            raise RuntimeError(f"expert-parallel receive buffer too small (capacity {self.cap} rows): rows were dropped")
+        if hasattr(self, "_c_local") and ops.ep_status():
+            raise RuntimeError("a barrier kernel of the expert-parallel layer ran out of time")
         if bool(self.overflowed.item()):
             raise RuntimeError(f"expert-parallel receive buffer too small (capacity {self.cap} rows): rows were dropped")
         st = ops.gemm_status()

@@ -277,3 +277,22 @@ def moe_block_recompute(block, Xn, recompute_x1_x3):
     """Re-forms zone and h (and x1, x3 when asked) after the forward's workspace has been reused."""
     _check(_lib.load().b200_moe_block_recompute(C.byref(block), _p(Xn), int(bool(recompute_x1_x3)), _stream()),
            "moe_block_recompute", 2)
+
+
+def ep_moe_block_fwd(block, Xn, X_combined):
+    """block: a filled `_lib.EpMoeBlock` (see ExpertParallelMoELayer.c_block). The whole expert-parallel forward of
+    this rank in one C call: 13 launches, three of them barrier kernels."""
+    _check(_lib.load().b200_ep_moe_block_fwd(C.byref(block), _p(Xn), _p(X_combined), _stream()), "ep_moe_block_fwd", 13)
+
+
+def ep_moe_block_bwd(block, Xn, dOut, dXn, dWr, dW1, dW3, dW2):
+    _check(_lib.load().b200_ep_moe_block_bwd(C.byref(block), _p(Xn), _p(dOut), _p(dXn), _p(dWr), _p(dW1), _p(dW3),
+                                             _p(dW2), _stream()), "ep_moe_block_bwd",
+           14 + sum(g is not None for g in (dW1, dW3, dW2)))
+
+
+def ep_status():
+    """Synchronises; returns (and clears) the status word of the barrier kernels: 1 = a wait ran out of time."""
+    v = C.c_int(0)
+    _check(_lib.load().b200_ep_status(C.byref(v)), "b200_ep_status", 0)
+    return v.value

@@ -33,8 +33,11 @@ def check_expert_parallel(dist, rank, world, transport, num_experts=8):
         batches.append((rand_bf16(rng, (T, d)), rand_bf16(rng, (T, d))))
     X, dOut = batches[rank]
     sl = slice(rank * El, (rank + 1) * El)
+    # "c": the buffers of the fused transport driven by b200_ep_moe_block_fwd / _bwd (barriers, counts exchange, plan
+    # and router-gradient sum by the library's own kernels, no torch.distributed call inside the step)
+    c_driver = transport == "c"
     layer = ExpertParallelMoELayer(T, d, E, k, f, dist, device=torch.device("cuda", torch.cuda.current_device()),
-                                   transport=transport)
+                                   transport="fused" if c_driver else transport)
     out = torch.zeros((T, d), dtype=torch.bfloat16, device="cuda")
     dXn = torch.empty_like(out)
     dWr = torch.zeros((E, d), dtype=torch.bfloat16, device="cuda")
@@ -45,8 +48,13 @@ def check_expert_parallel(dist, rank, world, transport, num_experts=8):
     for _ in range(2):  # the second pass reuses every buffer, local and remote
         for t_ in (out, dWr, dW1, dW3, dW2):
             t_.zero_()
-        layer.forward(Xd, Wrd, W1d, W3d, W2d, out)
-        layer.backward(Xd, Wrd, W1d, W3d, W2d, dOd, dXn, dWr, dW1, dW3, dW2)
+        if c_driver:
+            blk = layer.c_block(Wrd, W1d, W3d, W2d)
+            ops.ep_moe_block_fwd(blk, Xd, out)
+            ops.ep_moe_block_bwd(blk, Xd, dOd, dXn, dWr, dW1, dW3, dW2)
+        else:
+            layer.forward(Xd, Wrd, W1d, W3d, W2d, out)
+            layer.backward(Xd, Wrd, W1d, W3d, W2d, dOd, dXn, dWr, dW1, dW3, dW2)
     layer.check()  # no GEMM wait gave up, no receive buffer overflowed
 
     # oracle: every rank's batch through the single-GPU layer; this rank's logits come from its own GPU run
@@ -62,7 +70,8 @@ def check_expert_parallel(dist, rank, world, transport, num_experts=8):
         total_counts += fwd["counts"][:E]
         if r == rank:
             mine = (fwd, bwd["dXn"].copy())
-    np.testing.assert_array_equal(layer.x.local_counts.cpu().numpy(), total_counts[sl])
+    local_counts = layer._c_local["local_counts"] if c_driver else layer.x.local_counts
+    np.testing.assert_array_equal(local_counts.cpu().numpy(), total_counts[sl])
     np.testing.assert_array_equal(layer.home.token_mapping.cpu().numpy(), mine[0]["token_mapping"])
     assert_chain_close(f32(host_bits(out)), f32(mine[0]["out"]), what="out")
     assert_close(f32(host_bits(out)), f32(mine[0]["out"]), rtol=2e-2, atol=4e-3, what="out")

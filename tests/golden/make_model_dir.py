@@ -3,8 +3,8 @@
 
     python tests/golden/make_model_dir.py <path of the reference checkout>     (or set REFERENCE_ROOT)
 
-One layer, model_dim 64, 1 query / 1 kv head of 32, 4 routed experts of dim 32, top-2, bf16, no vocabulary (so no
-embedding or head files), seed 7: about 60 KB.
+One layer, model_dim 64, 1 query / 1 kv head of 32, 8 routed experts of dim 32, top-2, bf16, no vocabulary (so no
+embedding or head files), seed 7: about 110 KB.
 """
 import json
 import os
@@ -15,7 +15,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CONFIG = {
     "embed_dtype": "bf16", "attn_dtype": "bf16", "router_dtype": "bf16", "expert_dtype": "bf16", "head_dtype": "bf16",
     "vocab_size": 0, "model_dim": 64, "head_dim": 32, "n_layers": 1, "n_heads": 1, "n_kv_heads": 1,
-    "qk_norm_type": "none", "qk_norm_weight_type": "none", "num_shared_experts": 0, "num_routed_experts": 4,
+    "qk_norm_type": "none", "qk_norm_weight_type": "none", "num_shared_experts": 0, "num_routed_experts": 8,
     "top_k_routed_experts": 2, "expert_dim": 32, "expert_mlp_type": "swiglu", "rope_theta": 10000,
     "rms_norm_epsilon": 1e-5, "rand_seed": 7,
 }

@@ -98,7 +98,7 @@ def test_receive_buffer_overflow_is_reported_not_overrun(tmp_path):
     assert sorted(os.listdir(tmp_path)) == ["ok0", "ok1"]
 
 
-@pytest.mark.parametrize("transport", ["fused", "p2p", "nccl"])
+@pytest.mark.parametrize("transport", ["fused", "p2p", "nccl", "c"])
 def test_expert_parallel_two_ranks(tmp_path, transport):
     if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")

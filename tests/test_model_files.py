@@ -52,7 +52,7 @@ def test_config_txt_is_parsed_field_for_field():
     assert (cfg.embed_dtype, cfg.attn_dtype, cfg.router_dtype, cfg.expert_dtype, cfg.head_dtype) == (b"bf16",) * 5
     assert (cfg.vocab_size, cfg.num_layers, cfg.model_dim, cfg.head_dim, cfg.num_q_heads, cfg.num_kv_heads) == (0, 1, 64, 32, 1, 1)
     assert (cfg.qk_norm_type, cfg.qk_norm_weight_type, cfg.expert_mlp_type) == (b"none", b"none", b"swiglu")
-    assert (cfg.num_shared_experts, cfg.num_routed_experts, cfg.top_k_routed_experts, cfg.expert_dim) == (0, 4, 2, 32)
+    assert (cfg.num_shared_experts, cfg.num_routed_experts, cfg.top_k_routed_experts, cfg.expert_dim) == (0, 8, 2, 32)
     assert cfg.rope_theta == 10000 and abs(cfg.rms_norm_epsilon - 1e-5) < 1e-9
 
 
@@ -78,7 +78,7 @@ def test_layout_follows_the_writer_order_and_the_alignment_rule(alignment):
         assert lay.w1_first + e * lay.expert_stride_bytes == off[f"w1_{e}"]
         assert lay.w3_first + e * lay.expert_stride_bytes == off[f"w3_{e}"]
         assert lay.w2_first + e * lay.expert_stride_bytes == off[f"w2_{e}"]
-    assert lay.aligned_bytes == total and lay.num_experts_in_file == 4 and lay.first_routed_expert == 0
+    assert lay.aligned_bytes == total and lay.num_experts_in_file == 8 and lay.first_routed_expert == 0
     assert lay.raw_bytes == os.path.getsize(LAYER0)
     if alignment in (0, 16):  # every tensor of this model is a multiple of 16 bytes: the file is the laid-out block
         assert lay.aligned_bytes == os.path.getsize(LAYER0)
@@ -99,7 +99,7 @@ def test_file_is_read_whole_and_weights_are_bound():
     assert lib.b200_read_layer_file(LAYER0.encode(), C.c_void_p(base), lay.aligned_bytes + 2) == -1
     blk = L.MoeBlock()
     assert lib.b200_moe_block_bind_weights(C.byref(blk), C.byref(cfg), C.byref(lay), C.c_void_p(base)) == 0
-    assert (blk.model_dim, blk.num_experts, blk.top_k, blk.ffn_dim) == (64, 4, 2, 32)
+    assert (blk.model_dim, blk.num_experts, blk.top_k, blk.ffn_dim) == (64, 8, 2, 32)
     assert blk.Wr == base + lay.router and blk.W1 == base + lay.w1_first and blk.W3 == base + lay.w3_first
     assert blk.W2 == base + lay.w2_first
     assert blk.w1_stride_elems == blk.w3_stride_elems == blk.w2_stride_elems == 3 * 32 * 64

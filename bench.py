@@ -365,8 +365,10 @@ def run_gpu_arm(args, world):
     else:
         from ml_dataflow_b200.ep import ExpertParallelMoELayer
 
-        transport = os.environ.get("B200_EP_TRANSPORT", "fused")
-        layer = ExpertParallelMoELayer(T, d, E, k, f, dist, device=dev, transport=transport,
+        # "c" (default): the buffers of the "fused" transport driven by b200_ep_moe_block_fwd / _bwd, one C call per
+        # direction with the library's own barrier / plan kernels; the other names run the Python driver in ep.py
+        transport = os.environ.get("B200_EP_TRANSPORT", "c")
+        layer = ExpertParallelMoELayer(T, d, E, k, f, dist, device=dev, transport="fused" if transport == "c" else transport,
                                        slices=int(os.environ.get("B200_EP_SLICES", "1")))
         E_loc = E // world
     W1, W3, W2 = normal((E_loc, f, d), 0.02), normal((E_loc, f, d), 0.02), normal((E_loc, d, f), 0.02)
@@ -376,6 +378,7 @@ def run_gpu_arm(args, world):
     dW1, dW3, dW2 = torch.zeros_like(W1), torch.zeros_like(W3), torch.zeros_like(W2)
 
     block = layer.block(Wr, W1, W3, W2) if world == 1 else None
+    ep_block = layer.c_block(Wr, W1, W3, W2) if transport == "c" else None
 
     def step(Xs, dOs, outs, dXs):
         outs.zero_()
@@ -383,6 +386,9 @@ def run_gpu_arm(args, world):
             # one C call per direction (b200_moe_block_fwd / _bwd): the call a C host makes
             ops.moe_block_fwd(block, Xs, outs)
             ops.moe_block_bwd(block, Xs, dOs, dXs, dWr, dW1, dW3, dW2)
+        elif ep_block is not None and layer.profile is None:
+            ops.ep_moe_block_fwd(ep_block, Xs, outs)
+            ops.ep_moe_block_bwd(ep_block, Xs, dOs, dXs, dWr, dW1, dW3, dW2)
         else:
             # the same op sequence issued from Python, with events between the ops when profiling
             layer.forward(Xs, Wr, W1, W3, W2, outs)
@@ -546,7 +552,7 @@ def run_gpu_arm(args, world):
         for name, amount in exchange_work(cfg, world).items():
             if name in raw_ms:
                 ms = raw_ms[name]
-                if transport == "fused" and name.startswith("return"):
+                if transport in ("fused", "c") and name.startswith("return"):
                     # the rows went home inside the GEMM epilogues; what is left of this phase is the barrier
                     kernels[name] = dict(ms=round(ms, 4), bound="barrier (rows are stored by the GEMM epilogue)")
                     continue
@@ -568,7 +574,7 @@ def run_gpu_arm(args, world):
 
     # ---------------- after the timed regions: the target shape / the same-batch base on one GPU, EP parity
     extra = {}
-    del layer, block
+    del layer, block, ep_block
     torch.cuda.empty_cache()
     if world == 1 and args.tokens <= 0:
         # the target shape (T=32768 on one GPU) beside the headline configuration

@@ -635,6 +635,85 @@ int b200_ep_moe_block_fwd(const B200EpMoeBlock *block, const void *Xn, void *X_c
 int b200_ep_moe_block_bwd(const B200EpMoeBlock *block, const void *Xn, const void *dOut, void *dXn, void *dWr, void *dW1,
                           void *dW3, void *dW2, void *stream);
 
+/*
+ * ---- the bandwidth-bound ops of the block around the MoE feed-forward, and of the head ----------------------------
+ *
+ * bf16 tensors, fp32 arithmetic; any other datatype code returns -1. Argument order and meaning follow the
+ * reference's submitters minus the handle (the stream replaces stream_id); every tensor must be 16-byte aligned and
+ * n_cols / embed_dim / head_dim multiples of 8. The reference builds its kernels with --use_fast_math
+ * (backends/nvidia/src/ops/Makefile:19-21); these use full-precision expf / powf / sincosf / division, so results
+ * agree with the reference's to bf16 rounding, not bit for bit.
+ */
+
+/* dataflow_submit_default_rms_norm (libdataflowops/include/dataflow_ops.h:151-154; kernel norm/rms_norm.cu:226-340):
+ * out = bf16(x * r * w) per row, r = rsqrt(mean(x^2) + eps); r is kept in rms_vals[row] unless rms_vals is NULL. */
+int b200_rms_norm(int fwd_dt, int n_rows, int n_cols, float eps, const void *rms_weight, const void *X, void *out,
+                  float *rms_vals, void *stream);
+
+/* dataflow_submit_default_rms_norm_recompute (dataflow_ops.h:157-160; norm/rms_norm_recompute.cu:63-133): the same
+ * output from the kept rms_vals. */
+int b200_rms_norm_recompute(int fwd_dt, int n_rows, int n_cols, const void *rms_weight, const float *rms_vals, const void *X,
+                            void *out, void *stream);
+
+/* dataflow_submit_default_rms_norm_bwd_x (dataflow_ops.h:165-169; norm/rms_norm_bwd_x.cu:241-394): ACCUMULATES into dX:
+ * dX = bf16(f32(dX) + r * (up * w - (C / n) * x * r)), C = sum over the row of (x r w) * up; X_out, when not NULL,
+ * receives the recomputed forward output. n_cols up to 8192. eps is unused (as in the reference). */
+int b200_rms_norm_bwd_x(int fwd_dt, int bwd_dt, int n_rows, int n_cols, float eps, const float *fwd_rms_vals,
+                        const void *rms_weight, const void *X_inp, const void *upstream_dX, void *dX, void *X_out,
+                        void *stream);
+
+/* dataflow_submit_default_rms_norm_bwd_w (dataflow_ops.h:172-176; norm/rms_norm_bwd_w.cu:225-325 and
+ * rms_norm_bwd_w_combine.cu:200-294): dW[c] = bf16(f32(dW[c]) + sum over rows of up * x * r). Two launches: fp32
+ * partial sums of row slices in the workspace, then their sum in slice order (deterministic). The workspace decides
+ * how many slices run: b200_rms_norm_bwd_w_workspace_bytes gives the size that fills the GPU (2 slices per SM); a
+ * smaller one works with fewer slices, less than one fp32 row of n_cols is an error. */
+uint64_t b200_rms_norm_bwd_w_workspace_bytes(int n_rows, int n_cols);
+int b200_rms_norm_bwd_w(int fwd_dt, int bwd_dt, int n_rows, int n_cols, float eps, const float *fwd_rms_vals,
+                        const void *X_inp, const void *upstream_dX, void *dW, uint64_t workspace_bytes, void *workspace,
+                        void *stream);
+
+/* dataflow_submit_default_rope / _rope_bwd_x (dataflow_ops.h:195-203; attention_misc/rope.cu:152-256,
+ * rope_bwd_x.cu:146-248): in place on the interleaved pairs (2i, 2i+1) of every head of X_q [num_tokens][model_dim]
+ * and X_k [num_tokens][num_kv_heads * head_dim] (X_k may be NULL); angle = seq_positions[token] * theta^(-2i/head_dim);
+ * the backward applies the inverse rotation. head_dim up to 256. */
+int b200_rope(int fwd_dt, int num_tokens, int model_dim, int head_dim, int num_kv_heads, int theta, const int *seq_positions,
+              void *X_q, void *X_k, void *stream);
+int b200_rope_bwd_x(int bwd_dt, int num_tokens, int model_dim, int head_dim, int num_kv_heads, int theta,
+                    const int *seq_positions, void *dX_q, void *dX_k, void *stream);
+
+/* dataflow_submit_default_softmax (dataflow_ops.h:298-301; loss_misc/softmax.cu:249-394): row-wise softmax,
+ * out = bf16(exp(x - max) / sum); X and out may be the same buffer. */
+int b200_softmax(int fwd_dt, int bwd_dt, int n_rows, int n_cols, const void *X, void *out, void *stream);
+
+/* dataflow_submit_default_cross_entropy_loss (dataflow_ops.h:303-306; loss_misc/cross_entropy.cu:48-68): pred_logits
+ * holds the softmax OUTPUT; loss_vec[row] = -log(p[row][label]) and p[row][label] -= 1 in place, which leaves the
+ * gradient of the summed loss with respect to the logits in the buffer. loss_vec has n_rows + 1 entries. */
+int b200_cross_entropy_loss(int bwd_dt, int n_rows, int n_cols, void *pred_logits, const uint32_t *labels, float *loss_vec,
+                            void *stream);
+
+/* dataflow_submit_default_set_average_loss (dataflow_ops.h:308; cross_entropy.cu:70-119):
+ * loss_vec[n_tokens] = mean(loss_vec[0 .. n_tokens)). */
+int b200_set_average_loss(int n_tokens, float *loss_vec, void *stream);
+
+/* dataflow_submit_default_adamw_step (dataflow_ops.h:310-315; optimizer/adamw_step.cu:6-65): m = b1 m + (1-b1) g;
+ * v = b2 v + (1-b2) g^2; p -= lr * ((m / (1-b1^t)) / (sqrt(v / (1-b2^t)) + eps) + wd * p); all four tensors bf16,
+ * updated in place with one rounding each; step_num counts from 1. */
+int b200_adamw_step(int param_dt, int grad_dt, int mean_dt, int var_dt, uint64_t num_els, int step_num, float lr, float beta1,
+                    float beta2, float weight_decay, float epsilon, void *param, const void *grad, void *mean, void *var,
+                    void *stream);
+
+/* dataflow_submit_default_embedding_table / _bwd_w (dataflow_ops.h:136-146; preprocess/embedding_table.cu:81-116,
+ * embedding_table_bwd_w.cu:99-145): the batch's token ids sorted (sorted_token_ids), the position each came from
+ * (sorted_token_mapping), and for unique token u the range [start[u], start[u+1]) of sorted positions holding it.
+ * Forward: output[position] = table[id]. Backward: the gradient rows of a token are summed in bf16 in sorted order
+ * (one rounding per addition, as the reference does) and added to grad_embedding_table[id]. */
+int b200_embedding_table(int fwd_dt, int num_unique_tokens, int embed_dim, const uint32_t *sorted_token_ids,
+                         const uint32_t *sorted_token_mapping, const uint32_t *unique_token_sorted_inds_start,
+                         const void *embedding_table, void *output, void *stream);
+int b200_embedding_table_bwd_w(int bwd_dt, int num_unique_tokens, int embed_dim, const uint32_t *sorted_token_ids,
+                               const uint32_t *sorted_token_mapping, const uint32_t *unique_token_sorted_inds_start,
+                               const void *grad_stream, void *grad_embedding_table, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

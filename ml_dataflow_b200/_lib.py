@@ -63,6 +63,19 @@ SIGNATURES = {
     "b200_ep_reduce_router_grad": (_i, [_vp, _i, _i64, _vp, _vp]),
     "b200_ep_moe_block_fwd": (_i, [_vp, _vp, _vp, _vp]),
     "b200_ep_moe_block_bwd": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "b200_rms_norm": (_i, [_i, _i, _i, _f, _vp, _vp, _vp, _vp, _vp]),
+    "b200_rms_norm_recompute": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp]),
+    "b200_rms_norm_bwd_x": (_i, [_i, _i, _i, _i, _f, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "b200_rms_norm_bwd_w_workspace_bytes": (_u64, [_i, _i]),
+    "b200_rms_norm_bwd_w": (_i, [_i, _i, _i, _i, _f, _vp, _vp, _vp, _vp, _u64, _vp, _vp]),
+    "b200_rope": (_i, [_i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp]),
+    "b200_rope_bwd_x": (_i, [_i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp]),
+    "b200_softmax": (_i, [_i, _i, _i, _i, _vp, _vp, _vp]),
+    "b200_cross_entropy_loss": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp]),
+    "b200_set_average_loss": (_i, [_i, _vp, _vp]),
+    "b200_adamw_step": (_i, [_i, _i, _i, _i, _u64, _i, _f, _f, _f, _f, _f, _vp, _vp, _vp, _vp, _vp]),
+    "b200_embedding_table": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "b200_embedding_table_bwd_w": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp]),
     "b200_scatter_row_weights": (_i, [_i, _i, _vp, _vp, _vp, _vp]),
     "b200_gather_router_grad": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp]),
 }

@@ -514,6 +514,13 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
           idesc[sub] = ptx::make_idesc_bf16(CF::TILE_M, p.dual_b ? 2 * t.nw : t.nw, p.a_mn_major, p.b_mn_major);
           d_tmem[sub] = tmem_base + (uint32_t)(accs[sub] * ACC_COLS);
         }
+        if (SUP == 1 && leader) {
+          // one column tile per unit: its accumulator is waited for once, before the first stage. (Waiting inside the
+          // issue loop, as the two-tile units must, costs 7 % of a whole layer step: the tensor pipe queues only about
+          // two MMAs behind the one it runs, so whatever this thread does between two MMAs beyond ~170 cycles idles it.)
+          if (!xwait(tempty_bar(accs[0]), ((acc_par >> accs[0]) & 1u) ^ 1u, ST_MMA_TIMEOUT)) break;
+          ptx::tc_fence_after();
+        }
         for (int ks = 0; ks < ksteps; ks += CF::KSLABS) {
           const int nsl = min(CF::KSLABS, ksteps - ks);
           const bool last = ks + nsl == ksteps;
@@ -552,7 +559,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
 #pragma unroll
               for (int sub = 0; sub < SUP; sub++) {
                 if (sub >= t.nsub) break;
-                if (ks + j == 0) {
+                if (SUP == 2 && ks + j == 0) {
                   // the accumulator must have been drained by the epilogue of the unit before; column tile 1 is
                   // waited for only now, after the first MMAs of column tile 0 are on their way
                   [[maybe_unused]] const long long dbg_t2 = DBG_CLK();

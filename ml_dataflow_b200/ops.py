@@ -296,3 +296,71 @@ def ep_status():
     v = C.c_int(0)
     _check(_lib.load().b200_ep_status(C.byref(v)), "b200_ep_status", 0)
     return v.value
+
+
+# ---- the bandwidth-bound ops of the block around the MoE feed-forward and of the head (bf16) ----------------------
+def rms_norm(n_rows, n_cols, eps, rms_weight, X, out, rms_vals=None):
+    _check(_lib.load().b200_rms_norm(DT_BF16, n_rows, n_cols, eps, _p(rms_weight), _p(X), _p(out), _p(rms_vals), _stream()),
+           "rms_norm")
+
+
+def rms_norm_recompute(n_rows, n_cols, rms_weight, rms_vals, X, out):
+    _check(_lib.load().b200_rms_norm_recompute(DT_BF16, n_rows, n_cols, _p(rms_weight), _p(rms_vals), _p(X), _p(out),
+                                               _stream()), "rms_norm_recompute")
+
+
+def rms_norm_bwd_x(n_rows, n_cols, eps, fwd_rms_vals, rms_weight, X_inp, upstream_dX, dX, X_out=None):
+    _check(_lib.load().b200_rms_norm_bwd_x(DT_BF16, DT_BF16, n_rows, n_cols, eps, _p(fwd_rms_vals), _p(rms_weight), _p(X_inp),
+                                           _p(upstream_dX), _p(dX), _p(X_out), _stream()), "rms_norm_bwd_x")
+
+
+def rms_norm_bwd_w_workspace_bytes(n_rows, n_cols):
+    return int(_lib.load().b200_rms_norm_bwd_w_workspace_bytes(n_rows, n_cols))
+
+
+def rms_norm_bwd_w(n_rows, n_cols, eps, fwd_rms_vals, X_inp, upstream_dX, dW, workspace):
+    _check(_lib.load().b200_rms_norm_bwd_w(DT_BF16, DT_BF16, n_rows, n_cols, eps, _p(fwd_rms_vals), _p(X_inp), _p(upstream_dX),
+                                           _p(dW), workspace.numel() * workspace.element_size(), _p(workspace), _stream()),
+           "rms_norm_bwd_w", 2)
+
+
+def rope(num_tokens, model_dim, head_dim, num_kv_heads, theta, seq_positions, X_q, X_k):
+    _check(_lib.load().b200_rope(DT_BF16, num_tokens, model_dim, head_dim, num_kv_heads, theta, _p(seq_positions), _p(X_q),
+                                 _p(X_k), _stream()), "rope")
+
+
+def rope_bwd_x(num_tokens, model_dim, head_dim, num_kv_heads, theta, seq_positions, dX_q, dX_k):
+    _check(_lib.load().b200_rope_bwd_x(DT_BF16, num_tokens, model_dim, head_dim, num_kv_heads, theta, _p(seq_positions),
+                                       _p(dX_q), _p(dX_k), _stream()), "rope_bwd_x")
+
+
+def softmax(n_rows, n_cols, X, out):
+    _check(_lib.load().b200_softmax(DT_BF16, DT_BF16, n_rows, n_cols, _p(X), _p(out), _stream()), "softmax")
+
+
+def cross_entropy_loss(n_rows, n_cols, pred_logits, labels, loss_vec):
+    _check(_lib.load().b200_cross_entropy_loss(DT_BF16, n_rows, n_cols, _p(pred_logits), _p(labels), _p(loss_vec), _stream()),
+           "cross_entropy_loss")
+
+
+def set_average_loss(n_tokens, loss_vec):
+    _check(_lib.load().b200_set_average_loss(n_tokens, _p(loss_vec), _stream()), "set_average_loss")
+
+
+def adamw_step(num_els, step_num, lr, beta1, beta2, weight_decay, epsilon, param, grad, mean, var):
+    _check(_lib.load().b200_adamw_step(DT_BF16, DT_BF16, DT_BF16, DT_BF16, num_els, step_num, lr, beta1, beta2, weight_decay,
+                                       epsilon, _p(param), _p(grad), _p(mean), _p(var), _stream()), "adamw_step")
+
+
+def embedding_table(num_unique_tokens, embed_dim, sorted_token_ids, sorted_token_mapping, unique_token_sorted_inds_start,
+                    table, output):
+    _check(_lib.load().b200_embedding_table(DT_BF16, num_unique_tokens, embed_dim, _p(sorted_token_ids),
+                                            _p(sorted_token_mapping), _p(unique_token_sorted_inds_start), _p(table),
+                                            _p(output), _stream()), "embedding_table")
+
+
+def embedding_table_bwd_w(num_unique_tokens, embed_dim, sorted_token_ids, sorted_token_mapping,
+                          unique_token_sorted_inds_start, grad_stream, grad_table):
+    _check(_lib.load().b200_embedding_table_bwd_w(DT_BF16, num_unique_tokens, embed_dim, _p(sorted_token_ids),
+                                                  _p(sorted_token_mapping), _p(unique_token_sorted_inds_start),
+                                                  _p(grad_stream), _p(grad_table), _stream()), "embedding_table_bwd_w")

@@ -26,7 +26,7 @@ def reference_root():
 
 def build(force=False):
     if force or not os.path.exists(_LIB_PATH) or (
-        os.path.getmtime(_LIB_PATH) < os.path.getmtime(os.path.join(_HERE, "moe_oracle.c"))
+        os.path.getmtime(_LIB_PATH) < max(os.path.getmtime(os.path.join(_HERE, n)) for n in ("moe_oracle.c", "block_oracle.c"))
     ):
         subprocess.check_call(["make", "-C", _HERE, "liboracle.so"], stdout=subprocess.DEVNULL)
     if os.path.isdir(reference_root()):
@@ -304,3 +304,87 @@ def moe_backward(Xn, Wr, W1, W3, W2, top_k, fwd, dOut, grads=None):
         linear_wgrad(zx[b:b + n], dx3[b:b + n], grads["dW3"][e])
     linear_wgrad(Xn, dX_routed, grads["dWr"])
     return dict(dXn=dXn, dlogits=dX_routed, dx1=dx1, dx3=dx3, dZ=zone, h=hs, **grads)
+
+
+# ---- block ops (oracle/block_oracle.c): numpy in, numpy out; bf16 as uint16 bit patterns -------------------------
+def rms_norm(w, X, eps):
+    n_rows, n_cols = X.shape
+    out, rms = np.empty_like(X), np.empty(n_rows, np.float32)
+    lib().orc_rms_norm_bf16(n_rows, n_cols, C.c_float(eps), _p(w), _p(X), _p(out), _p(rms))
+    return out, rms
+
+
+def rms_norm_recompute(w, rms, X):
+    out = np.empty_like(X)
+    lib().orc_rms_norm_recompute_bf16(X.shape[0], X.shape[1], _p(w), _p(rms), _p(X), _p(out))
+    return out
+
+
+def rms_norm_bwd_x(rms, w, X, up, dX, want_x_out=False):
+    """Accumulates into a copy of dX; returns (dX_new, X_out or None)."""
+    dX = dX.copy()
+    x_out = np.empty_like(X) if want_x_out else None
+    lib().orc_rms_norm_bwd_x_bf16(X.shape[0], X.shape[1], _p(rms), _p(w), _p(X), _p(up), _p(dX), _p(x_out))
+    return dX, x_out
+
+
+def rms_norm_bwd_w(rms, X, up, dW):
+    dW = dW.copy()
+    lib().orc_rms_norm_bwd_w_bf16(X.shape[0], X.shape[1], _p(rms), _p(X), _p(up), _p(dW))
+    return dW
+
+
+def rope(head_dim, num_kv_heads, theta, seq_positions, X_q, X_k=None, backward=False):
+    X_q = X_q.copy()
+    X_k = None if X_k is None else X_k.copy()
+    fn = lib().orc_rope_bwd_x_bf16 if backward else lib().orc_rope_bf16
+    fn(X_q.shape[0], X_q.shape[1], head_dim, num_kv_heads, int(theta), _p(np.ascontiguousarray(seq_positions, np.int32)),
+       _p(X_q), _p(X_k))
+    return X_q, X_k
+
+
+def softmax(X):
+    out = np.empty_like(X)
+    lib().orc_softmax_bf16(X.shape[0], X.shape[1], _p(X), _p(out))
+    return out
+
+
+def cross_entropy_loss(p, labels):
+    """Returns (p with 1 subtracted at the labels, loss_vec of n_rows + 1 entries with the average in the last)."""
+    p = p.copy()
+    n = p.shape[0]
+    loss = np.zeros(n + 1, np.float32)
+    lib().orc_cross_entropy_loss_bf16(n, p.shape[1], _p(p), _p(np.ascontiguousarray(labels, np.uint32)), _p(loss))
+    lib().orc_set_average_loss(n, _p(loss))
+    return p, loss
+
+
+def adamw_step(step, lr, b1, b2, wd, eps, param, grad, mean, var):
+    param, mean, var = param.copy(), mean.copy(), var.copy()
+    f = C.c_float
+    lib().orc_adamw_step_bf16(C.c_uint64(param.size), step, f(lr), f(b1), f(b2), f(wd), f(eps), _p(param), _p(grad), _p(mean),
+                              _p(var))
+    return param, mean, var
+
+
+def sort_tokens(token_ids):
+    """The reference's host-side preparation for the embedding ops (sorted ids, their positions, start of each unique
+    id's run, with one closing entry)."""
+    token_ids = np.asarray(token_ids, np.uint32)
+    order = np.argsort(token_ids, kind="stable").astype(np.uint32)
+    sorted_ids = token_ids[order]
+    starts = np.flatnonzero(np.concatenate([[True], sorted_ids[1:] != sorted_ids[:-1]])).astype(np.uint32)
+    return sorted_ids, order, np.concatenate([starts, [len(token_ids)]]).astype(np.uint32)
+
+
+def embedding_table(sorted_ids, mapping, starts, table, n_tokens):
+    out = np.zeros((n_tokens, table.shape[1]), np.uint16)
+    lib().orc_embedding_table_bf16(len(starts) - 1, table.shape[1], _p(sorted_ids), _p(mapping), _p(starts), _p(table), _p(out))
+    return out
+
+
+def embedding_table_bwd_w(sorted_ids, mapping, starts, grad_stream, grad_table):
+    grad_table = grad_table.copy()
+    lib().orc_embedding_table_bwd_w_bf16(len(starts) - 1, grad_table.shape[1], _p(sorted_ids), _p(mapping), _p(starts),
+                                         _p(grad_stream), _p(grad_table))
+    return grad_table

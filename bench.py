@@ -112,6 +112,92 @@ class ClockSampler:
         return out
 
 
+# ------------------------------------------------------------------------------------------ block ops
+# rows: 8 sequences of the training step's 8192 tokens, so that every tensor of an op is larger than L2
+CFG_BLOCK = dict(T=65536, d=2048, heads=16, kv_heads=4, head_dim=128, vocab=128256, theta=500000)
+
+
+def block_ops_profile(dev, peaks, iters=5):
+    """The bandwidth-bound ops around the MoE feed-forward at the row shapes of the decoder training step (d=2048,
+    16 query / 4 kv heads of 128, vocabulary 128256) over 65536 token rows (inputs larger than L2): ms per launch
+    (CUDA events, L2 flushed before each launch) and algorithmic bytes / time against the measured HBM rate."""
+    import torch
+
+    from ml_dataflow_b200 import ops
+
+    c = CFG_BLOCK
+    T, d, V = c["T"], c["d"], c["vocab"]
+    kvd = c["kv_heads"] * c["head_dim"]
+    g = torch.Generator(device=dev).manual_seed(11)
+    bf = lambda shape, std=1.0: (torch.randn(shape, generator=g, device=dev) * std).to(torch.bfloat16)
+    X, up, dX, w = bf((T, d)), bf((T, d)), bf((T, d)), bf((d,))
+    out = torch.empty_like(X)
+    rms = torch.empty(T, dtype=torch.float32, device=dev)
+    dW = torch.zeros(d, dtype=torch.bfloat16, device=dev)
+    ws = torch.empty(ops.rms_norm_bwd_w_workspace_bytes(T, d), dtype=torch.uint8, device=dev)
+    q, kk = bf((T, d)), bf((T, kvd))
+    pos = (torch.arange(T, dtype=torch.int32, device=dev) % 8192).contiguous()
+    rows_sm = 2048  # softmax on a slice of the token rows: 2048 x 128256 bf16 = 0.5 GB each way
+    logits = bf((rows_sm, V), 2.0)
+    probs = torch.empty_like(logits)
+    labels = torch.randint(0, V, (rows_sm,), generator=g, device=dev, dtype=torch.int32)
+    loss = torch.zeros(rows_sm + 1, dtype=torch.float32, device=dev)
+    n_par = 64 << 20
+    par, grad, mean = bf((n_par,), 0.02), bf((n_par,), 0.01), bf((n_par,), 0.01)
+    var = bf((n_par,), 0.01).abs()
+    ids = torch.randint(0, V, (T,), generator=g, device=dev, dtype=torch.int64)
+    sorted_ids, order = torch.sort(ids, stable=True)
+    first = torch.ones(T, dtype=torch.bool, device=dev)
+    first[1:] = sorted_ids[1:] != sorted_ids[:-1]
+    starts = torch.cat([torch.nonzero(first).flatten(), torch.tensor([T], device=dev)]).to(torch.int32)
+    nu = int(starts.numel()) - 1
+    sid32, map32 = sorted_ids.to(torch.int32), order.to(torch.int32)
+    table = bf((V, d), 0.02)
+    gtab = torch.zeros_like(table)
+    emb = torch.empty((T, d), dtype=torch.bfloat16, device=dev)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    ops.rms_norm(T, d, 1e-5, w, X, out, rms)
+    cases = [
+        ("rms_norm", lambda: ops.rms_norm(T, d, 1e-5, w, X, out, rms), 4 * T * d),
+        ("rms_norm_bwd_x", lambda: ops.rms_norm_bwd_x(T, d, 1e-5, rms, w, X, up, dX, None), 8 * T * d),
+        ("rms_norm_bwd_w", lambda: ops.rms_norm_bwd_w(T, d, 1e-5, rms, X, up, dW, ws), 4 * T * d),
+        ("rope", lambda: ops.rope(T, d, c["head_dim"], c["kv_heads"], c["theta"], pos, q, kk), 4 * T * (d + kvd)),
+        ("softmax", lambda: ops.softmax(rows_sm, V, logits, probs), 4 * rows_sm * V),
+        ("adamw_step", lambda: ops.adamw_step(n_par, 1, 3e-4, 0.9, 0.95, 0.1, 1e-8, par, grad, mean, var), 14 * n_par),
+        ("embedding_table", lambda: ops.embedding_table(nu, d, sid32, map32, starts, table, emb), 2 * nu * d + 2 * T * d),
+        ("embedding_table_bwd_w", lambda: ops.embedding_table_bwd_w(nu, d, sid32, map32, starts, up, gtab),
+         2 * T * d + 4 * nu * d),
+    ]
+    res = {}
+    for name, fn, nbytes in cases:
+        fn()
+        ms = []
+        for _ in range(iters):
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ms.append(e0.elapsed_time(e1))
+        t = sorted(ms)[len(ms) // 2]
+        gbs = nbytes / (t * 1e-3) / 1e9
+        res[name] = dict(ms=round(t, 4), bound="hbm", achieved=round(gbs, 1), unit="GB/s", frac=round(gbs / peaks["hbm_gbs"], 4))
+    # one thread per row, one element each: a latency measurement, not a bandwidth one
+    ops.cross_entropy_loss(rows_sm, V, probs, labels, loss)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    ops.cross_entropy_loss(rows_sm, V, probs, labels, loss)
+    ops.set_average_loss(rows_sm, loss)
+    e1.record()
+    torch.cuda.synchronize()
+    res["cross_entropy_loss+set_average_loss"] = dict(ms=round(e0.elapsed_time(e1), 4), bound="latency", rows=rows_sm)
+    res["shapes"] = ("65536 token rows x d 2048 (norm, rope with 16q/4kv heads of 128, embedding over a 128256-row table), "
+                     "softmax on 2048 x 128256 logits, AdamW on 64 Mi parameters; median of %d launches, L2 flushed "
+                     "before each" % iters)
+    return res
+
+
 # ------------------------------------------------------------------------------------------ CPU arm
 def cpu_reference_run(cfg, tokens, steps, warmup):
     """Times the CPU oracle (fwd+bwd) on `tokens` tokens of the shape `cfg`, on every host core this process may use.
@@ -579,6 +665,8 @@ def run_gpu_arm(args, world):
     if world == 1 and args.tokens <= 0:
         # the target shape (T=32768 on one GPU) beside the headline configuration
         extra["ns_shape"] = single_gpu_layer_run(CFG_NS, dev, 10, 3, peaks, 0xB200)
+        torch.cuda.empty_cache()
+        extra["block_ops"] = block_ops_profile(dev, peaks)
     if world > 1:
         ep_parity = "ok"
         try:

@@ -156,8 +156,115 @@ rms_norm_bwd_x_kernel(int n_rows, int n_vec, float inv_n, const float *__restric
   }
 }
 
+// Rows of up to 4096 columns (forward) / 2048 columns (backward-x): one WARP per row, the whole row in the lanes'
+// registers, reduction by shuffles only. No block-wide barrier sits between a row's loads and its stores, and a block
+// of eight warps keeps eight rows in flight, which is what a few-KB row needs to cover the memory latency.
+constexpr int NORM_WARPS = 8;
+
+template <int VPL>  // 16-byte vectors per lane: the row has at most 32 * VPL of them
+__global__ void __launch_bounds__(NORM_WARPS * 32)
+rms_norm_warp_kernel(int n_rows, int n_vec, float inv_n, float eps, const uint4 *__restrict__ w, const uint4 *__restrict__ X,
+                     uint4 *__restrict__ out, float *__restrict__ rms_out, const float *__restrict__ rms_in) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warps = (int64_t)gridDim.x * NORM_WARPS;
+  for (int64_t row = (int64_t)blockIdx.x * NORM_WARPS + (threadIdx.x >> 5); row < n_rows; row += warps) {
+    const uint4 *x = X + row * n_vec;
+    uint4 v[VPL];
+#pragma unroll
+    for (int i = 0; i < VPL; i++) {
+      const int c = i * 32 + lane;
+      if (c < n_vec) v[i] = ld_stream(x + c);
+    }
+    float r;
+    if (rms_in == nullptr) {
+      float ss = 0.0f;
+#pragma unroll
+      for (int i = 0; i < VPL; i++) {
+        if (i * 32 + lane < n_vec) {
+          float f[8];
+          unpack8(v[i], f);
+#pragma unroll
+          for (int q = 0; q < 8; q++) ss += f[q] * f[q];
+        }
+      }
+      r = rsqrtf(warp_sum(ss) * inv_n + eps);
+      if (rms_out != nullptr && lane == 0) rms_out[row] = r;
+    } else {
+      r = rms_in[row];
+    }
+    uint4 *o = out + row * n_vec;
+#pragma unroll
+    for (int i = 0; i < VPL; i++) {
+      const int c = i * 32 + lane;
+      if (c < n_vec) {
+        float f[8], g[8];
+        unpack8(v[i], f);
+        unpack8(__ldg(w + c), g);
+#pragma unroll
+        for (int q = 0; q < 8; q++) f[q] = f[q] * r * g[q];
+        st_stream(o + c, pack8(f));
+      }
+    }
+  }
+}
+
+template <int VPL>
+__global__ void __launch_bounds__(NORM_WARPS * 32)
+rms_norm_bwd_x_warp_kernel(int n_rows, int n_vec, float inv_n, const float *__restrict__ rms, const uint4 *__restrict__ w,
+                           const uint4 *__restrict__ X, const uint4 *__restrict__ up, uint4 *__restrict__ dX,
+                           uint4 *__restrict__ X_out) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warps = (int64_t)gridDim.x * NORM_WARPS;
+  for (int64_t row = (int64_t)blockIdx.x * NORM_WARPS + (threadIdx.x >> 5); row < n_rows; row += warps) {
+    const int64_t base = row * n_vec;
+    const float r = rms[row];
+    uint4 xv[VPL], uv[VPL], dv[VPL];
+#pragma unroll
+    for (int i = 0; i < VPL; i++) {
+      const int c = i * 32 + lane;
+      if (c < n_vec) {
+        xv[i] = ld_stream(X + base + c);
+        uv[i] = ld_stream(up + base + c);
+        dv[i] = dX[base + c];
+      }
+    }
+    float csum = 0.0f;
+#pragma unroll
+    for (int i = 0; i < VPL; i++) {
+      const int c = i * 32 + lane;
+      if (c < n_vec) {
+        float x[8], u[8], g[8], o[8];
+        unpack8(xv[i], x);
+        unpack8(uv[i], u);
+        unpack8(__ldg(w + c), g);
+#pragma unroll
+        for (int q = 0; q < 8; q++) {
+          o[q] = x[q] * r * g[q];
+          csum += o[q] * u[q];
+        }
+        if (X_out != nullptr) st_stream(X_out + base + c, pack8(o));
+      }
+    }
+    const float c_div_n = warp_sum(csum) * inv_n;
+#pragma unroll
+    for (int i = 0; i < VPL; i++) {
+      const int c = i * 32 + lane;
+      if (c < n_vec) {
+        float x[8], u[8], g[8], d[8];
+        unpack8(xv[i], x);
+        unpack8(uv[i], u);
+        unpack8(__ldg(w + c), g);
+        unpack8(dv[i], d);
+#pragma unroll
+        for (int q = 0; q < 8; q++) d[q] += r * (u[q] * g[q] - c_div_n * (x[q] * r));
+        dX[base + c] = pack8(d);
+      }
+    }
+  }
+}
+
 // Weight gradient of RMSNorm, first pass (norm/rms_norm_bwd_w.cu:225-325): block b sums up * x * r over its slice of
-// the rows for every column into partial[b][.] (fp32). Thread = one 8-column vector; four rows in flight.
+// the rows for every column into partial[b][.] (fp32). Thread = one 8-column vector; eight rows in flight.
 __global__ void __launch_bounds__(NORM_THREADS)
 rms_norm_bwd_w_partial_kernel(int n_rows, int n_vec, const float *__restrict__ rms, const uint4 *__restrict__ X,
                               const uint4 *__restrict__ up, float *__restrict__ partial) {
@@ -168,17 +275,17 @@ rms_norm_bwd_w_partial_kernel(int n_rows, int n_vec, const float *__restrict__ r
   if (c >= n_vec) return;
   float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
   int row = r0;
-  for (; row + 4 <= r1; row += 4) {
-    uint4 xv[4], uv[4];
-    float rv[4];
+  for (; row + 8 <= r1; row += 8) {
+    uint4 xv[8], uv[8];
+    float rv[8];
 #pragma unroll
-    for (int j = 0; j < 4; j++) {
+    for (int j = 0; j < 8; j++) {
       xv[j] = ld_stream(X + (int64_t)(row + j) * n_vec + c);
       uv[j] = ld_stream(up + (int64_t)(row + j) * n_vec + c);
       rv[j] = rms[row + j];
     }
 #pragma unroll
-    for (int j = 0; j < 4; j++) {
+    for (int j = 0; j < 8; j++) {
       float x[8], u[8];
       unpack8(xv[j], x);
       unpack8(uv[j], u);
@@ -199,16 +306,36 @@ rms_norm_bwd_w_partial_kernel(int n_rows, int n_vec, const float *__restrict__ r
   dst[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
 }
 
-// second pass (norm/rms_norm_bwd_w_combine.cu:200-294): dW = bf16(f32(dW) + sum over blocks, in block order)
-__global__ void rms_norm_bwd_w_combine_kernel(int n_cols, int blocks, const float *__restrict__ partial,
-                                              __nv_bfloat16 *__restrict__ dW) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= n_cols) return;
+// second pass (norm/rms_norm_bwd_w_combine.cu:200-294): dW = bf16(f32(dW) + sum of the slices' partial sums). A
+// block takes 32 columns; its 8 warps each add every eighth slice (independent loads, 128 contiguous bytes per warp),
+// then the eight sums are added in warp order: the same order on every run.
+__global__ void __launch_bounds__(256)
+rms_norm_bwd_w_combine_kernel(int n_cols, int blocks, const float *__restrict__ partial, __nv_bfloat16 *__restrict__ dW) {
+  __shared__ float part[8][32];
+  const int lane = threadIdx.x & 31, grp = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + lane;
   float s = 0.0f;
-  for (int b = 0; b < blocks; b++) s += partial[(int64_t)b * n_cols + c];
-  dW[c] = __float2bfloat16_rn(__bfloat162float(dW[c]) + s);
+  if (c < n_cols) {
+    int b = grp;
+    for (; b + 24 < blocks; b += 32) {
+      const float v0 = partial[(int64_t)b * n_cols + c], v1 = partial[(int64_t)(b + 8) * n_cols + c];
+      const float v2 = partial[(int64_t)(b + 16) * n_cols + c], v3 = partial[(int64_t)(b + 24) * n_cols + c];
+      s += v0;
+      s += v1;
+      s += v2;
+      s += v3;
+    }
+    for (; b < blocks; b += 8) s += partial[(int64_t)b * n_cols + c];
+  }
+  part[grp][lane] = s;
+  __syncthreads();
+  if (grp == 0 && c < n_cols) {
+    float t = 0.0f;
+#pragma unroll
+    for (int g = 0; g < 8; g++) t += part[g][lane];
+    dW[c] = __float2bfloat16_rn(__bfloat162float(dW[c]) + t);
+  }
 }
-
 
 // ---- RoPE ----------------------------------------------------------------------------------------------------
 // attention_misc/rope.cu:152-256 and rope_bwd_x.cu:146-248: in place on interleaved pairs (2i, 2i+1) of every head,
@@ -255,11 +382,70 @@ rope_kernel(int num_tokens, int q_vec, int k_vec, int head_dim, float theta, flo
   }
 }
 
+// The same with one WARP per token, for head sizes whose vectors tile a warp (head_dim 64, 128 or 256): vector
+// c = lane + 32 i of a row always falls on the same four pairs of its head, so every lane forms just those four
+// angles and keeps them in registers; no shared memory, no barrier, all of a token's loads in flight at once.
+constexpr int ROPE_WARPS = 4;
+constexpr int ROPE_MAX_VPL = 12;  // 16-byte vectors per lane over the q and k rows together
+
+__global__ void __launch_bounds__(ROPE_WARPS * 32)
+rope_warp_kernel(int num_tokens, int q_vec, int k_vec, int head_dim, float theta, float sign,
+                 const int *__restrict__ seq_positions, uint4 *__restrict__ X_q, uint4 *__restrict__ X_k) {
+  const int lane = threadIdx.x & 31;
+  const int head_vec = head_dim >> 3;
+  const int p0 = (lane % head_vec) * 4;
+  float inv_freq[4];
+#pragma unroll
+  for (int j = 0; j < 4; j++) inv_freq[j] = powf(theta, -(float)(2 * (p0 + j)) / (float)head_dim);
+  const int qn = (q_vec + 31) >> 5, kn = (X_k != nullptr) ? (k_vec + 31) >> 5 : 0;
+  const int64_t warps = (int64_t)gridDim.x * ROPE_WARPS;
+  for (int64_t tok = (int64_t)blockIdx.x * ROPE_WARPS + (threadIdx.x >> 5); tok < num_tokens; tok += warps) {
+    uint4 v[ROPE_MAX_VPL];
+    uint4 *qrow = X_q + tok * q_vec, *krow = X_k ? X_k + tok * k_vec : nullptr;
+#pragma unroll
+    for (int i = 0; i < ROPE_MAX_VPL; i++) {
+      const int c = (i < qn ? i : i - qn) * 32 + lane;
+      if (i < qn) { if (c < q_vec) v[i] = qrow[c]; }
+      else if (i < qn + kn) { if (c < k_vec) v[i] = krow[c]; }
+    }
+    const float pos = (float)seq_positions[tok];
+    float cs[4], sn[4];
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      sincosf(pos * inv_freq[j], &sn[j], &cs[j]);
+      sn[j] *= sign;
+    }
+#pragma unroll
+    for (int i = 0; i < ROPE_MAX_VPL; i++) {
+      const bool is_q = i < qn;
+      const int c = (is_q ? i : i - qn) * 32 + lane;
+      if (i >= qn + kn || c >= (is_q ? q_vec : k_vec)) continue;
+      float f[8];
+      unpack8(v[i], f);
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        const float e = f[2 * j], o = f[2 * j + 1];
+        f[2 * j] = cs[j] * e - sn[j] * o;
+        f[2 * j + 1] = cs[j] * o + sn[j] * e;
+      }
+      (is_q ? qrow : krow)[c] = pack8(f);
+    }
+  }
+}
+
 // ---- softmax over long rows (the vocabulary) -------------------------------------------------------------------
 // loss_misc/softmax.cu:249-394: out = bf16(exp(x - max) / sum). One block per row; pass 1 folds maximum and sum of
 // eight elements at a time (one rescale per vector), pass 2 re-reads the row, which is still in L2 (a row of 128 K
 // bf16 is 250 KB, a few hundred rows are in flight) and writes the result.
-constexpr int SOFTMAX_THREADS = 512;
+constexpr int SOFTMAX_THREADS = 1024;
+constexpr float LOG2E = 1.4426950408889634f;
+// exp(a - b) as 2^((a - b) log2 e): the difference is formed first, so the result is as accurate as expf's to within
+// the rounding of one multiplication (relative 6e-8 * |a - b|; the differences of a softmax row stay within tens)
+__device__ __forceinline__ float exp_diff(float a, float b) {
+  float r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"((a - b) * LOG2E));  // 2 ulp; results below 2^-126 become 0
+  return r;
+}
 
 __global__ void __launch_bounds__(SOFTMAX_THREADS)
 softmax_kernel(int n_rows, int n_cols, const __nv_bfloat16 *__restrict__ X, __nv_bfloat16 *__restrict__ out) {
@@ -273,6 +459,7 @@ softmax_kernel(int n_rows, int n_cols, const __nv_bfloat16 *__restrict__ X, __nv
     const bool vec_ok = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(o)) & 15u) == 0;
     const int nv = vec_ok ? n_vec : 0;
     float m = NEG, s = 0.0f;
+#pragma unroll 4
     for (int c = threadIdx.x; c < nv; c += SOFTMAX_THREADS) {
       float f[8];
       unpack8(reinterpret_cast<const uint4 *>(x)[c], f);
@@ -282,14 +469,14 @@ softmax_kernel(int n_rows, int n_cols, const __nv_bfloat16 *__restrict__ X, __nv
       const float nm = fmaxf(m, vm);
       float part = 0.0f;
 #pragma unroll
-      for (int q = 0; q < 8; q++) part += expf(f[q] - nm);
-      s = s * expf(m - nm) + part;
+      for (int q = 0; q < 8; q++) part += exp_diff(f[q], nm);
+      s = s * exp_diff(m, nm) + part;
       m = nm;
     }
     for (int c = nv * 8 + threadIdx.x; c < n_cols; c += SOFTMAX_THREADS) {
       const float v = __bfloat162float(x[c]);
       const float nm = fmaxf(m, v);
-      s = s * expf(m - nm) + expf(v - nm);
+      s = s * exp_diff(m, nm) + exp_diff(v, nm);
       m = nm;
     }
     // (max, sum) pairs: warp, then block
@@ -297,7 +484,7 @@ softmax_kernel(int n_rows, int n_cols, const __nv_bfloat16 *__restrict__ X, __nv
     for (int off = 16; off > 0; off >>= 1) {
       const float pm = __shfl_xor_sync(0xffffffffu, m, off), ps = __shfl_xor_sync(0xffffffffu, s, off);
       const float nm = fmaxf(m, pm);
-      s = s * expf(m - nm) + ps * expf(pm - nm);
+      s = s * exp_diff(m, nm) + ps * exp_diff(pm, nm);
       m = nm;
     }
     __syncthreads();
@@ -312,18 +499,20 @@ softmax_kernel(int n_rows, int n_cols, const __nv_bfloat16 *__restrict__ X, __nv
     for (int off = 16; off > 0; off >>= 1) {
       const float pm = __shfl_xor_sync(0xffffffffu, m, off), ps = __shfl_xor_sync(0xffffffffu, s, off);
       const float nm = fmaxf(m, pm);
-      s = s * expf(m - nm) + ps * expf(pm - nm);
+      s = s * exp_diff(m, nm) + ps * exp_diff(pm, nm);
       m = nm;
     }
+    const float inv_s = 1.0f / s;
+#pragma unroll 4
     for (int c = threadIdx.x; c < nv; c += SOFTMAX_THREADS) {
       float f[8];
       unpack8(reinterpret_cast<const uint4 *>(x)[c], f);
 #pragma unroll
-      for (int q = 0; q < 8; q++) f[q] = expf(f[q] - m) / s;
+      for (int q = 0; q < 8; q++) f[q] = exp_diff(f[q], m) * inv_s;
       st_stream(reinterpret_cast<uint4 *>(o) + c, pack8(f));
     }
     for (int c = nv * 8 + threadIdx.x; c < n_cols; c += SOFTMAX_THREADS)
-      o[c] = __float2bfloat16_rn(expf(__bfloat162float(x[c]) - m) / s);
+      o[c] = __float2bfloat16_rn(exp_diff(__bfloat162float(x[c]), m) * inv_s);
   }
 }
 
@@ -402,6 +591,85 @@ embedding_kernel(int num_unique, int dim_vec, const uint32_t *__restrict__ sorte
   }
 }
 
+// warp per unique token for rows of up to 256 vectors (embed_dim <= 2048): the row sits in the lanes' registers
+constexpr int EMB_WARPS = 8;
+template <int VPL>
+__global__ void __launch_bounds__(EMB_WARPS * 32)
+embedding_warp_kernel(int num_unique, int dim_vec, const uint32_t *__restrict__ sorted_ids, const uint32_t *__restrict__ sorted_map,
+                      const uint32_t *__restrict__ starts, const uint4 *__restrict__ table, uint4 *__restrict__ output) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warps = (int64_t)gridDim.x * EMB_WARPS;
+  for (int64_t u = (int64_t)blockIdx.x * EMB_WARPS + (threadIdx.x >> 5); u < num_unique; u += warps) {
+    const uint32_t b = starts[u], e = starts[u + 1];
+    const uint4 *src = table + (int64_t)sorted_ids[b] * dim_vec;
+    uint4 v[VPL];
+#pragma unroll
+    for (int i = 0; i < VPL; i++)
+      if (i * 32 + lane < dim_vec) v[i] = ld_stream(src + i * 32 + lane);
+    for (uint32_t r = b; r < e; r++) {
+      uint4 *dst = output + (int64_t)sorted_map[r] * dim_vec;
+#pragma unroll
+      for (int i = 0; i < VPL; i++)
+        if (i * 32 + lane < dim_vec) st_stream(dst + i * 32 + lane, v[i]);
+    }
+  }
+}
+
+template <int VPL>
+__global__ void __launch_bounds__(EMB_WARPS * 32)
+embedding_bwd_w_warp_kernel(int num_unique, int dim_vec, const uint32_t *__restrict__ sorted_ids,
+                            const uint32_t *__restrict__ sorted_map, const uint32_t *__restrict__ starts,
+                            const uint4 *__restrict__ grad_stream, uint4 *__restrict__ grad_table) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warps = (int64_t)gridDim.x * EMB_WARPS;
+  for (int64_t u = (int64_t)blockIdx.x * EMB_WARPS + (threadIdx.x >> 5); u < num_unique; u += warps) {
+    const uint32_t b = starts[u], e = starts[u + 1];
+    uint4 *dst = grad_table + (int64_t)sorted_ids[b] * dim_vec;
+    if (e - b == 1) {
+      // the usual case with a large vocabulary: bf16(0 + g) is g itself, so the row is table + g with one rounding;
+      // both rows are requested at once
+      const uint4 *src = grad_stream + (int64_t)sorted_map[b] * dim_vec;
+      uint4 t[VPL], g4[VPL];
+#pragma unroll
+      for (int i = 0; i < VPL; i++) {
+        if (i * 32 + lane < dim_vec) {
+          t[i] = dst[i * 32 + lane];
+          g4[i] = ld_stream(src + i * 32 + lane);
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < VPL; i++) {
+        if (i * 32 + lane < dim_vec) {
+          float f[8], g[8];
+          unpack8(t[i], f);
+          unpack8(g4[i], g);
+#pragma unroll
+          for (int q = 0; q < 8; q++) f[q] += g[q];
+          dst[i * 32 + lane] = pack8(f);
+        }
+      }
+      continue;
+    }
+    for (int i = 0; i < VPL; i++) {
+      const int c = i * 32 + lane;
+      if (c >= dim_vec) break;
+      const uint4 t = dst[c];
+      float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+      for (uint32_t r = b; r < e; r++) {
+        float g[8];
+        unpack8(ld_stream(grad_stream + (int64_t)sorted_map[r] * dim_vec + c), g);
+#pragma unroll
+        for (int q = 0; q < 8; q++) acc[q] = bf16_round(acc[q] + g[q]);
+      }
+      float f[8];
+      unpack8(t, f);
+#pragma unroll
+      for (int q = 0; q < 8; q++) f[q] += acc[q];
+      dst[c] = pack8(f);
+    }
+  }
+}
+
 // preprocess/embedding_table_bwd_w.cu:99-145: the gradient rows of a token are added up in bf16, in sorted order,
 // from zero (one rounding per addition, as the reference's bf16 shared-memory accumulator does), then added to the
 // table row in bf16.
@@ -455,7 +723,17 @@ static int rms_norm_launch(const char *op, int n_rows, int n_cols, float eps, co
   cudaStream_t s = (cudaStream_t)stream;
   const uint4 *wv = (const uint4 *)w, *xv = (const uint4 *)X;
   uint4 *ov = (uint4 *)out;
-  if (vpt <= 1) rms_norm_kernel<1><<<grid, NORM_THREADS, 0, s>>>(n_rows, n_vec, inv_n, eps, wv, xv, ov, rms_out, rms_in);
+  if (n_vec <= 32 * 16) {
+    // warp per row
+    const int vpl = (n_vec + 31) / 32;
+    const int wgrid = block_ops_grid((n_rows + NORM_WARPS - 1) / NORM_WARPS, 8);
+#define B200_RMSW(V) rms_norm_warp_kernel<V><<<wgrid, NORM_WARPS * 32, 0, s>>>(n_rows, n_vec, inv_n, eps, wv, xv, ov, rms_out, rms_in)
+    if (vpl <= 2) B200_RMSW(2);
+    else if (vpl <= 4) B200_RMSW(4);
+    else if (vpl <= 8) B200_RMSW(8);
+    else B200_RMSW(16);
+#undef B200_RMSW
+  } else if (vpt <= 1) rms_norm_kernel<1><<<grid, NORM_THREADS, 0, s>>>(n_rows, n_vec, inv_n, eps, wv, xv, ov, rms_out, rms_in);
   else if (vpt <= 2) rms_norm_kernel<2><<<grid, NORM_THREADS, 0, s>>>(n_rows, n_vec, inv_n, eps, wv, xv, ov, rms_out, rms_in);
   else if (vpt <= NORM_MAX_VPT) rms_norm_kernel<4><<<grid, NORM_THREADS, 0, s>>>(n_rows, n_vec, inv_n, eps, wv, xv, ov, rms_out, rms_in);
   else rms_norm_kernel<0><<<grid, NORM_THREADS, 0, s>>>(n_rows, n_vec, inv_n, eps, wv, xv, ov, rms_out, rms_in);
@@ -498,17 +776,25 @@ extern "C" int b200_rms_norm_bwd_x(int fwd_dt, int bwd_dt, int n_rows, int n_col
   rms_norm_bwd_x_kernel<V><<<grid, NORM_THREADS, 0, s>>>(n_rows, n_vec, inv_n, fwd_rms_vals, (const uint4 *)rms_weight, \
                                                          (const uint4 *)X_inp, (const uint4 *)upstream_dX, (uint4 *)dX, \
                                                          (uint4 *)X_out)
-  if (vpt <= 1) B200_BWDX(1);
+#define B200_BWDXW(V)                                                                                                         \
+  rms_norm_bwd_x_warp_kernel<V><<<block_ops_grid((n_rows + NORM_WARPS - 1) / NORM_WARPS, 6), NORM_WARPS * 32, 0, s>>>(           \
+      n_rows, n_vec, inv_n, fwd_rms_vals, (const uint4 *)rms_weight, (const uint4 *)X_inp, (const uint4 *)upstream_dX, (uint4 *)dX, \
+      (uint4 *)X_out)
+  if (n_vec <= 32 * 2) B200_BWDXW(2);
+  else if (n_vec <= 32 * 4) B200_BWDXW(4);
+  else if (n_vec <= 32 * 8) B200_BWDXW(8);
+  else if (vpt <= 1) B200_BWDX(1);
   else if (vpt <= 2) B200_BWDX(2);
   else B200_BWDX(4);
+#undef B200_BWDXW
 #undef B200_BWDX
   B200_CHECK_LAUNCH("rms_norm_bwd_x");
   return 0;
 }
 
-// row slices of the first pass: two per SM, no more than the rows, no more than the workspace holds
+// row slices of the first pass: four per SM, no more than the rows, no more than the workspace holds
 static int bwd_w_slices(int n_rows, int n_cols, uint64_t workspace_bytes) {
-  int slices = block_ops_grid(n_rows, 2);
+  int slices = block_ops_grid(n_rows, 4);
   const uint64_t fit = workspace_bytes / ((uint64_t)n_cols * sizeof(float));
   if ((uint64_t)slices > fit) slices = (int)fit;
   return slices;
@@ -516,7 +802,7 @@ static int bwd_w_slices(int n_rows, int n_cols, uint64_t workspace_bytes) {
 
 extern "C" uint64_t b200_rms_norm_bwd_w_workspace_bytes(int n_rows, int n_cols) {
   if (n_rows <= 0 || n_cols <= 0) return 0;
-  return (uint64_t)block_ops_grid(n_rows, 2) * (uint64_t)n_cols * sizeof(float);
+  return (uint64_t)block_ops_grid(n_rows, 4) * (uint64_t)n_cols * sizeof(float);
 }
 
 extern "C" int b200_rms_norm_bwd_w(int fwd_dt, int bwd_dt, int n_rows, int n_cols, float eps, const float *fwd_rms_vals,
@@ -539,7 +825,7 @@ extern "C" int b200_rms_norm_bwd_w(int fwd_dt, int bwd_dt, int n_rows, int n_col
   rms_norm_bwd_w_partial_kernel<<<grid, NORM_THREADS, 0, s>>>(n_rows, n_vec, fwd_rms_vals, (const uint4 *)X_inp,
                                                              (const uint4 *)upstream_dX, (float *)workspace);
   B200_CHECK_LAUNCH("rms_norm_bwd_w");
-  rms_norm_bwd_w_combine_kernel<<<(n_cols + 255) / 256, 256, 0, s>>>(n_cols, slices, (const float *)workspace,
+  rms_norm_bwd_w_combine_kernel<<<(n_cols + 31) / 32, 256, 0, s>>>(n_cols, slices, (const float *)workspace,
                                                                     (__nv_bfloat16 *)dW);
   B200_CHECK_LAUNCH("rms_norm_bwd_w (combine)");
   return 0;
@@ -554,9 +840,14 @@ static int rope_launch(const char *op, int dt, int num_tokens, int model_dim, in
                ROPE_MAX_HEAD_DIM, model_dim, head_dim);
   B200_REQUIRE(seq_positions && X_q && b200_aligned16(X_q) && b200_aligned16(X_k), "%s: null or unaligned argument", op);
   if (num_tokens == 0) return 0;
-  rope_kernel<<<block_ops_grid(num_tokens, 16), ROPE_THREADS, 0, (cudaStream_t)stream>>>(
-      num_tokens, model_dim / 8, num_kv_heads * head_dim / 8, head_dim, (float)theta, sign, seq_positions, (uint4 *)X_q,
-      (uint4 *)X_k);
+  const int q_vec = model_dim / 8, k_vec = num_kv_heads * head_dim / 8;
+  const int lanes_vectors = (q_vec + 31) / 32 + (X_k ? (k_vec + 31) / 32 : 0);
+  if ((head_dim == 64 || head_dim == 128 || head_dim == 256) && lanes_vectors <= ROPE_MAX_VPL)
+    rope_warp_kernel<<<block_ops_grid((num_tokens + ROPE_WARPS - 1) / ROPE_WARPS, 16), ROPE_WARPS * 32, 0, (cudaStream_t)stream>>>(
+        num_tokens, q_vec, k_vec, head_dim, (float)theta, sign, seq_positions, (uint4 *)X_q, (uint4 *)X_k);
+  else
+    rope_kernel<<<block_ops_grid(num_tokens, 16), ROPE_THREADS, 0, (cudaStream_t)stream>>>(
+        num_tokens, q_vec, k_vec, head_dim, (float)theta, sign, seq_positions, (uint4 *)X_q, (uint4 *)X_k);
   B200_CHECK_LAUNCH(op);
   return 0;
 }
@@ -577,7 +868,7 @@ extern "C" int b200_softmax(int fwd_dt, int bwd_dt, int n_rows, int n_cols, cons
   B200_BF16_ONLY("softmax", bwd_dt);
   B200_REQUIRE(n_rows >= 0 && n_cols > 0 && X && out, "softmax: bad arguments");
   if (n_rows == 0) return 0;
-  softmax_kernel<<<block_ops_grid(n_rows, 4), SOFTMAX_THREADS, 0, (cudaStream_t)stream>>>(
+  softmax_kernel<<<block_ops_grid(n_rows, 1), SOFTMAX_THREADS, 0, (cudaStream_t)stream>>>(
       n_rows, n_cols, (const __nv_bfloat16 *)X, (__nv_bfloat16 *)out);
   B200_CHECK_LAUNCH("softmax");
   return 0;
@@ -637,9 +928,22 @@ extern "C" int b200_embedding_table(int fwd_dt, int num_unique_tokens, int embed
                       unique_token_sorted_inds_start, embedding_table, output))
     return -1;
   if (num_unique_tokens == 0) return 0;
-  embedding_kernel<<<block_ops_grid(num_unique_tokens, 8), 256, 0, (cudaStream_t)stream>>>(
-      num_unique_tokens, embed_dim / 8, sorted_token_ids, sorted_token_mapping, unique_token_sorted_inds_start,
-      (const uint4 *)embedding_table, (uint4 *)output);
+  const int dim_vec = embed_dim / 8;
+  const uint4 *tab = (const uint4 *)embedding_table;
+  uint4 *outv = (uint4 *)output;
+  cudaStream_t s = (cudaStream_t)stream;
+  const int wgrid = block_ops_grid((num_unique_tokens + EMB_WARPS - 1) / EMB_WARPS, 8);
+#define B200_EMB(V)                                                                                              \
+  embedding_warp_kernel<V><<<wgrid, EMB_WARPS * 32, 0, s>>>(num_unique_tokens, dim_vec, sorted_token_ids, sorted_token_mapping, \
+                                                           unique_token_sorted_inds_start, tab, outv)
+  if (dim_vec <= 64) B200_EMB(2);
+  else if (dim_vec <= 128) B200_EMB(4);
+  else if (dim_vec <= 256) B200_EMB(8);
+  else
+    embedding_kernel<<<block_ops_grid(num_unique_tokens, 8), 256, 0, s>>>(num_unique_tokens, dim_vec, sorted_token_ids,
+                                                                          sorted_token_mapping,
+                                                                          unique_token_sorted_inds_start, tab, outv);
+#undef B200_EMB
   B200_CHECK_LAUNCH("embedding_table");
   return 0;
 }
@@ -652,9 +956,21 @@ extern "C" int b200_embedding_table_bwd_w(int bwd_dt, int num_unique_tokens, int
                       unique_token_sorted_inds_start, grad_stream, grad_embedding_table))
     return -1;
   if (num_unique_tokens == 0) return 0;
-  embedding_bwd_w_kernel<<<block_ops_grid(num_unique_tokens, 8), 256, 0, (cudaStream_t)stream>>>(
-      num_unique_tokens, embed_dim / 8, sorted_token_ids, sorted_token_mapping, unique_token_sorted_inds_start,
-      (const uint4 *)grad_stream, (uint4 *)grad_embedding_table);
+  const int dim_vec = embed_dim / 8;
+  const uint4 *gs = (const uint4 *)grad_stream;
+  uint4 *gt = (uint4 *)grad_embedding_table;
+  cudaStream_t s = (cudaStream_t)stream;
+  const int wgrid = block_ops_grid((num_unique_tokens + EMB_WARPS - 1) / EMB_WARPS, 8);
+#define B200_EMBW(V)                                                                                                   \
+  embedding_bwd_w_warp_kernel<V><<<wgrid, EMB_WARPS * 32, 0, s>>>(num_unique_tokens, dim_vec, sorted_token_ids,            \
+                                                                 sorted_token_mapping, unique_token_sorted_inds_start, gs, gt)
+  if (dim_vec <= 64) B200_EMBW(2);
+  else if (dim_vec <= 128) B200_EMBW(4);
+  else if (dim_vec <= 256) B200_EMBW(8);
+  else
+    embedding_bwd_w_kernel<<<block_ops_grid(num_unique_tokens, 8), 256, 0, s>>>(
+        num_unique_tokens, dim_vec, sorted_token_ids, sorted_token_mapping, unique_token_sorted_inds_start, gs, gt);
+#undef B200_EMBW
   B200_CHECK_LAUNCH("embedding_table_bwd_w");
   return 0;
 }

@@ -324,13 +324,15 @@ def per_op_profile(layer, step, work, peaks, reps):
     import torch
 
     acc = {}
-    for _ in range(reps):
+    for it in range(reps + 1):
         layer.profile = []
         step()
         layer.mark("end")
         torch.cuda.synchronize()
         marks = layer.profile
         layer.profile = None
+        if it == 0:
+            continue  # the first marked step may set up communicators the timed path never used
         per_step = {}  # a phase that runs in slices is marked once per slice: sum inside the step
         for (name, ev), (_, nxt) in zip(marks[:-1], marks[1:]):
             per_step[name] = per_step.get(name, 0.0) + ev.elapsed_time(nxt)
@@ -702,7 +704,9 @@ def run_gpu_arm(args, world):
     line = dict(metric=METRIC, value=value, unit=UNIT, n_gpus=world, steps=steps, warmup=warmup, ms_per_step=ms_step,
                 higher_is_better=True, scaling="weak", vs_baseline=None, dtype="bf16", data="synthetic", impl="ours",
                 config=dict(workload=workload_name(cfg, world), T=T, d_model=d, experts=E, top_k=k, ffn=f,
-                            **({"exchange": transport} if world > 1 else {}),
+                            **({"exchange": transport, "per_op_times_from": "the Python driver of the same kernels (ep.py, events "
+                    "between the ops; its barriers are NCCL all-reduces where the C driver uses its own barrier kernel)"
+                    if transport == "c" else "the timed driver"} if world > 1 else {}),
                             l2="inputs exceed L2 (zone 2*T*k*d bytes per pass)"),
                 e2e=dict(value=e2e_value, unit=UNIT, h2d_bytes_per_step=io_bytes, d2h_bytes_per_step=io_bytes,
                          ms_per_step=ms_e2e, ratio_to_device_timed=round(e2e_value / value, 4),

@@ -546,7 +546,7 @@ int b200_moe_experts_bwd_x_scatter(int total_rows, int model_dim, int ffn_dim, i
  * epoch. `epoch` is a device word of this rank (zeroed once) that the kernel advances. payload (optional): payload_ints
  * ints that are stored into entry [rank][.] of every peer's payload array (peer_payload: int[world][payload_ints]
  * each) before the flag is raised - the counts exchange of the layer rides on its first barrier. The wait is bounded
- * (10 s unless b200_ep_set_barrier_timeout_ms says otherwise): a rank that never arrives raises status 1
+ * (2 s unless b200_ep_set_barrier_timeout_ms says otherwise): a rank that never arrives raises status 1
  * (b200_ep_status, which synchronises the device and clears the word) and the kernel returns; nothing hangs.
  * Every rank must issue the same sequence of barriers, and the ranks must be synchronised on the host once after
  * the flag arrays were zeroed.

@@ -38,6 +38,26 @@ def build(force=False, verbose=False):
     return LIB_PATH
 
 
+MICROBENCH = ["mma_queue_probe", "tma_feed_probe"]
+
+
+def build_microbench(force=False):
+    """The two stand-alone probes of the tensor pipe and the TMA feed (csrc/microbench/*.cu) as executables under
+    lib/microbench/ (built artefacts, not tracked). They measure the hardware figures the GEMM's design rests on."""
+    out_dir = os.path.join(LIB_DIR, "microbench")
+    os.makedirs(out_dir, exist_ok=True)
+    nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
+    paths = []
+    for name in MICROBENCH:
+        src, exe = os.path.join(CSRC, "microbench", name + ".cu"), os.path.join(out_dir, name)
+        newest = max(os.path.getmtime(src), os.path.getmtime(os.path.join(CSRC, "sm100_ptx.cuh")))
+        if force or not os.path.exists(exe) or os.path.getmtime(exe) < newest:
+            subprocess.check_call([nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+                                   "-o", exe, src])
+        paths.append(exe)
+    return paths
+
+
 ADAPTER_SRC = os.path.join(HERE, "backends", "nvidia", "b200_dataflow_ops.c")
 ADAPTER_PATH = os.path.join(LIB_DIR, "libb200moe_dataflow.so")
 

@@ -120,7 +120,7 @@ __global__ void ep_reduce_router_grad_kernel(EpPeers partials, int world, int64_
 
 using namespace b200;
 
-static unsigned long long g_ep_barrier_limit_ns = 10ull * 1000ull * 1000ull * 1000ull;
+static unsigned long long g_ep_barrier_limit_ns = 2ull * 1000ull * 1000ull * 1000ull;
 
 static int *ep_status_ptr() {
   static int *ptr[64];

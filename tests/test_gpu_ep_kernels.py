@@ -99,4 +99,4 @@ def test_barrier_gives_up_when_a_rank_never_arrives():
         # the device is still usable
         assert int((torch.ones(8, device="cuda") * 2).sum().item()) == 16
     finally:
-        lib.b200_ep_set_barrier_timeout_ms(10000)
+        lib.b200_ep_set_barrier_timeout_ms(2000)

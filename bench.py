@@ -465,6 +465,7 @@ def run_gpu_arm(args, world):
     dWr = torch.zeros_like(Wr)
     dW1, dW3, dW2 = torch.zeros_like(W1), torch.zeros_like(W3), torch.zeros_like(W2)
 
+    exchange_note = None
     block = layer.block(Wr, W1, W3, W2) if world == 1 else None
     ep_block = layer.c_block(Wr, W1, W3, W2) if transport == "c" else None
 
@@ -502,6 +503,18 @@ def run_gpu_arm(args, world):
     for _ in range(warmup):
         step(X, dOut, out, dXn)
     barrier()
+    if ep_block is not None:
+        # the C driver's barrier kernels give up after 2 s instead of hanging; if one did during warm-up on any rank,
+        # the Python driver of the same kernels (NCCL barriers) takes over and the line says so
+        bad = torch.tensor([ops.ep_status()], dtype=torch.int32, device=dev)
+        dist.all_reduce(bad, op=dist.ReduceOp.MAX)
+        if int(bad.item()) != 0:
+            ep_block = None
+            transport = "fused"
+            exchange_note = "the C driver's barrier timed out in warm-up; timed with the Python driver"
+            for _ in range(warmup):
+                step(X, dOut, out, dXn)
+            barrier()
     if not args.quick:
         # keep the GPUs busy until nvidia-smi has started sampling, so the clock record covers the timed region;
         # every rank runs the same number of extra steps (the step contains collectives when world > 1)
@@ -706,7 +719,8 @@ def run_gpu_arm(args, world):
                 config=dict(workload=workload_name(cfg, world), T=T, d_model=d, experts=E, top_k=k, ffn=f,
                             **({"exchange": transport, "per_op_times_from": "the Python driver of the same kernels (ep.py, events "
                     "between the ops; its barriers are NCCL all-reduces where the C driver uses its own barrier kernel)"
-                    if transport == "c" else "the timed driver"} if world > 1 else {}),
+                    if transport == "c" else "the timed driver",
+                    **({"exchange_note": exchange_note} if exchange_note else {})} if world > 1 else {}),
                             l2="inputs exceed L2 (zone 2*T*k*d bytes per pass)"),
                 e2e=dict(value=e2e_value, unit=UNIT, h2d_bytes_per_step=io_bytes, d2h_bytes_per_step=io_bytes,
                          ms_per_step=ms_e2e, ratio_to_device_timed=round(e2e_value / value, 4),

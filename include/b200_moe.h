@@ -7,14 +7,23 @@
  * stderr) - the convention of the reference's op submitters
  * (libdataflowops/src/submit_ops/moe_ops.c:30-36). Nothing here allocates
  * device memory: all buffers, scratch included, belong to the caller, as in
- * the reference where ops never allocate at submit time.
+ * the reference where ops never allocate at submit time. The one exception is
+ * b200_build_expert_mapping_static, whose scratch is an array inside the
+ * library (see there).
  *
- * Each declaration names the reference interface it stands in for
- * (paths are relative to the reference project root).
+ * Each declaration names the reference interface it stands in for (paths are
+ * relative to the reference project root) or says that the reference has no
+ * counterpart.
+ *
+ * Limits: the router and mapping ops take up to B200_MAX_EXPERTS experts; the grouped expert GEMMs
+ * (b200_moe_experts_*, b200_moe_block_*, b200_ep_moe_block_*) take up to 1024 experts per call (their group tables
+ * live in shared memory) and return -1 beyond; b200_build_expert_mapping_static additionally needs its tables to fit
+ * its 4 MiB array (64 experts always do; about 393 experts at large token counts).
  *
  * Threading: like the reference's op table (libdataflow/include/dataflow_table.h:6) the entry points expect one
- * submitting host thread per process and device; the library keeps small per-process caches (kernel attributes,
- * the address of its status word) that are filled on first use without locking.
+ * submitting host thread per process and device; the library keeps small caches per device ordinal (kernel
+ * attributes, SM count, the address of its status word on that device) that are filled on first use without locking,
+ * so one process may drive several devices by switching the current device between calls.
  *
  * Element types use the reference's DataflowDatatype numbering
  * (libdataflow/include/dataflow_common.h:46-74).
@@ -285,7 +294,10 @@ int b200_moe_experts_fwd(int total_rows, int model_dim, int ffn_dim, int num_exp
  *   (dx1, dx3) = swiglu'(x1, x3, dh);  hs = silu(x1)*x3 again if hs != NULL
  *   dZ     = dx1 W1 + dx3 W3           (must not alias dY_zone while dW2 is
  *                                       still to be computed from it)
- * dP must be zeroed by the caller (the kernel accumulates into it).
+ * dP must be zeroed by the caller (the kernel accumulates into it). The partial sums of a row come from several
+ * column tiles and are added with fp32 atomics, in whatever order the tiles finish: dP, and the router gradients
+ * formed from it, can differ in their last bits between two runs on the same inputs (the reference's router_bwd_x
+ * reduces each row inside one block in a fixed order). dx1, dx3, hs and dZ are bit-reproducible.
  */
 int b200_moe_experts_bwd_x(int total_rows, int model_dim, int ffn_dim, int num_experts, const void *dY_zone,
                            const float *row_weights, const void *x1, const void *x3, const void *W1,

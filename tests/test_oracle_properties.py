@@ -1,8 +1,8 @@
 """CPU: the oracle against independent statements of the same maths.
 
 The oracle (oracle/moe_oracle.c) is what every GPU kernel is compared with, so it is itself cross-checked here, on
-small cases, against (a) a literal pure-Python walk through the reference's selection rule as the survey of
-select_experts.cu:135-166 describes it (first k experts fill the slots in order; a later value must be strictly
+small cases, against (a) a literal pure-Python walk through the reference's selection rule, read off
+select_experts.cu:135-166 (first k experts fill the slots in order; a later value must be strictly
 greater than the running minimum to enter; it replaces the slot holding the minimum, ties among equal minima going to
 the slot with the larger expert index), (b) float64 numpy for the linear algebra, and (c) torch autograd on the CPU for
 the two hand-derived backward formulas (SwiGLU and the softmax-over-the-chosen-k gate). None of this needs a GPU.

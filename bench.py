@@ -277,7 +277,7 @@ def algorithmic_work(cfg):
         "prepare_experts_weighted": ("hbm", gather + 4 * R),
         "experts_bwd_x_gemm": ("tensor", 6 * R * d * f),
         "experts_bwd_w_gemm": ("tensor", 6 * R * d * f),
-        "unpermute": ("hbm", combine - 4 * R),
+        "unpermute": ("hbm", 2 * R * d + 2 * T * d + 4 * R),  # one pass that overwrites dXn: no read of the output
         "router_grad": ("hbm", 4 * R + 2 * T * E * 3 + 4 * T * d + 2 * T * d + 4 * E * d),
     }
 

@@ -153,6 +153,15 @@ int b200_merge_experts(int num_tokens, int model_dim, int top_k_experts, const v
                        void *stream);
 
 /*
+ * The un-permute of the backward in one pass: X_out[t, :] = bf16(sum_j zone[token_mapping[t, j], :]) (fp32 sum in slot
+ * order, one rounding), X_out is NOT read. The reference gets the same bits by zeroing dX and calling merge_experts
+ * with NULL weights (dataflow_transformer.c:3642-3660); this form saves the memset and the read of the zeros. No
+ * separate counterpart in the reference.
+ */
+int b200_unpermute_experts(int num_tokens, int model_dim, int top_k_experts, const void *expert_zones,
+                           const int *token_mapping, void *X_out, void *stream);
+
+/*
  * Replaces dataflow_submit_default_merge_expert_result (dataflow_ops.h:251-259;
  * moe/merge_expert_result.cu:3-115): one expert's read-modify-write combine.
  * num_tokens is that expert's row count, expert_zone its first row.
@@ -236,9 +245,10 @@ int b200_gemm_set_pair_mode(int on);
  * Work unit of the CTA-pair GEMMs: which kinds of launch let one fetch of the A rows feed two adjacent column tiles
  * (a 256 x 512 output block per CTA pair, a quarter fewer bytes staged per flop) - bit 0 the expert forward / dgrad
  * launches, bit 1 the expert weight gradients, bit 2 the dense matmul. A launch with too few units to fill the GPU
- * that way keeps one column tile per unit unless bit 3 is set. The environment variable B200_GEMM_WIDE=<0..15> sets the mask at
- * start-up. Results are identical either way (same MMAs per output element, same order). No counterpart in the
- * reference.
+ * that way keeps one column tile per unit unless bit 3 is set. Off by default (mask 0): with both accumulators of a unit
+ * finishing together the epilogue is not hidden, and no launch of the layer gains; the environment variable
+ * B200_GEMM_WIDE=<0..15> sets the mask at start-up. Results are identical either way (same MMAs per output element,
+ * same order). No counterpart in the reference.
  */
 int b200_gemm_set_wide_mode(int mask);
 

@@ -22,6 +22,7 @@ SIGNATURES = {
     "b200_prepare_experts_weighted": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp]),
     "b200_prepare_expert_zone": (_i, [_i, _vp, _i, _vp, _vp, _vp, _vp, _vp]),
     "b200_merge_experts": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp]),
+    "b200_unpermute_experts": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp]),
     "b200_merge_expert_result": (_i, [_i, _i, _i, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp]),
     "b200_router_bwd_x": (_i, [_i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "b200_router_gate_bwd_x": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp]),

@@ -304,8 +304,7 @@ extern "C" int b200_ep_moe_block_bwd(const B200EpMoeBlock *b, const void *Xn, co
       return -1;
   }
   if (ep_sync(b, nullptr, 0, stream)) return -1;
-  B200_CUDA(cudaMemsetAsync(dXn, 0, 2 * (size_t)T * d, s));
-  if (b200_merge_experts(T, d, k, b->dZ_home, b->token_mapping, nullptr, dXn, stream)) return -1;
+  if (b200_unpermute_experts(T, d, k, b->dZ_home, b->token_mapping, dXn, stream)) return -1;
   B200_CUDA(cudaMemsetAsync(b->dX_routed, 0, 2 * (size_t)T * E, s));
   if (b200_ep_gather_router_grad(T, k, b->token_expert_weights, b->token_mapping, b->chosen_experts, b->expert_counts,
                                  b->expert_counts_cumsum, b->dst_base, b->peer_dP, b->world, E, El, cap, b->dX_routed,

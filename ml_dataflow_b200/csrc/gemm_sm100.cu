@@ -1031,7 +1031,8 @@ static int pair_mode() {
 // Environment variable B200_GEMM_WIDE on first use; b200_gemm_set_wide_mode overrides it.
 constexpr int WIDE_GROUPED_M = 1, WIDE_GROUPED_K = 2, WIDE_DENSE = 4, WIDE_ALWAYS = 8;
 #ifndef B200_GEMM_WIDE_DEFAULT
-#define B200_GEMM_WIDE_DEFAULT (WIDE_GROUPED_K | WIDE_DENSE)
+#define B200_GEMM_WIDE_DEFAULT 0  // measured: no launch kind of the layer gains from it (forward 864 -> 794, weight
+                                  // gradients 904 -> 884 TFLOP/s at 4096 rows per expert, sustained, real data)
 #endif
 static int g_wide_mode = -1;
 

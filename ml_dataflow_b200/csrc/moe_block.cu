@@ -92,9 +92,8 @@ extern "C" int b200_moe_block_bwd(const B200MoeBlock *b, const void *Xn, const v
                                b->expert_counts_cumsum, stream))
       return -1;
   }
-  // un-permute into a zeroed dXn (3666-3682)
-  B200_CUDA(cudaMemsetAsync(dXn, 0, 2 * (size_t)T * d, s));
-  if (b200_merge_experts(T, d, k, b->dZ, b->token_mapping, nullptr, dXn, stream)) return -1;
+  // un-permute (3666-3682: merge_experts onto a zeroed dXn there; here one pass that overwrites, same bits)
+  if (b200_unpermute_experts(T, d, k, b->dZ, b->token_mapping, dXn, stream)) return -1;
   // router: dP -> [T][E] on the chosen columns, gate Jacobian, then the two router GEMMs (3707-3719, 4174-4185)
   B200_CUDA(cudaMemsetAsync(b->dX_routed, 0, 2 * (size_t)T * E, s));
   if (b200_gather_router_grad(T, E, k, b->token_mapping, b->chosen_experts, b->dP, b->dX_routed, stream)) return -1;

@@ -406,8 +406,7 @@ class ExpertParallelMoELayer:
             self.mark("return_bwd")
             self._barrier()
             self.mark("unpermute")
-            dXn.zero_()
-            ops.merge_experts(T, d, k, self.dZ_h, hm.token_mapping, None, dXn)
+            ops.unpermute_experts(T, d, k, self.dZ_h, hm.token_mapping, dXn)
             self.mark("router_grad")
             hm.dX_routed.zero_()
             ops.ep_gather_router_grad(T, k, hm.weights, hm.token_mapping, hm.chosen, hm.counts, hm.cumsum, x.dst_base,

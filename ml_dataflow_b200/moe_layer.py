@@ -130,8 +130,7 @@ class MoELayer:
         ops.moe_experts_bwd_w(R, d, f, E, self.dYz, self.h, self.zone, self.dx1, self.dx3, dW1, dW3, dW2,
                               f * d, f * d, d * f, self.counts, self.cumsum)
         self.mark("unpermute")
-        dXn.zero_()
-        ops.merge_experts(T, d, k, self.dZ, self.token_mapping, None, dXn)
+        ops.unpermute_experts(T, d, k, self.dZ, self.token_mapping, dXn)
         self.mark("router_grad")
         self.dX_routed.zero_()
         ops.gather_router_grad(T, E, k, self.token_mapping, self.chosen, self.dP, self.dX_routed)

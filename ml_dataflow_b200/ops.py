@@ -114,6 +114,12 @@ def merge_experts(num_tokens, model_dim, top_k_experts, expert_zones, token_mapp
                                           _p(token_expert_weights), _p(X_combined), _stream()), "merge_experts")
 
 
+def unpermute_experts(num_tokens, model_dim, top_k_experts, expert_zones, token_mapping, X_out):
+    """X_out[t] = sum of the token's k zone rows (overwrites; the backward's un-permute without the memset)."""
+    _check(_lib.load().b200_unpermute_experts(num_tokens, model_dim, top_k_experts, _p(expert_zones), _p(token_mapping),
+                                              _p(X_out), _stream()), "unpermute_experts")
+
+
 def merge_expert_result(num_tokens, model_dim, top_k_experts, expert_zone, expert_id, expert_counts_cumsum,
                         expert_mapping, token_expert_weights, chosen_experts, X_combined):
     _check(_lib.load().b200_merge_expert_result(num_tokens, model_dim, top_k_experts, _p(expert_zone), expert_id,

@@ -13,7 +13,7 @@ from helpers import assert_close, assert_close_with_slack, bf16_bits_to_f32
 pytestmark = pytest.mark.gpu
 
 
-DEFAULT_WIDE_MASK = 6  # the library default: weight gradients and dense launches, when the launch is large enough
+DEFAULT_WIDE_MASK = 0  # the library default: one column tile per unit everywhere
 
 
 @pytest.fixture(params=["pair", "wide", "single"], autouse=True)

@@ -42,6 +42,27 @@ def test_prepare_and_merge(oracle, T, d, E, k):
         assert_close(bf16_bits_to_f32(host_bits(out)), bf16_bits_to_f32(ref), rtol=1e-2, atol=1e-3, what="merge")
 
 
+@pytest.mark.parametrize("T,d,E,k", [(1, 8, 2, 1), (300, 1024, 16, 2), (257, 4096, 64, 8)])
+def test_unpermute_overwrites_with_the_bits_of_merge_onto_zeros(oracle, T, d, E, k):
+    """The backward's un-permute in one pass (no read of the output, no memset) against the reference's sequence:
+    zero dX, merge_experts with NULL weights - bit for bit, and against the oracle."""
+    require_b200()
+    from ml_dataflow_b200 import ops
+
+    rng = np.random.default_rng(T + d)
+    _, _, _, _, _, _, tm = routing(oracle, rng, T, E, k)
+    dZ = rand_bf16(rng, (T * k, d))
+    tmd, dZd = dev(tm), dev_bf16(dZ)
+    two_pass = torch.zeros((T, d), dtype=torch.bfloat16, device="cuda")
+    ops.merge_experts(T, d, k, dZd, tmd, None, two_pass)
+    one_pass = dev_bf16(rand_bf16(rng, (T, d)))  # garbage that must not show through
+    ops.unpermute_experts(T, d, k, dZd, tmd, one_pass)
+    torch.cuda.synchronize()
+    assert torch.equal(one_pass, two_pass)
+    ref = oracle.merge_experts(dZ, tm, None, np.zeros((T, d), np.uint16))
+    assert_close(bf16_bits_to_f32(host_bits(one_pass)), bf16_bits_to_f32(ref), rtol=1e-2, atol=1e-3, what="unpermute")
+
+
 def test_per_expert_zone_and_merge_result(oracle):
     require_b200()
     from ml_dataflow_b200 import ops

@@ -226,6 +226,17 @@ int b200_matmul(int a_dt, int b_dt, int c_dt, int d_dt, int to_trans_a, int to_t
                 uint64_t workspaceBytes, void *workspace, void *stream);
 
 /*
+ * The same product on operands that are slices of larger row-major arrays (one head of a [tokens][heads * head_dim]
+ * tensor, a score matrix with a padded row pitch): lda, ldb, ldd are the row pitches in elements of A, B and of
+ * C = D as stored, multiples of 8. M (the output's column count) must be a multiple of 8 but only a_m_extent of A's M
+ * rows / columns need exist: the rest reads as zeros, so a ragged key count can be rounded up without touching memory
+ * past the slice. K and N are free. No split reduction. No counterpart in the reference (its matmul op is packed).
+ */
+int b200_matmul_strided(int a_dt, int b_dt, int c_dt, int d_dt, int to_trans_a, int to_trans_b, int M, int K, int N,
+                        float alpha, float beta, const void *A, int64_t lda, int a_m_extent, const void *B, int64_t ldb,
+                        const void *C, void *D, int64_t ldd, void *stream);
+
+/*
  * The GEMM kernels bound every wait on a barrier (about 2 s). A kernel that gives up records a
  * non-zero code here and returns without finishing its tiles. This call synchronises the
  * device, reports the code (0 = none) and clears it. The reference has no counterpart: its
@@ -735,6 +746,38 @@ int b200_embedding_table(int fwd_dt, int num_unique_tokens, int embed_dim, const
 int b200_embedding_table_bwd_w(int bwd_dt, int num_unique_tokens, int embed_dim, const uint32_t *sorted_token_ids,
                                const uint32_t *sorted_token_mapping, const uint32_t *unique_token_sorted_inds_start,
                                const void *grad_stream, void *grad_embedding_table, void *stream);
+
+/*
+ * ---- attention ------------------------------------------------------------------------------------------------
+ *
+ * dataflow_submit_attention / dataflow_submit_attention_bwd (libdataflowops/include/dataflow_ops.h:70-105), which the
+ * reference forwards to an external flash-attention library (backends/nvidia/src/ops/src/external/attention_helper):
+ * softmax(Q K^T / sqrt(head_dim)) V per sequence and head over packed variable-length sequences, grouped query heads
+ * (query head h reads key / value head h / (num_q_heads / num_kv_heads)), optionally causal with the last query of a
+ * sequence aligned to its last key. x_q, x_attn_out, dx_out, dx_q: [total_q][num_q_heads * head_dim]; x_k, x_v, dx_k,
+ * dx_v: [total_k][num_kv_heads * head_dim]; softmax_lse: fp32 [num_q_heads][total_q] (log-sum-exp of the scaled
+ * scores, written by the forward, read by the backward). bf16 only.
+ *
+ * Differences from the reference's signature: the sequence offsets and lengths are HOST arrays here (the calls are
+ * issued per sequence and head from the host); dx_q / dx_k / dx_v are overwritten. This first form is not fused: it
+ * runs this library's tensor-core GEMMs on head slices with the score matrix of one (sequence, head) in the workspace
+ * (b200_attention_workspace_bytes: max_seqlen_q x max_seqlen_k x 6 bytes, plus two fp32 key / value gradient
+ * accumulators when is_training); the arithmetic (fp32 scores and statistics, probabilities rounded to bf16 before
+ * they multiply V or dO, fp32 accumulation, one rounding per output, probabilities re-formed from the log-sum-exp in
+ * the backward) is that of the published algorithm.
+ */
+uint64_t b200_attention_workspace_bytes(int is_training, int max_seqlen_q, int max_seqlen_k, int head_dim);
+
+int b200_attention_fwd(int fwd_dt, int num_seqs, int total_q, int total_k, const int *q_seq_offsets, const int *q_seq_lens,
+                       int max_seqlen_q, const int *k_seq_offsets, const int *k_seq_lens, int max_seqlen_k, int num_q_heads,
+                       int num_kv_heads, int head_dim, const void *x_q, const void *x_k, const void *x_v, void *x_attn_out,
+                       float *softmax_lse, int is_causal, uint64_t workspaceBytes, void *workspace, void *stream);
+
+int b200_attention_bwd(int bwd_dt, int num_seqs, int total_q, int total_k, const int *q_seq_offsets, const int *q_seq_lens,
+                       int max_seqlen_q, const int *k_seq_offsets, const int *k_seq_lens, int max_seqlen_k, int num_q_heads,
+                       int num_kv_heads, int head_dim, const void *x_q, const void *x_k, const void *x_v,
+                       const void *x_attn_out, const float *softmax_lse, const void *dx_out, void *dx_q, void *dx_k,
+                       void *dx_v, int is_causal, uint64_t workspaceBytes, void *workspace, void *stream);
 
 #ifdef __cplusplus
 }

@@ -29,6 +29,7 @@ SIGNATURES = {
     "b200_swiglu": (_i, [_i, _i, _vp, _vp, _vp, _vp]),
     "b200_swiglu_bwd_x": (_i, [_i, _i, _vp, _vp, _vp, _vp, _vp, _vp]),
     "b200_matmul": (_i, [_i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _f, _vp, _vp, _vp, _vp, _u64, _vp, _vp]),
+    "b200_matmul_strided": (_i, [_i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _f, _vp, _i64, _i, _vp, _i64, _vp, _vp, _i64, _vp]),
     "b200_gemm_status": (_i, [_vp]),
     "b200_gemm_set_pair_mode": (_i, [_i]),
     "b200_gemm_set_wide_mode": (_i, [_i]),
@@ -77,6 +78,10 @@ SIGNATURES = {
     "b200_adamw_step": (_i, [_i, _i, _i, _i, _u64, _i, _f, _f, _f, _f, _f, _vp, _vp, _vp, _vp, _vp]),
     "b200_embedding_table": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp]),
     "b200_embedding_table_bwd_w": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "b200_attention_workspace_bytes": (_u64, [_i, _i, _i, _i]),
+    "b200_attention_fwd": (_i, [_i, _i, _i, _i, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _i, _u64, _vp, _vp]),
+    "b200_attention_bwd": (_i, [_i, _i, _i, _i, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp,
+                                _vp, _i, _u64, _vp, _vp]),
     "b200_scatter_row_weights": (_i, [_i, _i, _vp, _vp, _vp, _vp]),
     "b200_gather_router_grad": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp]),
 }

@@ -1252,9 +1252,17 @@ extern "C" int b200_gemm_status(int *status_out) {
   return 0;
 }
 
-extern "C" int b200_matmul(int a_dt, int b_dt, int c_dt, int d_dt, int to_trans_a, int to_trans_b, int M, int K, int N,
-                           float alpha, float beta, const void *A, const void *B, const void *C, void *D,
-                           uint64_t workspaceBytes, void *workspace, void *stream) {
+// lda / ldb / ldd: row pitches in elements of A, B and of C = D as stored (0 = packed); a_m_extent: how many of A's M
+// rows (or columns, when A is stored [K][M]) exist in memory, the rest of M reads as zeros (0 = all M).
+static int matmul_impl(int a_dt, int b_dt, int c_dt, int d_dt, int to_trans_a, int to_trans_b, int M, int K, int N,
+                       float alpha, float beta, const void *A, const void *B, const void *C, void *D,
+                       uint64_t workspaceBytes, void *workspace, int64_t lda, int64_t ldb, int64_t ldd, int a_m_extent,
+                       void *stream) {
+  const bool packed = lda == 0 && ldb == 0 && ldd == 0 && a_m_extent == 0;
+  if (lda == 0) lda = to_trans_a ? K : M;
+  if (ldb == 0) ldb = to_trans_b ? N : K;
+  if (ldd == 0) ldd = M;
+  if (a_m_extent == 0) a_m_extent = M;
   B200_REQUIRE(a_dt == B200_DT_BF16 && b_dt == B200_DT_BF16, "matmul: A and B must be bf16 (got %d, %d)", a_dt, b_dt);
   B200_REQUIRE(d_dt == B200_DT_BF16 || d_dt == B200_DT_FP32, "matmul: D must be bf16 or fp32 (got %d)", d_dt);
   const bool use_c = (C != nullptr) && (c_dt != B200_DT_NONE) && (beta != 0.0f);
@@ -1262,8 +1270,11 @@ extern "C" int b200_matmul(int a_dt, int b_dt, int c_dt, int d_dt, int to_trans_
   B200_REQUIRE(M > 0 && N > 0 && K > 0, "matmul: M, K, N must be positive (got %d, %d, %d)", M, K, N);
   // every dimension that is the contiguous one of some operand must keep rows 16-byte aligned
   B200_REQUIRE(M % 8 == 0, "matmul: M must be a multiple of 8 (got %d)", M);
-  B200_REQUIRE(!(to_trans_a || !to_trans_b) || K % 8 == 0, "matmul: K must be a multiple of 8 for this layout (got %d)", K);
-  B200_REQUIRE(!to_trans_b || N % 8 == 0, "matmul: N must be a multiple of 8 when B is transposed (got %d)", N);
+  B200_REQUIRE(lda % 8 == 0 && ldb % 8 == 0 && ldd % 8 == 0 && lda >= (to_trans_a ? K : a_m_extent) &&
+                   ldb >= (to_trans_b ? N : K) && ldd >= M && a_m_extent >= 1 && a_m_extent <= M,
+               "matmul: the contiguous dimension of every operand (or its row pitch) must be a multiple of 8 elements and "
+               "cover the row (M %d, K %d, N %d, pitches %lld, %lld, %lld)", M, K, N, (long long)lda, (long long)ldb,
+               (long long)ldd);
   B200_REQUIRE(A && B && D, "matmul: null operand");
   B200_REQUIRE(b200_aligned16(D) && b200_aligned16(C), "matmul: C and D must be 16-byte aligned");
 
@@ -1284,16 +1295,17 @@ extern "C" int b200_matmul(int a_dt, int b_dt, int c_dt, int d_dt, int to_trans_
   p.c_fp32 = c_dt == B200_DT_FP32;
   p.D = D;
   p.C = use_c ? C : nullptr;
-  p.ldd = M;
+  p.ldd = ldd;
   if (p.a_mn_major) {
-    if (make_tmap(&p.tmA, B, 2, (uint64_t)N, (uint64_t)K, 1, (uint64_t)N * 2, 0)) return -1;
+    if (make_tmap(&p.tmA, B, 2, (uint64_t)N, (uint64_t)K, 1, (uint64_t)ldb * 2, 0)) return -1;
   } else {
-    if (make_tmap(&p.tmA, B, 2, (uint64_t)K, (uint64_t)N, 1, (uint64_t)K * 2, 0)) return -1;
+    if (make_tmap(&p.tmA, B, 2, (uint64_t)K, (uint64_t)N, 1, (uint64_t)ldb * 2, 0)) return -1;
   }
   if (p.b_mn_major) {
-    if (make_tmap(&p.tmB, A, 3, (uint64_t)M, (uint64_t)K, 1, (uint64_t)M * 2, (uint64_t)M * K * 2)) return -1;
+    if (make_tmap(&p.tmB, A, 3, (uint64_t)a_m_extent, (uint64_t)K, 1, (uint64_t)lda * 2, (uint64_t)lda * K * 2)) return -1;
   } else {
-    if (make_tmap(&p.tmB, A, 3, (uint64_t)K, (uint64_t)M, 1, (uint64_t)K * 2, (uint64_t)M * K * 2)) return -1;
+    if (make_tmap(&p.tmB, A, 3, (uint64_t)K, (uint64_t)a_m_extent, 1, (uint64_t)lda * 2, (uint64_t)lda * a_m_extent * 2))
+      return -1;
   }
   p.tmA2 = p.tmA;
   p.tmB2 = p.tmB;
@@ -1306,7 +1318,7 @@ extern "C" int b200_matmul(int a_dt, int b_dt, int c_dt, int d_dt, int to_trans_
   const int sms = sm_count_cached();
   const int64_t units = (pair_ok && pair_mode()) ? sms / 2 : sms;
   int splits = 1;
-  if (workspace != nullptr && b200_aligned16(workspace) && launched_tiles * 2 <= units && K >= 2048 && M % 4 == 0) {
+  if (packed && workspace != nullptr && b200_aligned16(workspace) && launched_tiles * 2 <= units && K >= 2048 && M % 4 == 0) {
     splits = (int)std::min<int64_t>(std::min<int64_t>(units / launched_tiles, K / 1024), 16);
     const uint64_t per_split = (uint64_t)N * M * sizeof(float);
     if ((uint64_t)splits * per_split > workspaceBytes) splits = (int)(workspaceBytes / per_split);
@@ -1329,6 +1341,23 @@ extern "C" int b200_matmul(int a_dt, int b_dt, int c_dt, int d_dt, int to_trans_
       c_dt == B200_DT_FP32, D, d_dt == B200_DT_FP32);
   B200_CHECK_LAUNCH("matmul split-k reduce");
   return 0;
+}
+
+extern "C" int b200_matmul(int a_dt, int b_dt, int c_dt, int d_dt, int to_trans_a, int to_trans_b, int M, int K, int N,
+                           float alpha, float beta, const void *A, const void *B, const void *C, void *D,
+                           uint64_t workspaceBytes, void *workspace, void *stream) {
+  B200_REQUIRE(!(to_trans_a || !to_trans_b) || K % 8 == 0, "matmul: K must be a multiple of 8 for this layout (got %d)", K);
+  B200_REQUIRE(!to_trans_b || N % 8 == 0, "matmul: N must be a multiple of 8 when B is transposed (got %d)", N);
+  return matmul_impl(a_dt, b_dt, c_dt, d_dt, to_trans_a, to_trans_b, M, K, N, alpha, beta, A, B, C, D, workspaceBytes,
+                     workspace, 0, 0, 0, 0, stream);
+}
+
+extern "C" int b200_matmul_strided(int a_dt, int b_dt, int c_dt, int d_dt, int to_trans_a, int to_trans_b, int M, int K, int N,
+                                   float alpha, float beta, const void *A, int64_t lda, int a_m_extent, const void *B,
+                                   int64_t ldb, const void *C, void *D, int64_t ldd, void *stream) {
+  B200_REQUIRE(lda > 0 && ldb > 0 && ldd > 0 && a_m_extent > 0, "matmul_strided: pitches and extent must be positive");
+  return matmul_impl(a_dt, b_dt, c_dt, d_dt, to_trans_a, to_trans_b, M, K, N, alpha, beta, A, B, C, D, 0, nullptr, lda, ldb,
+                     ldd, a_m_extent, stream);
 }
 
 static int check_grouped(const char *op, int total_rows, int model_dim, int ffn_dim, int num_experts,

@@ -370,3 +370,33 @@ def embedding_table_bwd_w(num_unique_tokens, embed_dim, sorted_token_ids, sorted
     _check(_lib.load().b200_embedding_table_bwd_w(DT_BF16, num_unique_tokens, embed_dim, _p(sorted_token_ids),
                                                   _p(sorted_token_mapping), _p(unique_token_sorted_inds_start),
                                                   _p(grad_stream), _p(grad_table), _stream()), "embedding_table_bwd_w")
+
+
+# ---- attention (packed variable-length sequences; sequence offsets / lengths are host lists) ------------------------
+def _int_array(values):
+    return (C.c_int * len(values))(*[int(v) for v in values])
+
+
+def attention_workspace_bytes(is_training, max_seqlen_q, max_seqlen_k, head_dim):
+    return int(_lib.load().b200_attention_workspace_bytes(int(bool(is_training)), max_seqlen_q, max_seqlen_k, head_dim))
+
+
+def attention_fwd(q_offsets, q_lens, k_offsets, k_lens, num_q_heads, num_kv_heads, head_dim, x_q, x_k, x_v, x_attn_out,
+                  softmax_lse, is_causal, workspace):
+    n = len(q_lens)
+    _check(_lib.load().b200_attention_fwd(DT_BF16, n, x_q.shape[0], x_k.shape[0], _int_array(q_offsets), _int_array(q_lens),
+                                          max(q_lens), _int_array(k_offsets), _int_array(k_lens), max(k_lens), num_q_heads,
+                                          num_kv_heads, head_dim, _p(x_q), _p(x_k), _p(x_v), _p(x_attn_out), _p(softmax_lse),
+                                          int(bool(is_causal)), workspace.numel() * workspace.element_size(), _p(workspace),
+                                          _stream()), "attention_fwd", 3 * n * num_q_heads)
+
+
+def attention_bwd(q_offsets, q_lens, k_offsets, k_lens, num_q_heads, num_kv_heads, head_dim, x_q, x_k, x_v, x_attn_out,
+                  softmax_lse, dx_out, dx_q, dx_k, dx_v, is_causal, workspace):
+    n = len(q_lens)
+    _check(_lib.load().b200_attention_bwd(DT_BF16, n, x_q.shape[0], x_k.shape[0], _int_array(q_offsets), _int_array(q_lens),
+                                          max(q_lens), _int_array(k_offsets), _int_array(k_lens), max(k_lens), num_q_heads,
+                                          num_kv_heads, head_dim, _p(x_q), _p(x_k), _p(x_v), _p(x_attn_out), _p(softmax_lse),
+                                          _p(dx_out), _p(dx_q), _p(dx_k), _p(dx_v), int(bool(is_causal)),
+                                          workspace.numel() * workspace.element_size(), _p(workspace), _stream()),
+           "attention_bwd", n * (9 * num_q_heads + 2 * num_kv_heads))

@@ -221,3 +221,110 @@ void orc_embedding_table_bwd_w_bf16(int num_unique_tokens, int embed_dim, const 
     }
   }
 }
+
+/* ---- attention ------------------------------------------------------------------------------------------------- */
+
+/* The op the reference takes from an external flash-attention library (dataflow_ops.h:70-105; flash-attention 2 / 3,
+ * Dao et al.): per sequence and query head, softmax(Q K^T / sqrt(d)) V with fp32 scores and statistics, probabilities
+ * rounded to bf16 before they multiply V, fp32 accumulation and one rounding of O; causal = the last query of a
+ * sequence sees every key, query i sees keys up to i + (Tk - Tq). Query head h reads key / value head
+ * h / (Hq / Hkv). lse[h][total_q] = log-sum-exp of the scaled scores. Parity unpinned: the library is not in the
+ * reference tree; this restates the published algorithm (tests check it against float64 softmax attention). */
+static int attn_vis(int i, int Tq, int Tk, int causal) {
+  if (!causal) return Tk;
+  int v = i + 1 + (Tk - Tq);
+  return v < 0 ? 0 : (v > Tk ? Tk : v);
+}
+
+void orc_attention_fwd_bf16(int num_seqs, int total_q, const int *q_off, const int *q_len, const int *k_off, const int *k_len,
+                            int Hq, int Hkv, int hd, const uint16_t *Q, const uint16_t *K, const uint16_t *V, uint16_t *O,
+                            float *lse, int causal) {
+  const int group = Hq / Hkv;
+  const float scale = 1.0f / sqrtf((float)hd);
+  const size_t Dq = (size_t)Hq * hd, Dk = (size_t)Hkv * hd;
+  for (int s = 0; s < num_seqs; s++) {
+    const int Tq = q_len[s], Tk = k_len[s];
+#pragma omp parallel for collapse(2) schedule(dynamic)
+    for (int h = 0; h < Hq; h++) {
+      for (int i = 0; i < Tq; i++) {
+        const int vis = attn_vis(i, Tq, Tk, causal);
+        const uint16_t *q = Q + (size_t)(q_off[s] + i) * Dq + (size_t)h * hd;
+        float *sc = (float *)malloc(sizeof(float) * (size_t)(vis > 0 ? vis : 1));
+        float m = -INFINITY;
+        for (int j = 0; j < vis; j++) {
+          const uint16_t *k = K + (size_t)(k_off[s] + j) * Dk + (size_t)(h / group) * hd;
+          float acc = 0.0f;
+          for (int c = 0; c < hd; c++) acc += b2f(q[c]) * b2f(k[c]);
+          sc[j] = acc * scale;
+          m = fmaxf(m, sc[j]);
+        }
+        double sum = 0.0;
+        for (int j = 0; j < vis; j++) sum += (double)expf(sc[j] - m);
+        uint16_t *o = O + (size_t)(q_off[s] + i) * Dq + (size_t)h * hd;
+        for (int j = 0; j < vis; j++) sc[j] = b2f(f2b(expf(sc[j] - m) / (float)sum)); /* the probability as bf16 */
+        for (int c = 0; c < hd; c++) {
+          float acc = 0.0f;
+          for (int j = 0; j < vis; j++) acc += sc[j] * b2f(V[(size_t)(k_off[s] + j) * Dk + (size_t)(h / group) * hd + c]);
+          o[c] = f2b(acc);
+        }
+        lse[(size_t)h * total_q + q_off[s] + i] = vis > 0 ? m + logf((float)sum) : -INFINITY;
+        free(sc);
+      }
+    }
+  }
+}
+
+/* Backward of the same: P = exp(S - lse) (bf16 where it multiplies dO), dP = dO V^T, delta_i = sum_c dO O,
+ * dS = P (dP - delta) (bf16 where it multiplies K and Q), dQ = scale dS K, dK = scale dS^T Q, dV = P^T dO; the key /
+ * value gradients are summed in fp32 over the query heads of a group and rounded once. dQ, dK, dV are overwritten. */
+void orc_attention_bwd_bf16(int num_seqs, int total_q, int total_k, const int *q_off, const int *q_len, const int *k_off,
+                            const int *k_len, int Hq, int Hkv, int hd, const uint16_t *Q, const uint16_t *K,
+                            const uint16_t *V, const uint16_t *O, const float *lse, const uint16_t *dO, uint16_t *dQ,
+                            uint16_t *dK, uint16_t *dV, int causal) {
+  const int group = Hq / Hkv;
+  const float scale = 1.0f / sqrtf((float)hd);
+  const size_t Dq = (size_t)Hq * hd, Dk = (size_t)Hkv * hd;
+  float *aK = (float *)calloc((size_t)total_k * Dk, sizeof(float));
+  float *aV = (float *)calloc((size_t)total_k * Dk, sizeof(float));
+  for (int s = 0; s < num_seqs; s++) {
+    const int Tq = q_len[s], Tk = k_len[s];
+#pragma omp parallel for schedule(dynamic)
+    for (int g = 0; g < Hkv; g++) { /* one thread owns the accumulators of a key / value head */
+      for (int h = g * group; h < (g + 1) * group; h++) {
+        for (int i = 0; i < Tq; i++) {
+          const int vis = attn_vis(i, Tq, Tk, causal);
+          const size_t qo = (size_t)(q_off[s] + i) * Dq + (size_t)h * hd;
+          const float l = lse[(size_t)h * total_q + q_off[s] + i];
+          float delta = 0.0f;
+          for (int c = 0; c < hd; c++) delta += b2f(dO[qo + c]) * b2f(O[qo + c]);
+          float *dq = (float *)calloc((size_t)hd, sizeof(float));
+          for (int j = 0; j < vis; j++) {
+            const size_t ko = (size_t)(k_off[s] + j) * Dk + (size_t)g * hd;
+            float sc = 0.0f, dp = 0.0f;
+            for (int c = 0; c < hd; c++) {
+              sc += b2f(Q[qo + c]) * b2f(K[ko + c]);
+              dp += b2f(dO[qo + c]) * b2f(V[ko + c]);
+            }
+            const float p = b2f(f2b(expf(sc * scale - l)));
+            const float ds = b2f(f2b(p * (dp - delta)));
+            for (int c = 0; c < hd; c++) {
+              aV[ko + c] += p * b2f(dO[qo + c]);
+              aK[ko + c] += scale * ds * b2f(Q[qo + c]);
+              dq[c] += ds * b2f(K[ko + c]);
+            }
+          }
+          for (int c = 0; c < hd; c++) dQ[qo + c] = f2b(scale * dq[c]);
+          free(dq);
+        }
+      }
+    }
+    for (int j = 0; j < Tk; j++)
+      for (size_t c = 0; c < Dk; c++) {
+        const size_t o = (size_t)(k_off[s] + j) * Dk + c;
+        dK[o] = f2b(aK[o]);
+        dV[o] = f2b(aV[o]);
+      }
+  }
+  free(aK);
+  free(aV);
+}

@@ -388,3 +388,21 @@ def embedding_table_bwd_w(sorted_ids, mapping, starts, grad_stream, grad_table):
     lib().orc_embedding_table_bwd_w_bf16(len(starts) - 1, grad_table.shape[1], _p(sorted_ids), _p(mapping), _p(starts),
                                          _p(grad_stream), _p(grad_table))
     return grad_table
+
+
+def attention_fwd(q_off, q_len, k_off, k_len, Hq, Hkv, hd, Q, K, V, causal=True):
+    """Returns (O bf16 bits [total_q, Hq*hd], lse float32 [Hq, total_q])."""
+    O = np.zeros_like(Q)
+    lse = np.zeros((Hq, Q.shape[0]), np.float32)
+    ia = lambda a: _p(np.ascontiguousarray(a, np.int32))
+    lib().orc_attention_fwd_bf16(len(q_len), Q.shape[0], ia(q_off), ia(q_len), ia(k_off), ia(k_len), Hq, Hkv, hd, _p(Q), _p(K),
+                                 _p(V), _p(O), _p(lse), int(bool(causal)))
+    return O, lse
+
+
+def attention_bwd(q_off, q_len, k_off, k_len, Hq, Hkv, hd, Q, K, V, O, lse, dO, causal=True):
+    dQ, dK, dV = np.zeros_like(Q), np.zeros_like(K), np.zeros_like(V)
+    ia = lambda a: _p(np.ascontiguousarray(a, np.int32))
+    lib().orc_attention_bwd_bf16(len(q_len), Q.shape[0], K.shape[0], ia(q_off), ia(q_len), ia(k_off), ia(k_len), Hq, Hkv, hd,
+                                 _p(Q), _p(K), _p(V), _p(O), _p(lse), _p(dO), _p(dQ), _p(dK), _p(dV), int(bool(causal)))
+    return dQ, dK, dV

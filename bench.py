@@ -183,6 +183,34 @@ def block_ops_profile(dev, peaks, iters=5):
         t = sorted(ms)[len(ms) // 2]
         gbs = nbytes / (t * 1e-3) / 1e9
         res[name] = dict(ms=round(t, 4), bound="hbm", achieved=round(gbs, 1), unit="GB/s", frac=round(gbs / peaks["hbm_gbs"], 4))
+    # attention at the decoder step's shape: one sequence of 8192 tokens, 16 query / 4 key-value heads of 128, causal.
+    # Useful flop: two products over the visible half of the score matrix forward, five backward.
+    del X, up, dX, out, q, kk, par, grad, mean, var, table, gtab, emb
+    torch.cuda.empty_cache()
+    Ta, Hq, Hkv, hd = 8192, c["heads"], c["kv_heads"], c["head_dim"]
+    aq, ak, av = bf((Ta, Hq * hd)), bf((Ta, Hkv * hd)), bf((Ta, Hkv * hd))
+    ao, ado = torch.empty_like(aq), bf((Ta, Hq * hd))
+    adq, adk, adv = torch.empty_like(aq), torch.empty_like(ak), torch.empty_like(av)
+    alse = torch.empty((Hq, Ta), dtype=torch.float32, device=dev)
+    aws = torch.empty(ops.attention_workspace_bytes(True, Ta, Ta, hd), dtype=torch.uint8, device=dev)
+    fwd_flop = 2 * 2 * Ta * Ta * hd * Hq / 2
+    for name, fn, flop in (
+            ("attention_fwd", lambda: ops.attention_fwd([0], [Ta], [0], [Ta], Hq, Hkv, hd, aq, ak, av, ao, alse, True, aws), fwd_flop),
+            ("attention_bwd", lambda: ops.attention_bwd([0], [Ta], [0], [Ta], Hq, Hkv, hd, aq, ak, av, ao, alse, ado, adq, adk,
+                                                        adv, True, aws), 2.5 * fwd_flop)):
+        fn()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(3):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        t = e0.elapsed_time(e1) / 3
+        tf = flop / (t * 1e-3) / 1e12
+        res[name] = dict(ms=round(t, 3), bound="tensor", achieved=round(tf, 1), unit="TFLOP/s (causal half only)",
+                         frac=round(tf / peaks["bf16_tflops"], 4),
+                         note="not fused: GEMMs per head and 4096-row query chunk with the score matrix in the workspace")
+    del aq, ak, av, ao, ado, adq, adk, adv, alse, aws
     # one thread per row, one element each: a latency measurement, not a bandwidth one
     ops.cross_entropy_loss(rows_sm, V, probs, labels, loss)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -194,7 +222,7 @@ def block_ops_profile(dev, peaks, iters=5):
     res["cross_entropy_loss+set_average_loss"] = dict(ms=round(e0.elapsed_time(e1), 4), bound="latency", rows=rows_sm)
     res["shapes"] = ("65536 token rows x d 2048 (norm, rope with 16q/4kv heads of 128, embedding over a 128256-row table), "
                      "softmax on 2048 x 128256 logits, AdamW on 64 Mi parameters; median of %d launches, L2 flushed "
-                     "before each" % iters)
+                     "before each; attention: one causal sequence of 8192 tokens, 16 query / 4 kv heads of 128" % iters)
     return res
 
 

@@ -13,6 +13,7 @@ CASES = [
     ([129], [129], 4, 4, 64, False),
     ([64, 40], [200, 40], 8, 2, 128, True),
     ([513], [513], 2, 1, 128, True),
+    ([4200, 100], [4300, 100], 2, 1, 32, True),   # more than one chunk of query rows, keys beyond the queries
 ]
 
 

@@ -4,7 +4,10 @@
 
 N = 1: one MoE layer fwd+bwd at T=8192, d=4096, 64 experts, top-8, ffn 1408 (bf16 weights N(0,0.02),
 activations / upstream gradient N(0,1), fp32 router logits from a bf16 router weight); synthetic seeded data.
-The line also carries `ns_shape`: the same layer at T=32768 on the one GPU (device-timed, with its GEMM fractions).
+The line also carries `ns_shape`: the same layer at T=32768 on the one GPU (device-timed, with its GEMM fractions),
+`block_ops`: the bandwidth-bound ops of the block around the MoE feed-forward and of the head, and attention, each
+against its own bound, and `decoder_step`: the full training step of the 16-layer MoE decoder configuration
+(forward, backward, AdamW; tokens/s).
 N > 1 (launched with torch.distributed.run, one rank per GPU): the expert-parallel layer, 64 experts sharded
 over the ranks, T=32768 tokens per GPU (weak scaling); rows travel over NVLink peer memory, out through the gather
 kernel and back through the epilogue of the last GEMM of each pass (B200_EP_TRANSPORT=fused|p2p|nccl). After the

@@ -120,7 +120,7 @@ class ClockSampler:
 CFG_BLOCK = dict(T=65536, d=2048, heads=16, kv_heads=4, head_dim=128, vocab=128256, theta=500000)
 
 
-def block_ops_profile(dev, peaks, iters=5):
+def block_ops_profile(dev, peaks, iters=5, with_attention=True):
     """The bandwidth-bound ops around the MoE feed-forward at the row shapes of the decoder training step (d=2048,
     16 query / 4 kv heads of 128, vocabulary 128256) over 65536 token rows (inputs larger than L2): ms per launch
     (CUDA events, L2 flushed before each launch) and algorithmic bytes / time against the measured HBM rate."""
@@ -190,6 +190,8 @@ def block_ops_profile(dev, peaks, iters=5):
     # Useful flop: two products over the visible half of the score matrix forward, five backward.
     del X, up, dX, out, q, kk, par, grad, mean, var, table, gtab, emb
     torch.cuda.empty_cache()
+    if not with_attention:
+        return res
     Ta, Hq, Hkv, hd = 8192, c["heads"], c["kv_heads"], c["head_dim"]
     aq, ak, av = bf((Ta, Hq * hd)), bf((Ta, Hkv * hd)), bf((Ta, Hkv * hd))
     ao, ado = torch.empty_like(aq), bf((Ta, Hq * hd))
@@ -833,8 +835,18 @@ def main():
     ap.add_argument("--tokens", type=int, default=0, help="override T (tokens per GPU); for profiler captures")
     ap.add_argument("--quick", action="store_true",
                     help="device-timed loop only, exactly --warmup/--steps iterations (for ncu launch lists)")
+    ap.add_argument("--block-ops", action="store_true",
+                    help="only the block / head ops record (one GPU; one launch of each kernel per repetition: for ncu)")
     args = ap.parse_args()
     world = int(os.environ.get("WORLD_SIZE", str(args.gpus)))
+    if args.block_ops:
+        import torch
+
+        dev = torch.device("cuda", 0)
+        torch.cuda.set_device(dev)
+        print(json.dumps(dict(block_ops=block_ops_profile(dev, read_peaks(), iters=max(1, args.steps if args.steps != 30 else 5),
+                                                          with_attention=False))), flush=True)
+        return
     if args.impl == "reference":
         run_reference_arm(args, CFG_1GPU if world == 1 else CFG_EP, world)
         return

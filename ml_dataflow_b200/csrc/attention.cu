@@ -18,6 +18,7 @@
 namespace b200 {
 
 constexpr int ATTN_THREADS = 256;
+constexpr int ATTN_CACHE = 32;  // scores a thread keeps of one row: rows of up to 8192 keys are read once
 constexpr float ATTN_LOG2E = 1.4426950408889634f;
 
 __device__ __forceinline__ float attn_block_max(float v, float *scratch) {
@@ -60,15 +61,44 @@ attn_softmax_kernel(int row0, int Tq, int Tk, int causal, const float *__restric
   const int vis = attn_visible(row0 + row, Tq, Tk, causal);
   const float *s = S + (int64_t)row * ldS;
   __nv_bfloat16 *p = P + (int64_t)row * ldP;
+  // rows of up to ATTN_THREADS * ATTN_CACHE scores are read once and kept in registers between the three passes
+  float cache[ATTN_CACHE];
+  const bool cached = vis <= ATTN_THREADS * ATTN_CACHE;
   float m = -INFINITY;
-  for (int j = threadIdx.x; j < vis; j += ATTN_THREADS) m = fmaxf(m, s[j]);
+  if (cached) {
+#pragma unroll
+    for (int i = 0; i < ATTN_CACHE; i++) {
+      const int j = i * ATTN_THREADS + threadIdx.x;
+      cache[i] = j < vis ? s[j] : -INFINITY;
+      m = fmaxf(m, cache[i]);
+    }
+  } else {
+    for (int j = threadIdx.x; j < vis; j += ATTN_THREADS) m = fmaxf(m, s[j]);
+  }
   m = attn_block_max(m, scratch);
   float sum = 0.0f;
-  for (int j = threadIdx.x; j < vis; j += ATTN_THREADS) sum += exp2f((s[j] - m) * ATTN_LOG2E);
+  if (cached) {
+#pragma unroll
+    for (int i = 0; i < ATTN_CACHE; i++) {
+      cache[i] = exp2f((cache[i] - m) * ATTN_LOG2E);  // 0 for the entries past the visible keys
+      sum += cache[i];
+    }
+  } else {
+    for (int j = threadIdx.x; j < vis; j += ATTN_THREADS) sum += exp2f((s[j] - m) * ATTN_LOG2E);
+  }
   sum = attn_block_sum(sum, scratch);
   const float inv = vis > 0 ? 1.0f / sum : 0.0f;
-  for (int j = threadIdx.x; j < cols; j += ATTN_THREADS)
-    p[j] = __float2bfloat16_rn(j < vis ? exp2f((s[j] - m) * ATTN_LOG2E) * inv : 0.0f);
+  if (cached) {
+#pragma unroll
+    for (int i = 0; i < ATTN_CACHE; i++) {
+      const int j = i * ATTN_THREADS + threadIdx.x;
+      if (j < cols) p[j] = __float2bfloat16_rn(j < vis ? cache[i] * inv : 0.0f);
+    }
+    for (int j = ATTN_CACHE * ATTN_THREADS + threadIdx.x; j < cols; j += ATTN_THREADS) p[j] = __float2bfloat16_rn(0.0f);
+  } else {
+    for (int j = threadIdx.x; j < cols; j += ATTN_THREADS)
+      p[j] = __float2bfloat16_rn(j < vis ? exp2f((s[j] - m) * ATTN_LOG2E) * inv : 0.0f);
+  }
   if (threadIdx.x == 0) lse[row] = vis > 0 ? m + logf(sum) : -INFINITY;
 }
 

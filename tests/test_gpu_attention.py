@@ -14,6 +14,7 @@ CASES = [
     ([64, 40], [200, 40], 8, 2, 128, True),
     ([513], [513], 2, 1, 128, True),
     ([4200, 100], [4300, 100], 2, 1, 32, True),   # more than one chunk of query rows, keys beyond the queries
+    ([16], [8300], 2, 1, 32, True),               # more keys than a block keeps in registers
 ]
 
 

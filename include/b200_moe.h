@@ -779,6 +779,11 @@ int b200_attention_bwd(int bwd_dt, int num_seqs, int total_q, int total_k, const
                        const void *x_attn_out, const float *softmax_lse, const void *dx_out, void *dx_q, void *dx_k,
                        void *dx_v, int is_causal, uint64_t workspaceBytes, void *workspace, void *stream);
 
+/* The fused attention kernels (head_dim 64 and 128) bound every wait on a barrier to two seconds; one that runs out
+ * records a code (21-26: which hand-over gave up) and the launch ends early with wrong results. Synchronises the device,
+ * returns the recorded code through status_out (0 = none) and clears it. No counterpart in the reference. */
+int b200_attention_status(int *status_out);
+
 #ifdef __cplusplus
 }
 #endif

@@ -82,6 +82,7 @@ SIGNATURES = {
     "b200_attention_fwd": (_i, [_i, _i, _i, _i, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _i, _u64, _vp, _vp]),
     "b200_attention_bwd": (_i, [_i, _i, _i, _i, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp,
                                 _vp, _i, _u64, _vp, _vp]),
+    "b200_attention_status": (_i, [_vp]),
     "b200_scatter_row_weights": (_i, [_i, _i, _vp, _vp, _vp, _vp]),
     "b200_gather_router_grad": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp]),
 }

@@ -11,7 +11,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB_DIR = os.path.join(HERE, "lib")
 LIB_PATH = os.path.join(LIB_DIR, "libb200moe.so")
-SOURCES = ["router.cu", "permute.cu", "ep_p2p.cu", "gemm_sm100.cu", "moe_block.cu", "model_files.cu", "ep_block.cu", "block_ops.cu", "attention.cu"]
+SOURCES = ["router.cu", "permute.cu", "ep_p2p.cu", "gemm_sm100.cu", "moe_block.cu", "model_files.cu", "ep_block.cu", "block_ops.cu", "attention.cu",
+           "attention_sm100.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-shared",

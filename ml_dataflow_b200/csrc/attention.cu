@@ -9,6 +9,7 @@
 // log-sum-exp instead of storing them. A fused kernel that keeps the scores in tensor memory is the next step; this
 // one makes the op available and is what such a kernel will be checked against.
 #include <math.h>
+#include <stdlib.h>
 
 #include <algorithm>
 
@@ -16,6 +17,12 @@
 #include "../../include/b200_moe.h"
 
 namespace b200 {
+
+// attention_sm100.cu: the fused kernels for head sizes 64 and 128
+bool attn_fused_supported(int head_dim);
+int attn_fused_fwd(int num_seqs, int total_q, int total_k, const int *q_off, const int *q_len, const int *k_off,
+                   const int *k_len, int num_q_heads, int num_kv_heads, int head_dim, const void *Q, const void *K,
+                   const void *V, void *O, float *lse, int is_causal, cudaStream_t s);
 
 constexpr int ATTN_THREADS = 256;
 constexpr int ATTN_CACHE = 32;  // scores a thread keeps of one row: rows of up to 8192 keys are read once
@@ -166,6 +173,17 @@ struct AttnWorkspace {
 
 int64_t round_up(int64_t v, int64_t m) { return (v + m - 1) / m * m; }
 
+// The fused kernels serve head sizes 64 and 128 unless the environment variable B200_ATTN_FUSED is "0" (read once; it
+// exists so that the two forms can be compared on the same inputs).
+bool use_fused(int head_dim) {
+  static int mode = -1;
+  if (mode < 0) {
+    const char *e = getenv("B200_ATTN_FUSED");
+    mode = (e && e[0] == '0') ? 0 : 1;
+  }
+  return mode == 1 && attn_fused_supported(head_dim);
+}
+
 // query rows per pass: 4096 under a causal mask, else the whole sequence. Smaller chunks skip more of the upper triangle
 // but the passes are then bound by the host's launch rate (measured at 8192 tokens, 16 heads: whole 4.3 ms, 2048-row
 // chunks 5.5 ms at 29 us per launch).
@@ -243,6 +261,9 @@ extern "C" int b200_attention_fwd(int fwd_dt, int num_seqs, int total_q, int tot
                "attention_fwd: the workspace holds %llu bytes, %llu are needed (b200_attention_workspace_bytes)",
                (unsigned long long)workspaceBytes, (unsigned long long)need);
   cudaStream_t s = (cudaStream_t)stream;
+  if (use_fused(head_dim))
+    return attn_fused_fwd(num_seqs, total_q, total_k, q_seq_offsets, q_seq_lens, k_seq_offsets, k_seq_lens, num_q_heads,
+                          num_kv_heads, head_dim, x_q, x_k, x_v, x_attn_out, softmax_lse, is_causal, s);
   const int BF = B200_DT_BF16, F32 = B200_DT_FP32, NONE = B200_DT_NONE;
   const int64_t Dq = (int64_t)num_q_heads * head_dim, Dk = (int64_t)num_kv_heads * head_dim;
   const int group = num_q_heads / num_kv_heads;

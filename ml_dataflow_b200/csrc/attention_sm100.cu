@@ -1,0 +1,428 @@
+// Fused softmax attention for sm_100a (head_dim 64 or 128, bf16): the scores and the probabilities never leave the SM.
+// It serves b200_attention_fwd / _bwd (attention.cu), which keep the unfused form for every other head size.
+//
+// Forward, one CTA per (query head, 256 query rows of one sequence): Q (two 128-row tiles) is fetched once by TMA; the
+// key and value tiles of 128 keys pass through a three-slot ring. One thread issues the tcgen05 MMAs
+//     S_g = Q_g K_j^T  (fp32, tensor memory)        O'_g = P_g V_j  (fp32, tensor memory)
+// and two groups of four warps (one per query tile, a thread per query row = per tensor-memory lane) turn S_g into
+// P_g = exp2((S_g - max) * scale * log2 e) with the running maximum and sum of the online softmax, write P_g as bf16
+// into shared memory in the layout the second MMA reads (128-byte swizzle, keys contiguous) and fold O'_g into the
+// row's output, which stays in registers (fp32) until it is divided by the sum and stored. While one group works on
+// its scores the tensor pipe runs the other group's P V and next Q K^T. Rounding points: scores, maximum, sum and the
+// output in fp32; P to bf16 (unnormalised, relative to the running maximum) before it multiplies V; one rounding of
+// the output.
+//
+// Every wait is bounded (two seconds); a wait that runs out raises the status word that b200_attention_status reads,
+// and the CTA leaves through the common teardown.
+#include <cuda.h>
+#include <math.h>
+
+#include "common.cuh"
+#include "sm100_ptx.cuh"
+#include "../../include/b200_moe.h"
+
+namespace b200 {
+namespace fa {
+
+constexpr int BM = 128;         // query rows per accumulator tile (tensor-memory lanes)
+constexpr int BN = 128;         // keys per step
+constexpr int QT = 2;           // query tiles per CTA
+constexpr int SLAB = 16384;     // 128 rows x 64 bf16, one swizzled slab
+constexpr int KV_SLOTS = 3;
+constexpr int FWD_THREADS = 32 * (2 + 4 * QT);  // warp 0 loads, warp 1 issues the MMAs, 8 softmax warps
+constexpr float LOG2E = 1.4426950408889634f;
+
+enum { ST_ATTN_Q = 21, ST_ATTN_KV_EMPTY = 22, ST_ATTN_KV_FULL = 23, ST_ATTN_P = 24, ST_ATTN_S = 25, ST_ATTN_PV = 26 };
+
+__device__ int g_attn_status = 0;
+
+struct FwdParams {
+  CUtensorMap tmQ, tmK, tmV;  // [rows][heads * HD] bf16, boxes of 64 columns x 128 rows, 128-byte swizzle
+  __nv_bfloat16 *O;
+  float *lse;  // [heads][total_q]
+  int q_off, Tq, k_off, Tk, causal, group, total_q;
+  int64_t ldO;
+  float scale;
+  int *status;
+};
+
+struct FwdTail {
+  uint64_t q_full, kv_full[KV_SLOTS], kv_empty[KV_SLOTS], s_full[QT], p_ready[QT], pv_full[QT];
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+template <int HD>
+constexpr size_t fwd_smem_bytes() {
+  // Q tiles, P tiles, the K / V ring, bookkeeping, and the slack that aligns the tiles to 1024 bytes
+  return 1024 + (size_t)QT * BM * HD * 2 + (size_t)QT * BM * BN * 2 + (size_t)KV_SLOTS * BN * HD * 2 + sizeof(FwdTail);
+}
+
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+template <int HD>
+__global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_sm100_kernel(const __grid_constant__ FwdParams p) {
+  constexpr int KSL = HD / 64;               // 64-column slabs of a Q / K tile
+  constexpr int Q_TILE = BM * HD * 2;        // bytes
+  constexpr int P_TILE = BM * BN * 2;
+  constexpr int KV_TILE = BN * HD * 2;
+  constexpr uint32_t TMEM_COLS = 512;        // S_0, S_1 (BN columns each), then O'_0, O'_1 (HD columns each)
+  extern __shared__ unsigned char attn_smem_raw[];
+  unsigned char *smem = reinterpret_cast<unsigned char *>(
+      (reinterpret_cast<uintptr_t>(attn_smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  unsigned char *sQ = smem, *sP = sQ + QT * Q_TILE, *sKV = sP + QT * P_TILE;
+  FwdTail *st = reinterpret_cast<FwdTail *>(sKV + KV_SLOTS * KV_TILE);
+  volatile int *abort_flag = &st->abort_flag;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  auto bar = [&](uint64_t *b) { return ptx::smem_u32(b); };
+  auto wait = [&](uint64_t *b, uint32_t par, int code) { return ptx::mbar_wait<false>(bar(b), par, abort_flag, p.status, code); };
+
+  if (tid == 0) {
+    ptx::mbar_init(bar(&st->q_full), 1);
+    for (int s = 0; s < KV_SLOTS; s++) {
+      ptx::mbar_init(bar(&st->kv_full[s]), 1);
+      ptx::mbar_init(bar(&st->kv_empty[s]), 1);
+    }
+    for (int g = 0; g < QT; g++) {
+      ptx::mbar_init(bar(&st->s_full[g]), 1);
+      ptx::mbar_init(bar(&st->p_ready[g]), BM);
+      ptx::mbar_init(bar(&st->pv_full[g]), 1);
+    }
+    st->abort_flag = 0;
+    ptx::fence_barrier_init();
+    ptx::fence_proxy_async_smem();
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(ptx::smem_u32(&st->tmem_base), TMEM_COLS);
+    ptx::tmem_relinquish();
+  }
+  if (warp == 0 && lane == 0) {
+    ptx::tma_prefetch_desc(&p.tmQ);
+    ptx::tma_prefetch_desc(&p.tmK);
+    ptx::tma_prefetch_desc(&p.tmV);
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = st->tmem_base;
+
+  // the CTAs with the most keys to visit (the last query rows under a causal mask) start first
+  const int qt = (int)gridDim.x - 1 - (int)blockIdx.x, h = (int)blockIdx.y, kvh = h / p.group;
+  const int r0 = qt * QT * BM;
+  const int shift = p.Tk - p.Tq;  // the last query is aligned with the last key
+  int nkb[QT], nkb_max = 0;
+#pragma unroll
+  for (int g = 0; g < QT; g++) {
+    const int first = r0 + g * BM;
+    if (first >= p.Tq) {
+      nkb[g] = 0;
+    } else {
+      const int last = min(first + BM - 1, p.Tq - 1);
+      const int vis = p.causal ? min(p.Tk, last + 1 + shift) : p.Tk;
+      nkb[g] = (vis + BN - 1) / BN;
+    }
+    nkb_max = max(nkb_max, nkb[g]);
+  }
+
+  if (warp == 0) {
+    // ================= loads =================
+    if (lane == 0) {
+      int nq = 0;
+      for (int g = 0; g < QT; g++) nq += nkb[g] > 0;
+      ptx::mbar_arrive_expect_tx(bar(&st->q_full), (uint32_t)(nq * Q_TILE));
+      for (int g = 0; g < QT; g++) {
+        if (nkb[g] == 0) continue;
+        for (int s = 0; s < KSL; s++)
+          ptx::tma_load_2d(ptx::smem_u32(sQ + g * Q_TILE + s * SLAB), &p.tmQ, bar(&st->q_full), h * HD + s * 64,
+                           p.q_off + r0 + g * BM);
+      }
+      for (int n = 0; n < 2 * nkb_max; n++) {  // K_0, V_0, K_1, V_1, ...
+        const int slot = n % KV_SLOTS;
+        const uint32_t par = (uint32_t)((n / KV_SLOTS) & 1);
+        if (!wait(&st->kv_empty[slot], par ^ 1u, ST_ATTN_KV_EMPTY)) break;
+        ptx::mbar_arrive_expect_tx(bar(&st->kv_full[slot]), (uint32_t)KV_TILE);
+        const CUtensorMap *m = (n & 1) ? &p.tmV : &p.tmK;
+        for (int s = 0; s < KSL; s++)
+          ptx::tma_load_2d(ptx::smem_u32(sKV + slot * KV_TILE + s * SLAB), m, bar(&st->kv_full[slot]), kvh * HD + s * 64,
+                           p.k_off + (n >> 1) * BN);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ================= MMA issue =================
+    if (lane == 0 && nkb_max > 0) {
+      const uint32_t idesc_s = ptx::make_idesc_bf16(BM, BN, 0, 0);
+      const uint32_t idesc_pv = ptx::make_idesc_bf16(BM, HD, 0, 1);  // V is read with its head dimension contiguous
+      const uint32_t q_base = ptx::smem_u32(sQ), p_base = ptx::smem_u32(sP), kv_base = ptx::smem_u32(sKV);
+      auto issue_s = [&](int g, int slot) {
+#pragma unroll
+        for (int k16 = 0; k16 < HD / 16; k16++) {
+          const uint32_t off = (uint32_t)((k16 >> 2) * SLAB + (k16 & 3) * 32);
+          ptx::umma_bf16(tmem_base + (uint32_t)(g * BN), ptx::make_smem_desc(q_base + g * Q_TILE + off, 0, 1024),
+                         ptx::make_smem_desc(kv_base + slot * KV_TILE + off, 0, 1024), idesc_s, k16 > 0);
+        }
+        ptx::umma_commit(bar(&st->s_full[g]));
+      };
+      auto issue_pv = [&](int g, int slot) {
+#pragma unroll
+        for (int k16 = 0; k16 < BN / 16; k16++) {
+          const uint32_t a_off = (uint32_t)((k16 >> 2) * SLAB + (k16 & 3) * 32);
+          ptx::umma_bf16(tmem_base + (uint32_t)(QT * BN + g * HD), ptx::make_smem_desc(p_base + g * P_TILE + a_off, 0, 1024),
+                         ptx::make_smem_desc(kv_base + slot * KV_TILE + k16 * 2048, SLAB, 1024), idesc_pv, k16 > 0);
+        }
+        ptx::umma_commit(bar(&st->pv_full[g]));
+      };
+      bool alive = wait(&st->q_full, 0, ST_ATTN_Q) && wait(&st->kv_full[0], 0, ST_ATTN_KV_FULL);
+      if (alive) {
+        ptx::tc_fence_after();
+        for (int g = 0; g < QT; g++)
+          if (nkb[g] > 0) issue_s(g, 0);
+        ptx::umma_commit(bar(&st->kv_empty[0]));
+      }
+      for (int j = 0; alive && j < nkb_max; j++) {
+        const int nv = 2 * j + 1, nk = 2 * j + 2;
+        const bool has_next = j + 1 < nkb_max;
+        if (!wait(&st->kv_full[nv % KV_SLOTS], (uint32_t)((nv / KV_SLOTS) & 1), ST_ATTN_KV_FULL)) break;
+        if (has_next && !wait(&st->kv_full[nk % KV_SLOTS], (uint32_t)((nk / KV_SLOTS) & 1), ST_ATTN_KV_FULL)) break;
+        for (int g = 0; g < QT; g++) {
+          if (j >= nkb[g]) continue;
+          // P_g of this step is in shared memory; the group has also folded O'_g of the step before and read all of S_g
+          if (!wait(&st->p_ready[g], (uint32_t)(j & 1), ST_ATTN_P)) {
+            alive = false;
+            break;
+          }
+          ptx::tc_fence_after();
+          issue_pv(g, nv % KV_SLOTS);
+          if (j + 1 < nkb[g]) issue_s(g, nk % KV_SLOTS);
+        }
+        if (!alive) break;
+        ptx::umma_commit(bar(&st->kv_empty[nv % KV_SLOTS]));
+        if (has_next) ptx::umma_commit(bar(&st->kv_empty[nk % KV_SLOTS]));
+      }
+    }
+    __syncwarp();
+  } else {
+    // ================= softmax and output (a thread per query row) =================
+    const int g = (warp - 2) >> 2, quarter = warp & 3;  // tensor-memory lanes a warp may read: 32 * (warp % 4) ...
+    const int trow = quarter * 32 + lane;
+    const int row = r0 + g * BM + trow;  // position of the query in its sequence
+    const int limit = p.causal ? min(p.Tk, row + 1 + shift) : p.Tk;  // keys this row sees
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+    const uint32_t s_addr = lane_addr + (uint32_t)(g * BN), o_addr = lane_addr + (uint32_t)(QT * BN + g * HD);
+    unsigned char *p_row = sP + g * P_TILE + trow * 128;
+    const float c = p.scale * LOG2E;
+    float acc[HD];
+#pragma unroll
+    for (int i = 0; i < HD; i++) acc[i] = 0.0f;
+    float m = -INFINITY, l = 0.0f;
+    for (int j = 0; j < nkb[g]; j++) {
+      if (!wait(&st->s_full[g], (uint32_t)(j & 1), ST_ATTN_S)) goto teardown;
+      ptx::tc_fence_after();
+      const int lim = limit - j * BN;  // columns below lim are visible
+      uint32_t r[32];
+      float mx = m;
+#pragma unroll
+      for (int c4 = 0; c4 < BN / 32; c4++) {
+        ptx::tmem_ld32(s_addr + c4 * 32, r);
+        ptx::tmem_ld_wait();
+        if (lim >= (c4 + 1) * 32) {
+#pragma unroll
+          for (int i = 0; i < 32; i++) mx = fmaxf(mx, __uint_as_float(r[i]));
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; i++)
+            if (c4 * 32 + i < lim) mx = fmaxf(mx, __uint_as_float(r[i]));
+        }
+      }
+      // a row that has seen no key yet keeps max = -inf: its probabilities are exp2(-inf) = 0 against a zero offset
+      const float mc = (mx == -INFINITY) ? 0.0f : mx * c;
+      const float alpha = (m == -INFINITY) ? 0.0f : ex2(m * c - mc);
+      float sum = 0.0f;
+#pragma unroll
+      for (int c4 = 0; c4 < BN / 32; c4++) {
+        ptx::tmem_ld32(s_addr + c4 * 32, r);
+        ptx::tmem_ld_wait();
+        float pr[32];
+        if (lim >= (c4 + 1) * 32) {
+#pragma unroll
+          for (int i = 0; i < 32; i++) pr[i] = ex2(fmaf(__uint_as_float(r[i]), c, -mc));
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; i++) pr[i] = (c4 * 32 + i < lim) ? ex2(fmaf(__uint_as_float(r[i]), c, -mc)) : 0.0f;
+        }
+#pragma unroll
+        for (int i = 0; i < 32; i++) sum += pr[i];
+        // keys c4*32 .. +31 of this row: slab c4 / 2, 16-byte chunks (c4 % 2) * 4 + q, swizzled with the row
+        unsigned char *slab = p_row + (c4 >> 1) * SLAB;
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+          const int chunk = ((c4 & 1) * 4 + q) ^ (trow & 7);
+          *reinterpret_cast<uint4 *>(slab + chunk * 16) = pack8(pr + q * 8);
+        }
+      }
+      l = l * alpha + sum;
+      m = mx;
+      ptx::fence_proxy_async_smem();
+      ptx::tc_fence_before();
+      ptx::mbar_arrive(bar(&st->p_ready[g]));
+      if (!wait(&st->pv_full[g], (uint32_t)(j & 1), ST_ATTN_PV)) goto teardown;
+      ptx::tc_fence_after();
+#pragma unroll
+      for (int c4 = 0; c4 < HD / 32; c4++) {
+        ptx::tmem_ld32(o_addr + c4 * 32, r);
+        ptx::tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; i++) acc[c4 * 32 + i] = fmaf(acc[c4 * 32 + i], alpha, __uint_as_float(r[i]));
+      }
+    }
+    if (nkb[g] > 0 && row < p.Tq) {
+      const float inv = l > 0.0f ? __fdividef(1.0f, l) : 0.0f;
+      __nv_bfloat16 *o = p.O + (int64_t)(p.q_off + row) * p.ldO + (int64_t)h * HD;
+#pragma unroll
+      for (int i = 0; i < HD; i += 8) {
+        float v[8];
+#pragma unroll
+        for (int t = 0; t < 8; t++) v[t] = acc[i + t] * inv;
+        *reinterpret_cast<uint4 *>(o + i) = pack8(v);
+      }
+      p.lse[(int64_t)h * p.total_q + p.q_off + row] = l > 0.0f ? m * p.scale + logf(l) : -INFINITY;
+    }
+  }
+
+teardown:
+  if (*abort_flag) {
+    // give copies that are still in flight time to land before shared memory is released
+    const uint64_t t0 = ptx::globaltimer_ns();
+    while (ptx::globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+}  // namespace fa
+}  // namespace b200
+
+// ---------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------
+using namespace b200;
+
+namespace {
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void *sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      return nullptr;
+    fn = reinterpret_cast<EncodeTiledFn>(sym);
+  }
+  return fn;
+}
+
+// bf16 [rows][cols] with a row pitch of `cols` elements; boxes of 64 columns x 128 rows, 128-byte swizzle, rows past
+// the end read as zeros
+int rows_map(CUtensorMap *m, const void *base, uint64_t rows, uint64_t cols) {
+  EncodeTiledFn fn = encode_fn();
+  B200_REQUIRE(fn != nullptr, "attention: cuTensorMapEncodeTiled is not available from this driver");
+  B200_REQUIRE(b200_aligned16(base) && (cols * 2) % 16 == 0, "attention: tensors must be 16-byte aligned with a 16-byte row pitch");
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {cols * 2};
+  cuuint32_t box[2] = {64, 128};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  B200_REQUIRE(r == CUDA_SUCCESS, "attention: cuTensorMapEncodeTiled failed with code %d", (int)r);
+  return 0;
+}
+
+constexpr int MAX_DEVICES = 64;
+
+int *attn_status_ptr() {
+  static int *ptr[MAX_DEVICES];
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) return nullptr;
+  if (!ptr[dev] && cudaGetSymbolAddress((void **)&ptr[dev], fa::g_attn_status) != cudaSuccess) ptr[dev] = nullptr;
+  return ptr[dev];
+}
+
+template <int HD>
+int launch_fwd(const fa::FwdParams &p, int num_q_heads, cudaStream_t s) {
+  static bool attr_set[MAX_DEVICES];
+  int dev = -1;
+  B200_CUDA(cudaGetDevice(&dev));
+  B200_REQUIRE(dev >= 0 && dev < MAX_DEVICES, "attention: device ordinal %d is out of range", dev);
+  constexpr size_t smem = fa::fwd_smem_bytes<HD>();
+  if (!attr_set[dev]) {
+    B200_CUDA(cudaFuncSetAttribute(fa::attn_fwd_sm100_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    attr_set[dev] = true;
+  }
+  const int tiles = (p.Tq + fa::QT * fa::BM - 1) / (fa::QT * fa::BM);
+  fa::attn_fwd_sm100_kernel<HD><<<dim3((unsigned)tiles, (unsigned)num_q_heads), fa::FWD_THREADS, smem, s>>>(p);
+  B200_CHECK_LAUNCH("attention_fwd (fused)");
+  return 0;
+}
+
+}  // namespace
+
+namespace b200 {
+
+bool attn_fused_supported(int head_dim) { return head_dim == 64 || head_dim == 128; }
+
+// Forward over every sequence of the packed batch (one launch per sequence); arguments as b200_attention_fwd.
+int attn_fused_fwd(int num_seqs, int total_q, int total_k, const int *q_off, const int *q_len, const int *k_off,
+                   const int *k_len, int num_q_heads, int num_kv_heads, int head_dim, const void *Q, const void *K,
+                   const void *V, void *O, float *lse, int is_causal, cudaStream_t s) {
+  fa::FwdParams p;
+  const uint64_t Dq = (uint64_t)num_q_heads * head_dim, Dk = (uint64_t)num_kv_heads * head_dim;
+  if (rows_map(&p.tmQ, Q, (uint64_t)total_q, Dq) || rows_map(&p.tmK, K, (uint64_t)total_k, Dk) ||
+      rows_map(&p.tmV, V, (uint64_t)total_k, Dk))
+    return -1;
+  p.O = (__nv_bfloat16 *)O;
+  p.lse = lse;
+  p.causal = is_causal;
+  p.group = num_q_heads / num_kv_heads;
+  p.total_q = total_q;
+  p.ldO = (int64_t)Dq;
+  p.scale = 1.0f / sqrtf((float)head_dim);
+  p.status = attn_status_ptr();
+  B200_REQUIRE(p.status != nullptr, "attention: the status word of this device is not reachable");
+  for (int sq = 0; sq < num_seqs; sq++) {
+    if (q_len[sq] == 0) continue;
+    p.q_off = q_off[sq];
+    p.Tq = q_len[sq];
+    p.k_off = k_off[sq];
+    p.Tk = k_len[sq];
+    if ((head_dim == 128 ? launch_fwd<128>(p, num_q_heads, s) : launch_fwd<64>(p, num_q_heads, s)) != 0) return -1;
+  }
+  return 0;
+}
+
+}  // namespace b200
+
+extern "C" int b200_attention_status(int *status_out) {
+  int v = 0;
+  B200_CUDA(cudaDeviceSynchronize());
+  B200_CUDA(cudaMemcpyFromSymbol(&v, fa::g_attn_status, sizeof(int)));
+  if (v != 0) {
+    int zero = 0;
+    B200_CUDA(cudaMemcpyToSymbol(fa::g_attn_status, &zero, sizeof(int)));
+  }
+  if (status_out) *status_out = v;
+  return 0;
+}

@@ -57,6 +57,13 @@ def gemm_status():
     return st.value
 
 
+def attention_status():
+    """Synchronises and returns the status word of the fused attention kernels (0 = every wait completed)."""
+    st = C.c_int()
+    _check(_lib.load().b200_attention_status(C.byref(st)), "b200_attention_status", 0)
+    return st.value
+
+
 def gemm_set_pair_mode(on):
     """1: CTA pairs (cta_group::2, 256-row tiles); 0: single-CTA 128-row tiles."""
     _check(_lib.load().b200_gemm_set_pair_mode(int(bool(on))), "b200_gemm_set_pair_mode", 0)

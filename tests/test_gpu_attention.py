@@ -48,7 +48,7 @@ def test_attention_forward_backward(oracle, q_len, k_len, Hq, Hkv, hd, causal):
     ws = torch.empty(nbytes, dtype=torch.uint8, device="cuda")
     ops.attention_fwd(q_off, q_len, k_off, k_len, Hq, Hkv, hd, Qd, Kd, Vd, O, lse, causal, ws)
     torch.cuda.synchronize()
-    assert ops.gemm_status() == 0
+    assert ops.gemm_status() == 0 and ops.attention_status() == 0
     np.testing.assert_allclose(lse.cpu().numpy(), ref_lse, rtol=1e-4, atol=1e-4)
     assert_chain_close(_f32(host_bits(O)), _f32(ref_O), limit=6e-3, what="attention output")
     assert_close(_f32(host_bits(O)), _f32(ref_O), rtol=2e-2, atol=8e-3, what="attention output")
@@ -58,7 +58,7 @@ def test_attention_forward_backward(oracle, q_len, k_len, Hq, Hkv, hd, causal):
     ops.attention_bwd(q_off, q_len, k_off, k_len, Hq, Hkv, hd, Qd, Kd, Vd, dev_bf16(ref_O), torch.from_numpy(ref_lse).cuda(),
                       dOd, dQ, dK, dV, causal, ws)
     torch.cuda.synchronize()
-    assert ops.gemm_status() == 0
+    assert ops.gemm_status() == 0 and ops.attention_status() == 0
     for got, ref, what in ((dQ, ref_dQ, "dQ"), (dK, ref_dK, "dK"), (dV, ref_dV, "dV")):
         assert_chain_close(_f32(host_bits(got)), _f32(ref), limit=8e-3, what=what)
         assert_close(_f32(host_bits(got)), _f32(ref), rtol=2e-2, atol=3e-2, max_bad_frac=2e-3, what=what)

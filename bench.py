@@ -197,7 +197,7 @@ def block_ops_profile(dev, peaks, iters=5, with_attention=True):
     ao, ado = torch.empty_like(aq), bf((Ta, Hq * hd))
     adq, adk, adv = torch.empty_like(aq), torch.empty_like(ak), torch.empty_like(av)
     alse = torch.empty((Hq, Ta), dtype=torch.float32, device=dev)
-    aws = torch.empty(ops.attention_workspace_bytes(True, Ta, Ta, hd), dtype=torch.uint8, device=dev)
+    aws = torch.empty(ops.attention_workspace_bytes(True, Hq, Hkv, hd, Ta, Ta, Ta), dtype=torch.uint8, device=dev)
     fwd_flop = 2 * 2 * Ta * Ta * hd * Hq / 2
     for name, fn, flop in (
             ("attention_fwd", lambda: ops.attention_fwd([0], [Ta], [0], [Ta], Hq, Hkv, hd, aq, ak, av, ao, alse, True, aws), fwd_flop),

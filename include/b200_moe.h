@@ -758,15 +758,25 @@ int b200_embedding_table_bwd_w(int bwd_dt, int num_unique_tokens, int embed_dim,
  * dx_v: [total_k][num_kv_heads * head_dim]; softmax_lse: fp32 [num_q_heads][total_q] (log-sum-exp of the scaled
  * scores, written by the forward, read by the backward). bf16 only.
  *
- * Differences from the reference's signature: the sequence offsets and lengths are HOST arrays here (the calls are
- * issued per sequence and head from the host); dx_q / dx_k / dx_v are overwritten. This first form is not fused: it
- * runs this library's tensor-core GEMMs on head slices with the score matrix of one (sequence, head) in the workspace
- * (b200_attention_workspace_bytes: max_seqlen_q x max_seqlen_k x 6 bytes, plus two fp32 key / value gradient
- * accumulators when is_training); the arithmetic (fp32 scores and statistics, probabilities rounded to bf16 before
- * they multiply V or dO, fp32 accumulation, one rounding per output, probabilities re-formed from the log-sum-exp in
- * the backward) is that of the published algorithm.
+ * Differences from the reference's signature: the sequence offsets and lengths are HOST arrays here (the launches are
+ * issued per sequence from the host); dx_q / dx_k / dx_v are overwritten.
+ *
+ * head_dim 64 and 128 run fused tcgen05 kernels (csrc/attention_sm100.cu): the forward for both (scores in tensor
+ * memory, probabilities through shared memory, no workspace), the backward for 128 (dK, dV accumulated in tensor
+ * memory per block of 128 keys, dQ added into an fp32 accumulator in the workspace with red.add and rounded once -
+ * the order of those additions is not fixed, so dQ may differ in the last bit between runs). Every other head size,
+ * and the backward at 64, runs this library's tensor-core GEMMs on head slices with the score matrix of one
+ * (sequence, head, 4096-row chunk) in the workspace. The arithmetic of both forms (fp32 scores and statistics,
+ * probabilities rounded to bf16 before they multiply V or dO, fp32 accumulation, one rounding per output,
+ * probabilities re-formed from the log-sum-exp in the backward) is that of the published algorithm.
+ *
+ * b200_attention_workspace_bytes mirrors dataflow_get_attention_workspace_size (dataflow_ops.h:93-97): the bytes a
+ * forward (is_training = 0) or a forward and backward (1) need for batches of at most max_total_q packed query rows
+ * and sequences of at most max_seqlen_q / max_seqlen_k. It may be 0 (fused forward); the calls then ignore the
+ * workspace arguments.
  */
-uint64_t b200_attention_workspace_bytes(int is_training, int max_seqlen_q, int max_seqlen_k, int head_dim);
+uint64_t b200_attention_workspace_bytes(int is_training, int num_q_heads, int num_kv_heads, int head_dim, int max_total_q,
+                                        int max_seqlen_q, int max_seqlen_k);
 
 int b200_attention_fwd(int fwd_dt, int num_seqs, int total_q, int total_k, const int *q_seq_offsets, const int *q_seq_lens,
                        int max_seqlen_q, const int *k_seq_offsets, const int *k_seq_lens, int max_seqlen_k, int num_q_heads,

@@ -78,7 +78,7 @@ SIGNATURES = {
     "b200_adamw_step": (_i, [_i, _i, _i, _i, _u64, _i, _f, _f, _f, _f, _f, _vp, _vp, _vp, _vp, _vp]),
     "b200_embedding_table": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp]),
     "b200_embedding_table_bwd_w": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp]),
-    "b200_attention_workspace_bytes": (_u64, [_i, _i, _i, _i]),
+    "b200_attention_workspace_bytes": (_u64, [_i, _i, _i, _i, _i, _i, _i]),
     "b200_attention_fwd": (_i, [_i, _i, _i, _i, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _i, _u64, _vp, _vp]),
     "b200_attention_bwd": (_i, [_i, _i, _i, _i, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp,
                                 _vp, _i, _u64, _vp, _vp]),

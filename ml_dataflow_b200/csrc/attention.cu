@@ -23,6 +23,12 @@ bool attn_fused_supported(int head_dim);
 int attn_fused_fwd(int num_seqs, int total_q, int total_k, const int *q_off, const int *q_len, const int *k_off,
                    const int *k_len, int num_q_heads, int num_kv_heads, int head_dim, const void *Q, const void *K,
                    const void *V, void *O, float *lse, int is_causal, cudaStream_t s);
+bool attn_fused_bwd_supported(int head_dim);
+uint64_t attn_fused_bwd_workspace(int total_q, int num_q_heads, int head_dim);
+int attn_fused_bwd(int num_seqs, int total_q, int total_k, const int *q_off, const int *q_len, const int *k_off,
+                   const int *k_len, int num_q_heads, int num_kv_heads, int head_dim, const void *Q, const void *K,
+                   const void *V, const void *O, const float *lse, const void *dO, void *dQ, void *dK, void *dV,
+                   int is_causal, void *workspace, cudaStream_t s);
 
 constexpr int ATTN_THREADS = 256;
 constexpr int ATTN_CACHE = 32;  // scores a thread keeps of one row: rows of up to 8192 keys are read once
@@ -233,11 +239,25 @@ int attn_check(const char *op, int dt, int num_seqs, int total_q, int total_k, c
   return 0;
 }
 
+// what a call needs: nothing for the fused forward, the dQ accumulator and delta for the fused backward, the score
+// matrices of one (sequence, head, chunk) for the unfused form
+uint64_t workspace_need(int is_training, int num_q_heads, int head_dim, int total_q, int max_seqlen_q, int max_seqlen_k,
+                        bool for_backward) {
+  const bool fused_fwd = use_fused(head_dim), fused_bwd = fused_fwd && attn_fused_bwd_supported(head_dim);
+  if (for_backward || is_training) {
+    if (fused_bwd) return attn_fused_bwd_workspace(total_q, num_q_heads, head_dim);
+    return attn_workspace_layout(1, max_seqlen_q, max_seqlen_k, head_dim, nullptr, nullptr);
+  }
+  return fused_fwd ? 0 : attn_workspace_layout(0, max_seqlen_q, max_seqlen_k, head_dim, nullptr, nullptr);
+}
+
 }  // namespace
 
-extern "C" uint64_t b200_attention_workspace_bytes(int is_training, int max_seqlen_q, int max_seqlen_k, int head_dim) {
-  if (max_seqlen_q <= 0 || max_seqlen_k <= 0 || head_dim <= 0) return 0;
-  return attn_workspace_layout(is_training, max_seqlen_q, max_seqlen_k, head_dim, nullptr, nullptr);
+extern "C" uint64_t b200_attention_workspace_bytes(int is_training, int num_q_heads, int num_kv_heads, int head_dim,
+                                                   int max_total_q, int max_seqlen_q, int max_seqlen_k) {
+  if (max_seqlen_q <= 0 || max_seqlen_k <= 0 || head_dim <= 0 || num_q_heads <= 0 || num_kv_heads <= 0 || max_total_q <= 0)
+    return 0;
+  return workspace_need(is_training, num_q_heads, head_dim, max_total_q, max_seqlen_q, max_seqlen_k, false);
 }
 
 #define ATTN_MM(...)                              \
@@ -255,15 +275,15 @@ extern "C" int b200_attention_fwd(int fwd_dt, int num_seqs, int total_q, int tot
     return -1;
   B200_REQUIRE(x_q && x_k && x_v && x_attn_out && softmax_lse, "attention_fwd: null tensor");
   if (num_seqs == 0 || total_q == 0) return 0;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (use_fused(head_dim))  // needs no workspace
+    return attn_fused_fwd(num_seqs, total_q, total_k, q_seq_offsets, q_seq_lens, k_seq_offsets, k_seq_lens, num_q_heads,
+                          num_kv_heads, head_dim, x_q, x_k, x_v, x_attn_out, softmax_lse, is_causal, s);
   AttnWorkspace w;
   const uint64_t need = attn_workspace_layout(0, max_seqlen_q, max_seqlen_k, head_dim, (unsigned char *)workspace, &w);
   B200_REQUIRE(workspace != nullptr && b200_aligned16(workspace) && workspaceBytes >= need,
                "attention_fwd: the workspace holds %llu bytes, %llu are needed (b200_attention_workspace_bytes)",
                (unsigned long long)workspaceBytes, (unsigned long long)need);
-  cudaStream_t s = (cudaStream_t)stream;
-  if (use_fused(head_dim))
-    return attn_fused_fwd(num_seqs, total_q, total_k, q_seq_offsets, q_seq_lens, k_seq_offsets, k_seq_lens, num_q_heads,
-                          num_kv_heads, head_dim, x_q, x_k, x_v, x_attn_out, softmax_lse, is_causal, s);
   const int BF = B200_DT_BF16, F32 = B200_DT_FP32, NONE = B200_DT_NONE;
   const int64_t Dq = (int64_t)num_q_heads * head_dim, Dk = (int64_t)num_kv_heads * head_dim;
   const int group = num_q_heads / num_kv_heads;
@@ -312,12 +332,21 @@ extern "C" int b200_attention_bwd(int bwd_dt, int num_seqs, int total_q, int tot
     return -1;
   B200_REQUIRE(x_q && x_k && x_v && x_attn_out && softmax_lse && dx_out && dx_q && dx_k && dx_v, "attention_bwd: null tensor");
   if (num_seqs == 0 || total_q == 0) return 0;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (use_fused(head_dim) && attn_fused_bwd_supported(head_dim)) {
+    const uint64_t need = attn_fused_bwd_workspace(total_q, num_q_heads, head_dim);
+    B200_REQUIRE(workspace != nullptr && b200_aligned16(workspace) && workspaceBytes >= need,
+                 "attention_bwd: the workspace holds %llu bytes, %llu are needed (b200_attention_workspace_bytes)",
+                 (unsigned long long)workspaceBytes, (unsigned long long)need);
+    return attn_fused_bwd(num_seqs, total_q, total_k, q_seq_offsets, q_seq_lens, k_seq_offsets, k_seq_lens, num_q_heads,
+                          num_kv_heads, head_dim, x_q, x_k, x_v, x_attn_out, softmax_lse, dx_out, dx_q, dx_k, dx_v, is_causal,
+                          workspace, s);
+  }
   AttnWorkspace w;
   const uint64_t need = attn_workspace_layout(1, max_seqlen_q, max_seqlen_k, head_dim, (unsigned char *)workspace, &w);
   B200_REQUIRE(workspace != nullptr && b200_aligned16(workspace) && workspaceBytes >= need,
                "attention_bwd: the workspace holds %llu bytes, %llu are needed (b200_attention_workspace_bytes)",
                (unsigned long long)workspaceBytes, (unsigned long long)need);
-  cudaStream_t s = (cudaStream_t)stream;
   const int BF = B200_DT_BF16, F32 = B200_DT_FP32, NONE = B200_DT_NONE;
   const int64_t Dq = (int64_t)num_q_heads * head_dim, Dk = (int64_t)num_kv_heads * head_dim;
   const int group = num_q_heads / num_kv_heads;

@@ -307,6 +307,342 @@ teardown:
   }
 }
 
+
+// ---------------------------------------------------------------------------------------
+// Backward (head_dim 128). One CTA per (block of 128 keys, key/value head) of one sequence; it walks the query heads of
+// the group and the 128-row query blocks that see its keys. K and V stay in shared memory; Q and dO tiles pass through
+// a three-slot ring. Per step, with the key rows on the tensor-memory lanes:
+//     S^T = K Q^T,  dP^T = V dO^T                       (fp32, tensor memory)
+//     P^T = exp2(S^T * scale * log2 e - lse * log2 e),  dS^T = P^T o (dP^T - delta)   (threads; bf16 into shared memory)
+//     dV += P^T dO,  dK += dS^T Q                       (accumulated in tensor memory over all steps of the CTA)
+//     dQ^T = K^T dS^T                                   (tensor memory, over the columns S^T occupied)
+// dQ^T is added to an fp32 accumulator in global memory (red.add, 128 contiguous bytes per warp and query) that a cast
+// kernel rounds once; dK (times the softmax scale) and dV are rounded once at the end of the CTA. The Q and dO tiles are
+// read by the tensor core both ways round - as [queries x dims] for S^T / dP^T and as [dims x queries] for dK / dV -
+// from the same swizzled bytes, and so are K and dS^T for dQ^T.
+// ---------------------------------------------------------------------------------------
+constexpr int BWD_THREADS = 32 * 10;  // warp 0 loads, warp 1 issues the MMAs, 8 warps for the element-wise work
+constexpr int BWD_HD = 128;
+constexpr int BWD_TILE = 128 * BWD_HD * 2;
+constexpr int RING = 3;
+
+enum { ST_BWD_KV = 31, ST_BWD_RING_EMPTY = 32, ST_BWD_RING_FULL = 33, ST_BWD_S = 34, ST_BWD_DP = 35, ST_BWD_P = 36,
+       ST_BWD_DS = 37, ST_BWD_DQ = 38, ST_BWD_DQ_EMPTY = 39, ST_BWD_ACC = 40, ST_BWD_STATS = 41 };
+
+struct BwdParams {
+  CUtensorMap tmQ, tmK, tmV, tmdO;
+  const float *lse, *delta;  // [heads][total_q]
+  float *dQacc;              // [total_q][heads * 128] fp32, zeroed by the caller
+  __nv_bfloat16 *dK, *dV;
+  int q_off, Tq, k_off, Tk, causal, group, total_q;
+  int64_t ldQ, ldK;
+  float scale;
+  int *status;
+};
+
+struct BwdTail {
+  uint64_t kv_full, ring_full[RING], ring_empty[RING], s_full, dp_full, p_ready, ds_ready, dq_full, dq_empty, acc_full,
+      stats_full, stats_free;
+  uint32_t tmem_base;
+  int abort_flag;
+  float stats[2][128];  // lse * log2 e and delta of the step's 128 queries
+};
+
+constexpr size_t bwd_smem_bytes() { return 1024 + (size_t)(4 + RING) * BWD_TILE + sizeof(BwdTail); }
+
+__global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_sm100_kernel(const __grid_constant__ BwdParams p) {
+  constexpr int HD = BWD_HD;
+  constexpr uint32_t TMEM_COLS = 512;  // S^T / dQ^T, dP^T, dK, dV: 128 columns each
+  constexpr uint32_t COL_S = 0, COL_DP = 128, COL_DK = 256, COL_DV = 384;
+  extern __shared__ unsigned char attn_smem_raw[];
+  unsigned char *smem = reinterpret_cast<unsigned char *>(
+      (reinterpret_cast<uintptr_t>(attn_smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  unsigned char *sK = smem, *sV = sK + BWD_TILE, *sPT = sV + BWD_TILE, *sDST = sPT + BWD_TILE, *sRing = sDST + BWD_TILE;
+  BwdTail *st = reinterpret_cast<BwdTail *>(sRing + RING * BWD_TILE);
+  volatile int *abort_flag = &st->abort_flag;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  auto bar = [&](uint64_t *b) { return ptx::smem_u32(b); };
+  auto wait = [&](uint64_t *b, uint32_t par, int code) { return ptx::mbar_wait<false>(bar(b), par, abort_flag, p.status, code); };
+
+  if (tid == 0) {
+    ptx::mbar_init(bar(&st->kv_full), 1);
+    for (int s = 0; s < RING; s++) {
+      ptx::mbar_init(bar(&st->ring_full[s]), 1);
+      ptx::mbar_init(bar(&st->ring_empty[s]), 1);
+    }
+    ptx::mbar_init(bar(&st->s_full), 1);
+    ptx::mbar_init(bar(&st->dp_full), 1);
+    ptx::mbar_init(bar(&st->p_ready), 256);
+    ptx::mbar_init(bar(&st->ds_ready), 256);
+    ptx::mbar_init(bar(&st->dq_full), 1);
+    ptx::mbar_init(bar(&st->dq_empty), 256);
+    ptx::mbar_init(bar(&st->acc_full), 1);
+    ptx::mbar_init(bar(&st->stats_full), 256);
+    ptx::mbar_init(bar(&st->stats_free), 256);
+    st->abort_flag = 0;
+    ptx::fence_barrier_init();
+    ptx::fence_proxy_async_smem();
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(ptx::smem_u32(&st->tmem_base), TMEM_COLS);
+    ptx::tmem_relinquish();
+  }
+  if (warp == 0 && lane == 0) {
+    ptx::tma_prefetch_desc(&p.tmQ);
+    ptx::tma_prefetch_desc(&p.tmK);
+    ptx::tma_prefetch_desc(&p.tmV);
+    ptx::tma_prefetch_desc(&p.tmdO);
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = st->tmem_base;
+
+  const int kb = (int)blockIdx.x, kvh = (int)blockIdx.y;  // the key blocks most queries see come first
+  const int shift = p.Tk - p.Tq;
+  const int nqb = (p.Tq + BM - 1) / BM;
+  const int qb_start = p.causal ? max(0, kb * BN - shift) / BM : 0;
+  const int per_head = nqb - qb_start;
+  const int n_steps = per_head > 0 ? per_head * p.group : 0;
+
+  if (warp == 0) {
+    // ================= loads =================
+    if (lane == 0 && n_steps > 0) {
+      ptx::mbar_arrive_expect_tx(bar(&st->kv_full), (uint32_t)(2 * BWD_TILE));
+      for (int s = 0; s < HD / 64; s++) {
+        ptx::tma_load_2d(ptx::smem_u32(sK + s * SLAB), &p.tmK, bar(&st->kv_full), kvh * HD + s * 64, p.k_off + kb * BN);
+        ptx::tma_load_2d(ptx::smem_u32(sV + s * SLAB), &p.tmV, bar(&st->kv_full), kvh * HD + s * 64, p.k_off + kb * BN);
+      }
+      for (int n = 0; n < 2 * n_steps; n++) {  // Q_0, dO_0, Q_1, dO_1, ...
+        const int i = n >> 1, h = kvh * p.group + i / per_head, qb = qb_start + i % per_head;
+        const int slot = n % RING;
+        const uint32_t par = (uint32_t)((n / RING) & 1);
+        if (!wait(&st->ring_empty[slot], par ^ 1u, ST_BWD_RING_EMPTY)) break;
+        ptx::mbar_arrive_expect_tx(bar(&st->ring_full[slot]), (uint32_t)BWD_TILE);
+        const CUtensorMap *m = (n & 1) ? &p.tmdO : &p.tmQ;
+        for (int s = 0; s < HD / 64; s++)
+          ptx::tma_load_2d(ptx::smem_u32(sRing + slot * BWD_TILE + s * SLAB), m, bar(&st->ring_full[slot]), h * HD + s * 64,
+                           p.q_off + qb * BM);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ================= MMA issue =================
+    if (lane == 0 && n_steps > 0) {
+      const uint32_t idesc_kk = ptx::make_idesc_bf16(128, 128, 0, 0);  // both operands with the reduction contiguous
+      const uint32_t idesc_km = ptx::make_idesc_bf16(128, 128, 0, 1);  // B read the other way round
+      const uint32_t idesc_mm = ptx::make_idesc_bf16(128, 128, 1, 1);  // both
+      const uint32_t k_base = ptx::smem_u32(sK), v_base = ptx::smem_u32(sV), pt_base = ptx::smem_u32(sPT),
+                     dst_base = ptx::smem_u32(sDST), ring_base = ptx::smem_u32(sRing);
+      // operand with the reduction index contiguous (rows = M or N), 16 reduction elements per step
+      auto kmaj = [&](uint32_t base, int k16) { return ptx::make_smem_desc(base + (uint32_t)((k16 >> 2) * SLAB + (k16 & 3) * 32), 0, 1024); };
+      // the same bytes read with the rows as the reduction index
+      auto mnmaj = [&](uint32_t base, int k16) { return ptx::make_smem_desc(base + (uint32_t)(k16 * 2048), SLAB, 1024); };
+      bool alive = wait(&st->kv_full, 0, ST_BWD_KV);
+      for (int i = 0; alive && i < n_steps; i++) {
+        const int nq = 2 * i, nd = 2 * i + 1;
+        const uint32_t q_tile = ring_base + (uint32_t)((nq % RING) * BWD_TILE), do_tile = ring_base + (uint32_t)((nd % RING) * BWD_TILE);
+        const uint32_t par = (uint32_t)(i & 1);
+        if (!wait(&st->ring_full[nq % RING], (uint32_t)((nq / RING) & 1), ST_BWD_RING_FULL)) break;
+        if (i > 0 && !wait(&st->dq_empty, par ^ 1u, ST_BWD_DQ_EMPTY)) break;
+        ptx::tc_fence_after();
+#pragma unroll
+        for (int k16 = 0; k16 < HD / 16; k16++)
+          ptx::umma_bf16(tmem_base + COL_S, kmaj(k_base, k16), kmaj(q_tile, k16), idesc_kk, k16 > 0);
+        ptx::umma_commit(bar(&st->s_full));
+        if (!wait(&st->ring_full[nd % RING], (uint32_t)((nd / RING) & 1), ST_BWD_RING_FULL)) break;
+        ptx::tc_fence_after();
+#pragma unroll
+        for (int k16 = 0; k16 < HD / 16; k16++)
+          ptx::umma_bf16(tmem_base + COL_DP, kmaj(v_base, k16), kmaj(do_tile, k16), idesc_kk, k16 > 0);
+        ptx::umma_commit(bar(&st->dp_full));
+        if (!wait(&st->p_ready, par, ST_BWD_P)) break;
+        ptx::tc_fence_after();
+#pragma unroll
+        for (int k16 = 0; k16 < BM / 16; k16++)
+          ptx::umma_bf16(tmem_base + COL_DV, kmaj(pt_base, k16), mnmaj(do_tile, k16), idesc_km, (i > 0 || k16 > 0));
+        ptx::umma_commit(bar(&st->ring_empty[nd % RING]));
+        if (!wait(&st->ds_ready, par, ST_BWD_DS)) break;
+        ptx::tc_fence_after();
+#pragma unroll
+        for (int k16 = 0; k16 < BM / 16; k16++)
+          ptx::umma_bf16(tmem_base + COL_DK, kmaj(dst_base, k16), mnmaj(q_tile, k16), idesc_km, (i > 0 || k16 > 0));
+        ptx::umma_commit(bar(&st->ring_empty[nq % RING]));
+#pragma unroll
+        for (int k16 = 0; k16 < BN / 16; k16++)
+          ptx::umma_bf16(tmem_base + COL_S, mnmaj(k_base, k16), mnmaj(dst_base, k16), idesc_mm, k16 > 0);
+        ptx::umma_commit(bar(&st->dq_full));
+        if (i == n_steps - 1) ptx::umma_commit(bar(&st->acc_full));
+      }
+    }
+    __syncwarp();
+  } else if (n_steps > 0) {
+    // ================= element-wise work: a thread per (tensor-memory lane, half of the columns) =================
+    const int quarter = warp & 3, half = (warp - 2) >> 2;
+    const int trow = quarter * 32 + lane;
+    const int key = kb * BN + trow;  // position of this lane's key in its sequence (steps 1-2 and the end)
+    const bool key_ok = key < p.Tk;
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(half * 64);
+    unsigned char *pt_row = sPT + half * SLAB + trow * 128, *dst_row = sDST + half * SLAB + trow * 128;
+    const float c = p.scale * LOG2E;
+    const int st_t = tid - 64;  // 0 .. 255
+    for (int i = 0; i < n_steps; i++) {
+      const int h = kvh * p.group + i / per_head, qb = qb_start + i % per_head;
+      const uint32_t par = (uint32_t)(i & 1);
+      const int q0 = qb * BM;
+      // every warp has finished with the statistics of the step before (a bounded wait, like all the others)
+      if (i > 0 && !wait(&st->stats_free, par ^ 1u, ST_BWD_STATS)) goto teardown;
+      {
+        const int col = st_t & 127, qa = q0 + col;
+        float v = 0.0f;
+        if (qa < p.Tq) {
+          const int64_t at = (int64_t)h * p.total_q + p.q_off + qa;
+          v = st_t < 128 ? p.lse[at] * LOG2E : p.delta[at];
+        }
+        st->stats[st_t >> 7][col] = v;
+      }
+      ptx::mbar_arrive(bar(&st->stats_full));
+      if (!wait(&st->stats_full, par, ST_BWD_STATS)) goto teardown;
+      // is every (key, query) pair of this step visible?
+      const bool full = (kb * BN + BN <= p.Tk) && (q0 + BM <= p.Tq) && (!p.causal || kb * BN + BN - 1 <= q0 + shift);
+      float prob[64];
+      uint32_t r[32];
+      if (!wait(&st->s_full, par, ST_BWD_S)) goto teardown;
+      ptx::tc_fence_after();
+#pragma unroll
+      for (int c2 = 0; c2 < 2; c2++) {
+        ptx::tmem_ld32(lane_addr + COL_S + c2 * 32, r);
+        ptx::tmem_ld_wait();
+#pragma unroll
+        for (int t = 0; t < 32; t++) {
+          const int col = half * 64 + c2 * 32 + t;
+          float pv = ex2(fmaf(__uint_as_float(r[t]), c, -st->stats[0][col]));
+          if (!full) {
+            const int qa = q0 + col;
+            const bool ok = key_ok && qa < p.Tq && (!p.causal || key <= qa + shift);
+            pv = ok ? pv : 0.0f;
+          }
+          prob[c2 * 32 + t] = pv;
+        }
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+          const int chunk = (c2 * 4 + q) ^ (trow & 7);
+          *reinterpret_cast<uint4 *>(pt_row + chunk * 16) = pack8(prob + c2 * 32 + q * 8);
+        }
+      }
+      ptx::fence_proxy_async_smem();
+      ptx::tc_fence_before();
+      ptx::mbar_arrive(bar(&st->p_ready));
+      if (!wait(&st->dp_full, par, ST_BWD_DP)) goto teardown;
+      ptx::tc_fence_after();
+#pragma unroll
+      for (int c2 = 0; c2 < 2; c2++) {
+        ptx::tmem_ld32(lane_addr + COL_DP + c2 * 32, r);
+        ptx::tmem_ld_wait();
+        float ds[32];
+#pragma unroll
+        for (int t = 0; t < 32; t++) {
+          const int col = half * 64 + c2 * 32 + t;
+          // the probability as the tensor core saw it (bf16), zero where masked
+          const float pb = bf16_round(prob[c2 * 32 + t]);
+          ds[t] = pb == 0.0f ? 0.0f : pb * (__uint_as_float(r[t]) - st->stats[1][col]);
+        }
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+          const int chunk = (c2 * 4 + q) ^ (trow & 7);
+          *reinterpret_cast<uint4 *>(dst_row + chunk * 16) = pack8(ds + q * 8);
+        }
+      }
+      ptx::mbar_arrive(bar(&st->stats_free));
+      ptx::fence_proxy_async_smem();
+      ptx::tc_fence_before();
+      ptx::mbar_arrive(bar(&st->ds_ready));
+      // dQ^T: this lane is head dimension trow, the columns are the step's queries
+      if (!wait(&st->dq_full, par, ST_BWD_DQ)) goto teardown;
+      ptx::tc_fence_after();
+      float *dq = p.dQacc + (int64_t)(p.q_off + q0) * p.ldQ + (int64_t)h * HD + trow;
+#pragma unroll
+      for (int c2 = 0; c2 < 2; c2++) {
+        ptx::tmem_ld32(lane_addr + COL_S + c2 * 32, r);
+        ptx::tmem_ld_wait();
+#pragma unroll
+        for (int t = 0; t < 32; t++) {
+          const int col = half * 64 + c2 * 32 + t;
+          if (q0 + col < p.Tq) atomicAdd(dq + (int64_t)col * p.ldQ, __uint_as_float(r[t]) * p.scale);
+        }
+      }
+      ptx::tc_fence_before();
+      ptx::mbar_arrive(bar(&st->dq_empty));
+    }
+    // dK and dV of this key block: one rounding
+    if (!wait(&st->acc_full, 0, ST_BWD_ACC)) goto teardown;
+    ptx::tc_fence_after();
+    {
+      uint32_t r[32];
+      __nv_bfloat16 *dk = p.dK + (int64_t)(p.k_off + key) * p.ldK + (int64_t)kvh * HD + half * 64;
+      __nv_bfloat16 *dv = p.dV + (int64_t)(p.k_off + key) * p.ldK + (int64_t)kvh * HD + half * 64;
+#pragma unroll
+      for (int c2 = 0; c2 < 2; c2++) {
+        float v[32];
+        ptx::tmem_ld32(lane_addr + COL_DK + c2 * 32, r);
+        ptx::tmem_ld_wait();
+#pragma unroll
+        for (int t = 0; t < 32; t++) v[t] = __uint_as_float(r[t]) * p.scale;
+        if (key_ok) {
+#pragma unroll
+          for (int q = 0; q < 4; q++) *reinterpret_cast<uint4 *>(dk + c2 * 32 + q * 8) = pack8(v + q * 8);
+        }
+        ptx::tmem_ld32(lane_addr + COL_DV + c2 * 32, r);
+        ptx::tmem_ld_wait();
+#pragma unroll
+        for (int t = 0; t < 32; t++) v[t] = __uint_as_float(r[t]);
+        if (key_ok) {
+#pragma unroll
+          for (int q = 0; q < 4; q++) *reinterpret_cast<uint4 *>(dv + c2 * 32 + q * 8) = pack8(v + q * 8);
+        }
+      }
+    }
+  }
+
+teardown:
+  if (*abort_flag) {
+    const uint64_t t0 = ptx::globaltimer_ns();
+    while (ptx::globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// delta[h][row] = sum_d dO[row, h, d] * O[row, h, d]; a warp per (row, head)
+__global__ void __launch_bounds__(256) attn_delta_all_kernel(int total_q, int heads, int head_dim,
+                                                             const __nv_bfloat16 *__restrict__ dO,
+                                                             const __nv_bfloat16 *__restrict__ O, float *__restrict__ delta) {
+  const int64_t w = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (w >= (int64_t)total_q * heads) return;
+  const int row = (int)(w / heads), h = (int)(w - (int64_t)row * heads);
+  const int64_t at = ((int64_t)row * heads + h) * head_dim;
+  float acc = 0.0f;
+  for (int c = (threadIdx.x & 31) * 4; c < head_dim; c += 128) {
+    const uint2 a = *reinterpret_cast<const uint2 *>(dO + at + c), b = *reinterpret_cast<const uint2 *>(O + at + c);
+    acc += bf16lo(a.x) * bf16lo(b.x) + bf16hi(a.x) * bf16hi(b.x) + bf16lo(a.y) * bf16lo(b.y) + bf16hi(a.y) * bf16hi(b.y);
+  }
+  acc = warp_sum(acc);
+  if ((threadIdx.x & 31) == 0) delta[(int64_t)h * total_q + row] = acc;
+}
+
+// fp32 -> bf16, eight elements per thread
+__global__ void __launch_bounds__(256) attn_round_kernel(int64_t n8, const float *__restrict__ src, __nv_bfloat16 *__restrict__ dst) {
+  const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
+  if (i >= n8) return;
+  const float4 a = reinterpret_cast<const float4 *>(src)[2 * i], b = reinterpret_cast<const float4 *>(src)[2 * i + 1];
+  const float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+  reinterpret_cast<uint4 *>(dst)[i] = pack8(v);
+}
+
 }  // namespace fa
 }  // namespace b200
 
@@ -410,6 +746,76 @@ int attn_fused_fwd(int num_seqs, int total_q, int total_k, const int *q_off, con
     p.Tk = k_len[sq];
     if ((head_dim == 128 ? launch_fwd<128>(p, num_q_heads, s) : launch_fwd<64>(p, num_q_heads, s)) != 0) return -1;
   }
+  return 0;
+}
+
+
+bool attn_fused_bwd_supported(int head_dim) { return head_dim == fa::BWD_HD; }
+
+// bytes of workspace the fused backward needs: the fp32 dQ accumulator and delta
+uint64_t attn_fused_bwd_workspace(int total_q, int num_q_heads, int head_dim) {
+  auto up = [](uint64_t v) { return (v + 255) / 256 * 256; };
+  return up((uint64_t)total_q * num_q_heads * head_dim * 4) + up((uint64_t)total_q * num_q_heads * 4);
+}
+
+// Backward over every sequence of the packed batch; arguments as b200_attention_bwd, the workspace sized by
+// attn_fused_bwd_workspace. dQ, dK and dV are overwritten.
+int attn_fused_bwd(int num_seqs, int total_q, int total_k, const int *q_off, const int *q_len, const int *k_off,
+                   const int *k_len, int num_q_heads, int num_kv_heads, int head_dim, const void *Q, const void *K,
+                   const void *V, const void *O, const float *lse, const void *dO, void *dQ, void *dK, void *dV,
+                   int is_causal, void *workspace, cudaStream_t s) {
+  fa::BwdParams p;
+  const uint64_t Dq = (uint64_t)num_q_heads * head_dim, Dk = (uint64_t)num_kv_heads * head_dim;
+  if (rows_map(&p.tmQ, Q, (uint64_t)total_q, Dq) || rows_map(&p.tmdO, dO, (uint64_t)total_q, Dq) ||
+      rows_map(&p.tmK, K, (uint64_t)total_k, Dk) || rows_map(&p.tmV, V, (uint64_t)total_k, Dk))
+    return -1;
+  const uint64_t acc_bytes = ((uint64_t)total_q * Dq * 4 + 255) / 256 * 256;
+  p.dQacc = (float *)workspace;
+  float *delta = (float *)((unsigned char *)workspace + acc_bytes);
+  p.delta = delta;
+  p.lse = lse;
+  p.dK = (__nv_bfloat16 *)dK;
+  p.dV = (__nv_bfloat16 *)dV;
+  p.causal = is_causal;
+  p.group = num_q_heads / num_kv_heads;
+  p.total_q = total_q;
+  p.ldQ = (int64_t)Dq;
+  p.ldK = (int64_t)Dk;
+  p.scale = 1.0f / sqrtf((float)head_dim);
+  p.status = attn_status_ptr();
+  B200_REQUIRE(p.status != nullptr, "attention: the status word of this device is not reachable");
+  static bool attr_set[MAX_DEVICES];
+  int dev = -1;
+  B200_CUDA(cudaGetDevice(&dev));
+  B200_REQUIRE(dev >= 0 && dev < MAX_DEVICES, "attention: device ordinal %d is out of range", dev);
+  if (!attr_set[dev]) {
+    B200_CUDA(cudaFuncSetAttribute(fa::attn_bwd_sm100_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   (int)fa::bwd_smem_bytes()));
+    attr_set[dev] = true;
+  }
+  B200_CUDA(cudaMemsetAsync(p.dQacc, 0, (size_t)total_q * Dq * 4, s));
+  const int64_t warps = (int64_t)total_q * num_q_heads;
+  fa::attn_delta_all_kernel<<<(unsigned)((warps + 7) / 8), 256, 0, s>>>(total_q, num_q_heads, head_dim,
+                                                                         (const __nv_bfloat16 *)dO, (const __nv_bfloat16 *)O, delta);
+  B200_CHECK_LAUNCH("attention_bwd (delta)");
+  for (int sq = 0; sq < num_seqs; sq++) {
+    if (k_len[sq] == 0) continue;
+    if (q_len[sq] == 0) {  // keys that no query of the batch reads
+      B200_CUDA(cudaMemsetAsync((__nv_bfloat16 *)dK + (int64_t)k_off[sq] * Dk, 0, (size_t)k_len[sq] * Dk * 2, s));
+      B200_CUDA(cudaMemsetAsync((__nv_bfloat16 *)dV + (int64_t)k_off[sq] * Dk, 0, (size_t)k_len[sq] * Dk * 2, s));
+      continue;
+    }
+    p.q_off = q_off[sq];
+    p.Tq = q_len[sq];
+    p.k_off = k_off[sq];
+    p.Tk = k_len[sq];
+    const int key_blocks = (p.Tk + fa::BN - 1) / fa::BN;
+    fa::attn_bwd_sm100_kernel<<<dim3((unsigned)key_blocks, (unsigned)num_kv_heads), fa::BWD_THREADS, fa::bwd_smem_bytes(), s>>>(p);
+    B200_CHECK_LAUNCH("attention_bwd (fused)");
+  }
+  const int64_t n8 = (int64_t)total_q * Dq / 8;
+  fa::attn_round_kernel<<<(unsigned)((n8 + 255) / 256), 256, 0, s>>>(n8, p.dQacc, (__nv_bfloat16 *)dQ);
+  B200_CHECK_LAUNCH("attention_bwd (dQ rounding)");
   return 0;
 }
 

@@ -85,7 +85,7 @@ class Decoder:
         # backward scratch shared by the layers
         self.dx, self.dxn, self.dattn = buf((T, c.d)), buf((T, c.d)), buf((T, Dq))
         self.dq, self.dk, self.dv = buf((T, Dq)), buf((T, Dk)), buf((T, Dk))
-        self.attn_ws = torch.empty(ops.attention_workspace_bytes(True, max_seqlen, max_seqlen, c.head_dim), dtype=torch.uint8,
+        self.attn_ws = torch.empty(max(256, ops.attention_workspace_bytes(True, c.n_heads, c.n_kv_heads, c.head_dim, T, max_seqlen, max_seqlen)), dtype=torch.uint8,
                                    device=dev)
         self.norm_ws = torch.empty(ops.rms_norm_bwd_w_workspace_bytes(T, c.d), dtype=torch.uint8, device=dev)
 

@@ -384,8 +384,9 @@ def _int_array(values):
     return (C.c_int * len(values))(*[int(v) for v in values])
 
 
-def attention_workspace_bytes(is_training, max_seqlen_q, max_seqlen_k, head_dim):
-    return int(_lib.load().b200_attention_workspace_bytes(int(bool(is_training)), max_seqlen_q, max_seqlen_k, head_dim))
+def attention_workspace_bytes(is_training, num_q_heads, num_kv_heads, head_dim, max_total_q, max_seqlen_q, max_seqlen_k):
+    return int(_lib.load().b200_attention_workspace_bytes(int(bool(is_training)), num_q_heads, num_kv_heads, head_dim,
+                                                          max_total_q, max_seqlen_q, max_seqlen_k))
 
 
 def attention_fwd(q_offsets, q_lens, k_offsets, k_lens, num_q_heads, num_kv_heads, head_dim, x_q, x_k, x_v, x_attn_out,

@@ -44,7 +44,7 @@ def test_attention_forward_backward(oracle, q_len, k_len, Hq, Hkv, hd, causal):
     Qd, Kd, Vd, dOd = dev_bf16(Q), dev_bf16(K), dev_bf16(V), dev_bf16(dO)
     O = torch.zeros_like(Qd)
     lse = torch.zeros((Hq, tq), dtype=torch.float32, device="cuda")
-    nbytes = ops.attention_workspace_bytes(True, max(q_len), max(k_len), hd)
+    nbytes = ops.attention_workspace_bytes(True, Hq, Hkv, hd, tq, max(q_len), max(k_len))
     ws = torch.empty(nbytes, dtype=torch.uint8, device="cuda")
     ops.attention_fwd(q_off, q_len, k_off, k_len, Hq, Hkv, hd, Qd, Kd, Vd, O, lse, causal, ws)
     torch.cuda.synchronize()
@@ -64,4 +64,5 @@ def test_attention_forward_backward(oracle, q_len, k_len, Hq, Hkv, hd, causal):
         assert_close(_f32(host_bits(got)), _f32(ref), rtol=2e-2, atol=3e-2, max_bad_frac=2e-3, what=what)
     # a workspace that is too small is refused
     with pytest.raises(RuntimeError):
-        ops.attention_fwd(q_off, q_len, k_off, k_len, Hq, Hkv, hd, Qd, Kd, Vd, O, lse, causal, ws[:1024])
+        ops.attention_bwd(q_off, q_len, k_off, k_len, Hq, Hkv, hd, Qd, Kd, Vd, dev_bf16(ref_O), torch.from_numpy(ref_lse).cuda(),
+                          dOd, dQ, dK, dV, causal, ws[:1024])

@@ -16,6 +16,7 @@
 // and the CTA leaves through the common teardown.
 #include <cuda.h>
 #include <math.h>
+#include <stddef.h>
 
 #include "common.cuh"
 #include "sm100_ptx.cuh"
@@ -40,7 +41,7 @@ struct FwdParams {
   CUtensorMap tmQ, tmK, tmV;  // [rows][heads * HD] bf16, boxes of 64 columns x 128 rows, 128-byte swizzle
   __nv_bfloat16 *O;
   float *lse;  // [heads][total_q]
-  int q_off, Tq, k_off, Tk, causal, group, total_q;
+  int q_off, Tq, k_off, Tk, causal, group, total_q, tiles, num_q_heads;
   int64_t ldO;
   float scale;
   int *status;
@@ -62,6 +63,19 @@ __device__ __forceinline__ float ex2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+
+// shared-memory accesses by 32-bit shared address (kept in program order among themselves)
+__device__ __forceinline__ float4 lds128(uint32_t addr) {
+  float4 v;
+  asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ void sts128(uint32_t addr, const uint4 &v) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+__device__ __forceinline__ void sts32(uint32_t addr, float v) {
+  asm volatile("st.shared.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
 }
 
 template <int HD>
@@ -110,8 +124,9 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_sm100_kernel(const __
   ptx::tc_fence_after();
   const uint32_t tmem_base = st->tmem_base;
 
-  // the CTAs with the most keys to visit (the last query rows under a causal mask) start first
-  const int qt = (int)gridDim.x - 1 - (int)blockIdx.x, h = (int)blockIdx.y, kvh = h / p.group;
+  // one-dimensional grid, query tile major: the tiles with the most keys to visit (the last query rows under a causal
+  // mask) start first on every head; neighbouring CTAs are the heads of one group and share their K / V tiles in L2
+  const int qt = p.tiles - 1 - (int)blockIdx.x / p.num_q_heads, h = (int)blockIdx.x % p.num_q_heads, kvh = h / p.group;
   const int r0 = qt * QT * BM;
   const int shift = p.Tk - p.Tq;  // the last query is aligned with the last key
   int nkb[QT], nkb_max = 0;
@@ -316,8 +331,8 @@ teardown:
 //     P^T = exp2(S^T * scale * log2 e - lse * log2 e),  dS^T = P^T o (dP^T - delta)   (threads; bf16 into shared memory)
 //     dV += P^T dO,  dK += dS^T Q                       (accumulated in tensor memory over all steps of the CTA)
 //     dQ^T = K^T dS^T                                   (tensor memory, over the columns S^T occupied)
-// dQ^T is added to an fp32 accumulator in global memory (red.add, 128 contiguous bytes per warp and query) that a cast
-// kernel rounds once; dK (times the softmax scale) and dV are rounded once at the end of the CTA. The Q and dO tiles are
+// dQ^T is staged in shared memory and added to an fp32 accumulator in global memory by bulk reductions
+// (cp.reduce.async.bulk, 128 contiguous bytes each) that a cast kernel rounds once; dK (times the softmax scale) and dV are rounded once at the end of the CTA. The Q and dO tiles are
 // read by the tensor core both ways round - as [queries x dims] for S^T / dP^T and as [dims x queries] for dK / dV -
 // from the same swizzled bytes, and so are K and dS^T for dQ^T.
 // ---------------------------------------------------------------------------------------
@@ -334,21 +349,23 @@ struct BwdParams {
   const float *lse, *delta;  // [heads][total_q]
   float *dQacc;              // [total_q][heads * 128] fp32, zeroed by the caller
   __nv_bfloat16 *dK, *dV;
-  int q_off, Tq, k_off, Tk, causal, group, total_q;
+  int q_off, Tq, k_off, Tk, causal, group, total_q, num_kv_heads;
   int64_t ldQ, ldK;
   float scale;
   int *status;
 };
 
 struct BwdTail {
-  uint64_t kv_full, ring_full[RING], ring_empty[RING], s_full, dp_full, p_ready, ds_ready, dq_full, dq_empty, acc_full,
-      stats_full, stats_free;
+  uint64_t kv_full, ring_full[RING], ring_empty[RING], s_full, dp_full, p_ready, ds_ready, dq_full, dq_read, dq_empty, acc_full,
+      stats0;
   uint32_t tmem_base;
   int abort_flag;
-  float stats[2][128];  // lse * log2 e and delta of the step's 128 queries
+  alignas(16) float stats[2][128];  // lse * log2 e and delta of the step's 128 queries (read 16 bytes at a time)
 };
 
 constexpr size_t bwd_smem_bytes() { return 1024 + (size_t)(4 + RING) * BWD_TILE + sizeof(BwdTail); }
+static_assert(bwd_smem_bytes() <= 232448, "the backward kernel's shared memory exceeds what one CTA can be given");
+static_assert(offsetof(BwdTail, stats) % 16 == 0, "the statistics are read with 16-byte loads");
 
 __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_sm100_kernel(const __grid_constant__ BwdParams p) {
   constexpr int HD = BWD_HD;
@@ -375,10 +392,10 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_sm100_kernel(const __
     ptx::mbar_init(bar(&st->p_ready), 256);
     ptx::mbar_init(bar(&st->ds_ready), 256);
     ptx::mbar_init(bar(&st->dq_full), 1);
+    ptx::mbar_init(bar(&st->dq_read), 256);
     ptx::mbar_init(bar(&st->dq_empty), 256);
     ptx::mbar_init(bar(&st->acc_full), 1);
-    ptx::mbar_init(bar(&st->stats_full), 256);
-    ptx::mbar_init(bar(&st->stats_free), 256);
+    ptx::mbar_init(bar(&st->stats0), 256);
     st->abort_flag = 0;
     ptx::fence_barrier_init();
     ptx::fence_proxy_async_smem();
@@ -398,7 +415,9 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_sm100_kernel(const __
   ptx::tc_fence_after();
   const uint32_t tmem_base = st->tmem_base;
 
-  const int kb = (int)blockIdx.x, kvh = (int)blockIdx.y;  // the key blocks most queries see come first
+  // one-dimensional grid, key block major: the key blocks most queries see (the first ones, under a causal mask) start
+  // first on every key/value head, the short ones fill in behind them
+  const int kb = (int)blockIdx.x / p.num_kv_heads, kvh = (int)blockIdx.x % p.num_kv_heads;
   const int shift = p.Tk - p.Tq;
   const int nqb = (p.Tq + BM - 1) / BM;
   const int qb_start = p.causal ? max(0, kb * BN - shift) / BM : 0;
@@ -444,7 +463,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_sm100_kernel(const __
         const uint32_t q_tile = ring_base + (uint32_t)((nq % RING) * BWD_TILE), do_tile = ring_base + (uint32_t)((nd % RING) * BWD_TILE);
         const uint32_t par = (uint32_t)(i & 1);
         if (!wait(&st->ring_full[nq % RING], (uint32_t)((nq / RING) & 1), ST_BWD_RING_FULL)) break;
-        if (i > 0 && !wait(&st->dq_empty, par ^ 1u, ST_BWD_DQ_EMPTY)) break;
+        if (i > 0 && !wait(&st->dq_read, par ^ 1u, ST_BWD_DQ_EMPTY)) break;
         ptx::tc_fence_after();
 #pragma unroll
         for (int k16 = 0; k16 < HD / 16; k16++)
@@ -464,6 +483,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_sm100_kernel(const __
         ptx::umma_commit(bar(&st->ring_empty[nd % RING]));
         if (!wait(&st->ds_ready, par, ST_BWD_DS)) break;
         ptx::tc_fence_after();
+        // dK before dQ^T: dq_full then also says that dS^T and P^T are done with, and the dQ staging lies over them
 #pragma unroll
         for (int k16 = 0; k16 < BM / 16; k16++)
           ptx::umma_bf16(tmem_base + COL_DK, kmaj(dst_base, k16), mnmaj(q_tile, k16), idesc_km, (i > 0 || k16 > 0));
@@ -483,28 +503,30 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_sm100_kernel(const __
     const int key = kb * BN + trow;  // position of this lane's key in its sequence (steps 1-2 and the end)
     const bool key_ok = key < p.Tk;
     const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(half * 64);
-    unsigned char *pt_row = sPT + half * SLAB + trow * 128, *dst_row = sDST + half * SLAB + trow * 128;
+    const uint32_t pt_addr = ptx::smem_u32(sPT + half * SLAB + trow * 128), dst_addr = ptx::smem_u32(sDST + half * SLAB + trow * 128);
+    const uint32_t stats_addr = ptx::smem_u32(&st->stats[0][0]), stage_addr = ptx::smem_u32(sPT);
     const float c = p.scale * LOG2E;
     const int st_t = tid - 64;  // 0 .. 255
+    // lse * log2 e (threads 0-127) or delta (128-255) of query st_t % 128 of step `step`: fetched a step ahead
+    auto stat_load = [&](int step) {
+      const int hh = kvh * p.group + step / per_head, qa = (qb_start + step % per_head) * BM + (st_t & 127);
+      if (step >= n_steps || qa >= p.Tq) return 0.0f;
+      const int64_t at = (int64_t)hh * p.total_q + p.q_off + qa;
+      return st_t < 128 ? p.lse[at] * LOG2E : p.delta[at];
+    };
+    st->stats[st_t >> 7][st_t & 127] = stat_load(0);
+    ptx::mbar_arrive(bar(&st->stats0));
+    if (!wait(&st->stats0, 0, ST_BWD_STATS)) goto teardown;
     for (int i = 0; i < n_steps; i++) {
       const int h = kvh * p.group + i / per_head, qb = qb_start + i % per_head;
       const uint32_t par = (uint32_t)(i & 1);
       const int q0 = qb * BM;
-      // every warp has finished with the statistics of the step before (a bounded wait, like all the others)
-      if (i > 0 && !wait(&st->stats_free, par ^ 1u, ST_BWD_STATS)) goto teardown;
-      {
-        const int col = st_t & 127, qa = q0 + col;
-        float v = 0.0f;
-        if (qa < p.Tq) {
-          const int64_t at = (int64_t)h * p.total_q + p.q_off + qa;
-          v = st_t < 128 ? p.lse[at] * LOG2E : p.delta[at];
-        }
-        st->stats[st_t >> 7][col] = v;
-      }
-      ptx::mbar_arrive(bar(&st->stats_full));
-      if (!wait(&st->stats_full, par, ST_BWD_STATS)) goto teardown;
-      // is every (key, query) pair of this step visible?
-      const bool full = (kb * BN + BN <= p.Tk) && (q0 + BM <= p.Tq) && (!p.causal || kb * BN + BN - 1 <= q0 + shift);
+      // every thread has left the step before: its statistics for this step are written, its part of the dQ staging
+      // area (which lies over P^T and dS^T) has been read by the bulk reductions
+      if (i > 0 && !wait(&st->dq_empty, par ^ 1u, ST_BWD_DQ_EMPTY)) goto teardown;
+      const float stat_next = stat_load(i + 1);  // in flight while this step computes
+      // queries of this step the lane's key is visible to: columns lo_rel <= col < hi_rel
+      const int lo_rel = (key_ok ? (p.causal ? key - shift : 0) : (1 << 30)) - q0, hi_rel = p.Tq - q0;
       float prob[64];
       uint32_t r[32];
       if (!wait(&st->s_full, par, ST_BWD_S)) goto teardown;
@@ -512,23 +534,19 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_sm100_kernel(const __
 #pragma unroll
       for (int c2 = 0; c2 < 2; c2++) {
         ptx::tmem_ld32(lane_addr + COL_S + c2 * 32, r);
+        float4 l4[8];
+#pragma unroll
+        for (int q = 0; q < 8; q++) l4[q] = lds128(stats_addr + (uint32_t)((half * 64 + c2 * 32 + q * 4) * 4));
         ptx::tmem_ld_wait();
 #pragma unroll
         for (int t = 0; t < 32; t++) {
           const int col = half * 64 + c2 * 32 + t;
-          float pv = ex2(fmaf(__uint_as_float(r[t]), c, -st->stats[0][col]));
-          if (!full) {
-            const int qa = q0 + col;
-            const bool ok = key_ok && qa < p.Tq && (!p.causal || key <= qa + shift);
-            pv = ok ? pv : 0.0f;
-          }
-          prob[c2 * 32 + t] = pv;
+          const float l2 = (t & 3) == 0 ? l4[t >> 2].x : (t & 3) == 1 ? l4[t >> 2].y : (t & 3) == 2 ? l4[t >> 2].z : l4[t >> 2].w;
+          const float pv = ex2(fmaf(__uint_as_float(r[t]), c, -l2));
+          prob[c2 * 32 + t] = (col >= lo_rel && col < hi_rel) ? pv : 0.0f;
         }
 #pragma unroll
-        for (int q = 0; q < 4; q++) {
-          const int chunk = (c2 * 4 + q) ^ (trow & 7);
-          *reinterpret_cast<uint4 *>(pt_row + chunk * 16) = pack8(prob + c2 * 32 + q * 8);
-        }
+        for (int q = 0; q < 4; q++) sts128(pt_addr + (uint32_t)((((c2 * 4 + q) ^ (trow & 7))) * 16), pack8(prob + c2 * 32 + q * 8));
       }
       ptx::fence_proxy_async_smem();
       ptx::tc_fence_before();
@@ -538,42 +556,58 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_sm100_kernel(const __
 #pragma unroll
       for (int c2 = 0; c2 < 2; c2++) {
         ptx::tmem_ld32(lane_addr + COL_DP + c2 * 32, r);
+        float4 d4[8];
+#pragma unroll
+        for (int q = 0; q < 8; q++) d4[q] = lds128(stats_addr + (uint32_t)((128 + half * 64 + c2 * 32 + q * 4) * 4));
         ptx::tmem_ld_wait();
         float ds[32];
 #pragma unroll
         for (int t = 0; t < 32; t++) {
-          const int col = half * 64 + c2 * 32 + t;
-          // the probability as the tensor core saw it (bf16), zero where masked
+          const float dl = (t & 3) == 0 ? d4[t >> 2].x : (t & 3) == 1 ? d4[t >> 2].y : (t & 3) == 2 ? d4[t >> 2].z : d4[t >> 2].w;
+          // the probability as the tensor core saw it (bf16); zero where masked, whatever dP holds there
           const float pb = bf16_round(prob[c2 * 32 + t]);
-          ds[t] = pb == 0.0f ? 0.0f : pb * (__uint_as_float(r[t]) - st->stats[1][col]);
+          ds[t] = pb == 0.0f ? 0.0f : pb * (__uint_as_float(r[t]) - dl);
         }
 #pragma unroll
-        for (int q = 0; q < 4; q++) {
-          const int chunk = (c2 * 4 + q) ^ (trow & 7);
-          *reinterpret_cast<uint4 *>(dst_row + chunk * 16) = pack8(ds + q * 8);
-        }
+        for (int q = 0; q < 4; q++) sts128(dst_addr + (uint32_t)((((c2 * 4 + q) ^ (trow & 7))) * 16), pack8(ds + q * 8));
       }
-      ptx::mbar_arrive(bar(&st->stats_free));
       ptx::fence_proxy_async_smem();
       ptx::tc_fence_before();
       ptx::mbar_arrive(bar(&st->ds_ready));
-      // dQ^T: this lane is head dimension trow, the columns are the step's queries
+      // once every thread is past its last read of this step's statistics, the next step's take their place
+      if (!wait(&st->ds_ready, par, ST_BWD_DS)) goto teardown;
+      st->stats[st_t >> 7][st_t & 127] = stat_next;
+      // dQ^T: this lane is head dimension trow, the columns are the step's queries. It is staged as [query][dim] fp32
+      // in shared memory (P^T and dS^T are done with: dq_full follows the MMAs that read them) and added to the
+      // accumulator in global memory by bulk reductions of 128 bytes (32 dims of one query), two per lane.
       if (!wait(&st->dq_full, par, ST_BWD_DQ)) goto teardown;
       ptx::tc_fence_after();
-      float *dq = p.dQacc + (int64_t)(p.q_off + q0) * p.ldQ + (int64_t)h * HD + trow;
-#pragma unroll
-      for (int c2 = 0; c2 < 2; c2++) {
-        ptx::tmem_ld32(lane_addr + COL_S + c2 * 32, r);
-        ptx::tmem_ld_wait();
-#pragma unroll
-        for (int t = 0; t < 32; t++) {
-          const int col = half * 64 + c2 * 32 + t;
-          if (q0 + col < p.Tq) atomicAdd(dq + (int64_t)col * p.ldQ, __uint_as_float(r[t]) * p.scale);
-        }
-      }
+      uint32_t r2[32];
+      ptx::tmem_ld32(lane_addr + COL_S, r);
+      ptx::tmem_ld32(lane_addr + COL_S + 32, r2);
+      ptx::tmem_ld_wait();
+      // the tensor core may overwrite these columns with the next S^T from here on
       ptx::tc_fence_before();
+      ptx::mbar_arrive(bar(&st->dq_read));
+#pragma unroll
+      for (int t = 0; t < 32; t++) {
+        sts32(stage_addr + (uint32_t)(((half * 64 + t) * HD + trow) * 4), __uint_as_float(r[t]) * p.scale);
+        sts32(stage_addr + (uint32_t)(((half * 64 + 32 + t) * HD + trow) * 4), __uint_as_float(r2[t]) * p.scale);
+      }
+      ptx::fence_proxy_async_smem();
+      __syncwarp();
+#pragma unroll
+      for (int rep = 0; rep < 2; rep++) {
+        const int col = half * 64 + rep * 32 + lane;
+        if (col < hi_rel)
+          ptx::bulk_reduce_add_f32(p.dQacc + (int64_t)(p.q_off + q0 + col) * p.ldQ + (int64_t)h * HD + quarter * 32,
+                                   stage_addr + (uint32_t)((col * HD + quarter * 32) * 4), 128);
+      }
+      ptx::bulk_commit_group();
+      ptx::bulk_wait_group_read0();
       ptx::mbar_arrive(bar(&st->dq_empty));
     }
+    ptx::bulk_wait_group0();
     // dK and dV of this key block: one rounding
     if (!wait(&st->acc_full, 0, ST_BWD_ACC)) goto teardown;
     ptx::tc_fence_after();
@@ -698,7 +732,7 @@ int *attn_status_ptr() {
 }
 
 template <int HD>
-int launch_fwd(const fa::FwdParams &p, int num_q_heads, cudaStream_t s) {
+int launch_fwd(fa::FwdParams &p, int num_q_heads, cudaStream_t s) {
   static bool attr_set[MAX_DEVICES];
   int dev = -1;
   B200_CUDA(cudaGetDevice(&dev));
@@ -708,8 +742,9 @@ int launch_fwd(const fa::FwdParams &p, int num_q_heads, cudaStream_t s) {
     B200_CUDA(cudaFuncSetAttribute(fa::attn_fwd_sm100_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     attr_set[dev] = true;
   }
-  const int tiles = (p.Tq + fa::QT * fa::BM - 1) / (fa::QT * fa::BM);
-  fa::attn_fwd_sm100_kernel<HD><<<dim3((unsigned)tiles, (unsigned)num_q_heads), fa::FWD_THREADS, smem, s>>>(p);
+  p.tiles = (p.Tq + fa::QT * fa::BM - 1) / (fa::QT * fa::BM);
+  p.num_q_heads = num_q_heads;
+  fa::attn_fwd_sm100_kernel<HD><<<(unsigned)(p.tiles * num_q_heads), fa::FWD_THREADS, smem, s>>>(p);
   B200_CHECK_LAUNCH("attention_fwd (fused)");
   return 0;
 }
@@ -778,6 +813,7 @@ int attn_fused_bwd(int num_seqs, int total_q, int total_k, const int *q_off, con
   p.dV = (__nv_bfloat16 *)dV;
   p.causal = is_causal;
   p.group = num_q_heads / num_kv_heads;
+  p.num_kv_heads = num_kv_heads;
   p.total_q = total_q;
   p.ldQ = (int64_t)Dq;
   p.ldK = (int64_t)Dk;
@@ -810,7 +846,7 @@ int attn_fused_bwd(int num_seqs, int total_q, int total_k, const int *q_off, con
     p.k_off = k_off[sq];
     p.Tk = k_len[sq];
     const int key_blocks = (p.Tk + fa::BN - 1) / fa::BN;
-    fa::attn_bwd_sm100_kernel<<<dim3((unsigned)key_blocks, (unsigned)num_kv_heads), fa::BWD_THREADS, fa::bwd_smem_bytes(), s>>>(p);
+    fa::attn_bwd_sm100_kernel<<<(unsigned)(key_blocks * num_kv_heads), fa::BWD_THREADS, fa::bwd_smem_bytes(), s>>>(p);
     B200_CHECK_LAUNCH("attention_bwd (fused)");
   }
   const int64_t n8 = (int64_t)total_q * Dq / 8;

@@ -215,6 +215,20 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
       : "memory");
 }
 
+// ---- bulk reduction shared -> global (fp32 add), bulk-group completion ---------------------------------
+// Both addresses 16-byte aligned, the size a multiple of 16 bytes. The shared-memory bytes must have been made
+// visible to the async proxy (fence_proxy_async_smem) by the threads that wrote them.
+__device__ __forceinline__ void bulk_reduce_add_f32(float *gdst, uint32_t smem_src, uint32_t bytes) {
+  asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.f32 [%0], [%1], %2;" ::"l"(gdst), "r"(smem_src),
+               "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// the source bytes of every committed group of this thread have been read
+__device__ __forceinline__ void bulk_wait_group_read0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// every committed group of this thread is complete
+__device__ __forceinline__ void bulk_wait_group0() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
 // ---- descriptors ------------------------------------------------------------------------
 // Shared-memory matrix descriptor (sm_100 format): start address >> 4 in bits [0,14), leading
 // byte offset >> 4 in [16,30), stride byte offset >> 4 in [32,46), version 1 in [46,48),

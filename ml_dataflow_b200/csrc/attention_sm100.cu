@@ -182,12 +182,12 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_sm100_kernel(const __
         }
         ptx::umma_commit(bar(&st->s_full[g]));
       };
-      auto issue_pv = [&](int g, int slot) {
+      auto issue_pv = [&](int g, int slot, bool first) {
 #pragma unroll
         for (int k16 = 0; k16 < BN / 16; k16++) {
           const uint32_t a_off = (uint32_t)((k16 >> 2) * SLAB + (k16 & 3) * 32);
           ptx::umma_bf16(tmem_base + (uint32_t)(QT * BN + g * HD), ptx::make_smem_desc(p_base + g * P_TILE + a_off, 0, 1024),
-                         ptx::make_smem_desc(kv_base + slot * KV_TILE + k16 * 2048, SLAB, 1024), idesc_pv, k16 > 0);
+                         ptx::make_smem_desc(kv_base + slot * KV_TILE + k16 * 2048, SLAB, 1024), idesc_pv, !first || k16 > 0);
         }
         ptx::umma_commit(bar(&st->pv_full[g]));
       };
@@ -205,13 +205,13 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_sm100_kernel(const __
         if (has_next && !wait(&st->kv_full[nk % KV_SLOTS], (uint32_t)((nk / KV_SLOTS) & 1), ST_ATTN_KV_FULL)) break;
         for (int g = 0; g < QT; g++) {
           if (j >= nkb[g]) continue;
-          // P_g of this step is in shared memory; the group has also folded O'_g of the step before and read all of S_g
+          // P_g of this step is in shared memory, the group has read all of S_g and, if the row maxima grew, rescaled O_g
           if (!wait(&st->p_ready[g], (uint32_t)(j & 1), ST_ATTN_P)) {
             alive = false;
             break;
           }
           ptx::tc_fence_after();
-          issue_pv(g, nv % KV_SLOTS);
+          issue_pv(g, nv % KV_SLOTS, j == 0);
           if (j + 1 < nkb[g]) issue_s(g, nk % KV_SLOTS);
         }
         if (!alive) break;
@@ -228,83 +228,114 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_sm100_kernel(const __
     const int limit = p.causal ? min(p.Tk, row + 1 + shift) : p.Tk;  // keys this row sees
     const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
     const uint32_t s_addr = lane_addr + (uint32_t)(g * BN), o_addr = lane_addr + (uint32_t)(QT * BN + g * HD);
-    unsigned char *p_row = sP + g * P_TILE + trow * 128;
+    const uint32_t p_addr = ptx::smem_u32(sP + g * P_TILE + trow * 128);
     const float c = p.scale * LOG2E;
-    float acc[HD];
-#pragma unroll
-    for (int i = 0; i < HD; i++) acc[i] = 0.0f;
+    // m is the score the probabilities are taken against: the row maximum of the first key block, raised (with the sum
+    // and the output in tensor memory rescaled) only when a later block's maximum exceeds it by more than 2^8
     float m = -INFINITY, l = 0.0f;
     for (int j = 0; j < nkb[g]; j++) {
       if (!wait(&st->s_full[g], (uint32_t)(j & 1), ST_ATTN_S)) goto teardown;
       ptx::tc_fence_after();
       const int lim = limit - j * BN;  // columns below lim are visible
-      uint32_t r[32];
-      float mx = m;
-#pragma unroll
-      for (int c4 = 0; c4 < BN / 32; c4++) {
-        ptx::tmem_ld32(s_addr + c4 * 32, r);
-        ptx::tmem_ld_wait();
+      // first pass over the scores: the row maximum (two chunks of 32 columns in flight)
+      uint32_t ra[32], rb[32];
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+      auto max32 = [&](const uint32_t *v, int c4) {
         if (lim >= (c4 + 1) * 32) {
 #pragma unroll
-          for (int i = 0; i < 32; i++) mx = fmaxf(mx, __uint_as_float(r[i]));
+          for (int i = 0; i < 32; i++) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(v[i]));
         } else {
 #pragma unroll
-          for (int i = 0; i < 32; i++)
-            if (c4 * 32 + i < lim) mx = fmaxf(mx, __uint_as_float(r[i]));
+          for (int i = 0; i < 32; i++) mx4[i & 3] = fmaxf(mx4[i & 3], c4 * 32 + i < lim ? __uint_as_float(v[i]) : -INFINITY);
+        }
+      };
+      ptx::tmem_ld32(s_addr, ra);
+      ptx::tmem_ld32(s_addr + 32, rb);
+      ptx::tmem_ld_wait();
+      max32(ra, 0);
+      ptx::tmem_ld32(s_addr + 64, ra);
+      max32(rb, 1);
+      ptx::tmem_ld32(s_addr + 96, rb);
+      ptx::tmem_ld_wait();
+      max32(ra, 2);
+      max32(rb, 3);
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+      if (j == 0) {
+        m = mx;
+      } else {
+        const bool grow = (mx - m) * c > 8.0f;
+        if (__any_sync(0xffffffffu, grow)) {  // tensor-memory accesses are warp-wide: every lane takes part
+          const float m_new = grow ? mx : m;
+          const float alpha = ex2((m - m_new) * c);  // 1 for the lanes that keep their offset
+          if (!wait(&st->pv_full[g], (uint32_t)((j - 1) & 1), ST_ATTN_PV)) goto teardown;
+          ptx::tc_fence_after();
+#pragma unroll
+          for (int c4 = 0; c4 < HD / 32; c4++) {
+            ptx::tmem_ld32(o_addr + c4 * 32, ra);
+            ptx::tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; i++) ra[i] = __float_as_uint(__uint_as_float(ra[i]) * alpha);
+            ptx::tmem_st32(o_addr + c4 * 32, ra);
+          }
+          ptx::tmem_st_wait();
+          l *= alpha;
+          m = m_new;
         }
       }
-      // a row that has seen no key yet keeps max = -inf: its probabilities are exp2(-inf) = 0 against a zero offset
-      const float mc = (mx == -INFINITY) ? 0.0f : mx * c;
-      const float alpha = (m == -INFINITY) ? 0.0f : ex2(m * c - mc);
-      float sum = 0.0f;
-#pragma unroll
-      for (int c4 = 0; c4 < BN / 32; c4++) {
-        ptx::tmem_ld32(s_addr + c4 * 32, r);
-        ptx::tmem_ld_wait();
-        float pr[32];
-        if (lim >= (c4 + 1) * 32) {
-#pragma unroll
-          for (int i = 0; i < 32; i++) pr[i] = ex2(fmaf(__uint_as_float(r[i]), c, -mc));
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; i++) pr[i] = (c4 * 32 + i < lim) ? ex2(fmaf(__uint_as_float(r[i]), c, -mc)) : 0.0f;
-        }
-#pragma unroll
-        for (int i = 0; i < 32; i++) sum += pr[i];
-        // keys c4*32 .. +31 of this row: slab c4 / 2, 16-byte chunks (c4 % 2) * 4 + q, swizzled with the row
-        unsigned char *slab = p_row + (c4 >> 1) * SLAB;
+      // a row that has seen no key yet keeps m = -inf: its probabilities are exp2(-inf) = 0 against a zero offset
+      const float mc = (m == -INFINITY) ? 0.0f : m * c;
+      // second pass: the probabilities, their sum, and P as bf16 in the layout the P V product reads
+      float sum4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+      auto probs32 = [&](const uint32_t *v, int c4) {
 #pragma unroll
         for (int q = 0; q < 4; q++) {
-          const int chunk = ((c4 & 1) * 4 + q) ^ (trow & 7);
-          *reinterpret_cast<uint4 *>(slab + chunk * 16) = pack8(pr + q * 8);
+          float pr[8];
+#pragma unroll
+          for (int i = 0; i < 8; i++) {
+            const float e = ex2(fmaf(__uint_as_float(v[q * 8 + i]), c, -mc));
+            pr[i] = (c4 * 32 + q * 8 + i < lim) ? e : 0.0f;
+            sum4[i & 3] += pr[i];
+          }
+          // keys c4*32 + q*8 .. +7 of this row: slab c4 / 2, 16-byte chunk (c4 % 2) * 4 + q, swizzled with the row
+          sts128(p_addr + (uint32_t)((c4 >> 1) * SLAB + ((((c4 & 1) * 4 + q) ^ (trow & 7)) * 16)), pack8(pr));
         }
-      }
-      l = l * alpha + sum;
-      m = mx;
+      };
+      ptx::tmem_ld32(s_addr, ra);
+      ptx::tmem_ld32(s_addr + 32, rb);
+      ptx::tmem_ld_wait();
+      probs32(ra, 0);
+      ptx::tmem_ld32(s_addr + 64, ra);
+      probs32(rb, 1);
+      ptx::tmem_ld32(s_addr + 96, rb);
+      ptx::tmem_ld_wait();
+      probs32(ra, 2);
+      probs32(rb, 3);
+      l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
       ptx::fence_proxy_async_smem();
       ptx::tc_fence_before();
       ptx::mbar_arrive(bar(&st->p_ready[g]));
-      if (!wait(&st->pv_full[g], (uint32_t)(j & 1), ST_ATTN_PV)) goto teardown;
-      ptx::tc_fence_after();
-#pragma unroll
-      for (int c4 = 0; c4 < HD / 32; c4++) {
-        ptx::tmem_ld32(o_addr + c4 * 32, r);
-        ptx::tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; i++) acc[c4 * 32 + i] = fmaf(acc[c4 * 32 + i], alpha, __uint_as_float(r[i]));
-      }
     }
-    if (nkb[g] > 0 && row < p.Tq) {
+    if (nkb[g] > 0) {
+      if (!wait(&st->pv_full[g], (uint32_t)((nkb[g] - 1) & 1), ST_ATTN_PV)) goto teardown;
+      ptx::tc_fence_after();
       const float inv = l > 0.0f ? __fdividef(1.0f, l) : 0.0f;
       __nv_bfloat16 *o = p.O + (int64_t)(p.q_off + row) * p.ldO + (int64_t)h * HD;
 #pragma unroll
-      for (int i = 0; i < HD; i += 8) {
-        float v[8];
+      for (int c4 = 0; c4 < HD / 32; c4++) {
+        uint32_t r[32];
+        ptx::tmem_ld32(o_addr + c4 * 32, r);
+        ptx::tmem_ld_wait();
+        if (row < p.Tq) {
 #pragma unroll
-        for (int t = 0; t < 8; t++) v[t] = acc[i + t] * inv;
-        *reinterpret_cast<uint4 *>(o + i) = pack8(v);
+          for (int i = 0; i < 32; i += 8) {
+            float v[8];
+#pragma unroll
+            for (int t = 0; t < 8; t++) v[t] = __uint_as_float(r[i + t]) * inv;
+            *reinterpret_cast<uint4 *>(o + c4 * 32 + i) = pack8(v);
+          }
+        }
       }
-      p.lse[(int64_t)h * p.total_q + p.q_off + row] = l > 0.0f ? m * p.scale + logf(l) : -INFINITY;
+      if (row < p.Tq) p.lse[(int64_t)h * p.total_q + p.q_off + row] = l > 0.0f ? m * p.scale + logf(l) : -INFINITY;
     }
   }
 

@@ -214,7 +214,8 @@ def block_ops_profile(dev, peaks, iters=5, with_attention=True):
         tf = flop / (t * 1e-3) / 1e12
         res[name] = dict(ms=round(t, 3), bound="tensor", achieved=round(tf, 1), unit="TFLOP/s (causal half only)",
                          frac=round(tf / peaks["bf16_tflops"], 4),
-                         note="not fused: GEMMs per head and 4096-row query chunk with the score matrix in the workspace")
+                         note="fused tcgen05 kernels (scores and probabilities stay on the SM); flop counted over the visible half of "
+                              "the score matrix only")
     del aq, ak, av, ao, ado, adq, adk, adv, alse, aws
     # one thread per row, one element each: a latency measurement, not a bandwidth one
     ops.cross_entropy_loss(rows_sm, V, probs, labels, loss)
@@ -275,9 +276,8 @@ def decoder_step_run(dev, peaks, steps=3, warmup=2):
                parameters=dec.num_params(), matmul_tflops=round(flop / (ms * 1e-3) / 1e12, 1),
                matmul_frac_of_burst_peak=round(flop / (ms * 1e-3) / 1e12 / peaks["bf16_tflops"], 4),
                loss_per_step=[round(x, 4) for x in losses],
-               note="the same batch every step, so the loss falls from ln(vocab) + 0.4 as the model memorises it; attention "
-                    "is the unfused first form (about two thirds of the step); matmul flop = 6 per active weight and "
-                    "token, attention excluded")
+               note="the same batch every step, so the loss falls from ln(vocab) + 0.4 as the model memorises it; matmul "
+                    "flop = 6 per active weight and token, attention excluded")
     del dec
     torch.cuda.empty_cache()
     return rec

@@ -362,8 +362,8 @@ teardown:
 //     P^T = exp2(S^T * scale * log2 e - lse * log2 e),  dS^T = P^T o (dP^T - delta)   (threads; bf16 into shared memory)
 //     dV += P^T dO,  dK += dS^T Q                       (accumulated in tensor memory over all steps of the CTA)
 //     dQ^T = K^T dS^T                                   (tensor memory, over the columns S^T occupied)
-// dQ^T is staged in shared memory and added to an fp32 accumulator in global memory by bulk reductions
-// (cp.reduce.async.bulk, 128 contiguous bytes each) that a cast kernel rounds once; dK (times the softmax scale) and dV are rounded once at the end of the CTA. The Q and dO tiles are
+// dQ^T is staged in shared memory and added to an fp32 accumulator in global memory by one tiled bulk reduction per
+// step (cp.reduce.async.bulk.tensor, 128 x 128 fp32) that a cast kernel rounds once; dK (times the softmax scale) and dV are rounded once at the end of the CTA. The Q and dO tiles are
 // read by the tensor core both ways round - as [queries x dims] for S^T / dP^T and as [dims x queries] for dK / dV -
 // from the same swizzled bytes, and so are K and dS^T for dQ^T.
 // ---------------------------------------------------------------------------------------
@@ -373,10 +373,11 @@ constexpr int BWD_TILE = 128 * BWD_HD * 2;
 constexpr int RING = 3;
 
 enum { ST_BWD_KV = 31, ST_BWD_RING_EMPTY = 32, ST_BWD_RING_FULL = 33, ST_BWD_S = 34, ST_BWD_DP = 35, ST_BWD_P = 36,
-       ST_BWD_DS = 37, ST_BWD_DQ = 38, ST_BWD_DQ_EMPTY = 39, ST_BWD_ACC = 40, ST_BWD_STATS = 41 };
+       ST_BWD_DS = 37, ST_BWD_DQ = 38, ST_BWD_DQ_EMPTY = 39, ST_BWD_ACC = 40, ST_BWD_STATS = 41, ST_BWD_STAGE = 42 };
 
 struct BwdParams {
   CUtensorMap tmQ, tmK, tmV, tmdO;
+  CUtensorMap tmdQ;  // the fp32 dQ accumulator [total_q][heads * 128], boxes of 128 x 128, no swizzle
   const float *lse, *delta;  // [heads][total_q]
   float *dQacc;              // [total_q][heads * 128] fp32, zeroed by the caller
   __nv_bfloat16 *dK, *dV;
@@ -387,7 +388,7 @@ struct BwdParams {
 };
 
 struct BwdTail {
-  uint64_t kv_full, ring_full[RING], ring_empty[RING], s_full, dp_full, p_ready, ds_ready, dq_full, dq_read, dq_empty, acc_full,
+  uint64_t kv_full, ring_full[RING], ring_empty[RING], s_full, dp_full, p_ready, ds_ready, dq_full, dq_read, stage_ready, dq_empty, acc_full,
       stats0;
   uint32_t tmem_base;
   int abort_flag;
@@ -424,7 +425,8 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_sm100_kernel(const __
     ptx::mbar_init(bar(&st->ds_ready), 256);
     ptx::mbar_init(bar(&st->dq_full), 1);
     ptx::mbar_init(bar(&st->dq_read), 256);
-    ptx::mbar_init(bar(&st->dq_empty), 256);
+    ptx::mbar_init(bar(&st->stage_ready), 256);
+    ptx::mbar_init(bar(&st->dq_empty), 1);
     ptx::mbar_init(bar(&st->acc_full), 1);
     ptx::mbar_init(bar(&st->stats0), 256);
     st->abort_flag = 0;
@@ -440,6 +442,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_sm100_kernel(const __
     ptx::tma_prefetch_desc(&p.tmK);
     ptx::tma_prefetch_desc(&p.tmV);
     ptx::tma_prefetch_desc(&p.tmdO);
+    ptx::tma_prefetch_desc(&p.tmdQ);
   }
   ptx::tc_fence_before();
   __syncthreads();
@@ -610,7 +613,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_sm100_kernel(const __
       st->stats[st_t >> 7][st_t & 127] = stat_next;
       // dQ^T: this lane is head dimension trow, the columns are the step's queries. It is staged as [query][dim] fp32
       // in shared memory (P^T and dS^T are done with: dq_full follows the MMAs that read them) and added to the
-      // accumulator in global memory by bulk reductions of 128 bytes (32 dims of one query), two per lane.
+      // accumulator in global memory by one tiled bulk reduction.
       if (!wait(&st->dq_full, par, ST_BWD_DQ)) goto teardown;
       ptx::tc_fence_after();
       uint32_t r2[32];
@@ -626,17 +629,16 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_sm100_kernel(const __
         sts32(stage_addr + (uint32_t)(((half * 64 + 32 + t) * HD + trow) * 4), __uint_as_float(r2[t]) * p.scale);
       }
       ptx::fence_proxy_async_smem();
-      __syncwarp();
-#pragma unroll
-      for (int rep = 0; rep < 2; rep++) {
-        const int col = half * 64 + rep * 32 + lane;
-        if (col < hi_rel)
-          ptx::bulk_reduce_add_f32(p.dQacc + (int64_t)(p.q_off + q0 + col) * p.ldQ + (int64_t)h * HD + quarter * 32,
-                                   stage_addr + (uint32_t)((col * HD + quarter * 32) * 4), 128);
+      ptx::mbar_arrive(bar(&st->stage_ready));
+      if (st_t == 0) {
+        // one tiled reduction adds the whole [128 queries][128 dims] block (rows past the end of the sequence hold
+        // zeros: their dS is masked; rows past the end of the array are clipped)
+        if (!wait(&st->stage_ready, par, ST_BWD_STAGE)) goto teardown;
+        ptx::tma_reduce_add_2d(&p.tmdQ, stage_addr, h * HD, p.q_off + q0);
+        ptx::bulk_commit_group();
+        ptx::bulk_wait_group_read0();
+        ptx::mbar_arrive(bar(&st->dq_empty));
       }
-      ptx::bulk_commit_group();
-      ptx::bulk_wait_group_read0();
-      ptx::mbar_arrive(bar(&st->dq_empty));
     }
     ptx::bulk_wait_group0();
     // dK and dV of this key block: one rounding
@@ -837,6 +839,18 @@ int attn_fused_bwd(int num_seqs, int total_q, int total_k, const int *q_off, con
     return -1;
   const uint64_t acc_bytes = ((uint64_t)total_q * Dq * 4 + 255) / 256 * 256;
   p.dQacc = (float *)workspace;
+  {
+    EncodeTiledFn fn = encode_fn();
+    B200_REQUIRE(fn != nullptr, "attention: cuTensorMapEncodeTiled is not available from this driver");
+    cuuint64_t dims[2] = {Dq, (cuuint64_t)total_q};
+    cuuint64_t strides[1] = {Dq * 4};
+    cuuint32_t box[2] = {128, 128};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(&p.tmdQ, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, workspace, dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    B200_REQUIRE(r == CUDA_SUCCESS, "attention: cuTensorMapEncodeTiled (dQ accumulator) failed with code %d", (int)r);
+  }
   float *delta = (float *)((unsigned char *)workspace + acc_bytes);
   p.delta = delta;
   p.lse = lse;

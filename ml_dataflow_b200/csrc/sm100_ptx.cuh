@@ -237,6 +237,14 @@ __device__ __forceinline__ void bulk_reduce_add_f32(float *gdst, uint32_t smem_s
                "r"(bytes)
                : "memory");
 }
+// tiled form: one box of the tensor map (fp32 elements) is added from shared memory; coordinates in elements, the
+// innermost one a multiple of 4 (16 bytes), none negative
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap *m, uint32_t smem_src, int c0, int c1) {
+  asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
+                   reinterpret_cast<uint64_t>(m)),
+               "r"(smem_src), "r"(c0), "r"(c1)
+               : "memory");
+}
 __device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // the source bytes of every committed group of this thread have been read
 __device__ __forceinline__ void bulk_wait_group_read0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }

@@ -362,8 +362,8 @@ teardown:
 //     P^T = exp2(S^T * scale * log2 e - lse * log2 e),  dS^T = P^T o (dP^T - delta)   (threads; bf16 into shared memory)
 //     dV += P^T dO,  dK += dS^T Q                       (accumulated in tensor memory over all steps of the CTA)
 //     dQ^T = K^T dS^T                                   (tensor memory, over the columns S^T occupied)
-// dQ^T is staged in shared memory and added to an fp32 accumulator in global memory by one tiled bulk reduction per
-// step (cp.reduce.async.bulk.tensor, 128 x 128 fp32) that a cast kernel rounds once; dK (times the softmax scale) and dV are rounded once at the end of the CTA. The Q and dO tiles are
+// dQ^T is staged in shared memory and added to an fp32 accumulator in global memory by two tiled bulk reductions per
+// step (cp.reduce.async.bulk.tensor, 64 queries x 128 dims fp32 each) that a cast kernel rounds once; dK (times the softmax scale) and dV are rounded once at the end of the CTA. The Q and dO tiles are
 // read by the tensor core both ways round - as [queries x dims] for S^T / dP^T and as [dims x queries] for dK / dV -
 // from the same swizzled bytes, and so are K and dS^T for dQ^T.
 // ---------------------------------------------------------------------------------------
@@ -377,7 +377,7 @@ enum { ST_BWD_KV = 31, ST_BWD_RING_EMPTY = 32, ST_BWD_RING_FULL = 33, ST_BWD_S =
 
 struct BwdParams {
   CUtensorMap tmQ, tmK, tmV, tmdO;
-  CUtensorMap tmdQ;  // the fp32 dQ accumulator [total_q][heads * 128], boxes of 128 x 128, no swizzle
+  CUtensorMap tmdQ;  // the fp32 dQ accumulator [total_q][heads * 128], boxes of 128 x 64 rows, no swizzle
   const float *lse, *delta;  // [heads][total_q]
   float *dQacc;              // [total_q][heads * 128] fp32, zeroed by the caller
   __nv_bfloat16 *dK, *dV;
@@ -388,7 +388,7 @@ struct BwdParams {
 };
 
 struct BwdTail {
-  uint64_t kv_full, ring_full[RING], ring_empty[RING], s_full, dp_full, p_ready, ds_ready, dq_full, dq_read, stage_ready, dq_empty, acc_full,
+  uint64_t kv_full, ring_full[RING], ring_empty[RING], s_full, dp_full, p_ready, ds_ready, dq_full, dq_read, stage_ready, dq_empty, dq_empty_b, acc_full,
       stats0;
   uint32_t tmem_base;
   int abort_flag;
@@ -427,6 +427,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_sm100_kernel(const __
     ptx::mbar_init(bar(&st->dq_read), 256);
     ptx::mbar_init(bar(&st->stage_ready), 256);
     ptx::mbar_init(bar(&st->dq_empty), 1);
+    ptx::mbar_init(bar(&st->dq_empty_b), 1);
     ptx::mbar_init(bar(&st->acc_full), 1);
     ptx::mbar_init(bar(&st->stats0), 256);
     st->abort_flag = 0;
@@ -555,8 +556,8 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_sm100_kernel(const __
       const int h = kvh * p.group + i / per_head, qb = qb_start + i % per_head;
       const uint32_t par = (uint32_t)(i & 1);
       const int q0 = qb * BM;
-      // every thread has left the step before: its statistics for this step are written, its part of the dQ staging
-      // area (which lies over P^T and dS^T) has been read by the bulk reductions
+      // every thread has left the step before: its statistics for this step are written, and the first half of the dQ
+      // staging area (which lies over P^T) has been read by its bulk reduction
       if (i > 0 && !wait(&st->dq_empty, par ^ 1u, ST_BWD_DQ_EMPTY)) goto teardown;
       const float stat_next = stat_load(i + 1);  // in flight while this step computes
       // queries of this step the lane's key is visible to: columns lo_rel <= col < hi_rel
@@ -585,6 +586,14 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_sm100_kernel(const __
       ptx::fence_proxy_async_smem();
       ptx::tc_fence_before();
       ptx::mbar_arrive(bar(&st->p_ready));
+      // the second half of the staging area lies over dS^T: its reduction of the step before has to have read it
+      if (i > 0) {
+        if (st_t == 0) {
+          ptx::bulk_wait_group_read0();
+          ptx::mbar_arrive(bar(&st->dq_empty_b));
+        }
+        if (!wait(&st->dq_empty_b, par ^ 1u, ST_BWD_DQ_EMPTY)) goto teardown;
+      }
       if (!wait(&st->dp_full, par, ST_BWD_DP)) goto teardown;
       ptx::tc_fence_after();
 #pragma unroll
@@ -613,7 +622,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_sm100_kernel(const __
       st->stats[st_t >> 7][st_t & 127] = stat_next;
       // dQ^T: this lane is head dimension trow, the columns are the step's queries. It is staged as [query][dim] fp32
       // in shared memory (P^T and dS^T are done with: dq_full follows the MMAs that read them) and added to the
-      // accumulator in global memory by one tiled bulk reduction.
+      // accumulator in global memory by tiled bulk reductions.
       if (!wait(&st->dq_full, par, ST_BWD_DQ)) goto teardown;
       ptx::tc_fence_after();
       uint32_t r2[32];
@@ -631,12 +640,15 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_sm100_kernel(const __
       ptx::fence_proxy_async_smem();
       ptx::mbar_arrive(bar(&st->stage_ready));
       if (st_t == 0) {
-        // one tiled reduction adds the whole [128 queries][128 dims] block (rows past the end of the sequence hold
-        // zeros: their dS is masked; rows past the end of the array are clipped)
+        // two tiled reductions add the [128 queries][128 dims] block, 64 queries each (rows past the end of the sequence
+        // hold zeros: their dS is masked; rows past the end of the array are clipped). The first half is waited for
+        // here, the second before the next step's dS^T is written, so that it drains behind the next step's P^T.
         if (!wait(&st->stage_ready, par, ST_BWD_STAGE)) goto teardown;
         ptx::tma_reduce_add_2d(&p.tmdQ, stage_addr, h * HD, p.q_off + q0);
         ptx::bulk_commit_group();
-        ptx::bulk_wait_group_read0();
+        ptx::tma_reduce_add_2d(&p.tmdQ, stage_addr + 64 * HD * 4, h * HD, p.q_off + q0 + 64);
+        ptx::bulk_commit_group();
+        ptx::bulk_wait_group_read1();
         ptx::mbar_arrive(bar(&st->dq_empty));
       }
     }
@@ -844,7 +856,7 @@ int attn_fused_bwd(int num_seqs, int total_q, int total_k, const int *q_off, con
     B200_REQUIRE(fn != nullptr, "attention: cuTensorMapEncodeTiled is not available from this driver");
     cuuint64_t dims[2] = {Dq, (cuuint64_t)total_q};
     cuuint64_t strides[1] = {Dq * 4};
-    cuuint32_t box[2] = {128, 128};
+    cuuint32_t box[2] = {128, 64};
     cuuint32_t estr[2] = {1, 1};
     CUresult r = fn(&p.tmdQ, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, workspace, dims, strides, box, estr,
                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,

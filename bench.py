@@ -837,6 +837,7 @@ def main():
                     help="device-timed loop only, exactly --warmup/--steps iterations (for ncu launch lists)")
     ap.add_argument("--block-ops", action="store_true",
                     help="only the block / head ops record (one GPU; one launch of each kernel per repetition: for ncu)")
+    ap.add_argument("--attention", action="store_true", help="with --block-ops: the attention forward / backward too")
     args = ap.parse_args()
     world = int(os.environ.get("WORLD_SIZE", str(args.gpus)))
     if args.block_ops:
@@ -845,7 +846,7 @@ def main():
         dev = torch.device("cuda", 0)
         torch.cuda.set_device(dev)
         print(json.dumps(dict(block_ops=block_ops_profile(dev, read_peaks(), iters=max(1, args.steps if args.steps != 30 else 5),
-                                                          with_attention=False))), flush=True)
+                                                          with_attention=args.attention))), flush=True)
         return
     if args.impl == "reference":
         run_reference_arm(args, CFG_1GPU if world == 1 else CFG_EP, world)

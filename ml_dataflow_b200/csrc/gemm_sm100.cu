@@ -93,17 +93,6 @@ enum StatusCode {
 };
 
 __device__ int g_gemm_status = 0;
-#ifdef B200_GEMM_DEBUG
-// timing experiments only; cycles summed over CTAs: 0 MMA thread waiting for operands, 1 waiting for a drained
-// accumulator, 2 MMA thread's lifetime, 3 epilogue warp 2 busy (accumulator ready -> released), 4 its sub-tiles,
-// 5 producer A waiting for a free stage, 6 producer A lifetime, 7 MMA thread inside the issue loop
-__device__ unsigned long long g_dbg_stats[8];
-#define DBG_CLK() clock64()
-#define DBG_ADD(i, v) atomicAdd(&g_dbg_stats[i], (unsigned long long)(v))
-#else
-#define DBG_CLK() 0ll
-#define DBG_ADD(i, v)
-#endif
 
 struct GemmParams {
   CUtensorMap tmA, tmA2, tmB, tmB2;
@@ -139,10 +128,6 @@ struct GemmParams {
   // tile whose fp32 result goes to D + i * d_group_stride, summed afterwards by splitk_reduce_kernel
   int k_splits, k_split_len;
   int k_hint;  // host only, GROUPED_K: average reduction length per group (rows / groups), for choosing the unit shape
-#ifdef B200_GEMM_DEBUG
-  int dbg;  // timing experiments only: bit 0 = the epilogue touches no global memory, bit 1 = every load fetches the
-            // same (cache-resident) boxes; results are garbage
-#endif
 };
 
 struct Tile {
@@ -365,9 +350,6 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
   // 16 bf16 columns of a row at `ptr` (n_left valid columns remain, a multiple of 8): one 32-byte access when
   // the launch allows it, else one or two 16-byte accesses
   auto ld16 = [&](const __nv_bfloat16 *ptr, int n_left, uint4 &lo, uint4 &hi) {
-#ifdef B200_GEMM_DEBUG
-    if (p.dbg & 1) return;
-#endif
     if (p.wide && n_left >= 16) {
       ld_global_256(ptr, lo, hi);
     } else {
@@ -376,9 +358,6 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
     }
   };
   auto st16 = [&](__nv_bfloat16 *ptr, int n_left, const uint4 &lo, const uint4 &hi) {
-#ifdef B200_GEMM_DEBUG
-    if (p.dbg & 1) return;
-#endif
     if (p.wide && n_left >= 16) {
       st_global_256(ptr, lo, hi);
     } else {
@@ -398,23 +377,11 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
     // issue the loads of one slab into (sA, sB), counted on `bar`; sB holds the B boxes of column tile 0, then
     // (at the fixed offset B_BLKS_SUB boxes) those of column tile 1
     auto slab = [&](Tile &tt, int ks, uint32_t sA, uint32_t sB, uint32_t bar) {
-#ifdef B200_GEMM_DEBUG
-      if (p.dbg & 2) ks &= 3;
-#endif
       const int ksteps_seg = (tt.k_len + BK - 1) / BK;
       const int seg = ks / ksteps_seg;
       const int kk = (ks - seg * ksteps_seg) * BK;
       const CUtensorMap *mA = seg ? &p.tmA2 : &p.tmA;
       const CUtensorMap *mB = seg ? &p.tmB2 : &p.tmB;
-#ifdef B200_GEMM_DEBUG
-      if (p.dbg & 2) {
-        tt.a_row0 = 0;
-        tt.k_row0 = 0;
-        tt.nt0 = 0;
-        tt.group = 0;
-        ks = ks & 3;
-      }
-#endif
       const int a_row = tt.a_row0 + row_off;
       const int g3 = (p.group_mode == GROUPED_M) ? tt.group : 0;
       auto ld2 = [&](uint32_t dst, const CUtensorMap *m, int c0, int c1) { ptx::tma_load_2d(dst, m, bar, c0, c1); };
@@ -457,8 +424,6 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
       int stage = 0;
       uint32_t phase = 0;
       bool alive = true;
-      [[maybe_unused]] long long dbg_wait = 0;
-      [[maybe_unused]] const long long dbg_begin = DBG_CLK();
       for (int tile = first_tile; alive && sched.get(tile, t); tile += tile_step) {
         const int ksteps = ((t.k_len + BK - 1) / BK) * p.k_segments;
         int b_loaded = 0;
@@ -468,12 +433,10 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
         }
         const int my_blks = (do_a ? A_BLKS : 0) + (do_b ? b_loaded : 0);
         for (int ks = 0; ks < ksteps; ks += CF::KSLABS) {
-          [[maybe_unused]] const long long dbg_t0 = DBG_CLK();
           if (!xwait(empty_bar(stage), phase ^ 1u, ST_PRODUCER_TIMEOUT)) {
             alive = false;
             break;
           }
-          dbg_wait += DBG_CLK() - dbg_t0;
           const int nsl = min(CF::KSLABS, ksteps - ks);
           ptx::mbar_arrive_expect_tx(full_bar(stage), (uint32_t)(nsl * my_blks * BLK_BYTES));
           for (int j = 0; j < nsl; j++) {
@@ -485,10 +448,6 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
             phase ^= 1u;
           }
         }
-      }
-      if (do_a) {
-        DBG_ADD(5, dbg_wait);
-        DBG_ADD(6, DBG_CLK() - dbg_begin);
       }
     }
     __syncwarp();
@@ -502,8 +461,6 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
       int seq = 0;
       uint32_t tail_par = 0;  // parity of tail_done[stage], one bit per stage
       bool alive = true;
-      [[maybe_unused]] long long dbg_w_full = 0, dbg_w_acc = 0, dbg_issue = 0;
-      [[maybe_unused]] const long long dbg_begin = DBG_CLK();
       for (int tile = first_tile; alive && sched.get(tile, t); tile += tile_step) {
         const int ksteps_seg = (t.k_len + BK - 1) / BK;
         const int ksteps = ksteps_seg * p.k_segments;
@@ -535,7 +492,6 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
           // every CTA watches its own slabs land; a stage whose last slab straddles the end of the expert's rows is
           // handed over by the tail warp instead, once it has cleared the rows past the end
           bool ok;
-          [[maybe_unused]] const long long dbg_t0 = DBG_CLK();
           if (p.group_mode == GROUPED_K && last && (t.k_len & 15) != 0) {
             ok = wait_local(tail_bar(stage), (tail_par >> stage) & 1u, ST_MMA_TIMEOUT);
             tail_par ^= 1u << stage;
@@ -550,8 +506,6 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
             alive = false;
             break;
           }
-          dbg_w_full += DBG_CLK() - dbg_t0;
-          [[maybe_unused]] const long long dbg_t1 = DBG_CLK();
           if (PAIR && !leader) {
             // ... the odd CTA then tells the even one that its half is in place
             ptx::mbar_arrive_remote(full_bar(stage), 0);
@@ -566,12 +520,10 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
                 if (SUP == 2 && ks + j == 0) {
                   // the accumulator must have been drained by the epilogue of the unit before; column tile 1 is
                   // waited for only now, after the first MMAs of column tile 0 are on their way
-                  [[maybe_unused]] const long long dbg_t2 = DBG_CLK();
                   if (!xwait(tempty_bar(accs[sub]), ((acc_par >> accs[sub]) & 1u) ^ 1u, ST_MMA_TIMEOUT)) {
                     alive = false;
                     break;
                   }
-                  dbg_w_acc += DBG_CLK() - dbg_t2;
                   ptx::tc_fence_after();
                 }
                 const uint32_t sB = sA + (A_BLKS + sub * CF::B_BLKS_SUB) * BLK_BYTES;
@@ -591,7 +543,6 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
             if (!alive) break;
             if (PAIR) ptx::umma_commit_pair(empty_bar(stage));
             else ptx::umma_commit(empty_bar(stage));
-            dbg_issue += DBG_CLK() - dbg_t1;
           }
           if (++stage == STAGES) {
             stage = 0;
@@ -609,12 +560,6 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
           acc_par ^= 1u << accs[sub];
         }
         seq++;
-      }
-      if (leader) {
-        DBG_ADD(0, dbg_w_full);
-        DBG_ADD(1, dbg_w_acc);
-        DBG_ADD(2, DBG_CLK() - dbg_begin);
-        DBG_ADD(7, dbg_issue - dbg_w_acc);
       }
     }
     __syncwarp();
@@ -689,7 +634,6 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
         const int acc = (SUP == 2) ? sub : (seq & 1);
         const uint32_t acc_phase = (acc_par >> acc) & 1u;
         const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * ACC_COLS);
-        [[maybe_unused]] long long dbg_e0 = 0;
         // t.nw is the logical width (per part when the accumulator holds x1 | x3); each warp takes half of it
         const int cbeg = chalf * (t.nw >> 1), cend = cbeg + (t.nw >> 1);
 
@@ -723,7 +667,6 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
           bool ok = xwait(tfull_bar(acc), acc_phase, ST_EPILOGUE_TIMEOUT);
           if (!__all_sync(0xffffffffu, ok)) goto teardown;
           ptx::tc_fence_after();
-          dbg_e0 = DBG_CLK();
 #pragma unroll
           for (int ch = 0; ch < 2; ch++) {  // 64 accumulator columns per TMEM round trip
             const int c0 = cbeg + ch * 64;
@@ -802,7 +745,6 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
           bool ok = xwait(tfull_bar(acc), acc_phase, ST_EPILOGUE_TIMEOUT);
           if (!__all_sync(0xffffffffu, ok)) goto teardown;
           ptx::tc_fence_after();
-          dbg_e0 = DBG_CLK();
           const int64_t base = orow * (int64_t)p.N + t.n0;
           // 32 columns of x1 and of x3 per TMEM round trip: 64 live accumulator registers leave the compiler room to
           // interleave the sixteen independent SwiGLU chains of a store group
@@ -853,7 +795,6 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
           bool ok = xwait(tfull_bar(acc), acc_phase, ST_EPILOGUE_TIMEOUT);
           if (!__all_sync(0xffffffffu, ok)) goto teardown;
           ptx::tc_fence_after();
-          dbg_e0 = DBG_CLK();
           float dp_part = 0.f;
 #pragma unroll
           for (int ch = 0; ch < 2; ch++) {
@@ -907,8 +848,6 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
           if (PAIR && !leader) ptx::mbar_arrive_remote(tempty_bar(acc), 0);
           else ptx::mbar_arrive(tempty_bar(acc));
           if (warp == 2 && leader) {
-            DBG_ADD(3, DBG_CLK() - dbg_e0);
-            DBG_ADD(4, 1);
           }
         }
         acc_par ^= 1u << acc;
@@ -1109,12 +1048,6 @@ template <int EPI>
 static int launch_gemm(GemmParams &p, int64_t max_tiles, cudaStream_t s, bool pair_ok = true, int64_t row_tiles_hint = 0) {
   p.status = status_ptr();
   B200_REQUIRE(p.status != nullptr, "gemm: status word unavailable");
-#ifdef B200_GEMM_DEBUG
-  {
-    const char *e = getenv("B200_GEMM_DBG");
-    p.dbg = e ? atoi(e) : 0;
-  }
-#endif
   {
     // 256-bit epilogue accesses need every bf16 row start to be 32-byte aligned
     auto a32 = [](const void *q) { return (reinterpret_cast<uintptr_t>(q) & 31u) == 0; };
@@ -1217,16 +1150,6 @@ extern "C" int b200_gemm_enumerate_tiles(int group_mode, int pair, int M, int N,
   return n;
 }
 
-#ifdef B200_GEMM_DEBUG
-// timing experiments only: reads and clears the cycle counters
-extern "C" int b200_dbg_gemm_stats(unsigned long long *out) {
-  B200_CUDA(cudaDeviceSynchronize());
-  B200_CUDA(cudaMemcpyFromSymbol(out, g_dbg_stats, sizeof(unsigned long long) * 8));
-  unsigned long long z[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-  B200_CUDA(cudaMemcpyToSymbol(g_dbg_stats, z, sizeof(z)));
-  return 0;
-}
-#endif
 
 extern "C" int b200_gemm_set_pair_mode(int on) {
   g_pair_mode = on ? 1 : 0;

@@ -15,6 +15,9 @@ CASES = [
     ([513], [513], 2, 1, 128, True),
     ([4200, 100], [4300, 100], 2, 1, 32, True),   # more than one chunk of query rows, keys beyond the queries
     ([16], [8300], 2, 1, 32, True),               # more keys than a block keeps in registers
+    ([0, 257], [5, 700], 4, 2, 128, False),       # fused kernels: a sequence without queries, several key blocks, no mask
+    ([385, 130], [900, 130], 8, 2, 128, True),    # fused kernels: three query tiles, keys beyond the queries, ragged ends
+    ([40], [40], 2, 2, 128, True),                # fused kernels: fewer rows in the whole batch than one tile
 ]
 
 

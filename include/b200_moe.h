@@ -794,6 +794,53 @@ int b200_attention_bwd(int bwd_dt, int num_seqs, int total_q, int total_k, const
  * returns the recorded code through status_out (0 = none) and clears it. No counterpart in the reference. */
 int b200_attention_status(int *status_out);
 
+/*
+ * ---- a whole decoder block ---------------------------------------------------------------------------------------
+ *
+ * RMSNorm -> q / k / v projections -> RoPE -> causal attention -> output projection + residual -> RMSNorm -> MoE
+ * feed-forward + residual: what dataflow_submit_transformer_moe_block (dataflow_transformer.c:2588-2986) issues op by
+ * op, and its backward (_bwd_x 3386-3719, _bwd_w 4060-4185), as one call each. All buffers are the caller's; the
+ * sequence description (offsets, lengths) is a HOST array as for b200_attention_fwd; positions is a device array of the
+ * tokens' positions in their sequences. Saved by the forward for the backward: rms1, q, k (after RoPE), v, attn, lse,
+ * x_mid, rms2, xn2 and what the MoE part keeps (B200MoeBlock). xn is scratch in both directions.
+ */
+typedef struct B200TransformerBlock {
+  int total_tokens, model_dim, num_q_heads, num_kv_heads, head_dim, theta;
+  float eps;
+  int num_seqs, max_seqlen;
+  const int *seq_offsets, *seq_lens; /* HOST [num_seqs] */
+  const int *positions;              /* device [T] */
+  /* bf16 weights: attn_norm, ffn_norm [d]; wq [Hq*hd][d]; wk, wv [Hkv*hd][d]; wo [d][Hq*hd] */
+  const void *attn_norm, *wq, *wk, *wv, *wo, *ffn_norm;
+  float *rms1, *rms2;                /* [T] */
+  void *q, *k, *v, *attn;            /* bf16 [T][Hq*hd], [T][Hkv*hd] x 2, [T][Hq*hd] */
+  float *lse;                        /* [Hq][T] */
+  void *x_mid, *xn2, *xn;            /* bf16 [T][d] */
+  void *attn_workspace;              /* b200_attention_workspace_bytes(is_training = 1, ...) */
+  uint64_t attn_workspace_bytes;
+  B200MoeBlock moe;                  /* the feed-forward part; its Xn is xn2 */
+} B200TransformerBlock;
+
+/* gradients the backward accumulates into (bf16, the shapes of the weights) */
+typedef struct B200TransformerBlockGrads {
+  void *attn_norm, *wq, *wk, *wv, *wo, *ffn_norm, *router, *W1, *W3, *W2;
+} B200TransformerBlockGrads;
+
+/* backward scratch, shared by every block of a model */
+typedef struct B200TransformerBlockScratch {
+  void *dxn, *dattn, *dq, *dk, *dv; /* bf16 [T][d], [T][Hq*hd], [T][Hq*hd], [T][Hkv*hd] x 2 */
+  void *norm_workspace;             /* b200_rms_norm_bwd_w_workspace_bytes(T, d) */
+  uint64_t norm_workspace_bytes;
+} B200TransformerBlockScratch;
+
+/* out [T][d] = block(x); x and out are two buffers (x is read again by the backward). */
+int b200_transformer_block_fwd(const B200TransformerBlock *block, const void *x, void *out, void *stream);
+
+/* dx [T][d] holds the gradient at the block's output on entry and at its input on return; the weight gradients are
+ * accumulated into (beta = 1), as by the reference's gradient GEMMs and norm kernels. */
+int b200_transformer_block_bwd(const B200TransformerBlock *block, const void *x, void *dx, const B200TransformerBlockGrads *grads,
+                               const B200TransformerBlockScratch *scratch, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -83,6 +83,8 @@ SIGNATURES = {
     "b200_attention_bwd": (_i, [_i, _i, _i, _i, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp,
                                 _vp, _i, _u64, _vp, _vp]),
     "b200_attention_status": (_i, [_vp]),
+    "b200_transformer_block_fwd": (_i, [_vp, _vp, _vp, _vp]),
+    "b200_transformer_block_bwd": (_i, [_vp, _vp, _vp, _vp, _vp, _vp]),
     "b200_scatter_row_weights": (_i, [_i, _i, _vp, _vp, _vp, _vp]),
     "b200_gather_router_grad": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp]),
 }
@@ -103,6 +105,27 @@ class MoeBlock(C.Structure):
         ("dY_zone", _vp), ("row_weights", _vp), ("dP", _vp), ("dx1", _vp), ("dx3", _vp), ("dZ", _vp),
         ("dX_routed", _vp),
     ]
+
+
+class TransformerBlock(C.Structure):
+    """ctypes mirror of B200TransformerBlock in include/b200_moe.h (same field order)."""
+    _fields_ = [
+        ("total_tokens", _i), ("model_dim", _i), ("num_q_heads", _i), ("num_kv_heads", _i), ("head_dim", _i), ("theta", _i),
+        ("eps", C.c_float), ("num_seqs", _i), ("max_seqlen", _i),
+        ("seq_offsets", _vp), ("seq_lens", _vp), ("positions", _vp),
+        ("attn_norm", _vp), ("wq", _vp), ("wk", _vp), ("wv", _vp), ("wo", _vp), ("ffn_norm", _vp),
+        ("rms1", _vp), ("rms2", _vp), ("q", _vp), ("k", _vp), ("v", _vp), ("attn", _vp), ("lse", _vp),
+        ("x_mid", _vp), ("xn2", _vp), ("xn", _vp), ("attn_workspace", _vp), ("attn_workspace_bytes", _u64),
+        ("moe", MoeBlock),
+    ]
+
+
+class TransformerBlockGrads(C.Structure):
+    _fields_ = [(n, _vp) for n in ("attn_norm", "wq", "wk", "wv", "wo", "ffn_norm", "router", "W1", "W3", "W2")]
+
+
+class TransformerBlockScratch(C.Structure):
+    _fields_ = [(n, _vp) for n in ("dxn", "dattn", "dq", "dk", "dv", "norm_workspace")] + [("norm_workspace_bytes", _u64)]
 
 
 class EpMoeBlock(C.Structure):

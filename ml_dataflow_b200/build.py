@@ -12,7 +12,7 @@ CSRC = os.path.join(HERE, "csrc")
 LIB_DIR = os.path.join(HERE, "lib")
 LIB_PATH = os.path.join(LIB_DIR, "libb200moe.so")
 SOURCES = ["router.cu", "permute.cu", "ep_p2p.cu", "gemm_sm100.cu", "moe_block.cu", "model_files.cu", "ep_block.cu", "block_ops.cu", "attention.cu",
-           "attention_sm100.cu"]
+           "attention_sm100.cu", "transformer_block.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-shared",

@@ -46,8 +46,11 @@ class Decoder:
 
     PARAMS = ("attn_norm", "wq", "wk", "wv", "wo", "ffn_norm", "router", "W1", "W3", "W2")
 
-    def __init__(self, cfg, max_tokens, max_seqlen, device="cuda", seed=0, std=0.02):
+    def __init__(self, cfg, max_tokens, max_seqlen, device="cuda", seed=0, std=0.02, c_blocks=True):
+        """c_blocks: run each block through the C driver (b200_transformer_block_fwd / _bwd, one call per block and
+        direction) instead of op by op from here; both issue the same ops in the same order."""
         self.cfg, self.T, self.max_seqlen = cfg, max_tokens, max_seqlen
+        self.c_blocks = c_blocks
         self.dev = dev = torch.device(device)
         gen = torch.Generator(device=dev).manual_seed(seed)
         c = cfg
@@ -88,6 +91,30 @@ class Decoder:
         self.attn_ws = torch.empty(max(256, ops.attention_workspace_bytes(True, c.n_heads, c.n_kv_heads, c.head_dim, T, max_seqlen, max_seqlen)), dtype=torch.uint8,
                                    device=dev)
         self.norm_ws = torch.empty(ops.rms_norm_bwd_w_workspace_bytes(T, c.d), dtype=torch.uint8, device=dev)
+
+    def _c_structs(self):
+        """The blocks as the C driver takes them (rebuilt per batch: the sequence description is per batch)."""
+        import ctypes as C
+
+        from . import _lib
+
+        c, T = self.cfg, self.T
+        p = lambda t: t.data_ptr()
+        n = len(self.seq_lens)
+        self._seq_arrays = ((C.c_int * n)(*self.seq_offs), (C.c_int * n)(*self.seq_lens))  # kept alive with the structs
+        offs, lens = (C.cast(a, C.c_void_p) for a in self._seq_arrays)
+        blocks, grads = [], []
+        for L, S, G in zip(self.layers, self.saved, self.grads):
+            moe = S["moe"].block(L["router"], L["W1"], L["W3"], L["W2"])
+            blocks.append(_lib.TransformerBlock(
+                T, c.d, c.n_heads, c.n_kv_heads, c.head_dim, c.theta, c.eps, n, max(self.seq_lens), offs, lens,
+                p(self.positions), p(L["attn_norm"]), p(L["wq"]), p(L["wk"]), p(L["wv"]), p(L["wo"]), p(L["ffn_norm"]),
+                p(S["rms1"]), p(S["rms2"]), p(S["q"]), p(S["k"]), p(S["v"]), p(S["attn"]), p(S["lse"]), p(S["x_mid"]),
+                p(S["xn2"]), p(self.xn), p(self.attn_ws), self.attn_ws.numel(), moe))
+            grads.append(_lib.TransformerBlockGrads(*[p(G[k]) for k in self.PARAMS]))
+        scratch = _lib.TransformerBlockScratch(p(self.dxn), p(self.dattn), p(self.dq), p(self.dk), p(self.dv), p(self.norm_ws),
+                                               self.norm_ws.numel())
+        return blocks, grads, scratch
 
     # ------------------------------------------------------------------------------------------------ helpers
     @staticmethod
@@ -131,8 +158,14 @@ class Decoder:
         sid, smap, starts, nu = self.tokens
         x = self.saved[0]["x"]
         ops.embedding_table(nu, c.d, sid, smap, starts, self.embed, x)
+        if self.c_blocks:
+            self._blocks, self._block_grads, self._block_scratch = self._c_structs()
         for li, (L, S) in enumerate(zip(self.layers, self.saved)):
             x = S["x"]
+            if self.c_blocks:
+                out = self.saved[li + 1]["x"] if li + 1 < c.n_layers else self.x_final
+                ops.transformer_block_fwd(self._blocks[li], x, out)
+                continue
             ops.rms_norm(T, c.d, c.eps, L["attn_norm"], x, self.xn, S["rms1"])
             self._linear(self.xn, L["wq"], S["q"])
             self._linear(self.xn, L["wk"], S["k"])
@@ -167,6 +200,9 @@ class Decoder:
         for li in reversed(range(c.n_layers)):
             L, S, G = self.layers[li], self.saved[li], self.grads[li]
             x, moe = S["x"], S["moe"]
+            if self.c_blocks:
+                ops.transformer_block_bwd(self._blocks[li], x, self.dx, self._block_grads[li], self._block_scratch)
+                continue
             # MoE part: dx is the gradient at the block's output; it also flows through the residual unchanged
             moe.backward(S["xn2"], L["router"], L["W1"], L["W3"], L["W2"], self.dx, self.dxn, G["router"], G["W1"], G["W3"],
                          G["W2"])

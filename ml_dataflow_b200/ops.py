@@ -384,6 +384,17 @@ def _int_array(values):
     return (C.c_int * len(values))(*[int(v) for v in values])
 
 
+def transformer_block_fwd(block, x, out):
+    """block: _lib.TransformerBlock; out = block(x)."""
+    _check(_lib.load().b200_transformer_block_fwd(C.byref(block), _p(x), _p(out), _stream()), "transformer_block_fwd", 20)
+
+
+def transformer_block_bwd(block, x, dx, grads, scratch):
+    """dx: the gradient at the block's output on entry, at its input on return; grads are accumulated into."""
+    _check(_lib.load().b200_transformer_block_bwd(C.byref(block), _p(x), _p(dx), C.byref(grads), C.byref(scratch), _stream()),
+           "transformer_block_bwd", 45)
+
+
 def attention_workspace_bytes(is_training, num_q_heads, num_kv_heads, head_dim, max_total_q, max_seqlen_q, max_seqlen_k):
     return int(_lib.load().b200_attention_workspace_bytes(int(bool(is_training)), num_q_heads, num_kv_heads, head_dim,
                                                           max_total_q, max_seqlen_q, max_seqlen_k))

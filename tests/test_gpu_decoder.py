@@ -2,7 +2,8 @@
 two packed sequences) through ml_dataflow_b200.decoder - every op on the sm_100a kernels - against the same model in
 float32 torch autograd with the routing held fixed (the experts each token chose on the GPU). Loss and every kind of
 gradient (embedding, projections, norms, router, experts, head) are compared as relative Frobenius errors: the GPU
-path rounds to bf16 after every op, the reference never does. Then one AdamW step must move every parameter."""
+path rounds to bf16 after every op, the reference never does. Then one AdamW step must move every parameter. Run twice:
+with every block going through the C driver (b200_transformer_block_fwd / _bwd) and op by op from Python."""
 import numpy as np
 import pytest
 
@@ -67,7 +68,8 @@ def _reference(dec, token_ids, labels, seq_lens):
     return loss.item() / token_ids.numel(), P, embed, final_norm, head
 
 
-def test_decoder_step_against_float32_autograd():
+@pytest.mark.parametrize("c_blocks", [True, False], ids=["c_block_driver", "op_by_op"])
+def test_decoder_step_against_float32_autograd(c_blocks):
     import torch
 
     from gpu_util import require_b200
@@ -80,7 +82,7 @@ def test_decoder_step_against_float32_autograd():
                         theta=10000)
     seq_lens = [40, 56]
     T = sum(seq_lens)
-    dec = Decoder(cfg, T, max(seq_lens), seed=3, std=0.1)
+    dec = Decoder(cfg, T, max(seq_lens), seed=3, std=0.1, c_blocks=c_blocks)
     g = torch.Generator(device="cuda").manual_seed(5)
     tokens = torch.randint(0, cfg.vocab, (T,), generator=g, device="cuda", dtype=torch.int32)
     tokens[:10] = tokens[0]  # a repeated token for the embedding backward

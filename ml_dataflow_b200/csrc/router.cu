@@ -8,7 +8,7 @@ namespace b200 {
 // ---------------------------------------------------------------------------------------
 // select_experts
 //
-// One thread per token. A block stages a [128 tokens x 64 experts] logits tile in shared
+// One thread per token. A block stages a [32 tokens x 64 experts] logits tile in shared
 // memory with coalesced loads (row pitch 65 floats so the per-thread row walk is bank
 // conflict free), then every thread replays the reference's sequential insert/evict rule
 // over its row so the slot order of chosen_experts is identical to the reference's
@@ -18,8 +18,9 @@ namespace b200 {
 // finishes last performs the exclusive scan and the host copy (select_experts.cu:207-294).
 // ---------------------------------------------------------------------------------------
 
-constexpr int SEL_TOKENS = 128;  // tokens per block = threads per block
+constexpr int SEL_TOKENS = 32;   // tokens per block = threads per block (one warp: 256 blocks at 8192 tokens)
 constexpr int SEL_EC = 64;       // experts per staged chunk
+static_assert(SEL_EC == 64, "the staging loop shifts by 6");
 constexpr int SEL_PITCH = SEL_EC + 1;
 
 template <typename T>
@@ -70,13 +71,13 @@ select_experts_kernel(int total_tokens, int n_experts, int top_k, const T *__res
 #pragma unroll
       for (int u = 0; u < 16; u++) {
         const int i = i0 + u * SEL_TOKENS;
-        const int r = i / ec, c = i - r * ec;
+        const int r = ec == SEL_EC ? i >> 6 : i / ec, c = i - r * ec;  // no division in the common 64-expert chunk
         v[u] = (i < n_stage) ? load_logit<T>(X_routed + (tok0 + r) * n_experts + e0 + c) : 0.f;
       }
 #pragma unroll
       for (int u = 0; u < 16; u++) {
         const int i = i0 + u * SEL_TOKENS;
-        const int r = i / ec, c = i - r * ec;
+        const int r = ec == SEL_EC ? i >> 6 : i / ec, c = i - r * ec;
         if (i < n_stage) tile[r * SEL_PITCH + c] = v[u];
       }
     }

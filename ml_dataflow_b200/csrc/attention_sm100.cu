@@ -388,7 +388,7 @@ struct BwdParams {
 };
 
 struct BwdTail {
-  uint64_t kv_full, ring_full[RING], ring_empty[RING], s_full, dp_full, p_ready, ds_ready, dq_full, dq_read, stage_ready, dq_empty, dq_empty_b, acc_full,
+  uint64_t kv_full, ring_full[RING], ring_empty[RING], s_full, dp_full, p_ready, ds_ready, dq_full, dq_read, dk_done, stage_ready, dq_empty, dq_empty_b, acc_full,
       stats0;
   uint32_t tmem_base;
   int abort_flag;
@@ -425,6 +425,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_sm100_kernel(const __
     ptx::mbar_init(bar(&st->ds_ready), 256);
     ptx::mbar_init(bar(&st->dq_full), 1);
     ptx::mbar_init(bar(&st->dq_read), 256);
+    ptx::mbar_init(bar(&st->dk_done), 1);
     ptx::mbar_init(bar(&st->stage_ready), 256);
     ptx::mbar_init(bar(&st->dq_empty), 1);
     ptx::mbar_init(bar(&st->dq_empty_b), 1);
@@ -518,15 +519,17 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_sm100_kernel(const __
         ptx::umma_commit(bar(&st->ring_empty[nd % RING]));
         if (!wait(&st->ds_ready, par, ST_BWD_DS)) break;
         ptx::tc_fence_after();
-        // dK before dQ^T: dq_full then also says that dS^T and P^T are done with, and the dQ staging lies over them
-#pragma unroll
-        for (int k16 = 0; k16 < BM / 16; k16++)
-          ptx::umma_bf16(tmem_base + COL_DK, kmaj(dst_base, k16), mnmaj(q_tile, k16), idesc_km, (i > 0 || k16 > 0));
-        ptx::umma_commit(bar(&st->ring_empty[nq % RING]));
+        // dQ^T first: the threads fetch it from tensor memory (and release those columns for the next S^T) while dK
+        // runs; dk_done then says that dS^T and P^T are done with - the dQ staging lies over them
 #pragma unroll
         for (int k16 = 0; k16 < BN / 16; k16++)
           ptx::umma_bf16(tmem_base + COL_S, mnmaj(k_base, k16), mnmaj(dst_base, k16), idesc_mm, k16 > 0);
         ptx::umma_commit(bar(&st->dq_full));
+#pragma unroll
+        for (int k16 = 0; k16 < BM / 16; k16++)
+          ptx::umma_bf16(tmem_base + COL_DK, kmaj(dst_base, k16), mnmaj(q_tile, k16), idesc_km, (i > 0 || k16 > 0));
+        ptx::umma_commit(bar(&st->ring_empty[nq % RING]));
+        ptx::umma_commit(bar(&st->dk_done));
         if (i == n_steps - 1) ptx::umma_commit(bar(&st->acc_full));
       }
     }
@@ -621,7 +624,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_sm100_kernel(const __
       if (!wait(&st->ds_ready, par, ST_BWD_DS)) goto teardown;
       st->stats[st_t >> 7][st_t & 127] = stat_next;
       // dQ^T: this lane is head dimension trow, the columns are the step's queries. It is staged as [query][dim] fp32
-      // in shared memory (P^T and dS^T are done with: dq_full follows the MMAs that read them) and added to the
+      // in shared memory (once dk_done says that the MMAs reading P^T and dS^T are finished) and added to the
       // accumulator in global memory by tiled bulk reductions.
       if (!wait(&st->dq_full, par, ST_BWD_DQ)) goto teardown;
       ptx::tc_fence_after();
@@ -632,6 +635,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_sm100_kernel(const __
       // the tensor core may overwrite these columns with the next S^T from here on
       ptx::tc_fence_before();
       ptx::mbar_arrive(bar(&st->dq_read));
+      if (!wait(&st->dk_done, par, ST_BWD_DQ)) goto teardown;
 #pragma unroll
       for (int t = 0; t < 32; t++) {
         sts32(stage_addr + (uint32_t)(((half * 64 + t) * HD + trow) * 4), __uint_as_float(r[t]) * p.scale);

@@ -21,6 +21,8 @@ host path delivers per GPU for those copies alone); `roofline` covers the groupe
 kernel) and `kernels` lists every op group with its own bound; `cpu_baseline` is the CPU oracle timed on a bounded
 token sample of the same shape, and on the CPU-runnable configuration (T=2048, d=1024, 16 experts, top-2) in full,
 on this box's host cores.
+`--block-ops` prints only the block / head ops record (one launch of each kernel per repetition, for profiler
+captures); with `--attention` the fused attention forward and backward too.
 `--impl reference` times that CPU restatement of the reference's algorithm only (the reference has no CPU
 implementation of this path of its own, and its CUDA kernels are what this repository replaces); under
 torch.distributed.run rank 0 alone runs it, on all host cores.

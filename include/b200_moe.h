@@ -758,8 +758,9 @@ int b200_embedding_table_bwd_w(int bwd_dt, int num_unique_tokens, int embed_dim,
  * dx_v: [total_k][num_kv_heads * head_dim]; softmax_lse: fp32 [num_q_heads][total_q] (log-sum-exp of the scaled
  * scores, written by the forward, read by the backward). bf16 only.
  *
- * Differences from the reference's signature: the sequence offsets and lengths are HOST arrays here (the launches are
- * issued per sequence from the host); dx_q / dx_k / dx_v are overwritten.
+ * Differences from the reference's signature: the sequence offsets and lengths are HOST arrays here (the fused kernels
+ * take them as a launch parameter, 48 sequences per launch; the GEMM-by-GEMM form loops over them on the host);
+ * dx_q / dx_k / dx_v are overwritten.
  *
  * head_dim 64 and 128 run fused tcgen05 kernels (csrc/attention_sm100.cu): the forward for both (scores in tensor
  * memory, probabilities through shared memory, no workspace), the backward for 128 (dK, dV accumulated in tensor

@@ -37,11 +37,20 @@ enum { ST_ATTN_Q = 21, ST_ATTN_KV_EMPTY = 22, ST_ATTN_KV_FULL = 23, ST_ATTN_P = 
 
 __device__ int g_attn_status = 0;
 
+// The sequences one launch covers: work units (forward: tiles of 256 query rows; backward: blocks of 128 keys) are
+// numbered through the sequences, first[s] being the first unit of sequence s and first[n] their number.
+constexpr int MAX_SEQS = 48;
+struct SeqTable {
+  int n;
+  int q_off[MAX_SEQS], Tq[MAX_SEQS], k_off[MAX_SEQS], Tk[MAX_SEQS], first[MAX_SEQS + 1];
+};
+
 struct FwdParams {
   CUtensorMap tmQ, tmK, tmV;  // [rows][heads * HD] bf16, boxes of 64 columns x 128 rows, 128-byte swizzle
   __nv_bfloat16 *O;
   float *lse;  // [heads][total_q]
-  int q_off, Tq, k_off, Tk, causal, group, total_q, tiles, num_q_heads;
+  SeqTable seqs;
+  int causal, group, total_q, num_q_heads;
   int64_t ldO;
   float scale;
   int *status;
@@ -126,18 +135,22 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_sm100_kernel(const __
 
   // one-dimensional grid, query tile major: the tiles with the most keys to visit (the last query rows under a causal
   // mask) start first on every head; neighbouring CTAs are the heads of one group and share their K / V tiles in L2
-  const int qt = p.tiles - 1 - (int)blockIdx.x / p.num_q_heads, h = (int)blockIdx.x % p.num_q_heads, kvh = h / p.group;
+  const int unit = (int)blockIdx.x / p.num_q_heads, h = (int)blockIdx.x % p.num_q_heads, kvh = h / p.group;
+  int sq = 0;
+  while (unit >= p.seqs.first[sq + 1]) sq++;
+  const int q_off = p.seqs.q_off[sq], Tq = p.seqs.Tq[sq], k_off = p.seqs.k_off[sq], Tk = p.seqs.Tk[sq];
+  const int qt = p.seqs.first[sq + 1] - 1 - unit;  // of this sequence, the last tile first
   const int r0 = qt * QT * BM;
-  const int shift = p.Tk - p.Tq;  // the last query is aligned with the last key
+  const int shift = Tk - Tq;  // the last query is aligned with the last key
   int nkb[QT], nkb_max = 0;
 #pragma unroll
   for (int g = 0; g < QT; g++) {
     const int first = r0 + g * BM;
-    if (first >= p.Tq) {
+    if (first >= Tq) {
       nkb[g] = 0;
     } else {
-      const int last = min(first + BM - 1, p.Tq - 1);
-      const int vis = p.causal ? min(p.Tk, last + 1 + shift) : p.Tk;
+      const int last = min(first + BM - 1, Tq - 1);
+      const int vis = p.causal ? min(Tk, last + 1 + shift) : Tk;
       nkb[g] = (vis + BN - 1) / BN;
     }
     nkb_max = max(nkb_max, nkb[g]);
@@ -153,7 +166,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_sm100_kernel(const __
         if (nkb[g] == 0) continue;
         for (int s = 0; s < KSL; s++)
           ptx::tma_load_2d(ptx::smem_u32(sQ + g * Q_TILE + s * SLAB), &p.tmQ, bar(&st->q_full), h * HD + s * 64,
-                           p.q_off + r0 + g * BM);
+                           q_off + r0 + g * BM);
       }
       for (int n = 0; n < 2 * nkb_max; n++) {  // K_0, V_0, K_1, V_1, ...
         const int slot = n % KV_SLOTS;
@@ -163,7 +176,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_sm100_kernel(const __
         const CUtensorMap *m = (n & 1) ? &p.tmV : &p.tmK;
         for (int s = 0; s < KSL; s++)
           ptx::tma_load_2d(ptx::smem_u32(sKV + slot * KV_TILE + s * SLAB), m, bar(&st->kv_full[slot]), kvh * HD + s * 64,
-                           p.k_off + (n >> 1) * BN);
+                           k_off + (n >> 1) * BN);
       }
     }
     __syncwarp();
@@ -225,7 +238,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_sm100_kernel(const __
     const int g = (warp - 2) >> 2, quarter = warp & 3;  // tensor-memory lanes a warp may read: 32 * (warp % 4) ...
     const int trow = quarter * 32 + lane;
     const int row = r0 + g * BM + trow;  // position of the query in its sequence
-    const int limit = p.causal ? min(p.Tk, row + 1 + shift) : p.Tk;  // keys this row sees
+    const int limit = p.causal ? min(Tk, row + 1 + shift) : Tk;  // keys this row sees
     const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
     const uint32_t s_addr = lane_addr + (uint32_t)(g * BN), o_addr = lane_addr + (uint32_t)(QT * BN + g * HD);
     const uint32_t p_addr = ptx::smem_u32(sP + g * P_TILE + trow * 128);
@@ -319,13 +332,13 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_sm100_kernel(const __
       if (!wait(&st->pv_full[g], (uint32_t)((nkb[g] - 1) & 1), ST_ATTN_PV)) goto teardown;
       ptx::tc_fence_after();
       const float inv = l > 0.0f ? __fdividef(1.0f, l) : 0.0f;
-      __nv_bfloat16 *o = p.O + (int64_t)(p.q_off + row) * p.ldO + (int64_t)h * HD;
+      __nv_bfloat16 *o = p.O + (int64_t)(q_off + row) * p.ldO + (int64_t)h * HD;
 #pragma unroll
       for (int c4 = 0; c4 < HD / 32; c4++) {
         uint32_t r[32];
         ptx::tmem_ld32(o_addr + c4 * 32, r);
         ptx::tmem_ld_wait();
-        if (row < p.Tq) {
+        if (row < Tq) {
 #pragma unroll
           for (int i = 0; i < 32; i += 8) {
             float v[8];
@@ -335,7 +348,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_sm100_kernel(const __
           }
         }
       }
-      if (row < p.Tq) p.lse[(int64_t)h * p.total_q + p.q_off + row] = l > 0.0f ? m * p.scale + logf(l) : -INFINITY;
+      if (row < Tq) p.lse[(int64_t)h * p.total_q + q_off + row] = l > 0.0f ? m * p.scale + logf(l) : -INFINITY;
     }
   }
 
@@ -381,7 +394,8 @@ struct BwdParams {
   const float *lse, *delta;  // [heads][total_q]
   float *dQacc;              // [total_q][heads * 128] fp32, zeroed by the caller
   __nv_bfloat16 *dK, *dV;
-  int q_off, Tq, k_off, Tk, causal, group, total_q, num_kv_heads;
+  SeqTable seqs;
+  int causal, group, total_q, num_kv_heads;
   int64_t ldQ, ldK;
   float scale;
   int *status;
@@ -453,9 +467,13 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_sm100_kernel(const __
 
   // one-dimensional grid, key block major: the key blocks most queries see (the first ones, under a causal mask) start
   // first on every key/value head, the short ones fill in behind them
-  const int kb = (int)blockIdx.x / p.num_kv_heads, kvh = (int)blockIdx.x % p.num_kv_heads;
-  const int shift = p.Tk - p.Tq;
-  const int nqb = (p.Tq + BM - 1) / BM;
+  const int unit = (int)blockIdx.x / p.num_kv_heads, kvh = (int)blockIdx.x % p.num_kv_heads;
+  int sq = 0;
+  while (unit >= p.seqs.first[sq + 1]) sq++;
+  const int q_off = p.seqs.q_off[sq], Tq = p.seqs.Tq[sq], k_off = p.seqs.k_off[sq], Tk = p.seqs.Tk[sq];
+  const int kb = unit - p.seqs.first[sq];
+  const int shift = Tk - Tq;
+  const int nqb = (Tq + BM - 1) / BM;
   const int qb_start = p.causal ? max(0, kb * BN - shift) / BM : 0;
   const int per_head = nqb - qb_start;
   const int n_steps = per_head > 0 ? per_head * p.group : 0;
@@ -465,8 +483,8 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_sm100_kernel(const __
     if (lane == 0 && n_steps > 0) {
       ptx::mbar_arrive_expect_tx(bar(&st->kv_full), (uint32_t)(2 * BWD_TILE));
       for (int s = 0; s < HD / 64; s++) {
-        ptx::tma_load_2d(ptx::smem_u32(sK + s * SLAB), &p.tmK, bar(&st->kv_full), kvh * HD + s * 64, p.k_off + kb * BN);
-        ptx::tma_load_2d(ptx::smem_u32(sV + s * SLAB), &p.tmV, bar(&st->kv_full), kvh * HD + s * 64, p.k_off + kb * BN);
+        ptx::tma_load_2d(ptx::smem_u32(sK + s * SLAB), &p.tmK, bar(&st->kv_full), kvh * HD + s * 64, k_off + kb * BN);
+        ptx::tma_load_2d(ptx::smem_u32(sV + s * SLAB), &p.tmV, bar(&st->kv_full), kvh * HD + s * 64, k_off + kb * BN);
       }
       for (int n = 0; n < 2 * n_steps; n++) {  // Q_0, dO_0, Q_1, dO_1, ...
         const int i = n >> 1, h = kvh * p.group + i / per_head, qb = qb_start + i % per_head;
@@ -477,7 +495,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_sm100_kernel(const __
         const CUtensorMap *m = (n & 1) ? &p.tmdO : &p.tmQ;
         for (int s = 0; s < HD / 64; s++)
           ptx::tma_load_2d(ptx::smem_u32(sRing + slot * BWD_TILE + s * SLAB), m, bar(&st->ring_full[slot]), h * HD + s * 64,
-                           p.q_off + qb * BM);
+                           q_off + qb * BM);
       }
     }
     __syncwarp();
@@ -539,7 +557,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_sm100_kernel(const __
     const int quarter = warp & 3, half = (warp - 2) >> 2;
     const int trow = quarter * 32 + lane;
     const int key = kb * BN + trow;  // position of this lane's key in its sequence (steps 1-2 and the end)
-    const bool key_ok = key < p.Tk;
+    const bool key_ok = key < Tk;
     const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(half * 64);
     const uint32_t pt_addr = ptx::smem_u32(sPT + half * SLAB + trow * 128), dst_addr = ptx::smem_u32(sDST + half * SLAB + trow * 128);
     const uint32_t stats_addr = ptx::smem_u32(&st->stats[0][0]), stage_addr = ptx::smem_u32(sPT);
@@ -548,8 +566,8 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_sm100_kernel(const __
     // lse * log2 e (threads 0-127) or delta (128-255) of query st_t % 128 of step `step`: fetched a step ahead
     auto stat_load = [&](int step) {
       const int hh = kvh * p.group + step / per_head, qa = (qb_start + step % per_head) * BM + (st_t & 127);
-      if (step >= n_steps || qa >= p.Tq) return 0.0f;
-      const int64_t at = (int64_t)hh * p.total_q + p.q_off + qa;
+      if (step >= n_steps || qa >= Tq) return 0.0f;
+      const int64_t at = (int64_t)hh * p.total_q + q_off + qa;
       return st_t < 128 ? p.lse[at] * LOG2E : p.delta[at];
     };
     st->stats[st_t >> 7][st_t & 127] = stat_load(0);
@@ -564,7 +582,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_sm100_kernel(const __
       if (i > 0 && !wait(&st->dq_empty, par ^ 1u, ST_BWD_DQ_EMPTY)) goto teardown;
       const float stat_next = stat_load(i + 1);  // in flight while this step computes
       // queries of this step the lane's key is visible to: columns lo_rel <= col < hi_rel
-      const int lo_rel = (key_ok ? (p.causal ? key - shift : 0) : (1 << 30)) - q0, hi_rel = p.Tq - q0;
+      const int lo_rel = (key_ok ? (p.causal ? key - shift : 0) : (1 << 30)) - q0, hi_rel = Tq - q0;
       float prob[64];
       uint32_t r[32];
       if (!wait(&st->s_full, par, ST_BWD_S)) goto teardown;
@@ -648,9 +666,9 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_sm100_kernel(const __
         // hold zeros: their dS is masked; rows past the end of the array are clipped). The first half is waited for
         // here, the second before the next step's dS^T is written, so that it drains behind the next step's P^T.
         if (!wait(&st->stage_ready, par, ST_BWD_STAGE)) goto teardown;
-        ptx::tma_reduce_add_2d(&p.tmdQ, stage_addr, h * HD, p.q_off + q0);
+        ptx::tma_reduce_add_2d(&p.tmdQ, stage_addr, h * HD, q_off + q0);
         ptx::bulk_commit_group();
-        ptx::tma_reduce_add_2d(&p.tmdQ, stage_addr + 64 * HD * 4, h * HD, p.q_off + q0 + 64);
+        ptx::tma_reduce_add_2d(&p.tmdQ, stage_addr + 64 * HD * 4, h * HD, q_off + q0 + 64);
         ptx::bulk_commit_group();
         ptx::bulk_wait_group_read1();
         ptx::mbar_arrive(bar(&st->dq_empty));
@@ -662,8 +680,8 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_sm100_kernel(const __
     ptx::tc_fence_after();
     {
       uint32_t r[32];
-      __nv_bfloat16 *dk = p.dK + (int64_t)(p.k_off + key) * p.ldK + (int64_t)kvh * HD + half * 64;
-      __nv_bfloat16 *dv = p.dV + (int64_t)(p.k_off + key) * p.ldK + (int64_t)kvh * HD + half * 64;
+      __nv_bfloat16 *dk = p.dK + (int64_t)(k_off + key) * p.ldK + (int64_t)kvh * HD + half * 64;
+      __nv_bfloat16 *dv = p.dV + (int64_t)(k_off + key) * p.ldK + (int64_t)kvh * HD + half * 64;
 #pragma unroll
       for (int c2 = 0; c2 < 2; c2++) {
         float v[32];
@@ -781,7 +799,7 @@ int *attn_status_ptr() {
 }
 
 template <int HD>
-int launch_fwd(fa::FwdParams &p, int num_q_heads, cudaStream_t s) {
+int launch_fwd(const fa::FwdParams &p, int units, int num_q_heads, cudaStream_t s) {
   static bool attr_set[MAX_DEVICES];
   int dev = -1;
   B200_CUDA(cudaGetDevice(&dev));
@@ -791,11 +809,31 @@ int launch_fwd(fa::FwdParams &p, int num_q_heads, cudaStream_t s) {
     B200_CUDA(cudaFuncSetAttribute(fa::attn_fwd_sm100_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     attr_set[dev] = true;
   }
-  p.tiles = (p.Tq + fa::QT * fa::BM - 1) / (fa::QT * fa::BM);
-  p.num_q_heads = num_q_heads;
-  fa::attn_fwd_sm100_kernel<HD><<<(unsigned)(p.tiles * num_q_heads), fa::FWD_THREADS, smem, s>>>(p);
+  fa::attn_fwd_sm100_kernel<HD><<<(unsigned)(units * num_q_heads), fa::FWD_THREADS, smem, s>>>(p);
   B200_CHECK_LAUNCH("attention_fwd (fused)");
   return 0;
+}
+
+// Fills the table with the next sequences that have work (at most MAX_SEQS), starting at *next; units_of gives a
+// sequence's number of work units. Returns the units in the table.
+template <typename F>
+int fill_table(fa::SeqTable &t, int *next, int num_seqs, const int *q_off, const int *q_len, const int *k_off,
+               const int *k_len, F units_of) {
+  t.n = 0;
+  t.first[0] = 0;
+  while (*next < num_seqs && t.n < fa::MAX_SEQS) {
+    const int sq = (*next)++;
+    const int u = units_of(sq);
+    if (u == 0) continue;
+    t.q_off[t.n] = q_off[sq];
+    t.Tq[t.n] = q_len[sq];
+    t.k_off[t.n] = k_off[sq];
+    t.Tk[t.n] = k_len[sq];
+    t.first[t.n + 1] = t.first[t.n] + u;
+    t.n++;
+  }
+  for (int i = t.n + 1; i <= fa::MAX_SEQS; i++) t.first[i] = t.first[t.n];
+  return t.first[t.n];
 }
 
 }  // namespace
@@ -804,7 +842,7 @@ namespace b200 {
 
 bool attn_fused_supported(int head_dim) { return head_dim == 64 || head_dim == 128; }
 
-// Forward over every sequence of the packed batch (one launch per sequence); arguments as b200_attention_fwd.
+// Forward over every sequence of the packed batch (one launch per 48 sequences); arguments as b200_attention_fwd.
 int attn_fused_fwd(int num_seqs, int total_q, int total_k, const int *q_off, const int *q_len, const int *k_off,
                    const int *k_len, int num_q_heads, int num_kv_heads, int head_dim, const void *Q, const void *K,
                    const void *V, void *O, float *lse, int is_causal, cudaStream_t s) {
@@ -822,17 +860,16 @@ int attn_fused_fwd(int num_seqs, int total_q, int total_k, const int *q_off, con
   p.scale = 1.0f / sqrtf((float)head_dim);
   p.status = attn_status_ptr();
   B200_REQUIRE(p.status != nullptr, "attention: the status word of this device is not reachable");
-  for (int sq = 0; sq < num_seqs; sq++) {
-    if (q_len[sq] == 0) continue;
-    p.q_off = q_off[sq];
-    p.Tq = q_len[sq];
-    p.k_off = k_off[sq];
-    p.Tk = k_len[sq];
-    if ((head_dim == 128 ? launch_fwd<128>(p, num_q_heads, s) : launch_fwd<64>(p, num_q_heads, s)) != 0) return -1;
+  p.num_q_heads = num_q_heads;
+  // one launch per MAX_SEQS sequences of the packed batch
+  for (int next = 0; next < num_seqs;) {
+    const int units = fill_table(p.seqs, &next, num_seqs, q_off, q_len, k_off, k_len,
+                                 [&](int sq) { return (q_len[sq] + fa::QT * fa::BM - 1) / (fa::QT * fa::BM); });
+    if (units == 0) continue;
+    if ((head_dim == 128 ? launch_fwd<128>(p, units, num_q_heads, s) : launch_fwd<64>(p, units, num_q_heads, s)) != 0) return -1;
   }
   return 0;
 }
-
 
 bool attn_fused_bwd_supported(int head_dim) { return head_dim == fa::BWD_HD; }
 
@@ -896,18 +933,17 @@ int attn_fused_bwd(int num_seqs, int total_q, int total_k, const int *q_off, con
                                                                          (const __nv_bfloat16 *)dO, (const __nv_bfloat16 *)O, delta);
   B200_CHECK_LAUNCH("attention_bwd (delta)");
   for (int sq = 0; sq < num_seqs; sq++) {
-    if (k_len[sq] == 0) continue;
-    if (q_len[sq] == 0) {  // keys that no query of the batch reads
-      B200_CUDA(cudaMemsetAsync((__nv_bfloat16 *)dK + (int64_t)k_off[sq] * Dk, 0, (size_t)k_len[sq] * Dk * 2, s));
-      B200_CUDA(cudaMemsetAsync((__nv_bfloat16 *)dV + (int64_t)k_off[sq] * Dk, 0, (size_t)k_len[sq] * Dk * 2, s));
-      continue;
-    }
-    p.q_off = q_off[sq];
-    p.Tq = q_len[sq];
-    p.k_off = k_off[sq];
-    p.Tk = k_len[sq];
-    const int key_blocks = (p.Tk + fa::BN - 1) / fa::BN;
-    fa::attn_bwd_sm100_kernel<<<(unsigned)(key_blocks * num_kv_heads), fa::BWD_THREADS, fa::bwd_smem_bytes(), s>>>(p);
+    if (k_len[sq] == 0 || q_len[sq] != 0) continue;
+    // keys that no query of the batch reads
+    B200_CUDA(cudaMemsetAsync((__nv_bfloat16 *)dK + (int64_t)k_off[sq] * Dk, 0, (size_t)k_len[sq] * Dk * 2, s));
+    B200_CUDA(cudaMemsetAsync((__nv_bfloat16 *)dV + (int64_t)k_off[sq] * Dk, 0, (size_t)k_len[sq] * Dk * 2, s));
+  }
+  for (int next = 0; next < num_seqs;) {
+    const int units = fill_table(p.seqs, &next, num_seqs, q_off, q_len, k_off, k_len, [&](int sq) {
+      return (q_len[sq] == 0 || k_len[sq] == 0) ? 0 : (k_len[sq] + fa::BN - 1) / fa::BN;
+    });
+    if (units == 0) continue;
+    fa::attn_bwd_sm100_kernel<<<(unsigned)(units * num_kv_heads), fa::BWD_THREADS, fa::bwd_smem_bytes(), s>>>(p);
     B200_CHECK_LAUNCH("attention_bwd (fused)");
   }
   const int64_t n8 = (int64_t)total_q * Dq / 8;

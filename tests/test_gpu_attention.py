@@ -18,6 +18,7 @@ CASES = [
     ([0, 257], [5, 700], 4, 2, 128, False),       # fused kernels: a sequence without queries, several key blocks, no mask
     ([385, 130], [900, 130], 8, 2, 128, True),    # fused kernels: three query tiles, keys beyond the queries, ragged ends
     ([40], [40], 2, 2, 128, True),                # fused kernels: fewer rows in the whole batch than one tile
+    (list(range(1, 61)), [n + (n % 3) * 50 for n in range(1, 61)], 4, 2, 128, True),  # more sequences than one launch's table
 ]
 
 

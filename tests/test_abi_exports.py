@@ -75,3 +75,52 @@ def test_host_only_entry_points_answer_without_a_gpu():
         assert n <= cap                      # 64 experts fit the built-in scratch at any token count
     assert ws(1 << 20, 4096, 8) > cap        # a problem the no-allocation variant must refuse
     assert ws(8192, 64, 8) <= ws(8192, 256, 8)
+
+
+def _struct_fields(name):
+    text = open(HEADER).read()
+    body = re.search(r"typedef struct " + name + r" \{(.*?)\} " + name + ";", text, flags=re.S).group(1)
+    body = re.sub(r"/\*.*?\*/", "", body, flags=re.S)
+    fields = []
+    for decl in body.split(";"):
+        decl = decl.strip()
+        if not decl:
+            continue
+        for part in decl.split(","):
+            fields.append(re.findall(r"[A-Za-z_][A-Za-z0-9_]*", part)[-1])
+    return fields
+
+
+def test_transformer_block_structure_mirrors_match_the_header():
+    from ml_dataflow_b200 import _lib
+
+    for name, mirror in (("B200TransformerBlock", _lib.TransformerBlock), ("B200TransformerBlockGrads", _lib.TransformerBlockGrads),
+                         ("B200TransformerBlockScratch", _lib.TransformerBlockScratch)):
+        assert _struct_fields(name) == [f[0] for f in mirror._fields_], name
+    # the MoE part sits inside the block structure by value
+    assert dict(_lib.TransformerBlock._fields_)["moe"] is _lib.MoeBlock
+
+
+def test_attention_workspace_sizes_and_argument_checks_without_a_gpu():
+    """Host-side logic only: the workspace formula and the argument checks run before any CUDA call."""
+    from ml_dataflow_b200 import _lib
+
+    lib = _lib.load()
+    ws = lib.b200_attention_workspace_bytes
+    up = lambda v: (v + 255) // 256 * 256
+    T, Hq, Hkv = 1000, 16, 4
+    # head size 128: fused both ways - nothing for inference, the fp32 dQ accumulator and delta for training
+    assert ws(0, Hq, Hkv, 128, T, 600, 600) == 0
+    assert ws(1, Hq, Hkv, 128, T, 600, 600) == up(T * Hq * 128 * 4) + up(T * Hq * 4)
+    # head size 64: fused forward, GEMM-by-GEMM backward (score matrices of one head and query chunk)
+    assert ws(0, Hq, Hkv, 64, T, 600, 600) == 0
+    assert ws(1, Hq, Hkv, 64, T, 600, 600) >= 600 * 600 * 6
+    # other head sizes: GEMM by GEMM both ways
+    assert ws(0, Hq, Hkv, 32, T, 600, 600) >= 600 * 600 * 6
+    assert ws(1, 0, Hkv, 128, T, 600, 600) == 0  # nonsense in, 0 out
+    # query heads must be a multiple of the key/value heads; only bf16; lengths within the stated maxima
+    ia = lambda *v: (ctypes.c_int * len(v))(*v)
+    bad = lib.b200_attention_fwd(5, 1, 8, 8, ia(0), ia(8), 8, ia(0), ia(8), 8, 3, 2, 128, None, None, None, None, None, 1, 0, None, None)
+    assert bad == -1
+    assert lib.b200_attention_fwd(3, 1, 8, 8, ia(0), ia(8), 8, ia(0), ia(8), 8, 4, 2, 128, None, None, None, None, None, 1, 0, None, None) == -1
+    assert lib.b200_attention_fwd(5, 1, 8, 8, ia(0), ia(9), 8, ia(0), ia(9), 8, 4, 2, 128, None, None, None, None, None, 1, 0, None, None) == -1

@@ -577,9 +577,8 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_sm100_kernel(const __
       const int h = kvh * p.group + i / per_head, qb = qb_start + i % per_head;
       const uint32_t par = (uint32_t)(i & 1);
       const int q0 = qb * BM;
-      // every thread has left the step before: its statistics for this step are written, and the first half of the dQ
-      // staging area (which lies over P^T) has been read by its bulk reduction
-      if (i > 0 && !wait(&st->dq_empty, par ^ 1u, ST_BWD_DQ_EMPTY)) goto teardown;
+      // every thread has left the step before: its statistics for this step are written
+      if (i > 0 && !wait(&st->stage_ready, par ^ 1u, ST_BWD_STAGE)) goto teardown;
       const float stat_next = stat_load(i + 1);  // in flight while this step computes
       // queries of this step the lane's key is visible to: columns lo_rel <= col < hi_rel
       const int lo_rel = (key_ok ? (p.causal ? key - shift : 0) : (1 << 30)) - q0, hi_rel = Tq - q0;
@@ -601,9 +600,18 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_sm100_kernel(const __
           const float pv = ex2(fmaf(__uint_as_float(r[t]), c, -l2));
           prob[c2 * 32 + t] = (col >= lo_rel && col < hi_rel) ? pv : 0.0f;
         }
-#pragma unroll
-        for (int q = 0; q < 4; q++) sts128(pt_addr + (uint32_t)((((c2 * 4 + q) ^ (trow & 7))) * 16), pack8(prob + c2 * 32 + q * 8));
       }
+      // P^T goes where the first half of the dQ staging area lies: the bulk reduction of the step before has to have
+      // read it (it drained while the probabilities above were formed)
+      if (i > 0) {
+        if (st_t == 0) {
+          ptx::bulk_wait_group_read1();
+          ptx::mbar_arrive(bar(&st->dq_empty));
+        }
+        if (!wait(&st->dq_empty, par ^ 1u, ST_BWD_DQ_EMPTY)) goto teardown;
+      }
+#pragma unroll
+      for (int q = 0; q < 8; q++) sts128(pt_addr + (uint32_t)(((q ^ (trow & 7))) * 16), pack8(prob + q * 8));
       ptx::fence_proxy_async_smem();
       ptx::tc_fence_before();
       ptx::mbar_arrive(bar(&st->p_ready));
@@ -663,15 +671,14 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_sm100_kernel(const __
       ptx::mbar_arrive(bar(&st->stage_ready));
       if (st_t == 0) {
         // two tiled reductions add the [128 queries][128 dims] block, 64 queries each (rows past the end of the sequence
-        // hold zeros: their dS is masked; rows past the end of the array are clipped). The first half is waited for
-        // here, the second before the next step's dS^T is written, so that it drains behind the next step's P^T.
+        // hold zeros: their dS is masked; rows past the end of the array are clipped). Neither is waited for here: the
+        // first half has to be read before the next step's P^T is stored, the second before its dS^T, and both drain
+        // while that step's probabilities are formed.
         if (!wait(&st->stage_ready, par, ST_BWD_STAGE)) goto teardown;
         ptx::tma_reduce_add_2d(&p.tmdQ, stage_addr, h * HD, q_off + q0);
         ptx::bulk_commit_group();
         ptx::tma_reduce_add_2d(&p.tmdQ, stage_addr + 64 * HD * 4, h * HD, q_off + q0 + 64);
         ptx::bulk_commit_group();
-        ptx::bulk_wait_group_read1();
-        ptx::mbar_arrive(bar(&st->dq_empty));
       }
     }
     ptx::bulk_wait_group0();

@@ -236,7 +236,7 @@ def block_ops_profile(dev, peaks, iters=5, with_attention=True):
 
 # ------------------------------------------------------------------------------------------ decoder step
 def decoder_step_run(dev, peaks, steps=3, warmup=2):
-    """The full training step of BASELINE configs[3] on one GPU: a random-init MoE decoder (16 layers, d=2048, 16 query /
+    """The full training step of the 16-layer decoder configuration on one GPU: a random-init MoE decoder (16 layers, d=2048, 16 query /
     4 kv heads of 128, 64 experts top-8 with ffn 1024, vocabulary 128256, untied embeddings), one sequence of 8192 tokens
     with token ids and labels uniform over the vocabulary, bf16 parameters and gradients, AdamW (lr 3e-4, betas
     0.9 / 0.95, weight decay 0.1): forward + backward + optimizer step through ml_dataflow_b200.decoder, device-timed."""

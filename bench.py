@@ -540,9 +540,11 @@ def run_gpu_arm(args, world):
     else:
         from ml_dataflow_b200.ep import ExpertParallelMoELayer
 
-        # "c" (default): the buffers of the "fused" transport driven by b200_ep_moe_block_fwd / _bwd, one C call per
-        # direction with the library's own barrier / plan kernels; the other names run the Python driver in ep.py
-        transport = os.environ.get("B200_EP_TRANSPORT", "c")
+        # "c" (default up to 4 GPUs): the buffers of the "fused" transport driven by b200_ep_moe_block_fwd / _bwd, one C
+        # call per direction with the library's own barrier / plan kernels; the other names run the Python driver in
+        # ep.py. At 8 GPUs the default is the Python driver of the same kernels: it is the one that has been run and
+        # checked at that size (no 8-GPU machine could be had for the C driver); B200_EP_TRANSPORT=c selects it there too.
+        transport = os.environ.get("B200_EP_TRANSPORT", "c" if world <= 4 else "fused")
         layer = ExpertParallelMoELayer(T, d, E, k, f, dist, device=dev, transport="fused" if transport == "c" else transport,
                                        slices=int(os.environ.get("B200_EP_SLICES", "1")))
         E_loc = E // world
@@ -553,6 +555,8 @@ def run_gpu_arm(args, world):
     dW1, dW3, dW2 = torch.zeros_like(W1), torch.zeros_like(W3), torch.zeros_like(W2)
 
     exchange_note = None
+    if world > 4 and transport == "fused" and "B200_EP_TRANSPORT" not in os.environ:
+        exchange_note = "Python driver of the fused-transport kernels: the C driver was validated on 2 and 4 GPUs only"
     block = layer.block(Wr, W1, W3, W2) if world == 1 else None
     ep_block = layer.c_block(Wr, W1, W3, W2) if transport == "c" else None
 

@@ -124,3 +124,14 @@ def test_attention_workspace_sizes_and_argument_checks_without_a_gpu():
     assert bad == -1
     assert lib.b200_attention_fwd(3, 1, 8, 8, ia(0), ia(8), 8, ia(0), ia(8), 8, 4, 2, 128, None, None, None, None, None, 1, 0, None, None) == -1
     assert lib.b200_attention_fwd(5, 1, 8, 8, ia(0), ia(9), 8, ia(0), ia(9), 8, 4, 2, 128, None, None, None, None, None, 1, 0, None, None) == -1
+
+
+def test_block_driver_refuses_bad_arguments_without_a_gpu():
+    """The block driver checks its structure before any CUDA call: null block, inconsistent MoE part."""
+    from ml_dataflow_b200 import _lib
+
+    lib = _lib.load()
+    assert lib.b200_transformer_block_fwd(None, None, None, None) == -1
+    blk = _lib.TransformerBlock()  # all zeros: bad dimensions
+    assert lib.b200_transformer_block_fwd(ctypes.byref(blk), None, None, None) == -1
+    assert lib.b200_transformer_block_bwd(ctypes.byref(blk), None, None, None, None, None) == -1

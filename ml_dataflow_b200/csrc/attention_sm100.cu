@@ -1,16 +1,17 @@
 // Fused softmax attention for sm_100a (head_dim 64 or 128, bf16): the scores and the probabilities never leave the SM.
-// It serves b200_attention_fwd / _bwd (attention.cu), which keep the unfused form for every other head size.
+// It serves b200_attention_fwd / _bwd (attention.cu), which keep the GEMM-by-GEMM form for every other head size (the
+// backward kernel here is for head_dim 128).
 //
 // Forward, one CTA per (query head, 256 query rows of one sequence): Q (two 128-row tiles) is fetched once by TMA; the
 // key and value tiles of 128 keys pass through a three-slot ring. One thread issues the tcgen05 MMAs
-//     S_g = Q_g K_j^T  (fp32, tensor memory)        O'_g = P_g V_j  (fp32, tensor memory)
+//     S_g = Q_g K_j^T  (fp32, tensor memory)        O_g += P_g V_j  (fp32, tensor memory)
 // and two groups of four warps (one per query tile, a thread per query row = per tensor-memory lane) turn S_g into
-// P_g = exp2((S_g - max) * scale * log2 e) with the running maximum and sum of the online softmax, write P_g as bf16
-// into shared memory in the layout the second MMA reads (128-byte swizzle, keys contiguous) and fold O'_g into the
-// row's output, which stays in registers (fp32) until it is divided by the sum and stored. While one group works on
-// its scores the tensor pipe runs the other group's P V and next Q K^T. Rounding points: scores, maximum, sum and the
-// output in fp32; P to bf16 (unnormalised, relative to the running maximum) before it multiplies V; one rounding of
-// the output.
+// P_g = exp2((S_g - m) * scale * log2 e), keep the row's sum, and write P_g as bf16 into shared memory in the layout
+// the second MMA reads (128-byte swizzle, keys contiguous). The offset m is the row maximum of the first key block; it
+// is raised - and the sum and O_g rescaled in tensor memory - only when a later block's maximum exceeds it by more than
+// 2^8, so the common step never touches O_g. While one group works on its scores the tensor pipe runs the other
+// group's P V and next Q K^T. At the end O_g is divided by the sum and stored. Rounding points: scores, maximum, sum and
+// the output in fp32; P to bf16 (unnormalised, relative to m) before it multiplies V; one rounding of the output.
 //
 // Every wait is bounded (two seconds); a wait that runs out raises the status word that b200_attention_status reads,
 // and the CTA leaves through the common teardown.

@@ -1,13 +1,13 @@
 // Causal / full softmax attention over variable-length sequences with grouped query heads, forward and backward:
 // the op the reference takes from an external flash-attention library (dataflow_submit_attention / _attention_bwd,
-// libdataflowops/include/dataflow_ops.h:70-105). First form: NOT fused. Per sequence and query head it is a sequence
-// of this library's own tcgen05 GEMMs on strided head slices (b200_matmul_strided) with the score matrix in the
-// caller's workspace, and three small kernels for the softmax, its backward and the fp32 -> bf16 hand-over of the key /
-// value gradients. The arithmetic follows the published algorithm the reference's library implements: scores and
-// softmax statistics in fp32, probabilities rounded to bf16 before they multiply V (and dO in the backward), fp32
-// accumulation, one rounding per output; the backward re-forms the probabilities from Q, K and the kept
-// log-sum-exp instead of storing them. A fused kernel that keeps the scores in tensor memory is the next step; this
-// one makes the op available and is what such a kernel will be checked against.
+// libdataflowops/include/dataflow_ops.h:70-105). This file holds the entry points and the GEMM-by-GEMM form: per
+// sequence and query head a sequence of this library's own tcgen05 GEMMs on strided head slices (b200_matmul_strided)
+// with the score matrix in the caller's workspace, and small kernels for the softmax, its backward and the fp32 -> bf16
+// hand-over of the key / value gradients. Head sizes 64 and 128 are served by the fused kernels of attention_sm100.cu
+// instead (forward both, backward 128), which were first checked against this form. The arithmetic of both follows
+// the published algorithm the reference's library implements: scores and softmax statistics in fp32, probabilities
+// rounded to bf16 before they multiply V (and dO in the backward), fp32 accumulation, one rounding per output; the
+// backward re-forms the probabilities from Q, K and the kept log-sum-exp instead of storing them.
 #include <math.h>
 #include <stdlib.h>
 

@@ -341,6 +341,15 @@ int b200_moe_experts_bwd_w(int total_rows, int model_dim, int ffn_dim, int num_e
                            int64_t dw2_stride_elems, const int *expert_counts, const int *expert_counts_cumsum,
                            void *stream);
 
+/* The same with beta = 0: the weight gradients are written, not added to, and the old contents of dW1 / dW3 / dW2 are
+ * not read (a tenth of the three launches' time at the benchmark shape). For the first micro-batch of a step, in place
+ * of zeroing the buffers and accumulating. No counterpart in the reference, whose gradient GEMMs always accumulate. */
+int b200_moe_experts_bwd_w_overwrite(int total_rows, int model_dim, int ffn_dim, int num_experts, const void *dY_zone,
+                           const void *hs, const void *zone_x, const void *dx1, const void *dx3, void *dW1,
+                           void *dW3, void *dW2, int64_t dw1_stride_elems, int64_t dw3_stride_elems,
+                           int64_t dw2_stride_elems, const int *expert_counts, const int *expert_counts_cumsum,
+                           void *stream);
+
 /* row_weights[token_mapping[t,j]] = token_expert_weights[t,j]; dP_tok[t, chosen[t,j]] (bf16 [T,E], pre-zeroed)
  * = bf16(dP[token_mapping[t,j]]). Small helpers around the fused backward. */
 int b200_scatter_row_weights(int num_tokens, int top_k, const int *token_mapping, const float *token_expert_weights,
@@ -446,6 +455,11 @@ int b200_moe_block_recompute_level(const B200MoeBlock *block, const void *Xn, in
  * recomputed (3494-3516): the router's dot product comes out of the W2-dgrad epilogue.
  */
 int b200_moe_block_bwd(const B200MoeBlock *block, const void *Xn, const void *dOut, void *dXn, void *dWr, void *dW1,
+                       void *dW3, void *dW2, void *stream);
+
+/* The same, writing dWr / dW1 / dW3 / dW2 instead of accumulating into them (b200_moe_experts_bwd_w_overwrite and a
+ * router weight-gradient GEMM with beta = 0). */
+int b200_moe_block_bwd_overwrite(const B200MoeBlock *block, const void *Xn, const void *dOut, void *dXn, void *dWr, void *dW1,
                        void *dW3, void *dW2, void *stream);
 
 /* ---- the reference's model directory -------------------------------------------------------------------- */
@@ -822,9 +836,11 @@ typedef struct B200TransformerBlock {
   B200MoeBlock moe;                  /* the feed-forward part; its Xn is xn2 */
 } B200TransformerBlock;
 
-/* gradients the backward accumulates into (bf16, the shapes of the weights) */
+/* gradients the backward accumulates into (bf16, the shapes of the weights); with overwrite != 0 it writes them
+ * instead and never reads their old contents (first micro-batch of a step: no zeroing pass is needed) */
 typedef struct B200TransformerBlockGrads {
   void *attn_norm, *wq, *wk, *wv, *wo, *ffn_norm, *router, *W1, *W3, *W2;
+  int overwrite;
 } B200TransformerBlockGrads;
 
 /* backward scratch, shared by every block of a model */
@@ -838,7 +854,7 @@ typedef struct B200TransformerBlockScratch {
 int b200_transformer_block_fwd(const B200TransformerBlock *block, const void *x, void *out, void *stream);
 
 /* dx [T][d] holds the gradient at the block's output on entry and at its input on return; the weight gradients are
- * accumulated into (beta = 1), as by the reference's gradient GEMMs and norm kernels. */
+ * accumulated into (beta = 1), as by the reference's gradient GEMMs and norm kernels, unless grads->overwrite is set. */
 int b200_transformer_block_bwd(const B200TransformerBlock *block, const void *x, void *dx, const B200TransformerBlockGrads *grads,
                                const B200TransformerBlockScratch *scratch, void *stream);
 

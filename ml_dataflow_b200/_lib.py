@@ -38,6 +38,8 @@ SIGNATURES = {
                                     _vp, _vp, _vp, _vp, _vp, _vp]),
     "b200_moe_experts_bwd_w": (_i, [_i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp,
                                     _vp]),
+    "b200_moe_experts_bwd_w_overwrite": (_i, [_i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp,
+                                    _vp]),
     "b200_ep_dispatch_rows": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i64, _i, _i, _vp]),
     "b200_ep_combine_rows": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i64, _vp, _vp]),
     "b200_ep_gather_router_grad": (_i, [_i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i64, _vp, _vp]),
@@ -50,6 +52,7 @@ SIGNATURES = {
     "b200_moe_block_fwd": (_i, [_vp, _vp, _vp, _vp]),
     "b200_moe_block_recompute": (_i, [_vp, _vp, _i, _vp]),
     "b200_moe_block_bwd": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "b200_moe_block_bwd_overwrite": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "b200_moe_saved_activations_bytes": (_u64, [_i, _i, _i, _i, _i]),
     "b200_moe_block_save_activations": (_i, [_vp, _i, _vp, _u64, _vp]),
     "b200_moe_block_restore_activations": (_i, [_vp, _i, _vp, _u64, _vp]),
@@ -121,7 +124,7 @@ class TransformerBlock(C.Structure):
 
 
 class TransformerBlockGrads(C.Structure):
-    _fields_ = [(n, _vp) for n in ("attn_norm", "wq", "wk", "wv", "wo", "ffn_norm", "router", "W1", "W3", "W2")]
+    _fields_ = [(n, _vp) for n in ("attn_norm", "wq", "wk", "wv", "wo", "ffn_norm", "router", "W1", "W3", "W2")] + [("overwrite", _i)]
 
 
 class TransformerBlockScratch(C.Structure):

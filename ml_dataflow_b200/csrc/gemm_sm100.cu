@@ -624,10 +624,22 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
     uint32_t acc_par = 0;  // bit a: parity of the next completion of accumulator a
     int seq = 0;
     for (int tile = first_tile; sched.get(tile, t); tile += tile_step) {
-      if (t.k_len == 0) continue;
       const int row_in_cta = quarter * 32 + lane;
       const bool row_ok = row_in_cta + row_off < t.m_valid;
       const int64_t orow = (int64_t)t.out_row0 + row_off + row_in_cta;
+      if (t.k_len == 0) {
+        // An expert without rows: nothing to add. When the weight gradient is written rather than accumulated (no C),
+        // its tiles are zeros - no MMA runs for them, so no accumulator is involved.
+        if (EPI == EPI_STORE && p.group_mode == GROUPED_K && p.C == nullptr && !p.out_fp32 && row_ok) {
+          for (int sub = 0; sub < t.nsub; sub++) {
+            sched.set_sub(t, sub);
+            __nv_bfloat16 *drow = static_cast<__nv_bfloat16 *>(p.D) + (int64_t)t.group * p.d_group_stride + orow * p.ldd + t.n0;
+            const int cbeg = chalf * (t.nw >> 1), cend = min(cbeg + (t.nw >> 1), t.n_valid);
+            for (int col = cbeg; col < cend; col += 8) *reinterpret_cast<uint4 *>(drow + col) = make_uint4(0, 0, 0, 0);
+          }
+        }
+        continue;
+      }
       for (int sub = 0; sub < t.nsub; sub++) {
         // the column tiles of a unit finish together; they are drained in order, each freeing its accumulator
         sched.set_sub(t, sub);
@@ -1510,7 +1522,7 @@ extern "C" int b200_moe_experts_bwd_x_scatter(int total_rows, int model_dim, int
 
 // One grouped wgrad: dW[e][Mrows][Ncols] += A[rows_e, Mrows]^T . B[rows_e, Ncols]
 static int launch_wgrad(int total_rows, int Mrows, int Ncols, int num_experts, const void *A, const void *B, void *dW,
-                        int64_t dw_stride, const int *counts, const int *cumsum, cudaStream_t s) {
+                        int64_t dw_stride, const int *counts, const int *cumsum, bool accumulate, cudaStream_t s) {
   B200_REQUIRE(dw_stride % 8 == 0 && b200_aligned16(dW), "moe_experts_bwd_w: gradient buffers must be 16-byte aligned");
   GemmParams p;
   zero_params(p);
@@ -1524,9 +1536,9 @@ static int launch_wgrad(int total_rows, int Mrows, int Ncols, int num_experts, c
   p.counts = counts;
   p.cumsum_incl = cumsum;
   p.alpha = 1.0f;
-  p.beta = 1.0f;
+  p.beta = accumulate ? 1.0f : 0.0f;
   p.D = dW;
-  p.C = dW;
+  p.C = accumulate ? dW : nullptr;  // without it the epilogue does not read the old gradient at all
   p.ldd = Ncols;
   p.d_group_stride = dw_stride;
   p.k_hint = total_rows / num_experts;
@@ -1540,11 +1552,10 @@ static int launch_wgrad(int total_rows, int Mrows, int Ncols, int num_experts, c
   return launch_gemm<EPI_STORE>(p, tiles, s, true, (int64_t)num_experts * ((Mrows + 255) / 256));
 }
 
-extern "C" int b200_moe_experts_bwd_w(int total_rows, int model_dim, int ffn_dim, int num_experts, const void *dY_zone,
-                                      const void *hs, const void *zone_x, const void *dx1, const void *dx3, void *dW1,
-                                      void *dW3, void *dW2, int64_t dw1_stride_elems, int64_t dw3_stride_elems,
-                                      int64_t dw2_stride_elems, const int *expert_counts,
-                                      const int *expert_counts_cumsum, void *stream) {
+static int experts_bwd_w(int total_rows, int model_dim, int ffn_dim, int num_experts, const void *dY_zone, const void *hs,
+                         const void *zone_x, const void *dx1, const void *dx3, void *dW1, void *dW3, void *dW2,
+                         int64_t dw1_stride_elems, int64_t dw3_stride_elems, int64_t dw2_stride_elems,
+                         const int *expert_counts, const int *expert_counts_cumsum, bool accumulate, void *stream) {
   if (check_grouped("moe_experts_bwd_w", total_rows, model_dim, ffn_dim, num_experts, expert_counts,
                     expert_counts_cumsum))
     return -1;
@@ -1553,20 +1564,38 @@ extern "C" int b200_moe_experts_bwd_w(int total_rows, int model_dim, int ffn_dim
   if (dW2) {
     B200_REQUIRE(dY_zone && hs, "moe_experts_bwd_w: dW2 needs dY_zone and hs");
     if (launch_wgrad(total_rows, model_dim, ffn_dim, num_experts, dY_zone, hs, dW2, dw2_stride_elems, expert_counts,
-                     expert_counts_cumsum, s))
+                     expert_counts_cumsum, accumulate, s))
       return -1;
   }
   if (dW1) {
     B200_REQUIRE(dx1 && zone_x, "moe_experts_bwd_w: dW1 needs dx1 and zone_x");
     if (launch_wgrad(total_rows, ffn_dim, model_dim, num_experts, dx1, zone_x, dW1, dw1_stride_elems, expert_counts,
-                     expert_counts_cumsum, s))
+                     expert_counts_cumsum, accumulate, s))
       return -1;
   }
   if (dW3) {
     B200_REQUIRE(dx3 && zone_x, "moe_experts_bwd_w: dW3 needs dx3 and zone_x");
     if (launch_wgrad(total_rows, ffn_dim, model_dim, num_experts, dx3, zone_x, dW3, dw3_stride_elems, expert_counts,
-                     expert_counts_cumsum, s))
+                     expert_counts_cumsum, accumulate, s))
       return -1;
   }
   return 0;
+}
+
+extern "C" int b200_moe_experts_bwd_w(int total_rows, int model_dim, int ffn_dim, int num_experts, const void *dY_zone,
+                                      const void *hs, const void *zone_x, const void *dx1, const void *dx3, void *dW1,
+                                      void *dW3, void *dW2, int64_t dw1_stride_elems, int64_t dw3_stride_elems,
+                                      int64_t dw2_stride_elems, const int *expert_counts,
+                                      const int *expert_counts_cumsum, void *stream) {
+  return experts_bwd_w(total_rows, model_dim, ffn_dim, num_experts, dY_zone, hs, zone_x, dx1, dx3, dW1, dW3, dW2,
+                       dw1_stride_elems, dw3_stride_elems, dw2_stride_elems, expert_counts, expert_counts_cumsum, true, stream);
+}
+
+extern "C" int b200_moe_experts_bwd_w_overwrite(int total_rows, int model_dim, int ffn_dim, int num_experts,
+                                                const void *dY_zone, const void *hs, const void *zone_x, const void *dx1,
+                                                const void *dx3, void *dW1, void *dW3, void *dW2, int64_t dw1_stride_elems,
+                                                int64_t dw3_stride_elems, int64_t dw2_stride_elems,
+                                                const int *expert_counts, const int *expert_counts_cumsum, void *stream) {
+  return experts_bwd_w(total_rows, model_dim, ffn_dim, num_experts, dY_zone, hs, zone_x, dx1, dx3, dW1, dW3, dW2,
+                       dw1_stride_elems, dw3_stride_elems, dw2_stride_elems, expert_counts, expert_counts_cumsum, false, stream);
 }

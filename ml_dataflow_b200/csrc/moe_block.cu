@@ -65,8 +65,10 @@ extern "C" int b200_moe_block_recompute(const B200MoeBlock *b, const void *Xn, i
   return b200_swiglu(T * k, f, b->x1, b->x3, b->h, stream);  // x1, x3 were saved: only h is re-formed
 }
 
-extern "C" int b200_moe_block_bwd(const B200MoeBlock *b, const void *Xn, const void *dOut, void *dXn, void *dWr,
-                                  void *dW1, void *dW3, void *dW2, void *stream) {
+// accumulate: the weight gradients are added to (the reference's beta = 1); otherwise they are written, and the old
+// contents of the gradient buffers are not read
+static int moe_block_bwd(const B200MoeBlock *b, const void *Xn, const void *dOut, void *dXn, void *dWr, void *dW1,
+                         void *dW3, void *dW2, bool accumulate, void *stream) {
   if (check_block("moe_block_bwd", b)) return -1;
   B200_REQUIRE(Xn && dOut && dXn && dWr, "moe_block_bwd: Xn / dOut / dXn / dWr missing");
   B200_REQUIRE(b->dY_zone && b->row_weights && b->dP && b->dx1 && b->dx3 && b->dZ && b->dX_routed,
@@ -87,9 +89,9 @@ extern "C" int b200_moe_block_bwd(const B200MoeBlock *b, const void *Xn, const v
     return -1;
   // the three weight gradients (h and the gathered zone are still resident from the forward)
   if (dW1 || dW3 || dW2) {
-    if (b200_moe_experts_bwd_w(R, d, f, E, b->dY_zone, b->h, b->zone, b->dx1, b->dx3, dW1, dW3, dW2,
-                               b->w1_stride_elems, b->w3_stride_elems, b->w2_stride_elems, b->expert_counts,
-                               b->expert_counts_cumsum, stream))
+    if ((accumulate ? b200_moe_experts_bwd_w : b200_moe_experts_bwd_w_overwrite)(
+            R, d, f, E, b->dY_zone, b->h, b->zone, b->dx1, b->dx3, dW1, dW3, dW2, b->w1_stride_elems, b->w3_stride_elems,
+            b->w2_stride_elems, b->expert_counts, b->expert_counts_cumsum, stream))
       return -1;
   }
   // un-permute (3666-3682: merge_experts onto a zeroed dXn there; here one pass that overwrites, same bits)
@@ -102,8 +104,19 @@ extern "C" int b200_moe_block_bwd(const B200MoeBlock *b, const void *Xn, const v
   if (b200_matmul(B200_DT_BF16, B200_DT_BF16, B200_DT_BF16, B200_DT_BF16, 0, 0, d, E, T, 1.0f, 1.0f, b->Wr,
                   b->dX_routed, dXn, dXn, 0, nullptr, stream))
     return -1;
-  return b200_matmul(B200_DT_BF16, B200_DT_BF16, B200_DT_BF16, B200_DT_BF16, 0, 1, d, T, E, 1.0f, 1.0f, Xn,
-                     b->dX_routed, dWr, dWr, b->matmul_workspace_bytes, b->matmul_workspace, stream);
+  return b200_matmul(B200_DT_BF16, B200_DT_BF16, accumulate ? B200_DT_BF16 : B200_DT_NONE, B200_DT_BF16, 0, 1, d, T, E, 1.0f,
+                     accumulate ? 1.0f : 0.0f, Xn, b->dX_routed, accumulate ? dWr : nullptr, dWr, b->matmul_workspace_bytes,
+                     b->matmul_workspace, stream);
+}
+
+extern "C" int b200_moe_block_bwd(const B200MoeBlock *b, const void *Xn, const void *dOut, void *dXn, void *dWr,
+                                  void *dW1, void *dW3, void *dW2, void *stream) {
+  return moe_block_bwd(b, Xn, dOut, dXn, dWr, dW1, dW3, dW2, true, stream);
+}
+
+extern "C" int b200_moe_block_bwd_overwrite(const B200MoeBlock *b, const void *Xn, const void *dOut, void *dXn, void *dWr,
+                                            void *dW1, void *dW3, void *dW2, void *stream) {
+  return moe_block_bwd(b, Xn, dOut, dXn, dWr, dW1, dW3, dW2, false, stream);
 }
 
 // ---------------------------------------------------------------------------------------------------------------

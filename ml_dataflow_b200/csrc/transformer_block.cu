@@ -21,9 +21,10 @@ int linear_dx(int T, int i, int o, const void *dy, const void *w, void *dx, bool
   return b200_matmul(BF, BF, accumulate ? BF : B200_DT_NONE, BF, 0, 0, i, o, T, 1.0f, accumulate ? 1.0f : 0.0f, w, dy,
                      accumulate ? dx : nullptr, dx, 0, nullptr, stream);
 }
-// dw[o][i] += dy[T][o]^T . x[T][i]
-int linear_dw(int T, int i, int o, const void *dy, const void *x, void *dw, void *stream) {
-  return b200_matmul(BF, BF, BF, BF, 0, 1, i, T, o, 1.0f, 1.0f, x, dy, dw, dw, 0, nullptr, stream);
+// dw[o][i] (+)= dy[T][o]^T . x[T][i]
+int linear_dw(int T, int i, int o, const void *dy, const void *x, void *dw, bool accumulate, void *stream) {
+  return b200_matmul(BF, BF, accumulate ? BF : B200_DT_NONE, BF, 0, 1, i, T, o, 1.0f, accumulate ? 1.0f : 0.0f, x, dy,
+                     accumulate ? dw : nullptr, dw, 0, nullptr, stream);
 }
 
 int check_block(const char *op, const B200TransformerBlock *b) {
@@ -71,14 +72,21 @@ extern "C" int b200_transformer_block_bwd(const B200TransformerBlock *b, const v
                "transformer_block_bwd: null gradient buffer");
   B200_REQUIRE(s->dxn && s->dattn && s->dq && s->dk && s->dv && s->norm_workspace, "transformer_block_bwd: null scratch buffer");
   const int T = b->total_tokens, d = b->model_dim, Dq = b->num_q_heads * b->head_dim, Dk = b->num_kv_heads * b->head_dim;
+  const bool acc = g->overwrite == 0;
+  if (!acc) {  // the norm-weight kernels only accumulate: start them from zero
+    B200_CUDA(cudaMemsetAsync(g->attn_norm, 0, (size_t)d * 2, (cudaStream_t)stream));
+    B200_CUDA(cudaMemsetAsync(g->ffn_norm, 0, (size_t)d * 2, (cudaStream_t)stream));
+  }
   // MoE part: dx is the gradient at the block's output and also flows through the residual unchanged
-  if (b200_moe_block_bwd(&b->moe, b->xn2, dx, s->dxn, g->router, g->W1, g->W3, g->W2, stream)) return -1;
+  if ((acc ? b200_moe_block_bwd : b200_moe_block_bwd_overwrite)(&b->moe, b->xn2, dx, s->dxn, g->router, g->W1, g->W3, g->W2,
+                                                                 stream))
+    return -1;
   if (b200_rms_norm_bwd_w(BF, BF, T, d, b->eps, b->rms2, b->x_mid, s->dxn, g->ffn_norm, s->norm_workspace_bytes,
                           s->norm_workspace, stream))
     return -1;
   if (b200_rms_norm_bwd_x(BF, BF, T, d, b->eps, b->rms2, b->ffn_norm, b->x_mid, s->dxn, dx, nullptr, stream)) return -1;
   // attention part: x_mid = x + attn . wo^T
-  if (linear_dw(T, Dq, d, dx, b->attn, g->wo, stream)) return -1;
+  if (linear_dw(T, Dq, d, dx, b->attn, g->wo, acc, stream)) return -1;
   if (linear_dx(T, Dq, d, dx, b->wo, s->dattn, false, stream)) return -1;
   if (b200_attention_bwd(BF, b->num_seqs, T, T, b->seq_offsets, b->seq_lens, b->max_seqlen, b->seq_offsets, b->seq_lens,
                          b->max_seqlen, b->num_q_heads, b->num_kv_heads, b->head_dim, b->q, b->k, b->v, b->attn, b->lse,
@@ -86,9 +94,9 @@ extern "C" int b200_transformer_block_bwd(const B200TransformerBlock *b, const v
     return -1;
   if (b200_rope_bwd_x(BF, T, Dq, b->head_dim, b->num_kv_heads, b->theta, b->positions, s->dq, s->dk, stream)) return -1;
   if (b200_rms_norm_recompute(BF, T, d, b->attn_norm, b->rms1, x, b->xn, stream)) return -1;
-  if (linear_dw(T, d, Dq, s->dq, b->xn, g->wq, stream)) return -1;
-  if (linear_dw(T, d, Dk, s->dk, b->xn, g->wk, stream)) return -1;
-  if (linear_dw(T, d, Dk, s->dv, b->xn, g->wv, stream)) return -1;
+  if (linear_dw(T, d, Dq, s->dq, b->xn, g->wq, acc, stream)) return -1;
+  if (linear_dw(T, d, Dk, s->dk, b->xn, g->wk, acc, stream)) return -1;
+  if (linear_dw(T, d, Dk, s->dv, b->xn, g->wv, acc, stream)) return -1;
   if (linear_dx(T, d, Dq, s->dq, b->wq, s->dxn, false, stream)) return -1;
   if (linear_dx(T, d, Dk, s->dk, b->wk, s->dxn, true, stream)) return -1;
   if (linear_dx(T, d, Dk, s->dv, b->wv, s->dxn, true, stream)) return -1;

@@ -111,7 +111,8 @@ class Decoder:
                 p(self.positions), p(L["attn_norm"]), p(L["wq"]), p(L["wk"]), p(L["wv"]), p(L["wo"]), p(L["ffn_norm"]),
                 p(S["rms1"]), p(S["rms2"]), p(S["q"]), p(S["k"]), p(S["v"]), p(S["attn"]), p(S["lse"]), p(S["x_mid"]),
                 p(S["xn2"]), p(self.xn), p(self.attn_ws), self.attn_ws.numel(), moe))
-            grads.append(_lib.TransformerBlockGrads(*[p(G[k]) for k in self.PARAMS]))
+            # one batch per step here: the blocks write their weight gradients, so nothing has to be zeroed first
+            grads.append(_lib.TransformerBlockGrads(*[p(G[k]) for k in self.PARAMS], 1))
         scratch = _lib.TransformerBlockScratch(p(self.dxn), p(self.dattn), p(self.dq), p(self.dk), p(self.dv), p(self.norm_ws),
                                                self.norm_ws.numel())
         return blocks, grads, scratch
@@ -244,6 +245,12 @@ class Decoder:
             ops.adamw_step(p.numel(), self.step_num, lr, beta1, beta2, weight_decay, eps, p, g, m, v)
 
     def zero_grads(self):
+        """Zeroes what the backward accumulates into. With the C block driver the blocks' gradients are written, not
+        accumulated (B200TransformerBlockGrads.overwrite), and only the embedding, final norm and head remain."""
+        if self.c_blocks:
+            for g in (self.g_embed, self.g_final_norm, self.g_head):
+                g.zero_()
+            return
         for _, g in self._all_params():
             g.zero_()
 

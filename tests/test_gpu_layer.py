@@ -313,3 +313,41 @@ def test_c_block_driver_matches_fast_path(T, d, E, k, f):
     assert same(out2, ob)
     with pytest.raises(RuntimeError):
         ops.moe_block_bwd(blk, Xd, dOd, xb, gb["dWr"], None, None, None)
+
+
+def test_block_backward_overwrite_equals_zero_then_accumulate():
+    """b200_moe_block_bwd_overwrite writes the same weight gradients that b200_moe_block_bwd adds to zeroed buffers,
+    bit for bit, whatever the buffers held before."""
+    import torch
+
+    from gpu_util import require_b200
+
+    require_b200()
+    from ml_dataflow_b200 import _lib, ops
+    from ml_dataflow_b200.moe_layer import MoELayer
+
+    T, d, E, k, f = 512, 256, 8, 2, 128
+    g = torch.Generator(device="cuda").manual_seed(11)
+    n = lambda shape, std: (torch.randn(shape, generator=g, device="cuda") * std).to(torch.bfloat16)
+    X, dOut, Wr = n((T, d), 1.0), n((T, d), 1.0), n((E, d), 0.1)
+    W1, W3, W2 = n((E, f, d), 0.1), n((E, f, d), 0.1), n((E, d, f), 0.1)
+    layer = MoELayer(T, d, E, k, f, device="cuda")
+    blk = layer.block(Wr, W1, W3, W2)
+    out = torch.zeros((T, d), dtype=torch.bfloat16, device="cuda")
+    ops.moe_block_fwd(blk, X, out)
+    grads_a = [torch.zeros_like(t) for t in (Wr, W1, W3, W2)]
+    dXa = torch.empty_like(X)
+    ops.moe_block_bwd(blk, X, dOut, dXa, *grads_a)
+    grads_b = [torch.full_like(t, 5.0) for t in (Wr, W1, W3, W2)]
+    dXb = torch.empty_like(X)
+    import ctypes as C
+
+    p = lambda t: C.c_void_p(t.data_ptr())
+    rc = _lib.load().b200_moe_block_bwd_overwrite(C.byref(blk), p(X), p(dOut), p(dXb), *[p(t) for t in grads_b],
+                                                  C.c_void_p(torch.cuda.current_stream().cuda_stream))
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert ops.gemm_status() == 0
+    assert torch.equal(dXa, dXb)
+    for a, b, name in zip(grads_a, grads_b, ("dWr", "dW1", "dW3", "dW2")):
+        assert torch.equal(a, b), name

@@ -10,7 +10,8 @@ against its own bound, and `decoder_step`: the full training step of the 16-laye
 (forward, backward, AdamW; tokens/s).
 N > 1 (launched with torch.distributed.run, one rank per GPU): the expert-parallel layer, 64 experts sharded
 over the ranks, T=32768 tokens per GPU (weak scaling); rows travel over NVLink peer memory, out through the gather
-kernel and back through the epilogue of the last GEMM of each pass (B200_EP_TRANSPORT=fused|p2p|nccl). After the
+kernel and back through the epilogue of the last GEMM of each pass (B200_EP_TRANSPORT=fused|c|p2p|nccl; `c_driver` is
+the same step through the C entry points b200_ep_moe_block_fwd / _bwd, timed after the main region). After the
 timed regions every rank runs one small expert-parallel layer against the CPU oracle (`ep_parity`; a mismatch
 replaces the line by an error and exit code 1), and rank 0 runs the same per-GPU batch on one GPU with all experts
 (`same_batch_1gpu`), from which `efficiency_same_batch` = value / (N x that value).
@@ -540,11 +541,12 @@ def run_gpu_arm(args, world):
     else:
         from ml_dataflow_b200.ep import ExpertParallelMoELayer
 
-        # "c" (default up to 4 GPUs): the buffers of the "fused" transport driven by b200_ep_moe_block_fwd / _bwd, one C
-        # call per direction with the library's own barrier / plan kernels; the other names run the Python driver in
-        # ep.py. At 8 GPUs the default is the Python driver of the same kernels: it is the one that has been run and
-        # checked at that size (no 8-GPU machine could be had for the C driver); B200_EP_TRANSPORT=c selects it there too.
-        transport = os.environ.get("B200_EP_TRANSPORT", "c" if world <= 4 else "fused")
+        # "fused" (default): rows out through the gather kernel, back through the epilogue of the last GEMM of each
+        # pass, driven op by op from ep.py. "c": the same buffers and kernels driven by b200_ep_moe_block_fwd / _bwd, one C
+        # call per direction with the library's own barrier / plan kernels; it is also timed after the main region
+        # (`c_driver`). The Python driver is the default because it measured 2-3 % faster at 2, 4 and 8 GPUs: its host
+        # gaps leave the GPUs below the power cap, where the back-to-back C driver runs into it.
+        transport = os.environ.get("B200_EP_TRANSPORT", "fused")
         layer = ExpertParallelMoELayer(T, d, E, k, f, dist, device=dev, transport="fused" if transport == "c" else transport,
                                        slices=int(os.environ.get("B200_EP_SLICES", "1")))
         E_loc = E // world
@@ -555,8 +557,6 @@ def run_gpu_arm(args, world):
     dW1, dW3, dW2 = torch.zeros_like(W1), torch.zeros_like(W3), torch.zeros_like(W2)
 
     exchange_note = None
-    if world > 4 and transport == "fused" and "B200_EP_TRANSPORT" not in os.environ:
-        exchange_note = "Python driver of the fused-transport kernels: the C driver was validated on 2 and 4 GPUs only"
     block = layer.block(Wr, W1, W3, W2) if world == 1 else None
     ep_block = layer.c_block(Wr, W1, W3, W2) if transport == "c" else None
 
@@ -766,6 +766,38 @@ def run_gpu_arm(args, world):
 
     # ---------------- after the timed regions: the target shape / the same-batch base on one GPU, EP parity
     extra = {}
+    if world > 1 and transport == "fused":
+        # the C driver of the same buffers and kernels, a short device-timed loop (every rank takes the same path: the
+        # status votes are reduced over the ranks before anything depends on them)
+        try:
+            ep_c = layer.c_block(Wr, W1, W3, W2)
+
+            def step_c():
+                out.zero_()
+                ops.ep_moe_block_fwd(ep_c, X, out)
+                ops.ep_moe_block_bwd(ep_c, X, dOut, dXn, dWr, dW1, dW3, dW2)
+
+            for _ in range(3):
+                step_c()
+            barrier()
+            bad_c = torch.tensor([1 if ops.ep_status() != 0 else 0], dtype=torch.int32, device=dev)
+            dist.all_reduce(bad_c, op=dist.ReduceOp.MAX)
+            if int(bad_c.item()) != 0:
+                extra["c_driver"] = dict(error="a barrier of the C driver timed out")
+            else:
+                c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                barrier()
+                c0.record()
+                for _ in range(5):
+                    step_c()
+                c1.record()
+                barrier()
+                ms_c = max_over_ranks(c0.elapsed_time(c1) / 5)
+                layer.check()
+                extra["c_driver"] = dict(ms_per_step=round(ms_c, 3), value=round(world * T / (ms_c * 1e-3), 1), unit=UNIT, steps=5,
+                                         note="b200_ep_moe_block_fwd / _bwd: one C call per direction, device barriers")
+        except Exception as exc:  # the main line stands without it
+            extra["c_driver"] = dict(error=f"{type(exc).__name__}: {str(exc)[:200]}")
     del layer, block, ep_block
     torch.cuda.empty_cache()
     if world == 1 and args.tokens <= 0:

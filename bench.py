@@ -544,8 +544,7 @@ def run_gpu_arm(args, world):
         # "fused" (default): rows out through the gather kernel, back through the epilogue of the last GEMM of each
         # pass, driven op by op from ep.py. "c": the same buffers and kernels driven by b200_ep_moe_block_fwd / _bwd, one C
         # call per direction with the library's own barrier / plan kernels; it is also timed after the main region
-        # (`c_driver`). The Python driver is the default because it measured 2-3 % faster at 2, 4 and 8 GPUs: its host
-        # gaps leave the GPUs below the power cap, where the back-to-back C driver runs into it.
+        # (`c_driver`). The two measure within about 3 % of each other at 2, 4 and 8 GPUs.
         transport = os.environ.get("B200_EP_TRANSPORT", "fused")
         layer = ExpertParallelMoELayer(T, d, E, k, f, dist, device=dev, transport="fused" if transport == "c" else transport,
                                        slices=int(os.environ.get("B200_EP_SLICES", "1")))
